@@ -1,0 +1,202 @@
+/*
+ * libnvmai_cuda_moe — CUDA (sm_100a) implementation of NVMAI's routed-expert
+ * MoE FFN on NVMAIRepack quantized weights, behind a C ABI in the style of the
+ * reference's NVMAIKernelsC target (sources/NVMAIKernelsC/include/nvmai_kernels.h,
+ * nvmai_expert_io.h): C99 types only, `nvmai_` prefix, opaque handle with
+ * create/destroy, work functions return 0 or an error code and leave outputs
+ * undefined on failure.
+ *
+ * Every work function ENQUEUES on the caller's CUDA stream (`stream` is a
+ * cudaStream_t passed as void*, NULL = the legacy default stream) and returns;
+ * this is the CUDA counterpart of the reference's `encode…(commandBuffer:)`
+ * methods.  All data pointers are DEVICE pointers unless the parameter name ends
+ * in `_host`.  A handle is single-owner and not thread-safe, like the
+ * reference's runner (sources/NVMAI/Runtime/Inference/RealForwardRunner.swift:128-134).
+ *
+ * Weight bytes are consumed exactly as NVMAIRepack wrote them: U32-packed
+ * codes, LSB first (code i of a row at bit i*bits), one 16-bit scale and one
+ * 16-bit bias per group of 64 inputs, w = q*scale + bias.  The library never
+ * copies or re-lays-out weights.  Tensor base addresses must be 16-byte aligned
+ * (routed expert blobs are 16 KiB aligned by construction,
+ * sources/NVMAIRepack/Core/Planning/RepackPlanner.swift:428).
+ */
+#ifndef NVMAI_CUDA_MOE_H
+#define NVMAI_CUDA_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define NVMAI_API __attribute__((visibility("default")))
+#else
+#define NVMAI_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes (0 = success; errno-style like nvmai_expert_io.h:46-55) ---- */
+#define NVMAI_CUDA_OK 0
+#define NVMAI_CUDA_EINVAL 22    /* bad shape, null pointer, misaligned tensor */
+#define NVMAI_CUDA_ERANGE 34    /* index / size outside the configured limits */
+#define NVMAI_CUDA_ENOMEM 12    /* device allocation failed */
+#define NVMAI_CUDA_ECUDA 1001   /* CUDA runtime error; see nvmai_cuda_moe_last_cuda_error */
+#define NVMAI_CUDA_ETIMEOUT 1002 /* a bounded device-side wait expired */
+#define NVMAI_CUDA_ENCCL 1003
+
+/* ---- enums ---- */
+#define NVMAI_META_BF16 0u   /* the reference's format (RepackPlanner.swift:302-305) */
+#define NVMAI_META_FP16 1u
+#define NVMAI_ACT_SILU 0u        /* moe.metal:134-139, FC_MOE_ACT_SILU = true (Qwen SwiGLU) */
+#define NVMAI_ACT_GELU_TANH 1u   /* moe.metal:82-89, the `MoE(context:)` default */
+#define NVMAI_OUT_FP16 0u    /* reference rounding points (moe.metal:808, utility.metal:102) */
+#define NVMAI_OUT_FP32 1u    /* h1 / h2 / hidden kept in fp32 (no fp16 overflow on wide-range weights) */
+#define NVMAI_ROUTER_DENSE_F16 0u  /* [E][D] fp16 gate matrix */
+#define NVMAI_ROUTER_AFFINE4 4u    /* affine codes + 16-bit scale/bias per 64 (moe.metal:157-214) */
+#define NVMAI_ROUTER_AFFINE8 8u
+#define NVMAI_GATE_NONE 0xFFFFFFFFu /* shared expert without a sigmoid gate */
+
+typedef struct nvmai_cuda_moe nvmai_cuda_moe;
+
+/* Mirrors the arguments of `MoE.init` (sources/NVMAI/Kernels/MoE/MoE.swift:60-149)
+ * plus the scratch the runner allocates around it (RealForwardRunner.swift:503-511). */
+typedef struct {
+    uint32_t d;              /* hidden size, multiple of 64 */
+    uint32_t f;              /* routed expert intermediate size, multiple of 64 */
+    uint32_t shared_f;       /* shared expert intermediate size (0 = no shared expert) */
+    uint32_t num_experts;    /* <= 256 (MoE.swift:164) */
+    uint32_t top_k;          /* decode entry points need 8 (MoE.swift:165); prefill router <= 64 */
+    uint32_t routed_bits;    /* 4 or 8 */
+    uint32_t shared_bits;    /* 4 or 8 */
+    uint32_t router_kind;    /* NVMAI_ROUTER_* */
+    uint32_t shared_gate_kind; /* NVMAI_ROUTER_* encoding of the [1][D] gate row, or NVMAI_GATE_NONE */
+    uint32_t meta_dtype;     /* NVMAI_META_* */
+    uint32_t activation;     /* NVMAI_ACT_* */
+    uint32_t out_dtype;      /* NVMAI_OUT_* : element type of h1, y and hidden */
+    uint32_t max_tokens;     /* largest token count of one call (decode batch or prefill chunk) */
+    uint32_t num_layers;     /* layers that may be registered */
+} nvmai_cuda_moe_config;
+
+/* Mirrors `MoEExpertOffsets` (MoE.swift:4-29) == `ExpertOffsets` (moe.metal:141-151): 9 x u32. */
+typedef struct {
+    uint32_t gate_w, gate_s, gate_b, up_w, up_s, up_b, down_w, down_s, down_b;
+} nvmai_expert_offsets;
+
+/* One affine (or dense) matrix: W | scales | biases as three device pointers,
+ * like `SharedExpertProjection` (SharedExpertInt4.swift:125-152). */
+typedef struct {
+    const void *w;
+    const void *scales;  /* NULL for a dense fp16 matrix */
+    const void *biases;
+} nvmai_affine_tensor;
+
+/* Per-layer weight views: `Model.routedExpertOffsets` + the runner's per-layer
+ * shared-expert projections (ModelExpertIO.swift:67-82, RealForwardRunner.swift:587-610). */
+typedef struct {
+    const void *experts;         /* num_experts blobs, expert_stride bytes apart */
+    uint64_t expert_stride;
+    nvmai_expert_offsets offsets;
+    nvmai_affine_tensor router;  /* [E][D] */
+    const void *effective_scale;   /* bf16[D] or NULL (= 1.0, RealForwardRunner.swift:612-632) */
+    const void *per_expert_scale;  /* bf16[E] or NULL (= 1.0) */
+    nvmai_affine_tensor shared_gate_proj, shared_up_proj, shared_down_proj; /* [Fs][D],[Fs][D],[D][Fs] */
+    nvmai_affine_tensor shared_gate;  /* [1][D] scalar-gate row (RealForwardRunner.swift:3884-3896) */
+} nvmai_cuda_moe_layer;
+
+/* Expert-blob byte offsets for (d, f, bits): `CPUExpertFFN.Offsets.init`
+ * (sources/NVMAI/Kernels/CPU/CPUExpertFFN.swift:42-59) generalised to 8-bit.
+ * Returns the expert stride in bytes (1,769,472 for 2048/512/4-bit). */
+NVMAI_API uint64_t nvmai_cuda_moe_expert_offsets(uint32_t d, uint32_t f, uint32_t bits, nvmai_expert_offsets *out);
+
+/* `MoE.init` (MoE.swift:60-149): validates the shape, allocates device scratch.
+ * NULL on failure with *out_err set (nvmai_expert_reader_create convention,
+ * nvmai_expert_io.h:20-44). */
+NVMAI_API nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *out_err);
+NVMAI_API void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h);
+
+/* Records the layer's device views (ModelExpertIO.swift:67-82). */
+NVMAI_API int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, const nvmai_cuda_moe_layer *weights);
+
+/* `MoE.encodeRouter` (MoE.swift:151-213) = router_gemv_r4 + router_topk_select_k8
+ * (moe.metal:174-285) for `tokens` rows of x (row stride x_stride elements;
+ * tokens = 1 is the reference's decode call, tokens > 1 is
+ * `PrefillRouter.encodeBlock`, PrefillRouter.swift:41-95).
+ * out_idx u32[tokens][top_k], out_w fp16[tokens][top_k]. */
+NVMAI_API int nvmai_cuda_moe_router(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride,
+                          uint32_t tokens, uint32_t *out_idx, void *out_w_f16, void *stream);
+
+/* `SharedExpertRuntime.encode` + scalar gate GEMV + `sigmoid_scalar_mul_fp16`
+ * (RealForwardRunner.swift:3866-3905): h1 = sigmoid(g.x) * down(act(gate.x)*up.x).
+ * h1 is out_dtype[tokens][d]. */
+NVMAI_API int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride,
+                                 uint32_t tokens, void *h1, void *stream);
+
+/* `MoE.encodeRoutedPersistentPhase1U16Load` / `…Phase1SubsetU16Load`
+ * (MoE.swift:295-392; moe.metal:642-727, 812-861):
+ * acts[slot*f + j] = half(act(gate_slot[j].x) * (up_slot[j].x)) for the 8 blobs
+ * in `blobs_host` (host array of 8 device pointers, the argument-buffer of
+ * MoE.swift:215-227).  active_slots_host NULL = all slots. */
+NVMAI_API int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_host,
+                                 const nvmai_expert_offsets *offsets, const void *x_f16, void *acts_f16,
+                                 const uint32_t *active_slots_host, uint32_t active_count, void *stream);
+
+/* `MoE.encodeRoutedPersistentPhase2Reduce` (MoE.swift:394-440; moe.metal:769-810, 863-892):
+ * y[i] = out(residual[i] + sum_{k=0..7} float(w[k]) * (down_k[i,:].acts_k)), partials added in slot order. */
+NVMAI_API int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_host,
+                                 const nvmai_expert_offsets *offsets, const void *acts_f16,
+                                 const void *routing_w_f16, const void *residual, void *y, void *stream);
+
+/* The whole MoE block of a decode step for `tokens` independent rows
+ * (RealForwardRunner.swift:1911-1995, 3866-3905, 3914-4312):
+ * router -> shared expert -> phase 1 -> phase 2 (h1 as residual) -> hidden += h2.
+ * x is the normalised input fp16[tokens][d]; hidden_inout out_dtype[tokens][d] may be
+ * NULL; h2_out (optional) receives the block output before the residual add.
+ * out_idx / out_w optional.  Experts stay on the device: no host read-back. */
+NVMAI_API int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
+                                void *hidden_inout, void *h2_out, uint32_t *out_idx, void *out_w_f16,
+                                void *stream);
+
+/* Benchmark driver for an FFN-only stack: runs layers 0..num_layers-1 on one
+ * token batch; between layers the block output is renormalised to unit RMS in
+ * fp32 and rounded to fp16 (a stand-in for the attention + rmsnorm the real model
+ * runs there, RealForwardRunner.swift:1900-1909).  x0 fp16[tokens][d];
+ * y_last out_dtype[tokens][d] = last layer's block output. */
+NVMAI_API int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t tokens, void *y_last,
+                                void *stream);
+
+/* Host-buffer convenience of the same call (copies x in, y out on `stream`, and
+ * synchronises): the end-to-end path a host runtime without device buffers uses. */
+NVMAI_API int nvmai_cuda_moe_stack_decode_host(nvmai_cuda_moe *h, const void *x0_f16_host, uint32_t tokens,
+                                     void *y_last_host, void *stream);
+
+/* out[r][i] = float(q)*scale + bias (Quantization.swift:104-119, 179-191) for a
+ * [rows][n] affine tensor: the dequantisation every kernel here applies,
+ * exposed so that it can be compared bit for bit. */
+NVMAI_API int nvmai_cuda_moe_dequant(uint32_t bits, uint32_t meta_dtype, const void *w, const void *scales,
+                           const void *biases, uint32_t rows, uint32_t n, float *out_f32, void *stream);
+
+/* y[m] = half(W[m,:].x): `DequantInt4GEMV.encode` / `DequantInt8GEMV.encode`
+ * (dequant_int4.metal:101-199, dequant_int8.metal:66-107). */
+NVMAI_API int nvmai_cuda_moe_affine_gemv(uint32_t bits, uint32_t meta_dtype, const void *w, const void *scales,
+                               const void *biases, const void *x_f16, void *y_f16, uint32_t m, uint32_t n,
+                               void *stream);
+
+/* `Elementwise` (sources/NVMAI/Kernels/Primitives/Elementwise.swift;
+ * utility.metal:32-44, 60-70, 94-103). */
+NVMAI_API int nvmai_cuda_moe_silu_mul_f16(const void *gate, const void *up, void *out, uint32_t count, void *stream);
+NVMAI_API int nvmai_cuda_moe_sigmoid_scalar_mul_f16(void *y, const void *gate, uint32_t count, void *stream);
+NVMAI_API int nvmai_cuda_moe_residual_add_f16(void *hidden, const void *delta, uint32_t count, void *stream);
+
+/* waitUntilCompleted + `.error` (RealForwardRunner.swift:3805-3837). */
+NVMAI_API int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream);
+NVMAI_API int nvmai_cuda_moe_last_cuda_error(const nvmai_cuda_moe *h);
+NVMAI_API const char *nvmai_cuda_moe_error_string(int code);
+
+/* Kernel launches issued through this library since load (bench accounting). */
+NVMAI_API uint64_t nvmai_cuda_moe_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVMAI_CUDA_MOE_H */

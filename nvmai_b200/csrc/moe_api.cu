@@ -1,0 +1,588 @@
+// C ABI of libnvmai_cuda_moe: handle, validation, launches.  The host-side
+// counterpart of the reference's Swift wrappers (sources/NVMAI/Kernels/MoE/MoE.swift,
+// SharedExpertInt4.swift, SharedExpertInt8.swift, Kernels/Primitives/Elementwise.swift):
+// the same shape checks, turned into error codes instead of preconditions.
+#include "../../include/nvmai_cuda_moe.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <new>
+#include <tuple>
+#include <vector>
+
+#include "decode_kernels.cuh"
+#include "misc_kernels.cuh"
+
+using namespace nvmai;
+
+static std::atomic<uint64_t> g_launches{0};
+
+struct LayerViews {
+    bool registered = false;
+    nvmai_cuda_moe_layer w{};
+};
+
+struct StackGraphKey {
+    const void *x0; void *y; uint32_t tokens; cudaStream_t stream;
+    bool operator<(const StackGraphKey &o) const {
+        return std::tie(x0, y, tokens, stream) < std::tie(o.x0, o.y, o.tokens, o.stream);
+    }
+};
+
+struct nvmai_cuda_moe {
+    nvmai_cuda_moe_config cfg{};
+    std::vector<LayerViews> layers;
+    int last_cuda_error = 0;
+    // device scratch (sized for max_tokens)
+    float *logits = nullptr;        // [T][E]
+    uint32_t *idx = nullptr;        // [T][K]
+    __half *w = nullptr;            // [T][K]
+    __half *acts = nullptr;         // [T][K][F]
+    __half *shared_act = nullptr;   // [T][Fs]
+    float *gate_val = nullptr;      // [T]
+    void *y = nullptr;              // [T][D] out_dtype
+    __half *xnorm = nullptr;        // [T][D]
+    unsigned int *counter = nullptr;
+    const void **blob_table = nullptr;   // unused on device; kept for symmetry
+    void *stage_x = nullptr;        // host-call staging: [T][D] fp16
+    void *stage_y = nullptr;        // host-call staging: [T][D] out_dtype
+    std::map<StackGraphKey, cudaGraphExec_t> stack_graphs;
+    bool graphs_stale = false;
+};
+
+namespace {
+
+inline size_t out_size(uint32_t out_dtype) { return out_dtype == NVMAI_OUT_FP16 ? 2 : 4; }
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool valid_bits(uint32_t b) { return b == 4 || b == 8; }
+
+int record(nvmai_cuda_moe *h, cudaError_t e) {
+    if (e == cudaSuccess) return NVMAI_CUDA_OK;
+    if (h) h->last_cuda_error = (int)e;
+    return NVMAI_CUDA_ECUDA;
+}
+
+int check_launch(nvmai_cuda_moe *h) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return record(h, cudaGetLastError());
+}
+
+RoutedSource source_from_blobs(const void *const *blobs, uint32_t top_k) {
+    RoutedSource s{};
+    for (uint32_t k = 0; k < kMaxTopK; ++k) s.blob[k] = k < top_k ? static_cast<const uint8_t *>(blobs[k]) : nullptr;
+    return s;
+}
+
+RoutedSource source_from_layer(const nvmai_cuda_moe *h, const LayerViews &lv, const uint32_t *idx) {
+    RoutedSource s{};
+    s.idx = idx;
+    s.base = static_cast<const uint8_t *>(lv.w.experts);
+    s.stride = lv.w.expert_stride;
+    s.num_experts = h->cfg.num_experts;
+    return s;
+}
+
+ExpertOffsets to_offsets(const nvmai_expert_offsets &o) {
+    ExpertOffsets r;
+    r.o[0] = o.gate_w; r.o[1] = o.gate_s; r.o[2] = o.gate_b;
+    r.o[3] = o.up_w; r.o[4] = o.up_s; r.o[5] = o.up_b;
+    r.o[6] = o.down_w; r.o[7] = o.down_s; r.o[8] = o.down_b;
+    return r;
+}
+
+AffineMat to_mat(const nvmai_affine_tensor &t) {
+    return AffineMat{static_cast<const uint8_t *>(t.w), static_cast<const uint16_t *>(t.scales),
+                     static_cast<const uint16_t *>(t.biases)};
+}
+
+// Offsets must keep every sub-tensor 16-byte aligned inside a 16-byte aligned blob
+// and stay inside the blob; the reference checks `offset + bytes <= length`
+// (SharedExpertInt4.swift:47-59).
+int check_offsets(const nvmai_cuda_moe_config &c, const nvmai_expert_offsets &o, uint64_t stride) {
+    const uint64_t gate_w = (uint64_t)c.f * c.d * c.routed_bits / 8, gate_m = (uint64_t)c.f * (c.d / 64) * 2;
+    const uint64_t down_w = (uint64_t)c.d * c.f * c.routed_bits / 8, down_m = (uint64_t)c.d * (c.f / 64) * 2;
+    const uint32_t offs[9] = {o.gate_w, o.gate_s, o.gate_b, o.up_w, o.up_s, o.up_b, o.down_w, o.down_s, o.down_b};
+    const uint64_t lens[9] = {gate_w, gate_m, gate_m, gate_w, gate_m, gate_m, down_w, down_m, down_m};
+    for (int i = 0; i < 9; ++i) {
+        if (offs[i] & 15u) return NVMAI_CUDA_EINVAL;
+        if (stride != 0 && (uint64_t)offs[i] + lens[i] > stride) return NVMAI_CUDA_ERANGE;
+    }
+    return NVMAI_CUDA_OK;
+}
+
+template <typename F>
+int dispatch_bits_meta(uint32_t bits, uint32_t meta, F &&f) {
+    if (bits == 4 && meta == NVMAI_META_BF16) return f(std::integral_constant<int, 4>{}, std::integral_constant<int, META_BF16>{});
+    if (bits == 4 && meta == NVMAI_META_FP16) return f(std::integral_constant<int, 4>{}, std::integral_constant<int, META_FP16>{});
+    if (bits == 8 && meta == NVMAI_META_BF16) return f(std::integral_constant<int, 8>{}, std::integral_constant<int, META_BF16>{});
+    if (bits == 8 && meta == NVMAI_META_FP16) return f(std::integral_constant<int, 8>{}, std::integral_constant<int, META_FP16>{});
+    return NVMAI_CUDA_EINVAL;
+}
+
+// ---- stage launchers ---------------------------------------------------------
+
+int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x, uint32_t x_stride, uint32_t tokens,
+                  uint32_t *out_idx, __half *out_w, bool with_router, bool with_shared, cudaStream_t st) {
+    const auto &c = h->cfg;
+    Stage1Params p{};
+    p.rW = static_cast<const uint8_t *>(lv.w.router.w);
+    p.rS = static_cast<const uint16_t *>(lv.w.router.scales);
+    p.rB = static_cast<const uint16_t *>(lv.w.router.biases);
+    p.eff = static_cast<const uint16_t *>(lv.w.effective_scale);
+    p.pes = static_cast<const uint16_t *>(lv.w.per_expert_scale);
+    p.router_kind = c.router_kind;
+    p.logits = h->logits;
+    p.out_idx = out_idx;
+    p.out_w = out_w;
+    p.counter = h->counter;
+    p.sgate = to_mat(lv.w.shared_gate_proj);
+    p.sup = to_mat(lv.w.shared_up_proj);
+    p.shared_f = with_shared ? c.shared_f : 0;
+    p.shared_act = h->shared_act;
+    p.gW = static_cast<const uint8_t *>(lv.w.shared_gate.w);
+    p.gS = static_cast<const uint16_t *>(lv.w.shared_gate.scales);
+    p.gB = static_cast<const uint16_t *>(lv.w.shared_gate.biases);
+    p.gate_kind = c.shared_gate_kind;
+    p.gate_val = h->gate_val;
+    p.x = x; p.x_stride = x_stride; p.tokens = tokens;
+    p.D = c.d; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation;
+    p.n_router_blocks = with_router ? (c.num_experts + 7) / 8 : 0;
+    p.n_shared_blocks = with_shared ? (c.shared_f / kTileRows) * tokens : 0;
+    const uint32_t gate_blocks = (with_shared && c.shared_gate_kind != NVMAI_GATE_NONE) ? 1 : 0;
+    const uint32_t grid = p.n_router_blocks + p.n_shared_blocks + gate_blocks;
+    if (grid == 0) return NVMAI_CUDA_OK;
+    return dispatch_bits_meta(c.shared_f ? c.shared_bits : 4, c.meta_dtype, [&](auto B, auto M) {
+        stage1_kernel<decltype(B)::value, decltype(M)::value><<<grid, kDecodeThreads, 0, st>>>(p);
+        return check_launch(h);
+    });
+}
+
+int launch_stage2(nvmai_cuda_moe *h, const RoutedSource &src, const ExpertOffsets &off, const __half *x,
+                  uint32_t x_stride, uint32_t tokens, __half *acts, const uint32_t *active_slots_dev,
+                  uint32_t n_slots, cudaStream_t st) {
+    const auto &c = h->cfg;
+    Stage2Params p{};
+    p.src = src; p.off = off; p.x = x; p.x_stride = x_stride; p.acts = acts;
+    p.active_slots = active_slots_dev;
+    p.D = c.d; p.F = c.f; p.top_k = c.top_k; p.act = c.activation;
+    dim3 grid(c.f / kTileRows, n_slots, tokens);
+    return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
+        stage2_kernel<decltype(B)::value, decltype(M)::value><<<grid, kDecodeThreads, 0, st>>>(p);
+        return check_launch(h);
+    });
+}
+
+int launch_stage3(nvmai_cuda_moe *h, Stage3Params p, uint32_t tokens, cudaStream_t st) {
+    const auto &c = h->cfg;
+    p.D = c.d; p.F = c.f;
+    dim3 grid(c.d / kTileRows, tokens);
+    const uint32_t warps = p.top_k + (p.shared_f ? 1 : 0);
+    const uint32_t threads = (warps < 1 ? 1 : warps) * 32;
+    return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
+        if (c.out_dtype == NVMAI_OUT_FP16)
+            stage3_kernel<decltype(B)::value, decltype(M)::value, OUT_F16><<<grid, threads, 0, st>>>(p);
+        else
+            stage3_kernel<decltype(B)::value, decltype(M)::value, OUT_F32><<<grid, threads, 0, st>>>(p);
+        return check_launch(h);
+    });
+}
+
+int check_layer(const nvmai_cuda_moe *h, uint32_t layer) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    if (layer >= h->layers.size()) return NVMAI_CUDA_ERANGE;
+    if (!h->layers[layer].registered) return NVMAI_CUDA_EINVAL;
+    return NVMAI_CUDA_OK;
+}
+
+int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint32_t tokens, void *hidden,
+                      void *h2_out, uint32_t *out_idx, __half *out_w, cudaStream_t st) {
+    const auto &c = h->cfg;
+    const LayerViews &lv = h->layers[layer];
+    uint32_t *idx = out_idx ? out_idx : h->idx;
+    __half *w = out_w ? out_w : h->w;
+    int rc = launch_stage1(h, lv, x, c.d, tokens, idx, w, true, c.shared_f != 0, st);
+    if (rc) return rc;
+    rc = launch_stage2(h, source_from_layer(h, lv, idx), to_offsets(lv.w.offsets), x, c.d, tokens, h->acts,
+                       nullptr, c.top_k, st);
+    if (rc) return rc;
+    Stage3Params p{};
+    p.src = source_from_layer(h, lv, idx);
+    p.off = to_offsets(lv.w.offsets);
+    p.acts = h->acts;
+    p.routing_w = w;
+    p.residual = nullptr;
+    p.sdown = to_mat(lv.w.shared_down_proj);
+    p.shared_f = c.shared_f;
+    p.shared_bits = c.shared_bits;
+    p.shared_act = h->shared_act;
+    p.gate_val = c.shared_gate_kind != NVMAI_GATE_NONE ? h->gate_val : nullptr;
+    p.h1_out = nullptr;
+    p.y = h2_out ? h2_out : h->y;
+    p.hidden = hidden;
+    p.top_k = c.top_k;
+    return launch_stage3(h, p, tokens, st);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------
+// exported functions
+// ------------------------------------------------------------------------------
+
+extern "C" {
+
+uint64_t nvmai_cuda_moe_expert_offsets(uint32_t d, uint32_t f, uint32_t bits, nvmai_expert_offsets *out) {
+    const uint64_t gate_w = (uint64_t)f * d * bits / 8, gate_m = (uint64_t)f * (d / 64) * 2;
+    const uint64_t down_w = (uint64_t)d * f * bits / 8, down_m = (uint64_t)d * (f / 64) * 2;
+    uint64_t o = 0;
+    nvmai_expert_offsets r;
+    r.gate_w = (uint32_t)o; o += gate_w;
+    r.gate_s = (uint32_t)o; o += gate_m;
+    r.gate_b = (uint32_t)o; o += gate_m;
+    r.up_w = (uint32_t)o; o += gate_w;
+    r.up_s = (uint32_t)o; o += gate_m;
+    r.up_b = (uint32_t)o; o += gate_m;
+    r.down_w = (uint32_t)o; o += down_w;
+    r.down_s = (uint32_t)o; o += down_m;
+    r.down_b = (uint32_t)o; o += down_m;
+    if (out) *out = r;
+    return o;
+}
+
+nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *out_err) {
+    auto fail = [&](int code) -> nvmai_cuda_moe * { if (out_err) *out_err = code; return nullptr; };
+    if (!config) return fail(NVMAI_CUDA_EINVAL);
+    const nvmai_cuda_moe_config &c = *config;
+    // MoE.swift:163-165 and SharedExpertInt4.swift:40-45, as error codes
+    if (c.d == 0 || c.d % 64 != 0 || c.f == 0 || c.f % 64 != 0 || c.shared_f % 64 != 0) return fail(NVMAI_CUDA_EINVAL);
+    if (c.num_experts == 0 || c.num_experts > (uint32_t)kMaxExperts) return fail(NVMAI_CUDA_ERANGE);
+    if (c.top_k == 0 || c.top_k > 32 || c.top_k > c.num_experts) return fail(NVMAI_CUDA_ERANGE);
+    if (!valid_bits(c.routed_bits) || (c.shared_f && !valid_bits(c.shared_bits))) return fail(NVMAI_CUDA_EINVAL);
+    if (c.router_kind != NVMAI_ROUTER_DENSE_F16 && c.router_kind != NVMAI_ROUTER_AFFINE4 &&
+        c.router_kind != NVMAI_ROUTER_AFFINE8) return fail(NVMAI_CUDA_EINVAL);
+    if (c.shared_gate_kind != NVMAI_GATE_NONE && c.shared_gate_kind != NVMAI_ROUTER_DENSE_F16 &&
+        c.shared_gate_kind != NVMAI_ROUTER_AFFINE4 && c.shared_gate_kind != NVMAI_ROUTER_AFFINE8)
+        return fail(NVMAI_CUDA_EINVAL);
+    if (c.meta_dtype > NVMAI_META_FP16 || c.activation > NVMAI_ACT_GELU_TANH || c.out_dtype > NVMAI_OUT_FP32)
+        return fail(NVMAI_CUDA_EINVAL);
+    if (c.max_tokens == 0 || c.num_layers == 0) return fail(NVMAI_CUDA_EINVAL);
+
+    nvmai_cuda_moe *h = new (std::nothrow) nvmai_cuda_moe();
+    if (!h) return fail(NVMAI_CUDA_ENOMEM);
+    h->cfg = c;
+    h->layers.resize(c.num_layers);
+    const size_t T = c.max_tokens;
+    auto alloc = [&](auto **ptr, size_t bytes) -> bool {
+        cudaError_t e = cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16);
+        if (e != cudaSuccess) { h->last_cuda_error = (int)e; return false; }
+        return true;
+    };
+    bool ok = alloc(&h->logits, T * c.num_experts * sizeof(float)) && alloc(&h->idx, T * c.top_k * 4) &&
+              alloc(&h->w, T * c.top_k * 2) && alloc(&h->acts, T * c.top_k * c.f * 2) &&
+              alloc(&h->shared_act, T * (c.shared_f ? c.shared_f : 8) * 2) && alloc(&h->gate_val, T * 4) &&
+              alloc(&h->y, T * c.d * out_size(c.out_dtype)) && alloc(&h->xnorm, T * c.d * 2) &&
+              alloc(&h->counter, 64) && alloc(&h->stage_x, T * c.d * 2) &&
+              alloc(&h->stage_y, T * c.d * out_size(c.out_dtype));
+    if (ok) ok = cudaMemset(h->counter, 0, 64) == cudaSuccess;
+    if (!ok) {
+        const bool oom = h->last_cuda_error == (int)cudaErrorMemoryAllocation;
+        nvmai_cuda_moe_destroy(h);
+        cudaGetLastError();
+        return fail(oom ? NVMAI_CUDA_ENOMEM : NVMAI_CUDA_ECUDA);
+    }
+    if (out_err) *out_err = NVMAI_CUDA_OK;
+    return h;
+}
+
+void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
+    if (!h) return;
+    for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
+    cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
+    cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter);
+    cudaFree(h->stage_x); cudaFree(h->stage_y);
+    delete h;
+}
+
+int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, const nvmai_cuda_moe_layer *wts) {
+    if (!h || !wts) return NVMAI_CUDA_EINVAL;
+    if (layer >= h->layers.size()) return NVMAI_CUDA_ERANGE;
+    const auto &c = h->cfg;
+    if (!wts->experts || !aligned16(wts->experts) || (wts->expert_stride & 15u)) return NVMAI_CUDA_EINVAL;
+    int rc = check_offsets(c, wts->offsets, wts->expert_stride);
+    if (rc) return rc;
+    auto tensor_ok = [&](const nvmai_affine_tensor &t, uint32_t kind_or_bits) {
+        if (!t.w || !aligned16(t.w)) return false;
+        if (kind_or_bits == 0) return true;   // dense: no meta
+        return t.scales && t.biases && aligned16(t.scales) && aligned16(t.biases);
+    };
+    if (!tensor_ok(wts->router, c.router_kind)) return NVMAI_CUDA_EINVAL;
+    if (c.shared_f) {
+        if (!tensor_ok(wts->shared_gate_proj, c.shared_bits) || !tensor_ok(wts->shared_up_proj, c.shared_bits) ||
+            !tensor_ok(wts->shared_down_proj, c.shared_bits)) return NVMAI_CUDA_EINVAL;
+        if (c.shared_gate_kind != NVMAI_GATE_NONE && !tensor_ok(wts->shared_gate, c.shared_gate_kind))
+            return NVMAI_CUDA_EINVAL;
+    }
+    if (wts->effective_scale && !aligned16(wts->effective_scale)) return NVMAI_CUDA_EINVAL;
+    h->layers[layer].w = *wts;
+    h->layers[layer].registered = true;
+    h->graphs_stale = true;
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_router(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride, uint32_t tokens,
+                          uint32_t *out_idx, void *out_w_f16, void *stream) {
+    int rc = check_layer(h, layer);
+    if (rc) return rc;
+    if (!x_f16 || !out_idx || !out_w_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
+    if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (x_stride < h->cfg.d || (x_stride % 8) != 0) return NVMAI_CUDA_EINVAL;   // PrefillRouter.swift:68
+    return launch_stage1(h, h->layers[layer], static_cast<const __half *>(x_f16), x_stride, tokens, out_idx,
+                         static_cast<__half *>(out_w_f16), true, false, static_cast<cudaStream_t>(stream));
+}
+
+int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride,
+                                 uint32_t tokens, void *h1, void *stream) {
+    int rc = check_layer(h, layer);
+    if (rc) return rc;
+    const auto &c = h->cfg;
+    if (c.shared_f == 0 || !x_f16 || !h1 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
+    if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (x_stride < c.d || (x_stride % 8) != 0) return NVMAI_CUDA_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const LayerViews &lv = h->layers[layer];
+    rc = launch_stage1(h, lv, static_cast<const __half *>(x_f16), x_stride, tokens, nullptr, nullptr, false, true, st);
+    if (rc) return rc;
+    Stage3Params p{};
+    p.sdown = to_mat(lv.w.shared_down_proj);
+    p.shared_f = c.shared_f;
+    p.shared_bits = c.shared_bits;
+    p.shared_act = h->shared_act;
+    p.gate_val = c.shared_gate_kind != NVMAI_GATE_NONE ? h->gate_val : nullptr;
+    p.y = h1;
+    p.top_k = 0;
+    return launch_stage3(h, p, tokens, st);
+}
+
+int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_host,
+                                 const nvmai_expert_offsets *offsets, const void *x_f16, void *acts_f16,
+                                 const uint32_t *active_slots_host, uint32_t active_count, void *stream) {
+    if (!h || !blobs_host || !offsets || !x_f16 || !acts_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
+    const auto &c = h->cfg;
+    if (c.top_k != (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;     // MoE.swift:442-445
+    int rc = check_offsets(c, *offsets, 0);
+    if (rc) return rc;
+    for (uint32_t k = 0; k < c.top_k; ++k)
+        if (!blobs_host[k] || !aligned16(blobs_host[k])) return NVMAI_CUDA_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t *slots_dev = nullptr;
+    uint32_t n_slots = c.top_k;
+    if (active_slots_host != nullptr) {
+        if (active_count == 0) return NVMAI_CUDA_OK;                 // MoE.swift:356
+        if (active_count > c.top_k) return NVMAI_CUDA_ERANGE;
+        // the slot list rides in the idx scratch (8 x u32), like the runner's moeMissActiveSlots buffer
+        rc = record(h, cudaMemcpyAsync(h->idx, active_slots_host, active_count * 4, cudaMemcpyHostToDevice, st));
+        if (rc) return rc;
+        slots_dev = h->idx;
+        n_slots = active_count;
+    }
+    return launch_stage2(h, source_from_blobs(blobs_host, c.top_k), to_offsets(*offsets),
+                         static_cast<const __half *>(x_f16), c.d, 1, static_cast<__half *>(acts_f16), slots_dev,
+                         n_slots, st);
+}
+
+int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_host,
+                                 const nvmai_expert_offsets *offsets, const void *acts_f16,
+                                 const void *routing_w_f16, const void *residual, void *y, void *stream) {
+    if (!h || !blobs_host || !offsets || !acts_f16 || !routing_w_f16 || !residual || !y) return NVMAI_CUDA_EINVAL;
+    if (!aligned16(acts_f16)) return NVMAI_CUDA_EINVAL;
+    const auto &c = h->cfg;
+    if (c.top_k != (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
+    int rc = check_offsets(c, *offsets, 0);
+    if (rc) return rc;
+    for (uint32_t k = 0; k < c.top_k; ++k)
+        if (!blobs_host[k] || !aligned16(blobs_host[k])) return NVMAI_CUDA_EINVAL;
+    Stage3Params p{};
+    p.src = source_from_blobs(blobs_host, c.top_k);
+    p.off = to_offsets(*offsets);
+    p.acts = static_cast<const __half *>(acts_f16);
+    p.routing_w = static_cast<const __half *>(routing_w_f16);
+    p.residual = residual;
+    p.y = y;
+    p.top_k = c.top_k;
+    return launch_stage3(h, p, 1, static_cast<cudaStream_t>(stream));
+}
+
+int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
+                                void *hidden_inout, void *h2_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    int rc = check_layer(h, layer);
+    if (rc) return rc;
+    if (!x_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
+    if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (h->cfg.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
+    return layer_decode_impl(h, layer, static_cast<const __half *>(x_f16), tokens, hidden_inout, h2_out, out_idx,
+                             static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
+}
+
+static int stack_enqueue(nvmai_cuda_moe *h, const __half *x0, uint32_t tokens, void *y_last, cudaStream_t st) {
+    const auto &c = h->cfg;
+    const __half *x = x0;
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+        const bool last = l + 1 == c.num_layers;
+        void *y = last ? y_last : h->y;
+        int rc = layer_decode_impl(h, l, x, tokens, nullptr, y, nullptr, nullptr, st);
+        if (rc) return rc;
+        if (!last) {
+            if (c.out_dtype == NVMAI_OUT_FP16)
+                rms_renorm_kernel<OUT_F16><<<tokens, 256, 0, st>>>(y, h->xnorm, c.d);
+            else
+                rms_renorm_kernel<OUT_F32><<<tokens, 256, 0, st>>>(y, h->xnorm, c.d);
+            rc = check_launch(h);
+            if (rc) return rc;
+            x = h->xnorm;
+        }
+    }
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t tokens, void *y_last, void *stream) {
+    if (!h || !x0_f16 || !y_last || !aligned16(x0_f16)) return NVMAI_CUDA_EINVAL;
+    const auto &c = h->cfg;
+    if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (c.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
+    for (uint32_t l = 0; l < c.num_layers; ++l)
+        if (!h->layers[l].registered) return NVMAI_CUDA_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // Launch-bound chain (4 small kernels per layer): replay it as a CUDA graph.
+    // The graph is captured once per (x0, y, tokens, stream); a stream that is
+    // itself being captured, or the legacy default stream, gets plain launches.
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (st != nullptr) cudaStreamIsCapturing(st, &cs);
+    if (st == nullptr || cs != cudaStreamCaptureStatusNone)
+        return stack_enqueue(h, static_cast<const __half *>(x0_f16), tokens, y_last, st);
+    if (h->graphs_stale) {
+        for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
+        h->stack_graphs.clear();
+        h->graphs_stale = false;
+    }
+    StackGraphKey key{x0_f16, y_last, tokens, st};
+    auto it = h->stack_graphs.find(key);
+    if (it == h->stack_graphs.end()) {
+        int rc = record(h, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        if (rc) return rc;
+        const uint64_t launches_before = g_launches.load();
+        rc = stack_enqueue(h, static_cast<const __half *>(x0_f16), tokens, y_last, st);
+        g_launches.store(launches_before);        // captured, not launched
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamEndCapture(st, &graph);
+        if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+        if ((rc = record(h, e))) return rc;
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if ((rc = record(h, e))) return rc;
+        it = h->stack_graphs.emplace(key, exec).first;
+    }
+    int rc = record(h, cudaGraphLaunch(it->second, st));
+    if (rc == NVMAI_CUDA_OK) g_launches.fetch_add((uint64_t)c.num_layers * 4 - 1, std::memory_order_relaxed);
+    return rc;
+}
+
+int nvmai_cuda_moe_stack_decode_host(nvmai_cuda_moe *h, const void *x0_f16_host, uint32_t tokens, void *y_last_host,
+                                     void *stream) {
+    if (!h || !x0_f16_host || !y_last_host) return NVMAI_CUDA_EINVAL;
+    const auto &c = h->cfg;
+    if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = record(h, cudaMemcpyAsync(h->stage_x, x0_f16_host, (size_t)tokens * c.d * 2, cudaMemcpyHostToDevice, st));
+    if (rc) return rc;
+    rc = nvmai_cuda_moe_stack_decode(h, h->stage_x, tokens, h->stage_y, stream);
+    if (rc) return rc;
+    rc = record(h, cudaMemcpyAsync(y_last_host, h->stage_y, (size_t)tokens * c.d * out_size(c.out_dtype),
+                                   cudaMemcpyDeviceToHost, st));
+    if (rc) return rc;
+    return record(h, cudaStreamSynchronize(st));
+}
+
+int nvmai_cuda_moe_dequant(uint32_t bits, uint32_t meta_dtype, const void *w, const void *scales, const void *biases,
+                           uint32_t rows, uint32_t n, float *out_f32, void *stream) {
+    if (!w || !scales || !biases || !out_f32 || n % 64 != 0 || rows == 0 || n == 0) return NVMAI_CUDA_EINVAL;
+    const size_t total = (size_t)rows * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dispatch_bits_meta(bits, meta_dtype, [&](auto B, auto M) {
+        dequant_kernel<decltype(B)::value, decltype(M)::value><<<blocks, 256, 0, st>>>(
+            static_cast<const uint8_t *>(w), static_cast<const uint16_t *>(scales),
+            static_cast<const uint16_t *>(biases), rows, n, out_f32);
+        return check_launch(nullptr);
+    });
+}
+
+int nvmai_cuda_moe_affine_gemv(uint32_t bits, uint32_t meta_dtype, const void *w, const void *scales,
+                               const void *biases, const void *x_f16, void *y_f16, uint32_t m, uint32_t n,
+                               void *stream) {
+    if (!w || !scales || !biases || !x_f16 || !y_f16 || m == 0 || n == 0 || n % 64 != 0) return NVMAI_CUDA_EINVAL;
+    if (!aligned16(w) || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
+    if (!valid_bits(bits) || meta_dtype > NVMAI_META_FP16) return NVMAI_CUDA_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned blocks = (m + 7) / 8;
+    if (meta_dtype == NVMAI_META_BF16)
+        affine_gemv_kernel<META_BF16><<<blocks, 256, 0, st>>>(bits, static_cast<const uint8_t *>(w),
+            static_cast<const uint16_t *>(scales), static_cast<const uint16_t *>(biases),
+            static_cast<const __half *>(x_f16), static_cast<__half *>(y_f16), m, n);
+    else
+        affine_gemv_kernel<META_FP16><<<blocks, 256, 0, st>>>(bits, static_cast<const uint8_t *>(w),
+            static_cast<const uint16_t *>(scales), static_cast<const uint16_t *>(biases),
+            static_cast<const __half *>(x_f16), static_cast<__half *>(y_f16), m, n);
+    return check_launch(nullptr);
+}
+
+int nvmai_cuda_moe_silu_mul_f16(const void *gate, const void *up, void *out, uint32_t count, void *stream) {
+    if (!gate || !up || !out) return NVMAI_CUDA_EINVAL;
+    if (count == 0) return NVMAI_CUDA_OK;
+    silu_mul_kernel<<<(count + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half *>(gate), static_cast<const __half *>(up), static_cast<__half *>(out), count);
+    return check_launch(nullptr);
+}
+
+int nvmai_cuda_moe_sigmoid_scalar_mul_f16(void *y, const void *gate, uint32_t count, void *stream) {
+    if (!y || !gate) return NVMAI_CUDA_EINVAL;
+    if (count == 0) return NVMAI_CUDA_OK;
+    sigmoid_scalar_mul_kernel<<<(count + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half *>(y), static_cast<const __half *>(gate), count);
+    return check_launch(nullptr);
+}
+
+int nvmai_cuda_moe_residual_add_f16(void *hidden, const void *delta, uint32_t count, void *stream) {
+    if (!hidden || !delta) return NVMAI_CUDA_EINVAL;
+    if (count == 0) return NVMAI_CUDA_OK;
+    residual_add_kernel<<<(count + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half *>(hidden), static_cast<const __half *>(delta), count);
+    return check_launch(nullptr);
+}
+
+int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream) {
+    return record(h, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+}
+
+int nvmai_cuda_moe_last_cuda_error(const nvmai_cuda_moe *h) { return h ? h->last_cuda_error : 0; }
+
+const char *nvmai_cuda_moe_error_string(int code) {
+    switch (code) {
+        case NVMAI_CUDA_OK: return "ok";
+        case NVMAI_CUDA_EINVAL: return "invalid argument (shape, null pointer or alignment)";
+        case NVMAI_CUDA_ERANGE: return "index or size out of range";
+        case NVMAI_CUDA_ENOMEM: return "device allocation failed";
+        case NVMAI_CUDA_ECUDA: return "CUDA runtime error";
+        case NVMAI_CUDA_ETIMEOUT: return "bounded device-side wait expired";
+        case NVMAI_CUDA_ENCCL: return "NCCL error";
+        default: return "unknown error";
+    }
+}
+
+uint64_t nvmai_cuda_moe_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,194 @@
+"""Thin ctypes wrapper over the C ABI, shaped like the reference's Swift kernel
+wrappers (`MoE`, `SharedExpertRuntime`, `Elementwise`; sources/NVMAI/Kernels).
+
+Device buffers are passed as anything with a `data_ptr()` (e.g. a CUDA torch
+tensor) or as a raw integer address; this module allocates nothing on the device
+itself.  Errors surface as `NvmaiError` carrying the library's error code.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+from . import _lib
+from . import format as fmt
+from ._lib import NvmaiError, check  # noqa: F401  (re-exported)
+
+
+def _ptr(buf) -> int | None:
+    if buf is None:
+        return None
+    if isinstance(buf, int):
+        return buf
+    return buf.data_ptr()
+
+
+def _stream(stream) -> int | None:
+    if stream is None:
+        return None
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream        # torch.cuda.Stream
+
+
+@dataclass
+class MoEConfig:
+    d: int = 2048
+    f: int = 512
+    shared_f: int = 512
+    num_experts: int = 256
+    top_k: int = 8
+    routed_bits: int = 4
+    shared_bits: int = 4
+    router_kind: int = fmt.ROUTER_DENSE_F16
+    shared_gate_kind: int = fmt.ROUTER_DENSE_F16
+    meta_dtype: int = fmt.META_BF16
+    activation: int = fmt.ACT_SILU
+    out_dtype: int = fmt.OUT_FP16
+    max_tokens: int = 1
+    num_layers: int = 1
+
+    def to_c(self) -> _lib.Config:
+        return _lib.Config(self.d, self.f, self.shared_f, self.num_experts, self.top_k, self.routed_bits,
+                           self.shared_bits, self.router_kind, self.shared_gate_kind, self.meta_dtype,
+                           self.activation, self.out_dtype, self.max_tokens, self.num_layers)
+
+
+def offsets_struct(off: dict[str, int]) -> _lib.ExpertOffsets:
+    return _lib.ExpertOffsets(*[off[n] for n in fmt.OFFSET_NAMES])
+
+
+def _tensor(t) -> _lib.AffineTensor:
+    if t is None:
+        return _lib.AffineTensor(None, None, None)
+    w, s, b = t
+    return _lib.AffineTensor(_ptr(w), _ptr(s), _ptr(b))
+
+
+class MoE:
+    """Counterpart of the reference's `MoE` + `SharedExpertRuntime` pair for one model."""
+
+    def __init__(self, config: MoEConfig):
+        self.config = config
+        self._lib = _lib.lib()
+        err = C.c_int(0)
+        cfg = config.to_c()
+        self._h = self._lib.nvmai_cuda_moe_create(C.byref(cfg), C.byref(err))
+        if not self._h:
+            raise NvmaiError(err.value, "nvmai_cuda_moe_create")
+        self._keep = {}
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.nvmai_cuda_moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- weights ---------------------------------------------------------------
+    def register_layer(self, layer: int, *, experts, expert_stride: int, offsets: dict[str, int], router,
+                       effective_scale=None, per_expert_scale=None, shared=None, shared_gate=None) -> None:
+        """router / shared[i] / shared_gate are (w, scales, biases) device buffers."""
+        L = _lib.Layer()
+        L.experts = _ptr(experts)
+        L.expert_stride = expert_stride
+        L.offsets = offsets_struct(offsets)
+        L.router = _tensor(router)
+        L.effective_scale = _ptr(effective_scale)
+        L.per_expert_scale = _ptr(per_expert_scale)
+        if shared is not None:
+            L.shared_gate_proj, L.shared_up_proj, L.shared_down_proj = (_tensor(t) for t in shared)
+        L.shared_gate = _tensor(shared_gate)
+        self._keep[layer] = (experts, router, effective_scale, per_expert_scale, shared, shared_gate)
+        check(self._lib.nvmai_cuda_moe_register_layer(self._h, layer, C.byref(L)), "register_layer")
+
+    # -- reference-shaped entry points -------------------------------------------
+    def encode_router(self, layer: int, x, out_idx, out_w, *, tokens: int = 1, x_stride: int | None = None,
+                      stream=None) -> None:
+        """`MoE.encodeRouter` (MoE.swift:151-213) / `PrefillRouter.encodeBlock`."""
+        check(self._lib.nvmai_cuda_moe_router(self._h, layer, _ptr(x), x_stride or self.config.d, tokens,
+                                              _ptr(out_idx), _ptr(out_w), _stream(stream)), "router")
+
+    def encode_shared_expert(self, layer: int, x, h1, *, tokens: int = 1, x_stride: int | None = None,
+                             stream=None) -> None:
+        """`SharedExpertRuntime.encode` + scalar gate + sigmoid mul (RealForwardRunner.swift:3866-3905)."""
+        check(self._lib.nvmai_cuda_moe_shared_expert(self._h, layer, _ptr(x), x_stride or self.config.d, tokens,
+                                                     _ptr(h1), _stream(stream)), "shared_expert")
+
+    def encode_routed_phase1(self, blobs, offsets: dict[str, int], x, acts, *, active_slots=None,
+                             stream=None) -> None:
+        """`encodeRoutedPersistentPhase1U16Load` / `…SubsetU16Load` (MoE.swift:295-392)."""
+        arr = (C.c_void_p * len(blobs))(*[_ptr(b) for b in blobs])
+        off = offsets_struct(offsets)
+        slots, n = None, 0
+        if active_slots is not None:
+            n = len(active_slots)
+            slots = (C.c_uint32 * max(n, 1))(*active_slots)
+        check(self._lib.nvmai_cuda_moe_routed_phase1(self._h, arr, C.byref(off), _ptr(x), _ptr(acts), slots, n,
+                                                     _stream(stream)), "routed_phase1")
+
+    def encode_routed_phase2(self, blobs, offsets: dict[str, int], acts, routing_w, residual, y, *,
+                             stream=None) -> None:
+        """`encodeRoutedPersistentPhase2Reduce` (MoE.swift:394-440)."""
+        arr = (C.c_void_p * len(blobs))(*[_ptr(b) for b in blobs])
+        off = offsets_struct(offsets)
+        check(self._lib.nvmai_cuda_moe_routed_phase2(self._h, arr, C.byref(off), _ptr(acts), _ptr(routing_w),
+                                                     _ptr(residual), _ptr(y), _stream(stream)), "routed_phase2")
+
+    # -- fused paths ----------------------------------------------------------------
+    def layer_decode(self, layer: int, x, tokens: int, *, hidden=None, h2_out=None, out_idx=None, out_w=None,
+                     stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_layer_decode(self._h, layer, _ptr(x), tokens, _ptr(hidden), _ptr(h2_out),
+                                                    _ptr(out_idx), _ptr(out_w), _stream(stream)), "layer_decode")
+
+    def stack_decode(self, x0, tokens: int, y_last, *, stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_stack_decode(self._h, _ptr(x0), tokens, _ptr(y_last), _stream(stream)),
+              "stack_decode")
+
+    def stack_decode_host(self, x0_host: int, tokens: int, y_last_host: int, *, stream=None) -> None:
+        """x0_host / y_last_host are HOST addresses (e.g. pinned numpy / torch CPU buffers)."""
+        check(self._lib.nvmai_cuda_moe_stack_decode_host(self._h, _ptr(x0_host), tokens, _ptr(y_last_host),
+                                                         _stream(stream)), "stack_decode_host")
+
+    def synchronize(self, stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_synchronize(self._h, _stream(stream)), "synchronize")
+
+
+# -- handle-free helpers ---------------------------------------------------------------
+
+def dequant(bits: int, meta: int, w, scales, biases, rows: int, n: int, out_f32, stream=None) -> None:
+    check(_lib.lib().nvmai_cuda_moe_dequant(bits, meta, _ptr(w), _ptr(scales), _ptr(biases), rows, n,
+                                            _ptr(out_f32), _stream(stream)), "dequant")
+
+
+def affine_gemv(bits: int, meta: int, w, scales, biases, x, y, m: int, n: int, stream=None) -> None:
+    """`DequantInt4GEMV.encode` / `DequantInt8GEMV.encode`."""
+    check(_lib.lib().nvmai_cuda_moe_affine_gemv(bits, meta, _ptr(w), _ptr(scales), _ptr(biases), _ptr(x), _ptr(y),
+                                                m, n, _stream(stream)), "affine_gemv")
+
+
+class Elementwise:
+    """`Elementwise` (sources/NVMAI/Kernels/Primitives/Elementwise.swift), the three MoE-side kernels."""
+
+    @staticmethod
+    def encode_silu_mul(gate, up, out, count: int, stream=None) -> None:
+        check(_lib.lib().nvmai_cuda_moe_silu_mul_f16(_ptr(gate), _ptr(up), _ptr(out), count, _stream(stream)),
+              "silu_mul")
+
+    @staticmethod
+    def encode_sigmoid_scalar_mul(y, gate, count: int, stream=None) -> None:
+        check(_lib.lib().nvmai_cuda_moe_sigmoid_scalar_mul_f16(_ptr(y), _ptr(gate), count, _stream(stream)),
+              "sigmoid_scalar_mul")
+
+    @staticmethod
+    def encode_residual_add(hidden, delta, count: int, stream=None) -> None:
+        check(_lib.lib().nvmai_cuda_moe_residual_add_f16(_ptr(hidden), _ptr(delta), count, _stream(stream)),
+              "residual_add")
+
+
+def launch_count() -> int:
+    return int(_lib.lib().nvmai_cuda_moe_launch_count())

@@ -1,0 +1,56 @@
+"""Seeded synthetic MoE layers with the benchmark's value distributions.
+
+Codes uniform over the code range; scale ~ U(0.005, 0.02) and bias ~ U(-0.08, 0)
+per (row, group), drawn in fp32 and rounded once to the 16-bit meta type; router
+gate dense fp16 ~ N(0, 0.02); hidden rows fp16 ~ N(0, 1).  numpy builds a layer on
+the host (tests, single-layer runs); `device_stack` builds many layers directly
+in device memory with torch's CUDA generator (tens of GB would be too slow to
+make on the host and upload).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import format as fmt
+
+
+def affine_tensor(rng: np.random.Generator, rows: int, n: int, bits: int, meta: int):
+    """(packed u8 [rows, n*bits/8], scales u16 [rows, n/64], biases u16 [rows, n/64])."""
+    packed = rng.integers(0, 256, size=(rows, n * bits // 8), dtype=np.uint8)
+    scales = rng.uniform(0.005, 0.02, size=(rows, n // fmt.GROUP)).astype(np.float32)
+    biases = rng.uniform(-0.08, 0.0, size=(rows, n // fmt.GROUP)).astype(np.float32)
+    return packed, fmt.f32_to_meta_bits(scales, meta), fmt.f32_to_meta_bits(biases, meta)
+
+
+def layer(seed: int, *, d: int = 2048, f: int = 512, shared_f: int = 512, num_experts: int = 256,
+          routed_bits: int = 4, shared_bits: int | None = None, meta: int = fmt.META_FP16,
+          router_kind: int = fmt.ROUTER_DENSE_F16, gate_kind: int = fmt.ROUTER_DENSE_F16) -> dict:
+    """One layer's host arrays: experts u8 [E, stride], router, shared projections, gate row."""
+    rng = np.random.default_rng(seed)
+    shared_bits = routed_bits if shared_bits is None else shared_bits
+    off, stride = fmt.expert_offsets(d, f, routed_bits)
+    experts = np.empty((num_experts, stride), dtype=np.uint8)
+    for e in range(num_experts):
+        experts[e] = fmt.pack_expert_blob(affine_tensor(rng, f, d, routed_bits, meta),
+                                          affine_tensor(rng, f, d, routed_bits, meta),
+                                          affine_tensor(rng, d, f, routed_bits, meta), d, f, routed_bits)
+    out = {"experts": experts, "stride": stride, "offsets": off}
+    if router_kind == fmt.ROUTER_DENSE_F16:
+        out["router"] = (fmt.f32_to_f16_bits(rng.normal(0.0, 0.02, size=(num_experts, d))), None, None)
+    else:
+        out["router"] = affine_tensor(rng, num_experts, d, router_kind, meta)
+    if shared_f:
+        out["shared"] = (affine_tensor(rng, shared_f, d, shared_bits, meta),
+                         affine_tensor(rng, shared_f, d, shared_bits, meta),
+                         affine_tensor(rng, d, shared_f, shared_bits, meta))
+        if gate_kind == fmt.ROUTER_DENSE_F16:
+            out["gate"] = (fmt.f32_to_f16_bits(rng.normal(0.0, 0.02, size=(1, d))), None, None)
+        elif gate_kind != fmt.GATE_NONE:
+            out["gate"] = affine_tensor(rng, 1, d, gate_kind, meta)
+    return out
+
+
+def hidden_rows(seed: int, tokens: int, d: int = 2048) -> np.ndarray:
+    """fp16 bit patterns [tokens, d] ~ N(0, 1)."""
+    rng = np.random.default_rng(seed)
+    return fmt.f32_to_f16_bits(rng.normal(0.0, 1.0, size=(tokens, d)))
