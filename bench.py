@@ -1,0 +1,411 @@
+#!/usr/bin/env python
+"""Benchmark of the routed-expert MoE FFN stack (35B-A3B shape) on B200.
+
+Workload (BASELINE.json configs[3]): 40 MoE FFN layers (hidden 2048, 256 routed
+experts, top-8, expert intermediate 512, one sigmoid-gated shared expert of 512),
+group-64 affine weights, all experts resident in HBM, batch-1 decode.  A step is
+one token through all 40 layers; `value` is tokens/s.  Weights are seeded
+synthetic with the benchmark's value distributions, generated on the device.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--bits 4|8] [--impl ours|reference]
+
+One JSON line is printed by rank 0.  `--impl reference` times the reference's
+CPU path (its own C GEMV from oracle/_ref when built, else the restated port) on
+the host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+D, F, FS, E, K, LAYERS = 2048, 512, 512, 256, 8, 40
+METRIC = "moe_ffn_stack_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def expert_bytes(bits: int) -> int:
+    return 2 * (F * D * bits // 8 + 2 * F * (D // 64) * 2) + (D * F * bits // 8 + 2 * D * (F // 64) * 2)
+
+
+def layer_bytes(bits: int) -> int:
+    """Algorithmic bytes of one layer at batch 1: 8 routed + 1 shared expert,
+    the dense fp16 router, the gate row, x in and y out."""
+    return K * expert_bytes(bits) + expert_bytes(bits) + E * D * 2 + D * 2 + D * 2 + D * 4
+
+
+def stage2_bytes(bits: int, out_elt: int) -> int:
+    """Algorithmic bytes of one launch of the dominant kernel (routed gate/up +
+    activation, 8 experts): codes + scales + biases of gate and up, x, acts out."""
+    return K * 2 * (F * D * bits // 8 + 2 * F * (D // 64) * 2) + D * 2 + K * F * out_elt
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        out, _ = self.proc.communicate(timeout=10)
+        sm, smax, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# reference CPU path (also the cpu_baseline leg of the GPU arm)
+# --------------------------------------------------------------------------------------
+
+class CpuReferenceStack:
+    """The 40-layer workload on the host cores with the reference's CPU arithmetic
+    (CPUExpertFFN.accumulate over nvmai_int4_affine_gemv).  Per layer only the
+    blobs a token uses are generated (8 routed + 1 shared), since the timing does
+    not depend on which of the 256 experts were picked; the router still scores
+    all 256 rows.  Rows of each GEMV are split across threads."""
+
+    def __init__(self, bits: int, layers: int, threads: int, seed: int = 7):
+        from nvmai_b200 import format as fmt
+        from nvmai_b200 import synthetic
+        from oracle import oracle as orc
+        self.orc, self.bits, self.layers, self.threads = orc, bits, layers, threads
+        self.lib = orc.lib()
+        ref = orc.ref_lib() if bits == 4 else None
+        self.kind = "reference" if ref is not None else "port"
+        self.ref = ref
+        rng = np.random.default_rng(seed)
+        self.off, self.stride = fmt.expert_offsets(D, F, bits)
+        self.blobs, self.routers, self.gates = [], [], []
+        for _ in range(layers):
+            lay = np.empty((K + 1, self.stride), dtype=np.uint8)
+            for e in range(K + 1):
+                lay[e] = fmt.pack_expert_blob(synthetic.affine_tensor(rng, F, D, bits, fmt.META_BF16),
+                                              synthetic.affine_tensor(rng, F, D, bits, fmt.META_BF16),
+                                              synthetic.affine_tensor(rng, D, F, bits, fmt.META_BF16), D, F, bits)
+            self.blobs.append(lay)
+            self.routers.append(rng.normal(0.0, 0.02, size=(E, D)).astype(np.float32))
+            self.gates.append(rng.normal(0.0, 0.02, size=D).astype(np.float32))
+        self.pool = ThreadPoolExecutor(max_workers=threads)
+        self.chunks_f = self._chunks(F)
+        self.chunks_d = self._chunks(D)
+
+    def _chunks(self, rows: int):
+        per = max(16, -(-rows * (K + 1) // (self.threads * 4)))
+        return [(r, min(r + per, rows)) for r in range(0, rows, per)]
+
+    def _gemv(self, blob: np.ndarray, w_off: int, s_off: int, b_off: int, x: np.ndarray, r0: int, r1: int, n: int,
+              out: np.ndarray) -> None:
+        orc = self.orc
+        row_bytes, groups = n * self.bits // 8, n // 64
+        base = blob.ctypes.data
+        w = base + w_off + r0 * row_bytes
+        s = base + s_off + r0 * groups * 2
+        b = base + b_off + r0 * groups * 2
+        o = out.ctypes.data + r0 * 4
+        if self.ref is not None:
+            import ctypes as C
+            self.ref.nvmai_int4_affine_gemv(C.cast(w, orc.u8p), C.cast(s, orc.u16p), C.cast(b, orc.u16p),
+                                            x.ctypes.data_as(orc.f32p), r1 - r0, n, C.cast(o, orc.f32p))
+        else:
+            self.lib.orc_affine_gemv_f32(self.bits, orc.META_BF16, w, s, b, orc.ptr(x), r1 - r0, n, o)
+
+    def token(self, x: np.ndarray) -> np.ndarray:
+        off = self.off
+        for l in range(self.layers):
+            blobs = self.blobs[l]
+            logits = self.routers[l] @ x
+            top = np.argsort(-logits, kind="stable")[:K]
+            ex = np.exp(logits[top] - logits[top[0]])
+            w = np.concatenate([ex / ex.sum(), [1.0 / (1.0 + np.exp(-float(self.gates[l] @ x)))]]).astype(np.float32)
+            g = np.empty((K + 1, F), dtype=np.float32)
+            u = np.empty((K + 1, F), dtype=np.float32)
+            jobs = []
+            for e in range(K + 1):
+                for r0, r1 in self.chunks_f:
+                    jobs.append(self.pool.submit(self._gemv, blobs[e], off["gate_w"], off["gate_s"], off["gate_b"], x,
+                                                 r0, r1, D, g[e]))
+                    jobs.append(self.pool.submit(self._gemv, blobs[e], off["up_w"], off["up_s"], off["up_b"], x,
+                                                 r0, r1, D, u[e]))
+            for j in jobs:
+                j.result()
+            act = np.ascontiguousarray((g / (1.0 + np.exp(-g))) * u, dtype=np.float32)   # CPUExpertFFN.swift:121-123
+            dn = np.empty((K + 1, D), dtype=np.float32)
+            jobs = [self.pool.submit(self._gemv, blobs[e], off["down_w"], off["down_s"], off["down_b"], act[e], r0, r1,
+                                     F, dn[e]) for e in range(K + 1) for r0, r1 in self.chunks_d]
+            for j in jobs:
+                j.result()
+            y = (w[:, None] * dn).sum(axis=0)
+            x = (y / np.sqrt(np.mean(y * y) + 1e-6)).astype(np.float16).astype(np.float32)
+        return x
+
+    def time_tokens(self, steps: int, warmup: int) -> float:
+        rng = np.random.default_rng(1)
+        xs = [rng.normal(size=D).astype(np.float16).astype(np.float32) for _ in range(max(steps, 1))]
+        for i in range(warmup):
+            self.token(xs[i % len(xs)])
+        t0 = time.perf_counter()
+        for i in range(steps):
+            self.token(xs[i % len(xs)])
+        return (time.perf_counter() - t0) / steps
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def base_record(args, n_gpus: int) -> dict:
+    return {
+        "metric": METRIC, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+        "higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+        "config": {"workload": f"configs[3]: 40-layer MoE FFN stack, 35B-A3B shape, {args.bits}-bit, batch-1 decode",
+                   "d": D, "f": F, "experts": E, "top_k": K, "layers": args.layers, "bits": args.bits,
+                   "meta": "bf16", "router": "dense fp16", "tokens_per_step": args.tokens},
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = host_threads()
+    layers = min(args.layers, args.ref_layers)
+    stack = CpuReferenceStack(args.bits, layers, threads)
+    warm = min(args.warmup, 1)
+    steps = max(1, min(args.steps, 5))
+    sec_per_token = stack.time_tokens(steps, warm) * (args.layers / layers)
+    val = 1.0 / sec_per_token
+    rec = base_record(args, args.gpus)
+    rec.update({"impl": "reference", "value": val, "ms_per_step": sec_per_token * 1e3, "scaling": "strong",
+                "dtype": "f32", "steps": steps, "warmup": warm,
+                "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": stack.kind,
+                                 "sample": f"{steps} tokens x {layers} of {args.layers} layers "
+                                           f"(8 routed + 1 shared expert and the router per layer), scaled to {args.layers}"},
+                "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0})
+    print(json.dumps(rec), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+
+def run_ours(args) -> None:
+    import torch
+    from nvmai_b200 import MoE, MoEConfig, launch_count, synthetic
+    from nvmai_b200 import format as fmt
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    tokens = args.tokens
+    cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
+                    router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16,
+                    meta_dtype=fmt.META_BF16, activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32,
+                    max_tokens=max(tokens, 1), num_layers=args.layers)
+    moe = MoE(cfg)
+    devs = []
+    for l in range(args.layers):
+        dev = synthetic.device_layer(1000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits,
+                                     meta=fmt.META_BF16)
+        synthetic.register_device_layer(moe, l, dev)
+        devs.append(dev)
+    torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(42 + rank)
+    n_inputs = 16      # distinct token inputs rotated through, so every step routes to different experts
+    xs = torch.randn(n_inputs, tokens, D, device="cuda", generator=gen).to(torch.float16)
+    x_in = torch.empty(tokens, D, dtype=torch.float16, device="cuda")
+    y = torch.empty(tokens, D, dtype=torch.float32, device="cuda")
+    xs_host = [xs[i].cpu().pin_memory() for i in range(n_inputs)]
+    y_host = torch.empty(tokens, D, dtype=torch.float32).pin_memory()
+    torch.cuda.synchronize()
+
+    def step(i: int) -> None:
+        x_in.copy_(xs[i % n_inputs], non_blocking=True)
+        moe.stack_decode(x_in, tokens, y, stream=stream)
+
+    def barrier() -> None:
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        barrier()
+        sampler = ClockSampler(local) if rank == 0 else None
+        l0 = launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(args.steps):
+            step(i)
+        end.record(stream)
+        barrier()
+        launches = launch_count() - l0
+        ms = start.elapsed_time(end)
+        assert torch.isfinite(y).all(), "non-finite output"
+
+        # end to end through the host-buffer entry point: pinned x in, y out, every step
+        for i in range(3):
+            moe.stack_decode_host(xs_host[i].data_ptr(), tokens, y_host.data_ptr(), stream=stream)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            moe.stack_decode_host(xs_host[i % n_inputs].data_ptr(), tokens, y_host.data_ptr(), stream=stream)
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        clocks = sampler.stop() if sampler else None
+
+    times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(times[0]), float(times[1])
+    ms_per_step = ms / args.steps
+    value = world * tokens / (ms_per_step / 1e3)       # interim multi-GPU mode: independent replicas
+    e2e_value = world * tokens / (e2e_ms / args.steps / 1e3)
+
+    rec = None
+    if rank == 0:
+        peak, which = measured_peaks()
+        roof = stage2_roofline(moe, cfg, devs, args, stream, peak, which)
+        step_bytes = args.layers * layer_bytes(args.bits)
+        roof["step_bytes"] = step_bytes
+        roof["step_frac"] = step_bytes / (ms_per_step / 1e3) / 1e9 / peak
+        rec = base_record(args, world)
+        rec.update({"value": value, "ms_per_step": ms_per_step, "scaling": "weak", "dtype": "f16xu%d->f32" % args.bits,
+                    "clocks": clocks, "gpu_launches": int(launches),
+                    "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": tokens * D * 2,
+                            "d2h_bytes_per_step": tokens * D * 4},
+                    "roofline": roof})
+        rec["config"]["l2"] = "working set 679 MB (4-bit) / 1246 MB (8-bit) per step exceeds the 126 MB L2; inputs rotate"
+        if world == 1 and not args.no_cpu_baseline:
+            threads = host_threads()
+            layers = min(args.layers, args.ref_layers)
+            cpu = CpuReferenceStack(args.bits, layers, threads)
+            sec = cpu.time_tokens(2, 1) * (args.layers / layers)
+            rec["cpu_baseline"] = {"value": 1.0 / sec, "unit": UNIT, "cores": threads, "kind": cpu.kind,
+                                   "sample": f"2 tokens x {layers} of {args.layers} layers, scaled to {args.layers}"}
+        print(json.dumps(rec), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> dict:
+    """Times the dominant kernel (routed gate/up + activation) alone: one launch per
+    layer with that layer's own experts (40 x 9.4 MB at 4-bit, larger than L2),
+    captured once as a CUDA graph and replayed, CUDA events on the launching stream."""
+    import torch
+    rng = np.random.default_rng(3)
+    x = torch.randn(D, device="cuda").to(torch.float16)
+    acts = torch.empty(K * F, dtype=torch.float32, device="cuda")
+    graph = torch.cuda.CUDAGraph()
+    plans = []
+    for dev in devs:
+        ids = rng.choice(E, size=K, replace=False)
+        base = dev["experts"].data_ptr()
+        plans.append(([base + int(e) * dev["stride"] for e in ids], dev["offsets"]))
+    with torch.cuda.stream(stream):
+        for blobs, off in plans[:2]:
+            moe.encode_routed_phase1(blobs, off, x, acts, stream=stream)
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for blobs, off in plans:
+                moe.encode_routed_phase1(blobs, off, x, acts, stream=stream)
+        reps = 20
+        for _ in range(3):
+            graph.replay()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        end.record(stream)
+        stream.synchronize()
+    us = start.elapsed_time(end) * 1e3 / (reps * len(plans))
+    nbytes = stage2_bytes(args.bits, 4)
+    achieved = nbytes / (us * 1e-6) / 1e9
+    traffic = None
+    tp = ROOT / "profiles" / "stage2_traffic.json"
+    if tp.exists():
+        traffic = json.loads(tp.read_text()).get(f"{args.bits}bit_bytes_per_launch")
+    return {"bound": "hbm", "kernel": "stage2_kernel (routed gate/up + activation)", "achieved": achieved, "peak": peak,
+            "peak_source": which, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+            "bytes_per_launch": nbytes, "us_per_launch": us}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bits", type=int, default=4, choices=[4, 8])
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

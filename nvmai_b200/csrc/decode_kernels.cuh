@@ -181,6 +181,38 @@ __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, in
     }
 }
 
+template <int OUT> __device__ __forceinline__ float load_out(const void *p, size_t i) {
+    if (OUT == OUT_F16) return __half2float(reinterpret_cast<const __half *>(p)[i]);
+    return reinterpret_cast<const float *>(p)[i];
+}
+template <int OUT> __device__ __forceinline__ void store_out(void *p, size_t i, float v) {
+    if (OUT == OUT_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+    else reinterpret_cast<float *>(p)[i] = v;
+}
+template <int OUT> __device__ __forceinline__ float round_out(float v) {
+    return OUT == OUT_F16 ? round_f16(v) : v;
+}
+
+// Rounding of intermediates the reference stores as half (gate/up of the shared
+// expert, activations, the scalar gate).  fp16 outputs: half, as the reference.
+// fp32 outputs ("wide range"): the same 11 significant bits, round-to-nearest-even,
+// but with fp32's exponent range, so that weights whose activations exceed 65504
+// do not overflow; the value is kept in an fp32 slot.
+__device__ __forceinline__ float round11(float v) {
+    uint32_t u = __float_as_uint(v);
+    if ((u & 0x7F800000u) == 0x7F800000u) return v;
+    u += 0xFFFu + ((u >> 13) & 1u);
+    u &= ~0x1FFFu;
+    return __uint_as_float(u);
+}
+template <int OUT> __device__ __forceinline__ float round_mid(float v) {
+    return OUT == OUT_F16 ? round_f16(v) : round11(v);
+}
+template <int OUT> __device__ __forceinline__ void store_mid(void *p, size_t i, float v) {
+    if (OUT == OUT_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+    else reinterpret_cast<float *>(p)[i] = round11(v);
+}
+
 // ---------------------------------------------------------------------------
 // Stage 1
 // ---------------------------------------------------------------------------
@@ -195,11 +227,11 @@ struct Stage1Params {
     // shared expert (optional: shared_f == 0 disables)
     AffineMat sgate, sup;
     uint32_t shared_f;
-    __half *shared_act;       // [tokens][shared_f]
+    void *shared_act;         // [tokens][shared_f], fp16 or fp32 (see round_mid)
     // scalar gate (optional)
     const uint8_t *gW; const uint16_t *gS; const uint16_t *gB;
     uint32_t gate_kind;       // 0 dense, 4, 8, 0xFFFFFFFF none
-    float *gate_val;          // [tokens], the fp16-rounded gate pre-activation
+    float *gate_val;          // [tokens], the rounded gate pre-activation
     // input
     const __half *x; uint32_t x_stride; uint32_t tokens;
     uint32_t D, E, K, act;
@@ -210,10 +242,11 @@ struct Stage1Params {
 // warps; gate and up are rounded to half before the activation, as both of the
 // reference's shared-expert paths do (SharedExpertInt4.swift:61-96;
 // dequant_int8.metal:159-163).
-template <int BITS, int META, int CH>
+template <int BITS, int META, int CH, int OUT>
 __device__ __forceinline__ void gate_up_tile(const AffineMat &gate, const AffineMat &up, int row0, int D,
                                              const __half *xrow_token, uint32_t act, bool round_gate_up,
-                                             __half *out_row /* [F] */, float *red /* smem 8*2*16 */) {
+                                             void *out_base, size_t out_row_offset /* elements */,
+                                             float *red /* smem 8*2*16 */) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int groups = D / kGroup;
@@ -236,12 +269,12 @@ __device__ __forceinline__ void gate_up_tile(const AffineMat &gate, const Affine
             gsum += red[(w * 2 + 0) * 16 + threadIdx.x];
             usum += red[(w * 2 + 1) * 16 + threadIdx.x];
         }
-        if (round_gate_up) { gsum = round_f16(gsum); usum = round_f16(usum); }
-        out_row[row0 + threadIdx.x] = __float2half_rn(hidden_act(gsum, act) * usum);
+        if (round_gate_up) { gsum = round_mid<OUT>(gsum); usum = round_mid<OUT>(usum); }
+        store_mid<OUT>(out_base, out_row_offset + row0 + threadIdx.x, hidden_act(gsum, act) * usum);
     }
 }
 
-template <int SBITS, int META>
+template <int SBITS, int META, int OUT>
 __global__ void __launch_bounds__(kDecodeThreads) stage1_kernel(Stage1Params p) {
     __shared__ float red[8 * 2 * 16];
     __shared__ bool is_last;
@@ -275,14 +308,14 @@ __global__ void __launch_bounds__(kDecodeThreads) stage1_kernel(Stage1Params p) 
         const uint32_t tiles = p.shared_f / kTileRows;
         const uint32_t tok = sb / tiles, tile = sb % tiles;
         constexpr int CH = SBITS == 4 ? 4 : 2;
-        gate_up_tile<SBITS, META, CH>(p.sgate, p.sup, tile * kTileRows, p.D, p.x + (size_t)tok * p.x_stride,
-                                      p.act, true, p.shared_act + (size_t)tok * p.shared_f, red);
+        gate_up_tile<SBITS, META, CH, OUT>(p.sgate, p.sup, tile * kTileRows, p.D, p.x + (size_t)tok * p.x_stride,
+                                           p.act, true, p.shared_act, (size_t)tok * p.shared_f, red);
     } else {
         // scalar gate g = half(W_g . x), one warp per token (RealForwardRunner.swift:3884-3896)
         for (uint32_t tok = warp; tok < p.tokens; tok += 8) {
             const float v = router_row_logit<META>(p.gate_kind, p.gW, p.gS, p.gB,
                                                    p.x + (size_t)tok * p.x_stride, nullptr, 0, p.D);
-            if (lane == 0) p.gate_val[tok] = round_f16(v);
+            if (lane == 0) p.gate_val[tok] = round_mid<OUT>(v);
         }
     }
 }
@@ -295,12 +328,12 @@ struct Stage2Params {
     RoutedSource src;
     ExpertOffsets off;
     const __half *x; uint32_t x_stride;
-    __half *acts;                       // [tokens][top_k][F]
+    void *acts;                         // [tokens][top_k][F], fp16 or fp32 (see round_mid)
     const uint32_t *active_slots;       // device, or nullptr = identity
     uint32_t D, F, top_k, act;
 };
 
-template <int BITS, int META>
+template <int BITS, int META, int OUT>
 __global__ void __launch_bounds__(kDecodeThreads) stage2_kernel(Stage2Params p) {
     __shared__ float red[8 * 2 * 16];
     const uint32_t tok = blockIdx.z;
@@ -313,8 +346,8 @@ __global__ void __launch_bounds__(kDecodeThreads) stage2_kernel(Stage2Params p) 
     const AffineMat up = {blob + p.off.o[3], reinterpret_cast<const uint16_t *>(blob + p.off.o[4]),
                           reinterpret_cast<const uint16_t *>(blob + p.off.o[5])};
     constexpr int CH = BITS == 4 ? 4 : 2;
-    gate_up_tile<BITS, META, CH>(gate, up, blockIdx.x * kTileRows, p.D, p.x + (size_t)tok * p.x_stride, p.act,
-                                 false, p.acts + ((size_t)tok * p.top_k + slot) * p.F, red);
+    gate_up_tile<BITS, META, CH, OUT>(gate, up, blockIdx.x * kTileRows, p.D, p.x + (size_t)tok * p.x_stride, p.act,
+                                      false, p.acts, ((size_t)tok * p.top_k + slot) * p.F, red);
 }
 
 // ---------------------------------------------------------------------------
@@ -326,12 +359,12 @@ __global__ void __launch_bounds__(kDecodeThreads) stage2_kernel(Stage2Params p) 
 struct Stage3Params {
     RoutedSource src;
     ExpertOffsets off;
-    const __half *acts;                 // [tokens][top_k][F]
+    const void *acts;                   // [tokens][top_k][F], fp16 or fp32
     const __half *routing_w;            // [tokens][top_k]
     const void *residual;               // out_dtype[tokens][D] or nullptr (standalone phase 2)
     // shared expert (fused path; shared_f == 0 disables)
     AffineMat sdown; uint32_t shared_f; uint32_t shared_bits;
-    const __half *shared_act;           // [tokens][shared_f]
+    const void *shared_act;             // [tokens][shared_f], fp16 or fp32
     const float *gate_val;              // [tokens] or nullptr (ungated)
     void *h1_out;                       // optional out_dtype[tokens][D]
     void *y;                            // out_dtype[tokens][D]  (block output h2)
@@ -339,49 +372,84 @@ struct Stage3Params {
     uint32_t D, F, top_k;
 };
 
-template <int OUT> __device__ __forceinline__ float load_out(const void *p, size_t i) {
-    if (OUT == OUT_F16) return __half2float(reinterpret_cast<const __half *>(p)[i]);
-    return reinterpret_cast<const float *>(p)[i];
-}
-template <int OUT> __device__ __forceinline__ void store_out(void *p, size_t i, float v) {
-    if (OUT == OUT_F16) reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
-    else reinterpret_cast<float *>(p)[i] = v;
-}
-template <int OUT> __device__ __forceinline__ float round_out(float v) {
-    return OUT == OUT_F16 ? round_f16(v) : v;
+// Activation row of one warp as tensor-core B operand.  fp16 rows are read in
+// place.  fp32 rows (11-bit values, any exponent) are scaled by a power of two
+// that puts the row's largest magnitude in [2^14, 2^15), converted to half
+// (exact) and staged in shared memory; the accumulator is scaled back afterwards.
+// While the row is being reduced the warp's weight tile is prefetched into L2.
+template <int OUT>
+__device__ __forceinline__ const __half *stage_row(const void *rows, size_t row_offset, int n, __half *smem_row,
+                                                   const uint8_t *tile_w, size_t tile_bytes, float &scale_up) {
+    scale_up = 1.0f;
+    if (OUT == OUT_F16) return reinterpret_cast<const __half *>(rows) + row_offset;
+    const int lane = threadIdx.x & 31;
+    for (size_t o = (size_t)lane * 128; o < tile_bytes; o += 32 * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(tile_w + o));
+    const float *src = reinterpret_cast<const float *>(rows) + row_offset;
+    float m = 0.0f;
+    for (int i = lane * 4; i < n; i += 128) {
+        const float4 v = *reinterpret_cast<const float4 *>(src + i);
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const uint32_t ebits = (__float_as_uint(m) >> 23) & 0xFFu;
+    float scale_down = 1.0f;
+    if (ebits > 14u) {
+        scale_down = __uint_as_float((268u - ebits) << 23);
+        scale_up = __uint_as_float((ebits - 14u) << 23);
+    }
+    for (int i = lane * 4; i < n; i += 128) {
+        const float4 v = *reinterpret_cast<const float4 *>(src + i);
+        __half2 lo = __floats2half2_rn(v.x * scale_down, v.y * scale_down);
+        __half2 hi = __floats2half2_rn(v.z * scale_down, v.w * scale_down);
+        uint2 packed = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+        *reinterpret_cast<uint2 *>(smem_row + i) = packed;
+    }
+    __syncwarp();
+    return smem_row;
 }
 
 template <int BITS, int META, int OUT>
 __global__ void __launch_bounds__(kDecodeThreads + 32) stage3_kernel(Stage3Params p) {
     __shared__ float part[(kMaxTopK + 1) * 16];
+    extern __shared__ __align__(16) unsigned char dyn_smem[];   // fp32 mode: (top_k+1) rows of max(F, shared_f) halves
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t tok = blockIdx.y;
     const int row0 = blockIdx.x * kTileRows;
+    const int row_halves = max(p.F, p.shared_f);
+    __half *smem_row = reinterpret_cast<__half *>(dyn_smem) + (size_t)warp * row_halves;
     if (warp < (int)p.top_k) {
         const uint8_t *blob = routed_blob(p.src, tok, warp, p.top_k);
         const AffineMat mats[1] = {{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
                                     reinterpret_cast<const uint16_t *>(blob + p.off.o[8])}};
         float acc[1][4] = {};
-        const __half *arow = p.acts + ((size_t)tok * p.top_k + warp) * p.F;
+        const size_t row_bytes = (size_t)p.F * BITS / 8;
+        float scale_up;
+        const __half *arow = stage_row<OUT>(p.acts, ((size_t)tok * p.top_k + warp) * p.F, p.F, smem_row,
+                                            mats[0].w + (size_t)row0 * row_bytes, kTileRows * row_bytes, scale_up);
         constexpr int CH = BITS == 4 ? 4 : 2;
         tile_accumulate<BITS, META, 1, CH>(mats, row0, p.F, 0, p.F / kGroup, g == 0 ? arow : nullptr, acc);
         const float wk = __half2float(p.routing_w[(size_t)tok * p.top_k + warp]);
         if (t == 0) {
-            part[warp * 16 + g] = wk * acc[0][0];          // moe.metal:802
-            part[warp * 16 + g + 8] = wk * acc[0][2];
+            part[warp * 16 + g] = wk * (acc[0][0] * scale_up);          // moe.metal:802
+            part[warp * 16 + g + 8] = wk * (acc[0][2] * scale_up);
         }
     } else if (warp == (int)p.top_k && p.shared_f != 0) {
         const AffineMat mats[1] = {p.sdown};
         float acc[1][4] = {};
-        const __half *arow = p.shared_act + (size_t)tok * p.shared_f;
+        const size_t row_bytes = (size_t)p.shared_f * p.shared_bits / 8;
+        float scale_up;
+        const __half *arow = stage_row<OUT>(p.shared_act, (size_t)tok * p.shared_f, p.shared_f, smem_row,
+                                            mats[0].w + (size_t)row0 * row_bytes, kTileRows * row_bytes, scale_up);
         if (p.shared_bits == 4)
             tile_accumulate<4, META, 1, 4>(mats, row0, p.shared_f, 0, p.shared_f / kGroup, g == 0 ? arow : nullptr, acc);
         else
             tile_accumulate<8, META, 1, 2>(mats, row0, p.shared_f, 0, p.shared_f / kGroup, g == 0 ? arow : nullptr, acc);
         if (t == 0) {
-            part[kMaxTopK * 16 + g] = acc[0][0];
-            part[kMaxTopK * 16 + g + 8] = acc[0][2];
+            part[kMaxTopK * 16 + g] = acc[0][0] * scale_up;
+            part[kMaxTopK * 16 + g + 8] = acc[0][2] * scale_up;
         }
     }
     __syncthreads();

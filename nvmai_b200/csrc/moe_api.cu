@@ -41,8 +41,8 @@ struct nvmai_cuda_moe {
     float *logits = nullptr;        // [T][E]
     uint32_t *idx = nullptr;        // [T][K]
     __half *w = nullptr;            // [T][K]
-    __half *acts = nullptr;         // [T][K][F]
-    __half *shared_act = nullptr;   // [T][Fs]
+    void *acts = nullptr;           // [T][K][F]   fp16 or fp32 by out_dtype
+    void *shared_act = nullptr;     // [T][Fs]     fp16 or fp32 by out_dtype
     float *gate_val = nullptr;      // [T]
     void *y = nullptr;              // [T][D] out_dtype
     __half *xnorm = nullptr;        // [T][D]
@@ -115,6 +115,12 @@ int check_offsets(const nvmai_cuda_moe_config &c, const nvmai_expert_offsets &o,
 }
 
 template <typename F>
+int dispatch_out(uint32_t out_dtype, F &&f) {
+    if (out_dtype == NVMAI_OUT_FP16) return f(std::integral_constant<int, OUT_F16>{});
+    return f(std::integral_constant<int, OUT_F32>{});
+}
+
+template <typename F>
 int dispatch_bits_meta(uint32_t bits, uint32_t meta, F &&f) {
     if (bits == 4 && meta == NVMAI_META_BF16) return f(std::integral_constant<int, 4>{}, std::integral_constant<int, META_BF16>{});
     if (bits == 4 && meta == NVMAI_META_FP16) return f(std::integral_constant<int, 4>{}, std::integral_constant<int, META_FP16>{});
@@ -156,13 +162,15 @@ int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x, uint
     const uint32_t grid = p.n_router_blocks + p.n_shared_blocks + gate_blocks;
     if (grid == 0) return NVMAI_CUDA_OK;
     return dispatch_bits_meta(c.shared_f ? c.shared_bits : 4, c.meta_dtype, [&](auto B, auto M) {
-        stage1_kernel<decltype(B)::value, decltype(M)::value><<<grid, kDecodeThreads, 0, st>>>(p);
-        return check_launch(h);
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            stage1_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value><<<grid, kDecodeThreads, 0, st>>>(p);
+            return check_launch(h);
+        });
     });
 }
 
 int launch_stage2(nvmai_cuda_moe *h, const RoutedSource &src, const ExpertOffsets &off, const __half *x,
-                  uint32_t x_stride, uint32_t tokens, __half *acts, const uint32_t *active_slots_dev,
+                  uint32_t x_stride, uint32_t tokens, void *acts, const uint32_t *active_slots_dev,
                   uint32_t n_slots, cudaStream_t st) {
     const auto &c = h->cfg;
     Stage2Params p{};
@@ -171,8 +179,10 @@ int launch_stage2(nvmai_cuda_moe *h, const RoutedSource &src, const ExpertOffset
     p.D = c.d; p.F = c.f; p.top_k = c.top_k; p.act = c.activation;
     dim3 grid(c.f / kTileRows, n_slots, tokens);
     return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
-        stage2_kernel<decltype(B)::value, decltype(M)::value><<<grid, kDecodeThreads, 0, st>>>(p);
-        return check_launch(h);
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            stage2_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value><<<grid, kDecodeThreads, 0, st>>>(p);
+            return check_launch(h);
+        });
     });
 }
 
@@ -182,12 +192,13 @@ int launch_stage3(nvmai_cuda_moe *h, Stage3Params p, uint32_t tokens, cudaStream
     dim3 grid(c.d / kTileRows, tokens);
     const uint32_t warps = p.top_k + (p.shared_f ? 1 : 0);
     const uint32_t threads = (warps < 1 ? 1 : warps) * 32;
+    const size_t row_halves = c.f > p.shared_f ? c.f : p.shared_f;
+    const size_t dyn = c.out_dtype == NVMAI_OUT_FP32 ? (size_t)warps * row_halves * 2 : 0;
     return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
-        if (c.out_dtype == NVMAI_OUT_FP16)
-            stage3_kernel<decltype(B)::value, decltype(M)::value, OUT_F16><<<grid, threads, 0, st>>>(p);
-        else
-            stage3_kernel<decltype(B)::value, decltype(M)::value, OUT_F32><<<grid, threads, 0, st>>>(p);
-        return check_launch(h);
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            stage3_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value><<<grid, threads, dyn, st>>>(p);
+            return check_launch(h);
+        });
     });
 }
 
@@ -282,8 +293,9 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
         return true;
     };
     bool ok = alloc(&h->logits, T * c.num_experts * sizeof(float)) && alloc(&h->idx, T * c.top_k * 4) &&
-              alloc(&h->w, T * c.top_k * 2) && alloc(&h->acts, T * c.top_k * c.f * 2) &&
-              alloc(&h->shared_act, T * (c.shared_f ? c.shared_f : 8) * 2) && alloc(&h->gate_val, T * 4) &&
+              alloc(&h->w, T * c.top_k * 2) && alloc(&h->acts, T * c.top_k * c.f * out_size(c.out_dtype)) &&
+              alloc(&h->shared_act, T * (c.shared_f ? c.shared_f : 8) * out_size(c.out_dtype)) &&
+              alloc(&h->gate_val, T * 4) &&
               alloc(&h->y, T * c.d * out_size(c.out_dtype)) && alloc(&h->xnorm, T * c.d * 2) &&
               alloc(&h->counter, 64) && alloc(&h->stage_x, T * c.d * 2) &&
               alloc(&h->stage_y, T * c.d * out_size(c.out_dtype));
@@ -390,8 +402,7 @@ int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_hos
         n_slots = active_count;
     }
     return launch_stage2(h, source_from_blobs(blobs_host, c.top_k), to_offsets(*offsets),
-                         static_cast<const __half *>(x_f16), c.d, 1, static_cast<__half *>(acts_f16), slots_dev,
-                         n_slots, st);
+                         static_cast<const __half *>(x_f16), c.d, 1, acts_f16, slots_dev, n_slots, st);
 }
 
 int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_host,
@@ -408,7 +419,7 @@ int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_hos
     Stage3Params p{};
     p.src = source_from_blobs(blobs_host, c.top_k);
     p.off = to_offsets(*offsets);
-    p.acts = static_cast<const __half *>(acts_f16);
+    p.acts = acts_f16;
     p.routing_w = static_cast<const __half *>(routing_w_f16);
     p.residual = residual;
     p.y = y;

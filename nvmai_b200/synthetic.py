@@ -54,3 +54,52 @@ def hidden_rows(seed: int, tokens: int, d: int = 2048) -> np.ndarray:
     """fp16 bit patterns [tokens, d] ~ N(0, 1)."""
     rng = np.random.default_rng(seed)
     return fmt.f32_to_f16_bits(rng.normal(0.0, 1.0, size=(tokens, d)))
+
+
+# ---------------------------------------------------------------------------
+# device-side generation (torch is plumbing here: allocation + RNG only)
+# ---------------------------------------------------------------------------
+
+def _device_affine(torch, gen, rows: int, n: int, bits: int, meta: int, device):
+    mdt = torch.bfloat16 if meta == fmt.META_BF16 else torch.float16
+    w = torch.randint(0, 256, (rows, n * bits // 8), dtype=torch.uint8, device=device, generator=gen)
+    s = (torch.rand(rows, n // fmt.GROUP, device=device, generator=gen) * 0.015 + 0.005).to(mdt)
+    b = (torch.rand(rows, n // fmt.GROUP, device=device, generator=gen) * 0.08 - 0.08).to(mdt)
+    return w, s, b
+
+
+def device_layer(seed: int, *, d: int = 2048, f: int = 512, shared_f: int = 512, num_experts: int = 256,
+                 routed_bits: int = 4, shared_bits: int | None = None, meta: int = fmt.META_BF16,
+                 expert_ids=None, device="cuda") -> dict:
+    """One layer generated in device memory with the benchmark distributions
+    (dense fp16 router and gate row).  `expert_ids` restricts generation to a
+    subset of blobs (expert-parallel ranks own 256/N of them); the returned
+    `experts` tensor then holds only those, in the given order."""
+    import torch
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    shared_bits = routed_bits if shared_bits is None else shared_bits
+    off, stride = fmt.expert_offsets(d, f, routed_bits)
+    n_local = num_experts if expert_ids is None else len(expert_ids)
+    mdt = torch.bfloat16 if meta == fmt.META_BF16 else torch.float16
+    experts = torch.randint(0, 256, (n_local, stride), dtype=torch.uint8, device=device, generator=gen)
+    gate_m = f * (d // fmt.GROUP) * 2
+    down_m = d * (f // fmt.GROUP) * 2
+    for name, nbytes, lo, width in (("gate_s", gate_m, 0.005, 0.015), ("gate_b", gate_m, -0.08, 0.08),
+                                    ("up_s", gate_m, 0.005, 0.015), ("up_b", gate_m, -0.08, 0.08),
+                                    ("down_s", down_m, 0.005, 0.015), ("down_b", down_m, -0.08, 0.08)):
+        vals = (torch.rand(n_local, nbytes // 2, device=device, generator=gen) * width + lo).to(mdt)
+        experts[:, off[name]:off[name] + nbytes] = vals.view(torch.uint8)
+    out = {"experts": experts, "stride": stride, "offsets": off}
+    out["router"] = ((torch.randn(num_experts, d, device=device, generator=gen) * 0.02).to(torch.float16), None, None)
+    if shared_f:
+        out["shared"] = [_device_affine(torch, gen, shared_f, d, shared_bits, meta, device),
+                         _device_affine(torch, gen, shared_f, d, shared_bits, meta, device),
+                         _device_affine(torch, gen, d, shared_f, shared_bits, meta, device)]
+        out["gate"] = ((torch.randn(1, d, device=device, generator=gen) * 0.02).to(torch.float16), None, None)
+    return out
+
+
+def register_device_layer(moe, layer: int, dev: dict) -> None:
+    moe.register_layer(layer, experts=dev["experts"], expert_stride=dev["stride"], offsets=dev["offsets"],
+                       router=dev["router"], shared=dev.get("shared"), shared_gate=dev.get("gate"))

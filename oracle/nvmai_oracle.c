@@ -80,6 +80,24 @@ uint16_t orc_f32_to_f16(float x) {
 
 static inline float orc_round_f16(float x) { return orc_f16_to_f32(orc_f32_to_f16(x)); }
 
+/* Wide-range stand-in for half(): round to nearest-even at 11 significant bits
+ * (fp16's precision) but keep fp32's exponent range.  Identical to
+ * float(half(x)) wherever x is a normal fp16 value; never overflows.  Used where
+ * the reference rounds an intermediate to half and the configuration runs with
+ * fp32 outputs (out_dtype 1). */
+float orc_round11(float x) {
+    union { uint32_t u; float f; } c;
+    c.f = x;
+    if ((c.u & 0x7F800000u) == 0x7F800000u) return x;   /* inf / nan unchanged */
+    c.u += 0xFFFu + ((c.u >> 13) & 1u);
+    c.u &= ~0x1FFFu;
+    return c.f;
+}
+
+static inline float orc_round_mid(float x, int out_dtype) {
+    return out_dtype == ORC_OUT_FP16 ? orc_round_f16(x) : orc_round11(x);
+}
+
 static inline uint16_t orc_f64_to_f16(double x) {
     /* double -> half in one rounding (avoids double rounding through float) */
     _Float16 h = (_Float16)x;
@@ -464,10 +482,11 @@ void orc_topk_softmax(const float *logits, size_t E, size_t K, const uint16_t *p
  * acts[slot*F+f] = half(act(gate_row.x) * (up_row.x)) with x fp16 and the two
  * row sums rounded to fp32.  blobs[slot] points at the slot's expert blob.
  * active_slots/active_count mirror the subset variants (:685-727, :835-861);
- * pass NULL/0 for all top_k slots. */
+ * pass NULL/0 for all top_k slots.  acts is fp16 (out_dtype 0, the reference)
+ * or fp32 holding values rounded to 11 significant bits (out_dtype 1). */
 void orc_gpu_phase1(const uint8_t *const *blobs, const uint32_t off[9], int bits, int meta,
                     int act, const uint16_t *x_f16, size_t D, size_t F, size_t top_k,
-                    const uint32_t *active_slots, size_t active_count, uint16_t *acts_f16) {
+                    const uint32_t *active_slots, size_t active_count, int out_dtype, void *acts) {
     float *x = (float *)malloc(D * sizeof(float));
     for (size_t i = 0; i < D; ++i) x[i] = orc_f16_to_f32(x_f16[i]);
     const size_t groups = D / ORC_GROUP, row_bytes = D * (size_t)bits / 8;
@@ -483,7 +502,8 @@ void orc_gpu_phase1(const uint8_t *const *blobs, const uint32_t off[9], int bits
             float u = (float)orc_row_dot64(bits, meta, base + off[3] + f * row_bytes,
                                            (const uint16_t *)(base + off[4]) + f * groups,
                                            (const uint16_t *)(base + off[5]) + f * groups, x, D);
-            acts_f16[slot * F + f] = orc_f32_to_f16(orc_act(g, act) * u);
+            if (out_dtype == ORC_OUT_FP16) ((uint16_t *)acts)[slot * F + f] = orc_f32_to_f16(orc_act(g, act) * u);
+            else ((float *)acts)[slot * F + f] = orc_round11(orc_act(g, act) * u);
         }
     }
     free(x);
@@ -494,13 +514,15 @@ void orc_gpu_phase1(const uint8_t *const *blobs, const uint32_t off[9], int bits
  * residual and the 8 partials IN SLOT ORDER in fp32 (:804-808) and rounds to
  * half.  residual/out are fp16 (out_dtype 0, the reference) or fp32 (1). */
 void orc_gpu_phase2(const uint8_t *const *blobs, const uint32_t off[9], int bits, int meta,
-                    const uint16_t *acts_f16, const uint16_t *w_f16, const void *residual,
+                    const void *acts, const uint16_t *w_f16, const void *residual,
                     size_t D, size_t F, size_t top_k, int out_dtype, void *y) {
     float *a = (float *)malloc(F * sizeof(float));
     float *partial = (float *)malloc(top_k * D * sizeof(float));
     const size_t groups = F / ORC_GROUP, row_bytes = F * (size_t)bits / 8;
     for (size_t k = 0; k < top_k; ++k) {
-        for (size_t i = 0; i < F; ++i) a[i] = orc_f16_to_f32(acts_f16[k * F + i]);
+        for (size_t i = 0; i < F; ++i)
+            a[i] = out_dtype == ORC_OUT_FP16 ? orc_f16_to_f32(((const uint16_t *)acts)[k * F + i])
+                                             : ((const float *)acts)[k * F + i];
         const uint8_t *base = blobs[k];
         const float wk = orc_f16_to_f32(w_f16[k]);
         for (size_t d = 0; d < D; ++d) {
@@ -538,6 +560,14 @@ void orc_gpu_affine_gemv_f16(int bits, int meta, const uint8_t *W, const uint16_
     free(x);
 }
 
+/* Same GEMV on an fp32 activation vector, result left in fp32. */
+static void orc_gpu_affine_gemv_x32(int bits, int meta, const uint8_t *W, const uint16_t *S,
+                                    const uint16_t *B, const float *x, size_t M, size_t N, float *y) {
+    const size_t groups = N / ORC_GROUP, row_bytes = N * (size_t)bits / 8;
+    for (size_t m = 0; m < M; ++m)
+        y[m] = (float)orc_row_dot64(bits, meta, W + m * row_bytes, S + m * groups, B + m * groups, x, N);
+}
+
 /* Shared expert + scalar gate, reference GPU rounding points:
  *   gate/up rounded to half BEFORE the activation, act rounded to half
  *     (4-bit: SharedExpertInt4.swift:61-96 -> dequant_int4_gemv_simd stores half,
@@ -545,31 +575,30 @@ void orc_gpu_affine_gemv_f16(int bits, int meta, const uint8_t *W, const uint16_
  *   h1 = half(down.act) (dequant_int*_gemv_simd),
  *   g  = half(W_g.x)    (RealForwardRunner.swift:3884-3896, m = 1),
  *   h1 = half(float(h1) / (1 + exp(-g)))  (utility.metal:60-70).
- * With out_dtype fp32 the two roundings of h1 are skipped (needed when the
- * synthetic 8-bit weights push h1 past the fp16 range); everything else is
- * unchanged.  gate_* may be NULL for an ungated shared expert.
+ * With out_dtype fp32 the two roundings of h1 are skipped and the roundings of
+ * gate, up, act and g keep 11 significant bits without fp16's exponent limit
+ * (orc_round11): the benchmark's 8-bit weights push act and h1 past 65504.  gate_* may be NULL for an ungated shared expert.
  * proj[p] = {W, scales, biases} for p = gate, up, down. */
 void orc_gpu_shared_expert(const uint8_t *const proj[9], int bits, int meta, int act,
                            const uint8_t *gate_W, const uint16_t *gate_S,
                            const uint16_t *gate_B, int gate_bits, const uint16_t *x_f16,
                            size_t D, size_t F, int out_dtype, void *h1) {
-    uint16_t *g16 = (uint16_t *)malloc(F * 2), *u16 = (uint16_t *)malloc(F * 2);
-    uint16_t *a16 = (uint16_t *)malloc(F * 2);
+    float *x = (float *)malloc(D * sizeof(float));
+    float *g = (float *)malloc(F * sizeof(float)), *u = (float *)malloc(F * sizeof(float));
+    float *a = (float *)malloc(F * sizeof(float));
     float *down = (float *)malloc(D * sizeof(float));
-    orc_gpu_affine_gemv_f16(bits, meta, proj[0], (const uint16_t *)proj[1],
-                            (const uint16_t *)proj[2], x_f16, F, D, g16, NULL);
-    orc_gpu_affine_gemv_f16(bits, meta, proj[3], (const uint16_t *)proj[4],
-                            (const uint16_t *)proj[5], x_f16, F, D, u16, NULL);
+    for (size_t i = 0; i < D; ++i) x[i] = orc_f16_to_f32(x_f16[i]);
+    orc_gpu_affine_gemv_x32(bits, meta, proj[0], (const uint16_t *)proj[1], (const uint16_t *)proj[2], x, F, D, g);
+    orc_gpu_affine_gemv_x32(bits, meta, proj[3], (const uint16_t *)proj[4], (const uint16_t *)proj[5], x, F, D, u);
     for (size_t i = 0; i < F; ++i)
-        a16[i] = orc_f32_to_f16(orc_act(orc_f16_to_f32(g16[i]), act) * orc_f16_to_f32(u16[i]));
-    orc_gpu_affine_gemv_f16(bits, meta, proj[6], (const uint16_t *)proj[7],
-                            (const uint16_t *)proj[8], a16, D, F, NULL, down);
+        a[i] = orc_round_mid(orc_act(orc_round_mid(g[i], out_dtype), act) * orc_round_mid(u[i], out_dtype), out_dtype);
+    orc_gpu_affine_gemv_x32(bits, meta, proj[6], (const uint16_t *)proj[7], (const uint16_t *)proj[8], a, D, F, down);
     float gate = 0.0f;
     int gated = gate_W != NULL;
     if (gated) {
-        uint16_t g;
-        orc_gpu_affine_gemv_f16(gate_bits, meta, gate_W, gate_S, gate_B, x_f16, 1, D, &g, NULL);
-        gate = orc_f16_to_f32(g);
+        float gv;
+        orc_gpu_affine_gemv_x32(gate_bits, meta, gate_W, gate_S, gate_B, x, 1, D, &gv);
+        gate = orc_round_mid(gv, out_dtype);
     }
     for (size_t d = 0; d < D; ++d) {
         if (out_dtype == ORC_OUT_FP16) {
@@ -582,7 +611,7 @@ void orc_gpu_shared_expert(const uint8_t *const proj[9], int bits, int meta, int
             ((float *)h1)[d] = v;
         }
     }
-    free(g16); free(u16); free(a16); free(down);
+    free(x); free(g); free(u); free(a); free(down);
 }
 
 /* utility.metal:94-103 : hidden = half(float(hidden) + float(delta)). */
@@ -747,7 +776,7 @@ void orc_gpu_layer_decode(const orc_layer *L, const uint16_t *x_f16, void *hidde
             /* dense fp16 gate row: same rounding points, g = half(w.x) */
             orc_gpu_shared_expert(L->shared, L->shared_bits, L->meta, L->act, NULL, NULL, NULL, 0,
                                   x_f16, D, L->Fs, L->out_dtype, h1);
-            float g = orc_round_f16(orc_dense_row_dot_f16((const uint16_t *)L->sgate_W, x_f16, D));
+            float g = orc_round_mid(orc_dense_row_dot_f16((const uint16_t *)L->sgate_W, x_f16, D), L->out_dtype);
             for (size_t d = 0; d < D; ++d) {
                 if (L->out_dtype == ORC_OUT_FP16) {
                     float v = orc_f16_to_f32(((uint16_t *)h1)[d]);
@@ -773,8 +802,8 @@ void orc_gpu_layer_decode(const orc_layer *L, const uint16_t *x_f16, void *hidde
         uint32_t e = idx[k] < E ? idx[k] : (uint32_t)E - 1;   /* RealForwardRunner.swift:3933-3939 clamp */
         blobs[k] = L->experts + (uint64_t)e * L->stride;
     }
-    uint16_t *acts = (uint16_t *)malloc(K * F * 2);
-    orc_gpu_phase1(blobs, L->off, L->routed_bits, L->meta, L->act, x_f16, D, F, K, NULL, 0, acts);
+    void *acts = malloc(K * F * 4);
+    orc_gpu_phase1(blobs, L->off, L->routed_bits, L->meta, L->act, x_f16, D, F, K, NULL, 0, L->out_dtype, acts);
     void *h2 = malloc(D * esz);
     orc_gpu_phase2(blobs, L->off, L->routed_bits, L->meta, acts, w16, h1, D, F, K, L->out_dtype, h2);
     if (hidden_inout) orc_gpu_residual_add(hidden_inout, h2, D, L->out_dtype);

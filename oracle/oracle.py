@@ -106,6 +106,7 @@ def _declare(L: C.CDLL) -> None:
     L.orc_f32_to_bf16_trunc.argtypes = [C.c_float]; L.orc_f32_to_bf16_trunc.restype = C.c_uint16
     L.orc_f16_to_f32.argtypes = [C.c_uint16]; L.orc_f16_to_f32.restype = C.c_float
     L.orc_f32_to_f16.argtypes = [C.c_float]; L.orc_f32_to_f16.restype = C.c_uint16
+    L.orc_round11.argtypes = [C.c_float]; L.orc_round11.restype = C.c_float
     L.orc_splitmix_next.argtypes = [C.POINTER(C.c_uint64)]; L.orc_splitmix_next.restype = C.c_uint64
     L.orc_splitmix_uniform.argtypes = [C.POINTER(C.c_uint64), C.c_float, C.c_float]
     L.orc_splitmix_uniform.restype = C.c_float
@@ -128,7 +129,7 @@ def _declare(L: C.CDLL) -> None:
     L.orc_router_logits_dense_f16.argtypes = [vp, vp, vp, sz, sz, vp, vp]
     L.orc_router_logits_dense_f16.restype = None
     L.orc_topk_softmax.argtypes = [vp, sz, sz, vp, vp, vp, vp, vp]; L.orc_topk_softmax.restype = None
-    L.orc_gpu_phase1.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, vp, sz, sz, sz, vp, sz, vp]
+    L.orc_gpu_phase1.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, vp, sz, sz, sz, vp, sz, C.c_int, vp]
     L.orc_gpu_phase1.restype = None
     L.orc_gpu_phase2.argtypes = [vp, vp, C.c_int, C.c_int, vp, vp, vp, sz, sz, sz, C.c_int, vp]
     L.orc_gpu_phase2.restype = None

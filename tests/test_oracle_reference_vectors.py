@@ -75,12 +75,12 @@ def run_phases(case, act, active_splits=None, out_dtype=orc.OUT_FP16):
     acts = np.zeros(K * F, dtype=np.uint16)
     if active_splits is None:
         L.orc_gpu_phase1(ptrs, orc.ptr(case["off"]), case["bits"], orc.META_BF16, act, orc.ptr(case["x_f16"]),
-                         D, F, K, None, 0, orc.ptr(acts))
+                         D, F, K, None, 0, orc.OUT_FP16, orc.ptr(acts))
     else:
         for slots in active_splits:
             s = np.array(slots, dtype=np.uint32)
             L.orc_gpu_phase1(ptrs, orc.ptr(case["off"]), case["bits"], orc.META_BF16, act,
-                             orc.ptr(case["x_f16"]), D, F, K, orc.ptr(s), s.size, orc.ptr(acts))
+                             orc.ptr(case["x_f16"]), D, F, K, orc.ptr(s), s.size, orc.OUT_FP16, orc.ptr(acts))
     y = np.zeros(D, dtype=np.uint16)
     L.orc_gpu_phase2(ptrs, orc.ptr(case["off"]), case["bits"], orc.META_BF16, orc.ptr(acts),
                      orc.ptr(case["w_f16"]), orc.ptr(case["residual_f16"]), D, F, K, out_dtype, orc.ptr(y))
