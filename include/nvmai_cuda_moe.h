@@ -157,6 +157,15 @@ NVMAI_API int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, con
                                 void *hidden_inout, void *h2_out, uint32_t *out_idx, void *out_w_f16,
                                 void *stream);
 
+/* `PrefillRouter.makeTokenExpertPairs` + `PrefillMoEGrouping.groupTokenExpertPairs`
+ * (PrefillRouter.swift:97-117, PrefillMoEGrouping.swift:90-192) on the device: the
+ * tokens*top_k (token, expert, rank, weight) records sorted by (expert, token,
+ * rank), 16 bytes each with fields at 0/4/8/12 like `PrefillTokenExpertPair`;
+ * expert_offsets[e] = first sorted position (0xFFFFFFFF when e has no pair),
+ * expert_counts[e] = its number of pairs.  idx / w as written by the router. */
+NVMAI_API int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const void *w_f16, uint32_t tokens,
+                               void *sorted_pairs, uint32_t *expert_offsets, uint32_t *expert_counts, void *stream);
+
 /* Benchmark driver for an FFN-only stack: runs layers 0..num_layers-1 on one
  * token batch; between layers the block output is renormalised to unit RMS in
  * fp32 and rounded to fp16 (a stand-in for the attention + rmsnorm the real model

@@ -40,42 +40,26 @@ __device__ __forceinline__ uint16_t ldg_u16(const void *p) {
 }
 
 // ---- exact code -> half2 unpacking ---------------------------------------
+// A code placed in the low mantissa bits of a half whose exponent field is zero
+// is the subnormal  code * 2^-24 : an exact value that costs one AND to form, no
+// magic-number OR and no subtract.  The tensor core multiplies subnormal fp16
+// inputs exactly, so sum(q*x) comes out scaled by kCodeScale = 2^-24, which is
+// folded into the group's scale (a power of two: exact).
+constexpr float kCodeUnscale = 16777216.0f;   // 2^24
+
 // 4-bit: a u32 holds codes n0..n7, n_j at bit 4j (low nibble = even index,
-// Quantization.swift:36).  The four results are the pairs (n0,n4) (n1,n5)
-// (n2,n6) (n3,n7) as exact integers in half precision:
-//   (w & 0x000F000F) | 0x6400 = 1024 + n        -> minus 1024
-//   (w & 0x00F000F0) | 0x6400 = 1024 + 16 n     -> times 1/16, minus 64
-// Both steps are exact in fp16.
+// Quantization.swift:36).  Results: the pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7).
 __device__ __forceinline__ void unpack_u4x8(uint32_t w, uint32_t (&p)[4]) {
-    const uint32_t kMagic = 0x64006400u;
-    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-    const __half2 kInv16 = __half2half2(__ushort_as_half(0x2C00));   // 1/16
-    const __half2 kNeg64 = __half2half2(__ushort_as_half(0xD400));   // -64
-    uint32_t lo0 = (w & 0x000F000Fu) | kMagic;
-    uint32_t hi0 = (w & 0x00F000F0u) | kMagic;
-    uint32_t w8 = w >> 8;
-    uint32_t lo1 = (w8 & 0x000F000Fu) | kMagic;
-    uint32_t hi1 = (w8 & 0x00F000F0u) | kMagic;
-    __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&lo0), k1024);
-    __half2 r1 = __hfma2(*reinterpret_cast<__half2 *>(&hi0), kInv16, kNeg64);
-    __half2 r2 = __hsub2(*reinterpret_cast<__half2 *>(&lo1), k1024);
-    __half2 r3 = __hfma2(*reinterpret_cast<__half2 *>(&hi1), kInv16, kNeg64);
-    p[0] = *reinterpret_cast<uint32_t *>(&r0);
-    p[1] = *reinterpret_cast<uint32_t *>(&r1);
-    p[2] = *reinterpret_cast<uint32_t *>(&r2);
-    p[3] = *reinterpret_cast<uint32_t *>(&r3);
+    p[0] = w & 0x000F000Fu;
+    p[1] = (w >> 4) & 0x000F000Fu;
+    p[2] = (w >> 8) & 0x000F000Fu;
+    p[3] = (w >> 12) & 0x000F000Fu;
 }
 
-// 8-bit: a u32 holds codes b0..b3.  Results: (b0,b1) (b2,b3) as exact halves:
-// bytes {b, 0x64} form the half 1024 + b; subtract 1024.
+// 8-bit: a u32 holds codes b0..b3.  Results: the pairs (b0,b2) (b1,b3).
 __device__ __forceinline__ void unpack_u8x4(uint32_t w, uint32_t (&p)[2]) {
-    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-    uint32_t a = __byte_perm(w, 0x64646464u, 0x4140);
-    uint32_t b = __byte_perm(w, 0x64646464u, 0x4342);
-    __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&a), k1024);
-    __half2 r1 = __hsub2(*reinterpret_cast<__half2 *>(&b), k1024);
-    p[0] = *reinterpret_cast<uint32_t *>(&r0);
-    p[1] = *reinterpret_cast<uint32_t *>(&r1);
+    p[0] = w & 0x00FF00FFu;
+    p[1] = (w >> 8) & 0x00FF00FFu;
 }
 
 // ---- tensor-core step ------------------------------------------------------

@@ -6,6 +6,7 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -14,7 +15,7 @@
 #include <tuple>
 #include <vector>
 
-#include "decode_kernels.cuh"
+#include "grouped_decode.cuh"
 #include "misc_kernels.cuh"
 
 using namespace nvmai;
@@ -47,6 +48,14 @@ struct nvmai_cuda_moe {
     void *y = nullptr;              // [T][D] out_dtype
     __half *xnorm = nullptr;        // [T][D]
     unsigned int *counter = nullptr;
+    unsigned int *status = nullptr;  // set by a kernel whose bounded wait expired
+    // batched decode: pair grouping and per-pair partial results
+    uint32_t *sorted_pair = nullptr, *inv = nullptr, *expert_offsets = nullptr, *expert_counts = nullptr;
+    WorkItem *work = nullptr;
+    uint32_t *n_work = nullptr;
+    float *partial = nullptr;        // [T*K][D]
+    float *shared_partial = nullptr; // [T][D]
+    uint32_t max_work = 0;
     const void **blob_table = nullptr;   // unused on device; kept for symmetry
     void *stage_x = nullptr;        // host-call staging: [T][D] fp16
     void *stage_y = nullptr;        // host-call staging: [T][D] out_dtype
@@ -131,8 +140,52 @@ int dispatch_bits_meta(uint32_t bits, uint32_t meta, F &&f) {
 
 // ---- stage launchers ---------------------------------------------------------
 
-int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x, uint32_t x_stride, uint32_t tokens,
-                  uint32_t *out_idx, __half *out_w, bool with_router, bool with_shared, cudaStream_t st) {
+// Kernels here use more than the default 48 KB of dynamic shared memory; the
+// opt-in is per function and sticky, so it is raised once per (function, size).
+template <typename Kern>
+cudaError_t ensure_smem(Kern kern, size_t bytes) {
+    static std::map<const void *, size_t> granted;
+    const void *key = reinterpret_cast<const void *>(kern);
+    auto it = granted.find(key);
+    if (it != granted.end() && it->second >= bytes) return cudaSuccess;
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return e;
+    }
+    granted[key] = bytes;
+    return cudaSuccess;
+}
+
+// pdl: launch with programmatic stream serialization, so that the kernel's
+// prologue (its weight copies) may overlap the previous kernel's tail.
+template <typename Kern, typename Params>
+int launch_kernel(nvmai_cuda_moe *h, Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                  const Params &p) {
+    cudaError_t e = ensure_smem(kern, smem);
+    if (e != cudaSuccess) return record(h, e);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, kern, p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return record(h, e);
+}
+
+constexpr size_t kMaxSmem = 227 * 1024;
+
+// with_shared: the shared expert's gate/up tiles run here (one block per token and
+// tile); with_gate: the scalar gate row.  The batched path runs the tiles in its
+// grouped stage instead and asks for the gate only.
+int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const XSource &xsrc, uint32_t tokens,
+                  uint32_t *out_idx, __half *out_w, bool with_router, bool with_shared, bool with_gate, bool pdl,
+                  cudaStream_t st) {
     const auto &c = h->cfg;
     Stage1Params p{};
     p.rW = static_cast<const uint8_t *>(lv.w.router.w);
@@ -154,50 +207,61 @@ int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x, uint
     p.gB = static_cast<const uint16_t *>(lv.w.shared_gate.biases);
     p.gate_kind = c.shared_gate_kind;
     p.gate_val = h->gate_val;
-    p.x = x; p.x_stride = x_stride; p.tokens = tokens;
+    p.xsrc = xsrc; p.tokens = tokens;
     p.D = c.d; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation;
-    p.n_router_blocks = with_router ? (c.num_experts + 7) / 8 : 0;
-    p.n_shared_blocks = with_shared ? (c.shared_f / kTileRows) * tokens : 0;
-    const uint32_t gate_blocks = (with_shared && c.shared_gate_kind != NVMAI_GATE_NONE) ? 1 : 0;
-    const uint32_t grid = p.n_router_blocks + p.n_shared_blocks + gate_blocks;
+    p.status = h->status;
+    p.tokens_per_chunk = tokens <= 8 ? tokens : 8;
+    const uint32_t chunks = (tokens + p.tokens_per_chunk - 1) / p.tokens_per_chunk;
+    p.router_row_blocks = (c.num_experts + kRowsPerRouterBlock - 1) / kRowsPerRouterBlock;
+    p.n_router_blocks = with_router ? p.router_row_blocks * chunks : 0;
+    p.n_shared_blocks = with_shared ? ((c.shared_f + kBlockFeatures - 1) / kBlockFeatures) * tokens : 0;
+    const bool gated = with_gate && c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
+    p.n_gate_blocks = gated ? chunks : 0;
+    const uint32_t grid = p.n_router_blocks + p.n_shared_blocks + p.n_gate_blocks;
     if (grid == 0) return NVMAI_CUDA_OK;
+    size_t smem = 0;
+    if (with_router) smem = std::max(smem, RowsLayout(c.d, c.router_kind).total);
+    if (gated) smem = std::max(smem, RowsLayout(c.d, c.shared_gate_kind).total);
+    if (with_shared) smem = std::max(smem, GateUpLayout(c.d, c.shared_bits).total);
     return dispatch_bits_meta(c.shared_f ? c.shared_bits : 4, c.meta_dtype, [&](auto B, auto M) {
         return dispatch_out(c.out_dtype, [&](auto O) {
-            stage1_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value><<<grid, kDecodeThreads, 0, st>>>(p);
-            return check_launch(h);
+            return launch_kernel(h, stage1_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>,
+                                 dim3(grid), dim3(kDecodeThreads), smem, st, pdl, p);
         });
     });
 }
 
 int launch_stage2(nvmai_cuda_moe *h, const RoutedSource &src, const ExpertOffsets &off, const __half *x,
                   uint32_t x_stride, uint32_t tokens, void *acts, const uint32_t *active_slots_dev,
-                  uint32_t n_slots, cudaStream_t st) {
+                  uint32_t n_slots, bool pdl, cudaStream_t st) {
     const auto &c = h->cfg;
     Stage2Params p{};
     p.src = src; p.off = off; p.x = x; p.x_stride = x_stride; p.acts = acts;
     p.active_slots = active_slots_dev;
     p.D = c.d; p.F = c.f; p.top_k = c.top_k; p.act = c.activation;
-    dim3 grid(c.f / kTileRows, n_slots, tokens);
+    p.status = h->status;
+    dim3 grid((c.f + kBlockFeatures - 1) / kBlockFeatures, n_slots, tokens);
+    const size_t smem = GateUpLayout(c.d, c.routed_bits).total;
     return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
         return dispatch_out(c.out_dtype, [&](auto O) {
-            stage2_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value><<<grid, kDecodeThreads, 0, st>>>(p);
-            return check_launch(h);
+            return launch_kernel(h, stage2_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>, grid,
+                                 dim3(kDecodeThreads), smem, st, pdl, p);
         });
     });
 }
 
-int launch_stage3(nvmai_cuda_moe *h, Stage3Params p, uint32_t tokens, cudaStream_t st) {
+int launch_stage3(nvmai_cuda_moe *h, Stage3Params p, uint32_t tokens, bool pdl, cudaStream_t st) {
     const auto &c = h->cfg;
     p.D = c.d; p.F = c.f;
+    p.status = h->status;
     dim3 grid(c.d / kTileRows, tokens);
-    const uint32_t warps = p.top_k + (p.shared_f ? 1 : 0);
-    const uint32_t threads = (warps < 1 ? 1 : warps) * 32;
-    const size_t row_halves = c.f > p.shared_f ? c.f : p.shared_f;
-    const size_t dyn = c.out_dtype == NVMAI_OUT_FP32 ? (size_t)warps * row_halves * 2 : 0;
+    const uint32_t units = p.top_k + (p.shared_f ? 1 : 0);
+    const uint32_t threads = (units < 1 ? 1 : units) * kDownSplit * 32;
+    const size_t smem = DownLayout(c.f, p.shared_f, c.routed_bits, p.shared_bits, units).total;
     return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
         return dispatch_out(c.out_dtype, [&](auto O) {
-            stage3_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value><<<grid, threads, dyn, st>>>(p);
-            return check_launch(h);
+            return launch_kernel(h, stage3_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>, grid,
+                                 dim3(threads), smem, st, pdl, p);
         });
     });
 }
@@ -209,16 +273,92 @@ int check_layer(const nvmai_cuda_moe *h, uint32_t layer) {
     return NVMAI_CUDA_OK;
 }
 
-int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint32_t tokens, void *hidden,
-                      void *h2_out, uint32_t *out_idx, __half *out_w, cudaStream_t st) {
+constexpr uint32_t kGroupedMinTokens = 4;   // below this every token runs its own blocks
+
+int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, uint32_t tokens,
+                       TokenExpertPair *pairs_out, uint32_t *offsets_out, uint32_t *counts_out, bool with_work,
+                       bool pdl, cudaStream_t st) {
+    const auto &c = h->cfg;
+    GroupParams g{};
+    g.idx = idx; g.weights = w; g.tokens = tokens; g.K = c.top_k; g.E = c.num_experts;
+    g.sorted_pair = h->sorted_pair; g.inv = h->inv;
+    g.expert_offsets = offsets_out ? offsets_out : h->expert_offsets;
+    g.expert_counts = counts_out ? counts_out : h->expert_counts;
+    g.pairs_out = pairs_out;
+    g.work = with_work ? h->work : nullptr;
+    g.n_work = h->n_work;
+    g.shared_chunks = (with_work && c.shared_f) ? (tokens + kPairsPerItem - 1) / kPairsPerItem : 0;
+    return launch_kernel(h, group_pairs_kernel, dim3(1), dim3(kGroupThreads), 0, st, pdl, g);
+}
+
+// Batched tail of a layer: group pairs by expert, gate/up and down per (tile, work
+// item), then the per-token weighted sum in rank order.
+int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, uint32_t tokens, const uint32_t *idx,
+                 const __half *w, void *hidden, void *y, cudaStream_t st) {
+    const auto &c = h->cfg;
+    int rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st);
+    if (rc) return rc;
+    const uint32_t P = tokens * c.top_k;
+    const uint32_t routed_bound = std::min(P, c.num_experts + P / kPairsPerItem);
+    const uint32_t shared_chunks = c.shared_f ? (tokens + kPairsPerItem - 1) / kPairsPerItem : 0;
+    GroupedStage2Params p2{};
+    p2.experts = static_cast<const uint8_t *>(lv.w.experts); p2.stride = lv.w.expert_stride; p2.num_experts = c.num_experts;
+    p2.off = to_offsets(lv.w.offsets);
+    p2.work = h->work; p2.n_work = h->n_work; p2.sorted_pair = h->sorted_pair;
+    p2.x = x_rows; p2.x_stride = c.d; p2.acts = h->acts;
+    p2.sgate = to_mat(lv.w.shared_gate_proj); p2.sup = to_mat(lv.w.shared_up_proj);
+    p2.shared_f = c.shared_f; p2.shared_bits = c.shared_bits; p2.shared_act = h->shared_act;
+    p2.D = c.d; p2.F = c.f; p2.K = c.top_k; p2.act = c.activation; p2.status = h->status;
+    const uint32_t fmax = std::max(c.f, c.shared_f);
+    size_t smem2 = GroupedGateUpLayout(c.d, c.routed_bits).total;
+    if (c.shared_f) smem2 = std::max(smem2, GroupedGateUpLayout(c.d, c.shared_bits).total);
+    rc = dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            return launch_kernel(h, grouped_stage2_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>,
+                                 dim3(fmax / kTileFeatures, routed_bound + shared_chunks), dim3(kDecodeThreads), smem2,
+                                 st, true, p2);
+        });
+    });
+    if (rc) return rc;
+    GroupedStage3Params p3{};
+    p3.experts = p2.experts; p3.stride = p2.stride; p3.num_experts = c.num_experts; p3.off = p2.off;
+    p3.work = h->work; p3.n_work = h->n_work; p3.acts = h->acts; p3.partial = h->partial;
+    p3.sdown = to_mat(lv.w.shared_down_proj); p3.shared_f = c.shared_f; p3.shared_bits = c.shared_bits;
+    p3.shared_act = h->shared_act; p3.shared_partial = h->shared_partial;
+    p3.D = c.d; p3.F = c.f; p3.status = h->status;
+    const size_t smem3 = GroupedDownLayout(c.f, c.shared_f, c.routed_bits, c.shared_bits).total;
+    rc = dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            return launch_kernel(h, grouped_stage3_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>,
+                                 dim3(c.d / kTileRows, routed_bound + shared_chunks), dim3(kDecodeThreads), smem3, st,
+                                 true, p3);
+        });
+    });
+    if (rc) return rc;
+    CombineParams pc{};
+    pc.partial = h->partial; pc.shared_partial = c.shared_f ? h->shared_partial : nullptr;
+    pc.inv = h->inv; pc.routing_w = w;
+    pc.gate_val = (c.shared_f && c.shared_gate_kind != NVMAI_GATE_NONE) ? h->gate_val : nullptr;
+    pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
+    return dispatch_out(c.out_dtype, [&](auto O) {
+        return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
+    });
+}
+
+// xsrc: where stage 1 gets its rows; x_rows: the fp16 rows stages 2 reads (the
+// same buffer, or the buffer stage 1 writes its normalised rows to).
+int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, const __half *x_rows, uint32_t tokens,
+                      void *hidden, void *h2_out, uint32_t *out_idx, __half *out_w, cudaStream_t st) {
     const auto &c = h->cfg;
     const LayerViews &lv = h->layers[layer];
     uint32_t *idx = out_idx ? out_idx : h->idx;
     __half *w = out_w ? out_w : h->w;
-    int rc = launch_stage1(h, lv, x, c.d, tokens, idx, w, true, c.shared_f != 0, st);
+    const bool grouped = tokens >= kGroupedMinTokens;
+    int rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, c.shared_f != 0 && !grouped, c.shared_f != 0, true, st);
     if (rc) return rc;
-    rc = launch_stage2(h, source_from_layer(h, lv, idx), to_offsets(lv.w.offsets), x, c.d, tokens, h->acts,
-                       nullptr, c.top_k, st);
+    if (grouped) return grouped_tail(h, lv, x_rows, tokens, idx, w, hidden, h2_out ? h2_out : h->y, st);
+    rc = launch_stage2(h, source_from_layer(h, lv, idx), to_offsets(lv.w.offsets), x_rows, c.d, tokens, h->acts,
+                       nullptr, c.top_k, true, st);
     if (rc) return rc;
     Stage3Params p{};
     p.src = source_from_layer(h, lv, idx);
@@ -235,7 +375,7 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint32
     p.y = h2_out ? h2_out : h->y;
     p.hidden = hidden;
     p.top_k = c.top_k;
-    return launch_stage3(h, p, tokens, st);
+    return launch_stage3(h, p, tokens, true, st);
 }
 
 }  // namespace
@@ -281,6 +421,20 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
     if (c.meta_dtype > NVMAI_META_FP16 || c.activation > NVMAI_ACT_GELU_TANH || c.out_dtype > NVMAI_OUT_FP32)
         return fail(NVMAI_CUDA_EINVAL);
     if (c.max_tokens == 0 || c.num_layers == 0) return fail(NVMAI_CUDA_EINVAL);
+    // every block stages its weight tile in shared memory: the tile must fit
+    {
+        size_t need = GateUpLayout(c.d, c.routed_bits).total;
+        need = std::max(need, RowsLayout(c.d, c.router_kind).total);
+        if (c.shared_f) need = std::max(need, GateUpLayout(c.d, c.shared_bits).total);
+        const uint32_t warps = (c.top_k < (uint32_t)kMaxTopK ? c.top_k : (uint32_t)kMaxTopK) + (c.shared_f ? 1 : 0);
+        need = std::max(need, DownLayout(c.f, c.shared_f, c.routed_bits, c.shared_bits, warps).total);
+        if (c.max_tokens >= kGroupedMinTokens) {
+            need = std::max(need, GroupedGateUpLayout(c.d, c.routed_bits).total);
+            if (c.shared_f) need = std::max(need, GroupedGateUpLayout(c.d, c.shared_bits).total);
+            need = std::max(need, GroupedDownLayout(c.f, c.shared_f, c.routed_bits, c.shared_bits).total);
+        }
+        if (need > kMaxSmem) return fail(NVMAI_CUDA_ERANGE);
+    }
 
     nvmai_cuda_moe *h = new (std::nothrow) nvmai_cuda_moe();
     if (!h) return fail(NVMAI_CUDA_ENOMEM);
@@ -297,9 +451,19 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
               alloc(&h->shared_act, T * (c.shared_f ? c.shared_f : 8) * out_size(c.out_dtype)) &&
               alloc(&h->gate_val, T * 4) &&
               alloc(&h->y, T * c.d * out_size(c.out_dtype)) && alloc(&h->xnorm, T * c.d * 2) &&
-              alloc(&h->counter, 64) && alloc(&h->stage_x, T * c.d * 2) &&
+              alloc(&h->counter, (T / 8 + 2) * 4) && alloc(&h->status, 64) && alloc(&h->stage_x, T * c.d * 2) &&
               alloc(&h->stage_y, T * c.d * out_size(c.out_dtype));
-    if (ok) ok = cudaMemset(h->counter, 0, 64) == cudaSuccess;
+    if (ok) ok = cudaMemset(h->counter, 0, (T / 8 + 2) * 4) == cudaSuccess && cudaMemset(h->status, 0, 64) == cudaSuccess;
+    {
+        const size_t P = T * c.top_k;
+        h->max_work = (uint32_t)(std::min(P, c.num_experts + P / kPairsPerItem) + (T + kPairsPerItem - 1) / kPairsPerItem);
+        if (ok) ok = alloc(&h->sorted_pair, P * 4) && alloc(&h->inv, P * 4) && alloc(&h->expert_offsets, kMaxExperts * 4) &&
+                     alloc(&h->expert_counts, kMaxExperts * 4) && alloc(&h->work, (size_t)h->max_work * sizeof(WorkItem)) &&
+                     alloc(&h->n_work, 16);
+        // per-pair partial rows are only needed by the batched path
+        if (ok && T >= kGroupedMinTokens)
+            ok = alloc(&h->partial, P * c.d * sizeof(float)) && alloc(&h->shared_partial, T * c.d * sizeof(float));
+    }
     if (!ok) {
         const bool oom = h->last_cuda_error == (int)cudaErrorMemoryAllocation;
         nvmai_cuda_moe_destroy(h);
@@ -314,8 +478,10 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     if (!h) return;
     for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
-    cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter);
+    cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y);
+    cudaFree(h->sorted_pair); cudaFree(h->inv); cudaFree(h->expert_offsets); cudaFree(h->expert_counts);
+    cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->partial); cudaFree(h->shared_partial);
     delete h;
 }
 
@@ -352,8 +518,9 @@ int nvmai_cuda_moe_router(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, 
     if (!x_f16 || !out_idx || !out_w_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
     if (x_stride < h->cfg.d || (x_stride % 8) != 0) return NVMAI_CUDA_EINVAL;   // PrefillRouter.swift:68
-    return launch_stage1(h, h->layers[layer], static_cast<const __half *>(x_f16), x_stride, tokens, out_idx,
-                         static_cast<__half *>(out_w_f16), true, false, static_cast<cudaStream_t>(stream));
+    const XSource xsrc{static_cast<const __half *>(x_f16), x_stride, nullptr, nullptr};
+    return launch_stage1(h, h->layers[layer], xsrc, tokens, out_idx, static_cast<__half *>(out_w_f16), true, false,
+                         false, false, static_cast<cudaStream_t>(stream));
 }
 
 int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride,
@@ -366,7 +533,8 @@ int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *
     if (x_stride < c.d || (x_stride % 8) != 0) return NVMAI_CUDA_EINVAL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const LayerViews &lv = h->layers[layer];
-    rc = launch_stage1(h, lv, static_cast<const __half *>(x_f16), x_stride, tokens, nullptr, nullptr, false, true, st);
+    const XSource xsrc{static_cast<const __half *>(x_f16), x_stride, nullptr, nullptr};
+    rc = launch_stage1(h, lv, xsrc, tokens, nullptr, nullptr, false, true, true, false, st);
     if (rc) return rc;
     Stage3Params p{};
     p.sdown = to_mat(lv.w.shared_down_proj);
@@ -376,7 +544,7 @@ int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *
     p.gate_val = c.shared_gate_kind != NVMAI_GATE_NONE ? h->gate_val : nullptr;
     p.y = h1;
     p.top_k = 0;
-    return launch_stage3(h, p, tokens, st);
+    return launch_stage3(h, p, tokens, false, st);
 }
 
 int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_host,
@@ -402,7 +570,7 @@ int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_hos
         n_slots = active_count;
     }
     return launch_stage2(h, source_from_blobs(blobs_host, c.top_k), to_offsets(*offsets),
-                         static_cast<const __half *>(x_f16), c.d, 1, acts_f16, slots_dev, n_slots, st);
+                         static_cast<const __half *>(x_f16), c.d, 1, acts_f16, slots_dev, n_slots, false, st);
 }
 
 int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_host,
@@ -424,7 +592,7 @@ int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_hos
     p.residual = residual;
     p.y = y;
     p.top_k = c.top_k;
-    return launch_stage3(h, p, 1, static_cast<cudaStream_t>(stream));
+    return launch_stage3(h, p, 1, false, static_cast<cudaStream_t>(stream));
 }
 
 int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
@@ -434,27 +602,34 @@ int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x
     if (!x_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
     if (h->cfg.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
-    return layer_decode_impl(h, layer, static_cast<const __half *>(x_f16), tokens, hidden_inout, h2_out, out_idx,
-                             static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
+    const XSource xsrc{static_cast<const __half *>(x_f16), h->cfg.d, nullptr, nullptr};
+    return layer_decode_impl(h, layer, xsrc, static_cast<const __half *>(x_f16), tokens, hidden_inout, h2_out,
+                             out_idx, static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
+}
+
+// Layer l > 0 reads the previous layer's block output and renormalises it inside
+// its own stage 1 (every block derives the same rows; block 0 stores them for
+// stage 2), so a layer is exactly three launches.
+int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const void *w_f16, uint32_t tokens,
+                               void *sorted_pairs, uint32_t *expert_offsets, uint32_t *expert_counts, void *stream) {
+    if (!h || !idx || !sorted_pairs || !expert_offsets || !expert_counts) return NVMAI_CUDA_EINVAL;
+    if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
+    return launch_group_pairs(h, idx, static_cast<const __half *>(w_f16), tokens,
+                              static_cast<TokenExpertPair *>(sorted_pairs), expert_offsets, expert_counts, false, false,
+                              static_cast<cudaStream_t>(stream));
 }
 
 static int stack_enqueue(nvmai_cuda_moe *h, const __half *x0, uint32_t tokens, void *y_last, cudaStream_t st) {
     const auto &c = h->cfg;
-    const __half *x = x0;
     for (uint32_t l = 0; l < c.num_layers; ++l) {
         const bool last = l + 1 == c.num_layers;
         void *y = last ? y_last : h->y;
-        int rc = layer_decode_impl(h, l, x, tokens, nullptr, y, nullptr, nullptr, st);
+        XSource xsrc{};
+        const __half *x_rows;
+        if (l == 0) { xsrc.x = x0; xsrc.x_stride = c.d; x_rows = x0; }
+        else { xsrc.y_prev = h->y; xsrc.x_out = h->xnorm; x_rows = h->xnorm; }
+        int rc = layer_decode_impl(h, l, xsrc, x_rows, tokens, nullptr, y, nullptr, nullptr, st);
         if (rc) return rc;
-        if (!last) {
-            if (c.out_dtype == NVMAI_OUT_FP16)
-                rms_renorm_kernel<OUT_F16><<<tokens, 256, 0, st>>>(y, h->xnorm, c.d);
-            else
-                rms_renorm_kernel<OUT_F32><<<tokens, 256, 0, st>>>(y, h->xnorm, c.d);
-            rc = check_launch(h);
-            if (rc) return rc;
-            x = h->xnorm;
-        }
     }
     return NVMAI_CUDA_OK;
 }
@@ -467,7 +642,7 @@ int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t 
     for (uint32_t l = 0; l < c.num_layers; ++l)
         if (!h->layers[l].registered) return NVMAI_CUDA_EINVAL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // Launch-bound chain (4 small kernels per layer): replay it as a CUDA graph.
+    // Launch-bound chain (3 small kernels per layer): replay it as a CUDA graph.
     // The graph is captured once per (x0, y, tokens, stream); a stream that is
     // itself being captured, or the legacy default stream, gets plain launches.
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -498,7 +673,7 @@ int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t 
         it = h->stack_graphs.emplace(key, exec).first;
     }
     int rc = record(h, cudaGraphLaunch(it->second, st));
-    if (rc == NVMAI_CUDA_OK) g_launches.fetch_add((uint64_t)c.num_layers * 4 - 1, std::memory_order_relaxed);
+    if (rc == NVMAI_CUDA_OK) g_launches.fetch_add((uint64_t)c.num_layers * 3, std::memory_order_relaxed);
     return rc;
 }
 
@@ -576,7 +751,16 @@ int nvmai_cuda_moe_residual_add_f16(void *hidden, const void *delta, uint32_t co
 }
 
 int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream) {
-    return record(h, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int rc = record(h, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    if (rc || !h) return rc;
+    unsigned int st = 0;
+    rc = record(h, cudaMemcpy(&st, h->status, sizeof(st), cudaMemcpyDeviceToHost));
+    if (rc) return rc;
+    if (st != 0) {      // a kernel gave up a bounded wait; its outputs are undefined
+        cudaMemset(h->status, 0, sizeof(st));
+        return NVMAI_CUDA_ETIMEOUT;
+    }
+    return NVMAI_CUDA_OK;
 }
 
 int nvmai_cuda_moe_last_cuda_error(const nvmai_cuda_moe *h) { return h ? h->last_cuda_error : 0; }

@@ -139,6 +139,12 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_routed_phase2(self._h, arr, C.byref(off), _ptr(acts), _ptr(routing_w),
                                                      _ptr(residual), _ptr(y), _stream(stream)), "routed_phase2")
 
+    def group_pairs(self, idx, w, tokens: int, sorted_pairs, expert_offsets, expert_counts, *, stream=None) -> None:
+        """`makeTokenExpertPairs` + `groupTokenExpertPairs` (PrefillMoEGrouping.swift:90-192) on the device."""
+        check(self._lib.nvmai_cuda_moe_group_pairs(self._h, _ptr(idx), _ptr(w), tokens, _ptr(sorted_pairs),
+                                                   _ptr(expert_offsets), _ptr(expert_counts), _stream(stream)),
+              "group_pairs")
+
     # -- fused paths ----------------------------------------------------------------
     def layer_decode(self, layer: int, x, tokens: int, *, hidden=None, h2_out=None, out_idx=None, out_w=None,
                      stream=None) -> None:

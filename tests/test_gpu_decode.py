@@ -304,11 +304,38 @@ def test_layer_decode_reference_format_fp16_out():
     _check_layer(host, cfg, 1, seed=78, tol_gpu_oracle=2e-3)     # one fp16 ulp of the output
 
 
-@pytest.mark.parametrize("tokens", [4, 16])
+@pytest.mark.parametrize("tokens", [2, 4, 16, 64])
 def test_layer_decode_batch(tokens):
-    """configs[1]: independent rows, 8-bit"""
+    """configs[1]: independent rows, 8-bit; from 4 rows on, rows that picked the same
+    expert are grouped and share one read of its weights"""
     host, cfg = _layer_case(8, fmt.META_FP16, fmt.OUT_FP32, tokens, seed=5)
     _check_layer(host, cfg, tokens, seed=6 + tokens, tol_gpu_oracle=5e-4)
+
+
+def test_layer_decode_batch_4bit_reference_rounding():
+    """grouped path with the reference's fp16 rounding points and a ragged batch (11 rows)"""
+    host, cfg = _layer_case(4, fmt.META_BF16, fmt.OUT_FP16, 11, seed=15, router_kind=fmt.ROUTER_AFFINE8,
+                            gate_kind=fmt.ROUTER_AFFINE8)
+    _check_layer(host, cfg, 11, seed=16, tol_gpu_oracle=2e-3)
+
+
+def test_batched_result_equals_row_by_row():
+    """grouping must not change a row's result: batch of 9 == nine single-row calls, bitwise"""
+    host, cfg = _layer_case(4, fmt.META_BF16, fmt.OUT_FP32, 9, seed=41, d=256, f=128, e=32)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    x = synthetic.hidden_rows(42, 9, cfg.d)
+    xd = gu.to_dev(x)
+    batch = gu.dev_empty(9 * cfg.d, "f32")
+    moe.layer_decode(0, xd, 9, h2_out=batch)
+    sync()
+    got = batch.cpu().numpy().reshape(9, cfg.d)
+    for t in range(9):
+        one = gu.dev_empty(cfg.d, "f32")
+        moe.layer_decode(0, xd.data_ptr() + t * cfg.d * 2, 1, h2_out=one)
+        sync()
+        assert np.array_equal(one.cpu().numpy().view(np.uint32), got[t].view(np.uint32)), f"row {t}"
 
 
 def test_layer_decode_small_shape_and_determinism():
@@ -337,6 +364,61 @@ def test_hidden_residual_add():
     sync()
     want = (orc.f16_bits_to_f32(hid0[0]) + orc.f16_bits_to_f32(gu.from_dev(h2, np.uint16))).astype(np.float16)
     assert np.array_equal(gu.from_dev(hid, np.float16).ravel(), want)
+
+
+# ---------------------------------------------------------------------------
+# pair grouping
+# ---------------------------------------------------------------------------
+
+def _device_grouping(pairs, tokens, top_k, num_experts):
+    cfg = MoEConfig(d=128, f=64, shared_f=0, num_experts=num_experts, top_k=top_k, routed_bits=4, shared_bits=4,
+                    router_kind=fmt.ROUTER_AFFINE8, shared_gate_kind=fmt.GATE_NONE, max_tokens=max(tokens, 1))
+    moe = MoE(cfg)
+    idx = np.zeros((tokens, top_k), dtype=np.uint32)
+    w = np.zeros((tokens, top_k), dtype=np.uint16)
+    for t, e, r, bits in pairs:
+        idx[t, r] = e
+        w[t, r] = bits
+    n = tokens * top_k
+    out = gu.dev_empty(n * 16, "u8")
+    off, cnt = gu.dev_empty(num_experts, "u32"), gu.dev_empty(num_experts, "u32")
+    moe.group_pairs(gu.to_dev(idx), gu.to_dev(w), tokens, out, off, cnt)
+    sync()
+    return (out.cpu().numpy().view(orc.PAIR_DTYPE), gu.from_dev(off, np.uint32), gu.from_dev(cnt, np.uint32))
+
+
+def test_grouping_literal_tables():
+    """PrefillMoEGroupingTests.swift:5-53, 55-82: exact sorted-pair order, offsets, counts, weight bits"""
+    t = rv.GROUPING_TABLE_1
+    s, off, cnt = _device_grouping(t["pairs"], t["query_count"], t["top_k"], t["num_experts"])
+    assert s["expert"].tolist() == t["sorted_experts"]
+    assert [[int(a), int(b)] for a, b in zip(s["token"], s["rank"])] == t["sorted_token_rank"]
+    assert off.tolist() == t["offsets"] and cnt.tolist() == t["counts"]
+    t2 = rv.GROUPING_TABLE_2
+    s2, _, _ = _device_grouping(t2["pairs"], t2["query_count"], t2["top_k"], t2["num_experts"])
+    assert s2["weight_bits"].tolist() == t2["sorted_weight_bits"]
+
+
+@pytest.mark.parametrize("tokens", [1, 37, 256, 1500])
+def test_grouping_matches_oracle_on_random_routes(tokens):
+    """sortedness, a permutation of the input, and equality with the restated
+    groupTokenExpertPairs on seeded routes (more than one 1024-pair pass at 1500)"""
+    import ctypes as C
+    rng = np.random.default_rng(tokens)
+    K, E = 8, 256
+    idx = np.stack([rng.choice(E, size=K, replace=False) for _ in range(tokens)]).astype(np.uint32)
+    pairs = [(t, int(idx[t, r]), r, (t * K + r) & 0xFFFF) for t in range(tokens) for r in range(K)]
+    s, off, cnt = _device_grouping(pairs, tokens, K, E)
+    arr = rv.pairs_array(pairs)
+    n = len(pairs)
+    want = np.zeros(n, dtype=orc.PAIR_DTYPE)
+    woff, wcnt = np.zeros(E, dtype=np.uint32), np.zeros(E, dtype=np.uint32)
+    groups, tiles = np.zeros((n, 3), dtype=np.uint32), np.zeros((n, 4), dtype=np.uint32)
+    ng, nt = C.c_size_t(0), C.c_size_t(0)
+    rc = orc.lib().orc_group_pairs(orc.ptr(arr), n, tokens, K, E, 16, None, 0, orc.ptr(want), orc.ptr(woff),
+                                   orc.ptr(wcnt), orc.ptr(groups), C.byref(ng), orc.ptr(tiles), C.byref(nt))
+    assert rc == 0
+    assert np.array_equal(s, want) and np.array_equal(off, woff) and np.array_equal(cnt, wcnt)
 
 
 # ---------------------------------------------------------------------------
