@@ -197,6 +197,15 @@ NVMAI_API int nvmai_cuda_moe_silu_mul_f16(const void *gate, const void *up, void
 NVMAI_API int nvmai_cuda_moe_sigmoid_scalar_mul_f16(void *y, const void *gate, uint32_t count, void *stream);
 NVMAI_API int nvmai_cuda_moe_residual_add_f16(void *hidden, const void *delta, uint32_t count, void *stream);
 
+/* Optional per-kernel timeline of the single-token decode stages, the counterpart
+ * of the reference's NVMAI_KERNEL_STATS command-buffer times
+ * (RealForwardRunner.swift:1086-1133): with tracing on, every stage launch of
+ * layer_decode / stack_decode stores GPU-timer nanoseconds at
+ * [layer][stage 0..2][8]: {start of block 0, latest block end, six phase marks of
+ * block 0}.  read_trace synchronises the device. */
+NVMAI_API int nvmai_cuda_moe_set_trace(nvmai_cuda_moe *h, int enable);
+NVMAI_API int nvmai_cuda_moe_read_trace(nvmai_cuda_moe *h, uint64_t *out_host, uint32_t layers);
+
 /* waitUntilCompleted + `.error` (RealForwardRunner.swift:3805-3837). */
 NVMAI_API int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream);
 NVMAI_API int nvmai_cuda_moe_last_cuda_error(const nvmai_cuda_moe *h);

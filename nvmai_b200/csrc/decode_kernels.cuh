@@ -34,6 +34,14 @@ struct RoutedSource {
     const uint8_t *base;
     unsigned long long stride;
     uint32_t num_experts;
+    // Deferred selection: when set, the consumer block selects the token's experts
+    // itself from the router logits [tokens][num_experts] (every block reaches the
+    // same result), which takes the serial select-then-publish step off the
+    // critical path between the router and the expert stages.
+    const float *logits;
+    const uint16_t *pes;      // per-expert scale (bf16) for the routing weights, or nullptr
+    uint32_t *publish_idx;    // [tokens][top_k]: one block per token stores what it selected
+    __half *publish_w;
 };
 
 struct ExpertOffsets { uint32_t o[9]; };
@@ -44,6 +52,9 @@ __device__ __forceinline__ const uint8_t *routed_blob(const RoutedSource &src, u
     uint32_t e = src.idx[(size_t)token * top_k + slot];
     e = min(e, src.num_experts - 1u);
     return src.base + (size_t)e * src.stride;
+}
+__device__ __forceinline__ const uint8_t *expert_blob(const RoutedSource &src, uint32_t e) {
+    return src.base + (size_t)min(e, src.num_experts - 1u) * src.stride;
 }
 
 // ---------------------------------------------------------------------------
@@ -161,9 +172,12 @@ __device__ __forceinline__ float router_row_logit(uint32_t kind, const uint8_t *
 }
 
 // ---------------------------------------------------------------------------
-// Top-k + softmax over the selected logits (moe.metal:233-285), one warp per
-// token.  Order: score descending, ties to the lower expert index.
+// Top-k + softmax over the selected logits (moe.metal:233-285).  Order: score
+// descending, ties to the lower expert index; NaN logits are never selected.
 // ---------------------------------------------------------------------------
+
+// One warp per token, K sequential arg-max passes.  Used where only a warp is
+// at hand; the block-wide version below replaces it on the decode path.
 __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, int K, const uint16_t *pes,
                                                   uint32_t *out_idx, __half *out_w) {
     const int lane = threadIdx.x & 31;
@@ -183,18 +197,23 @@ __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, in
 #pragma unroll
         for (int i = 0; i < kMaxExperts / 32; ++i) {
             const int e = lane + 32 * i;
-            const bool free_slot = !((taken >> i) & 1u) && e < E;
-            if (free_slot && (v[i] > best || (v[i] == best && e < best_e))) { best = v[i]; best_e = e; }
+            // bitwise, not short-circuit, logic: short-circuit operators become divergent branches here
+            const bool free_slot = (!((taken >> i) & 1u)) & (e < E);
+            const bool better = free_slot & ((v[i] > best) | ((v[i] == best) & (e < best_e)));
+            best = better ? v[i] : best;
+            best_e = better ? e : best_e;
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
             const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+            const bool better = (ob > best) | ((ob == best) & (oe < best_e));
+            best = better ? ob : best;
+            best_e = better ? oe : best_e;
         }
-        if (best_e == 0x7fffffff) best_e = 0;               // nothing selectable (every logit NaN)
-        if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
-        if (k == 0) top0 = best;
+        best_e = best_e == 0x7fffffff ? 0 : best_e;         // nothing selectable (every logit NaN)
+        taken |= ((best_e & 31) == lane) ? (1u << (best_e >> 5)) : 0u;
+        top0 = k == 0 ? best : top0;
         if (k == lane) { sel_score = best; sel_idx = (uint32_t)best_e; }
     }
     // softmax over the K selected scores only, summed in rank order (moe.metal:271-277)
@@ -206,6 +225,120 @@ __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, in
         out_idx[lane] = sel_idx;
         out_w[lane] = __float2half_rn(w * gain);
     }
+}
+
+// Block-wide selection into sel_idx[K] / sel_score[K] (shared memory), no softmax;
+// K <= 8.  Thread e < 256 owns expert e.  Two levels of ranking by counting, so
+// that nothing waits on a chain of arg-max rounds: (1) inside each warp every lane
+// ranks its logit against the other 31 (one shuffle each); the eight best of a
+// warp become candidates; (2) each of the <= 64 candidates ranks itself against
+// the others through shared memory; ranks below K are the selection, in order.
+// Order everywhere: score descending, ties to the lower index (moe.metal:252-258).
+// `cand` holds 64 float + 64 u32 of shared memory.  Ends with the block in sync.
+__device__ __forceinline__ void topk_select_block(const float *logits, int E, int K, uint32_t *sel_idx,
+                                                  float *sel_score, float *cand) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float *cand_score = cand;
+    uint32_t *cand_idx = reinterpret_cast<uint32_t *>(cand + 64);
+    if (tid < 64) { cand_score[tid] = -INFINITY; cand_idx[tid] = 0xFFFFFFFFu; }
+    if (tid < K) { sel_idx[tid] = 0; sel_score[tid] = -INFINITY; }
+    __syncthreads();
+    if (tid < kMaxExperts) {
+        float s = tid < E ? __ldcg(logits + tid) : -INFINITY;
+        const bool valid = tid < E && s == s && s > -INFINITY;   // NaN and -inf are never selected (moe.metal:246-258)
+        if (!valid) s = -INFINITY;
+        int rank = 0;
+#pragma unroll
+        for (int o = 1; o < 32; ++o) {
+            const int src = (lane + o) & 31;
+            const float os = __shfl_sync(0xffffffffu, s, src);
+            // branch-free on purpose; an unselectable neighbour carries -inf and loses every comparison
+            rank += (int)((os > s) | ((os == s) & (src < lane)));
+        }
+        if (valid && rank < 8) { cand_score[warp * 8 + rank] = s; cand_idx[warp * 8 + rank] = (uint32_t)tid; }
+    }
+    __syncthreads();
+    if (tid < 64) {
+        const float s = cand_score[tid];
+        const uint32_t e = cand_idx[tid];
+        if (e != 0xFFFFFFFFu) {
+            int rank = 0;
+#pragma unroll 16
+            for (int j = 0; j < 64; ++j) {
+                const float os = cand_score[j];
+                const uint32_t oe = cand_idx[j];      // empty slots: -inf score, index 0xFFFFFFFF: they lose every comparison
+                rank += (int)((os > s) | ((os == s) & (oe < e)));
+            }
+            if (rank < K) { sel_idx[rank] = e; sel_score[rank] = s; }
+        }
+    }
+    __syncthreads();
+}
+
+// Routing weights of a selection (moe.metal:271-285): softmax over the K selected
+// scores summed in rank order, times the per-expert scale, rounded to half.
+__device__ __forceinline__ void routing_weights_warp(const uint32_t *sel_idx, const float *sel_score, int K,
+                                                     const uint16_t *pes, uint32_t *out_idx, __half *out_w) {
+    const int lane = threadIdx.x & 31;
+    const float top0 = sel_score[0];
+    float sum_exp = 0.0f;
+    for (int k = 0; k < K; ++k) sum_exp += expf(sel_score[k] - top0);
+    if (lane < K) {
+        const uint32_t e = sel_idx[lane];
+        const float w = expf(sel_score[lane] - top0) / sum_exp;
+        const float gain = pes ? __uint_as_float(((uint32_t)ldg_u16(pes + e)) << 16) : 1.0f;
+        out_idx[lane] = e;
+        out_w[lane] = __float2half_rn(w * gain);
+    }
+}
+
+// Whole block, one token: every thread ranks one expert against all the others
+// (rank = number of experts that sort before it), which takes one pass over the
+// logits in shared memory instead of K dependent arg-max rounds; the K experts
+// of rank < K land in rank order, then one warp does the softmax.
+// `work` holds kMaxExperts floats + 32 floats + 32 u32 of shared memory.
+__device__ __forceinline__ void topk_softmax_block(const float *logits, int E, int K, const uint16_t *pes,
+                                                   uint32_t *out_idx, __half *out_w, float *work) {
+    float *sl = work;                                   // [kMaxExperts]
+    float *sel_score = work + kMaxExperts;              // [32]
+    uint32_t *sel_idx = reinterpret_cast<uint32_t *>(work + kMaxExperts + 32);
+    for (int e = threadIdx.x; e < kMaxExperts; e += blockDim.x) {
+        float v = e < E ? __ldcg(logits + e) : -INFINITY;
+        sl[e] = v;
+    }
+    if (threadIdx.x < 32) { sel_score[threadIdx.x] = -INFINITY; sel_idx[threadIdx.x] = 0; }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const float s = sl[e];
+        int rank = 0;
+        if (s == s) {                                   // NaN never ranks
+            const float4 *v4 = reinterpret_cast<const float4 *>(sl);
+#pragma unroll 8
+            for (int j = 0; j < kMaxExperts / 4; ++j) {
+                const float4 q = v4[j];
+                rank += (int)((q.x > s) | ((q.x == s) & (4 * j + 0 < e)));
+                rank += (int)((q.y > s) | ((q.y == s) & (4 * j + 1 < e)));
+                rank += (int)((q.z > s) | ((q.z == s) & (4 * j + 2 < e)));
+                rank += (int)((q.w > s) | ((q.w == s) & (4 * j + 3 < e)));
+            }
+            if (rank < K) { sel_score[rank] = s; sel_idx[rank] = (uint32_t)e; }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float top0 = sel_score[0];
+        float sum_exp = 0.0f;
+        for (int k = 0; k < K; ++k) sum_exp += expf(sel_score[k] - top0);   // rank order, moe.metal:271-277
+        if (lane < K) {
+            const uint32_t e = sel_idx[lane];
+            const float w = expf(sel_score[lane] - top0) / sum_exp;
+            const float gain = pes ? __uint_as_float(((uint32_t)ldg_u16(pes + e)) << 16) : 1.0f;
+            out_idx[lane] = e;
+            out_w[lane] = __float2half_rn(w * gain);
+        }
+    }
+    __syncthreads();
 }
 
 template <int OUT> __device__ __forceinline__ float load_out(const void *p, size_t i) {

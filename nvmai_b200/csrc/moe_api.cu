@@ -56,6 +56,10 @@ struct nvmai_cuda_moe {
     float *partial = nullptr;        // [T*K][D]
     float *shared_partial = nullptr; // [T][D]
     uint32_t max_work = 0;
+    // optional kernel timeline (the counterpart of the reference's NVMAI_KERNEL_STATS)
+    unsigned long long *trace = nullptr;   // [num_layers][3 stages][start, end]
+    bool trace_on = false;
+    unsigned long long *cur_trace = nullptr;   // slot handed to the next stage launch
     const void **blob_table = nullptr;   // unused on device; kept for symmetry
     void *stage_x = nullptr;        // host-call staging: [T][D] fp16
     void *stage_y = nullptr;        // host-call staging: [T][D] out_dtype
@@ -185,7 +189,7 @@ constexpr size_t kMaxSmem = 227 * 1024;
 // grouped stage instead and asks for the gate only.
 int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const XSource &xsrc, uint32_t tokens,
                   uint32_t *out_idx, __half *out_w, bool with_router, bool with_shared, bool with_gate, bool pdl,
-                  cudaStream_t st) {
+                  cudaStream_t st, bool defer_topk = false) {
     const auto &c = h->cfg;
     Stage1Params p{};
     p.rW = static_cast<const uint8_t *>(lv.w.router.w);
@@ -198,6 +202,7 @@ int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const XSource &xsrc, 
     p.out_idx = out_idx;
     p.out_w = out_w;
     p.counter = h->counter;
+    p.defer_topk = defer_topk ? 1u : 0u;
     p.sgate = to_mat(lv.w.shared_gate_proj);
     p.sup = to_mat(lv.w.shared_up_proj);
     p.shared_f = with_shared ? c.shared_f : 0;
@@ -208,6 +213,7 @@ int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const XSource &xsrc, 
     p.gate_kind = c.shared_gate_kind;
     p.gate_val = h->gate_val;
     p.xsrc = xsrc; p.tokens = tokens;
+    p.trace = h->cur_trace;
     p.D = c.d; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation;
     p.status = h->status;
     p.tokens_per_chunk = tokens <= 8 ? tokens : 8;
@@ -240,6 +246,7 @@ int launch_stage2(nvmai_cuda_moe *h, const RoutedSource &src, const ExpertOffset
     p.active_slots = active_slots_dev;
     p.D = c.d; p.F = c.f; p.top_k = c.top_k; p.act = c.activation;
     p.status = h->status;
+    p.trace = h->cur_trace;
     dim3 grid((c.f + kBlockFeatures - 1) / kBlockFeatures, n_slots, tokens);
     const size_t smem = GateUpLayout(c.d, c.routed_bits).total;
     return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
@@ -254,6 +261,7 @@ int launch_stage3(nvmai_cuda_moe *h, Stage3Params p, uint32_t tokens, bool pdl, 
     const auto &c = h->cfg;
     p.D = c.d; p.F = c.f;
     p.status = h->status;
+    p.trace = h->cur_trace;
     dim3 grid(c.d / kTileRows, tokens);
     const uint32_t units = p.top_k + (p.shared_f ? 1 : 0);
     const uint32_t threads = (units < 1 ? 1 : units) * kDownSplit * 32;
@@ -348,20 +356,37 @@ int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, 
 // xsrc: where stage 1 gets its rows; x_rows: the fp16 rows stages 2 reads (the
 // same buffer, or the buffer stage 1 writes its normalised rows to).
 int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, const __half *x_rows, uint32_t tokens,
-                      void *hidden, void *h2_out, uint32_t *out_idx, __half *out_w, cudaStream_t st) {
+                      void *hidden, void *h2_out, uint32_t *out_idx, __half *out_w, cudaStream_t st,
+                      const LayerViews *next_layer = nullptr) {
     const auto &c = h->cfg;
     const LayerViews &lv = h->layers[layer];
     uint32_t *idx = out_idx ? out_idx : h->idx;
     __half *w = out_w ? out_w : h->w;
     const bool grouped = tokens >= kGroupedMinTokens;
-    int rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, c.shared_f != 0 && !grouped, c.shared_f != 0, true, st);
+    auto slot = [&](int stage) { return (h->trace_on && !grouped) ? h->trace + ((size_t)layer * 3 + stage) * kTraceWords : nullptr; };
+    h->cur_trace = slot(0);
+    // single-token path: the expert stages select the experts themselves from the logits
+    // (the block-wide selection wants one thread per expert in the down stage's block too)
+    const bool defer = !grouped && (c.top_k + (c.shared_f ? 1 : 0)) * kDownSplit * 32 >= (uint32_t)kMaxExperts;
+    int rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, c.shared_f != 0 && !grouped, c.shared_f != 0, true, st,
+                           defer);
     if (rc) return rc;
+    h->cur_trace = nullptr;
     if (grouped) return grouped_tail(h, lv, x_rows, tokens, idx, w, hidden, h2_out ? h2_out : h->y, st);
-    rc = launch_stage2(h, source_from_layer(h, lv, idx), to_offsets(lv.w.offsets), x_rows, c.d, tokens, h->acts,
-                       nullptr, c.top_k, true, st);
+    h->cur_trace = slot(1);
+    RoutedSource src = source_from_layer(h, lv, idx);
+    if (defer) {
+        src.logits = h->logits;
+        src.pes = static_cast<const uint16_t *>(lv.w.per_expert_scale);
+        src.publish_idx = idx;
+        src.publish_w = w;
+    }
+    rc = launch_stage2(h, src, to_offsets(lv.w.offsets), x_rows, c.d, tokens, h->acts, nullptr, c.top_k, true, st);
+    h->cur_trace = nullptr;
     if (rc) return rc;
+    h->cur_trace = slot(2);
     Stage3Params p{};
-    p.src = source_from_layer(h, lv, idx);
+    p.src = src;
     p.off = to_offsets(lv.w.offsets);
     p.acts = h->acts;
     p.routing_w = w;
@@ -375,7 +400,26 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
     p.y = h2_out ? h2_out : h->y;
     p.hidden = hidden;
     p.top_k = c.top_k;
-    return launch_stage3(h, p, tokens, true, st);
+    if (next_layer != nullptr) {    // stack driver: warm the L2 with what the next layer's first stage reads
+        const auto &nw = next_layer->w;
+        const size_t router_bytes = c.router_kind == 0 ? (size_t)c.num_experts * c.d * 2
+                                                       : (size_t)c.num_experts * c.d * c.router_kind / 8;
+        const size_t router_meta = c.router_kind == 0 ? 0 : (size_t)c.num_experts * (c.d / 64) * 2;
+        const size_t sw = (size_t)c.shared_f * c.d * c.shared_bits / 8, sm = (size_t)c.shared_f * (c.d / 64) * 2;
+        int n = 0;
+        auto add = [&](const void *ptr, size_t bytes) { if (ptr && bytes && n < 6) { p.next_ptr[n] = ptr; p.next_bytes[n] = bytes; ++n; } };
+        add(nw.router.w, router_bytes);
+        add(nw.router.scales, router_meta);
+        add(nw.router.biases, router_meta);
+        if (c.shared_f) {
+            add(nw.shared_gate_proj.w, sw);
+            add(nw.shared_up_proj.w, sw);
+            add(nw.shared_gate_proj.scales, sm);   // the remaining meta arrays are small; the copies fetch them
+        }
+    }
+    rc = launch_stage3(h, p, tokens, true, st);
+    h->cur_trace = nullptr;
+    return rc;
 }
 
 }  // namespace
@@ -459,7 +503,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
         h->max_work = (uint32_t)(std::min(P, c.num_experts + P / kPairsPerItem) + (T + kPairsPerItem - 1) / kPairsPerItem);
         if (ok) ok = alloc(&h->sorted_pair, P * 4) && alloc(&h->inv, P * 4) && alloc(&h->expert_offsets, kMaxExperts * 4) &&
                      alloc(&h->expert_counts, kMaxExperts * 4) && alloc(&h->work, (size_t)h->max_work * sizeof(WorkItem)) &&
-                     alloc(&h->n_work, 16);
+                     alloc(&h->n_work, 16) && alloc(&h->trace, (size_t)c.num_layers * 3 * kTraceWords * sizeof(unsigned long long));
         // per-pair partial rows are only needed by the batched path
         if (ok && T >= kGroupedMinTokens)
             ok = alloc(&h->partial, P * c.d * sizeof(float)) && alloc(&h->shared_partial, T * c.d * sizeof(float));
@@ -481,7 +525,7 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y);
     cudaFree(h->sorted_pair); cudaFree(h->inv); cudaFree(h->expert_offsets); cudaFree(h->expert_counts);
-    cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->partial); cudaFree(h->shared_partial);
+    cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->trace); cudaFree(h->partial); cudaFree(h->shared_partial);
     delete h;
 }
 
@@ -628,7 +672,8 @@ static int stack_enqueue(nvmai_cuda_moe *h, const __half *x0, uint32_t tokens, v
         const __half *x_rows;
         if (l == 0) { xsrc.x = x0; xsrc.x_stride = c.d; x_rows = x0; }
         else { xsrc.y_prev = h->y; xsrc.x_out = h->xnorm; x_rows = h->xnorm; }
-        int rc = layer_decode_impl(h, l, xsrc, x_rows, tokens, nullptr, y, nullptr, nullptr, st);
+        int rc = layer_decode_impl(h, l, xsrc, x_rows, tokens, nullptr, y, nullptr, nullptr, st,
+                                   last ? nullptr : &h->layers[l + 1]);
         if (rc) return rc;
     }
     return NVMAI_CUDA_OK;
@@ -748,6 +793,19 @@ int nvmai_cuda_moe_residual_add_f16(void *hidden, const void *delta, uint32_t co
     residual_add_kernel<<<(count + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<__half *>(hidden), static_cast<const __half *>(delta), count);
     return check_launch(nullptr);
+}
+
+int nvmai_cuda_moe_set_trace(nvmai_cuda_moe *h, int enable) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    h->trace_on = enable != 0;
+    h->graphs_stale = true;     // captured launches carry (or do not carry) the trace slots
+    return record(h, cudaMemset(h->trace, 0, (size_t)h->cfg.num_layers * 3 * kTraceWords * sizeof(unsigned long long)));
+}
+
+int nvmai_cuda_moe_read_trace(nvmai_cuda_moe *h, uint64_t *out_host, uint32_t layers) {
+    if (!h || !out_host || layers > h->cfg.num_layers) return NVMAI_CUDA_EINVAL;
+    return record(h, cudaMemcpy(out_host, h->trace, (size_t)layers * 3 * kTraceWords * sizeof(unsigned long long),
+                                cudaMemcpyDeviceToHost));
 }
 
 int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream) {

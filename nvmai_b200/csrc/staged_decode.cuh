@@ -12,11 +12,12 @@ constexpr int kRowsPerRouterBlock = 8;
 // device's addressing); every offset is a multiple of 16 bytes
 // ---------------------------------------------------------------------------
 struct GateUpLayout {     // kTilesPerBlock tiles of 8 gate rows + the matching 8 up rows, and the token's x row
-    size_t xs, w0, w_step, meta0, meta_step, red, wsum, total;
+    size_t xs, xsum, w0, w_step, meta0, meta_step, red, wsum, total;
     __host__ __device__ GateUpLayout(int D, int bits) {
         const size_t stride = (size_t)D * bits / 8 + (bits == 4 ? 32 : 64);
         size_t o = 16 * kTilesPerBlock;      // one transaction barrier per tile
         xs = o; o += (size_t)D * 2;
+        xsum = o; o += ((size_t)(D / kGroup) * sizeof(float) + 15) & ~(size_t)15;
         w_step = kTileRows * stride;         // tile rows 0-7 gate, 8-15 up
         w0 = o; o += kTilesPerBlock * w_step;
         meta_step = (((size_t)kTileRows * (D / kGroup) * 2) + 15) & ~(size_t)15;
@@ -60,7 +61,7 @@ struct DownLayout {       // per warp: barrier, activation row, 16-row down tile
         meta0 = o; o += 2 * meta_step;
         region = (o + 127) & ~(size_t)127;
         part = (size_t)warps * region;
-        total = part + (kMaxTopK + 1) * 2 * 16 * sizeof(float);
+        total = part + ((kMaxTopK + 1) * 2 * 16 + 32) * sizeof(float);   // partial sums + routing weights
     }
     __host__ __device__ size_t meta(int i) const { return meta0 + i * meta_step; }
 };
@@ -85,9 +86,20 @@ __device__ __forceinline__ void stage_x(const XSource &src, uint32_t tok, int D,
         for (int i = threadIdx.x * 8; i < D; i += blockDim.x * 8)
             *reinterpret_cast<uint4 *>(xs + i) = *reinterpret_cast<const uint4 *>(xrow + i);
     } else {
+        // one trip to memory: the row stays in registers between the sum of squares
+        // and the scaling (up to 16 values per thread; longer rows are re-read)
+        constexpr int kKeep = 16;
         const size_t base = (size_t)tok * D;
+        float keep[kKeep];
         float ss = 0.0f;
-        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            keep[j] = i < D ? load_out<OUT>(src.y_prev, base + i) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) ss = fmaf(keep[j], keep[j], ss);
+        for (int i = threadIdx.x + kKeep * blockDim.x; i < D; i += blockDim.x) {
             const float v = load_out<OUT>(src.y_prev, base + i);
             ss = fmaf(v, v, ss);
         }
@@ -97,7 +109,16 @@ __device__ __forceinline__ void stage_x(const XSource &src, uint32_t tok, int D,
         float tot = 0.0f;
         for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += wsum[i];
         const float sc = rsqrtf(tot / (float)D + 1e-6f);
-        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < D) {
+                const __half h = __float2half_rn(keep[j] * sc);
+                xs[i] = h;
+                if (write_back) src.x_out[base + i] = h;
+            }
+        }
+        for (int i = threadIdx.x + kKeep * blockDim.x; i < D; i += blockDim.x) {
             const __half h = __float2half_rn(load_out<OUT>(src.y_prev, base + i) * sc);
             xs[i] = h;
             if (write_back) src.x_out[base + i] = h;
@@ -197,20 +218,24 @@ __device__ __forceinline__ void gate_up_compute(unsigned char *smem, const GateU
             }
         }
     } else {
-        float *xsum = reinterpret_cast<float *>(smem + L.wsum) ;   // unused on this path; sums go through registers below
-        (void)xsum;
+        // any shape: group sums through shared memory, one generic pass per tile
+        float *xsum = reinterpret_cast<float *>(smem + L.xsum);
+        for (int base = g_begin; base < g_end; base += 4) {
+            const int G = base + (lane >> 3);
+            float v = 0.0f;
+            if (G < g_end) v = sum8_halves(*reinterpret_cast<const uint4 *>(xs + (size_t)G * kGroup + (lane & 7) * 8));
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            if ((lane & 7) == 0 && G < g_end) xsum[G] = v;
+        }
+        __syncwarp();
         for (int tile = 0; tile < n_tiles; ++tile) {
             if (tile > 0) ok = mbar_wait(reinterpret_cast<uint64_t *>(smem + 16 * tile), 0, status) && ok;
             const SmemTile tiles[1] = {{smem + L.w(tile), reinterpret_cast<const uint16_t *>(smem + L.meta(tile, 0)),
                                         reinterpret_cast<const uint16_t *>(smem + L.meta(tile, 1))}};
             float acc[1][4] = {};
-            for (int G = g_begin; G < g_end; ++G) {     // any shape: one group at a time, sums on the fly
-                float v = sum8_halves(*reinterpret_cast<const uint4 *>(xs + (size_t)G * kGroup + (lane & 7) * 8));
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                v += __shfl_xor_sync(0xffffffffu, v, 4);
-                tile_accumulate_smem<BITS, META, 1, 0, true>(tiles, D, G, G + 1, xs, &v - G, acc);
-            }
+            tile_accumulate_auto<BITS, META, 1, true>(tiles, D, g_begin, g_end - g_begin, xs, xsum, acc);
             if (t == 0) {
                 red[(tile * kDecodeWarps + warp) * 16 + g] = acc[0][0];
                 red[(tile * kDecodeWarps + warp) * 16 + g + 8] = acc[0][2];
@@ -242,6 +267,7 @@ struct Stage1Params {
     float *logits;            // [tokens][E]
     uint32_t *out_idx; __half *out_w;
     unsigned int *counter;    // zero on entry; reset by the last router block
+    uint32_t defer_topk;      // 1: stop at the logits; the expert stages select for themselves
     // shared expert (shared_f == 0 disables)
     AffineMat sgate, sup;
     uint32_t shared_f;
@@ -258,6 +284,7 @@ struct Stage1Params {
     uint32_t router_row_blocks;      // n_router_blocks = router_row_blocks * token chunks
     uint32_t tokens_per_chunk;       // tokens one router / gate block walks through
     unsigned int *status;
+    unsigned long long *trace;   // optional {start, end} timestamps of this launch
 };
 
 // rows [row0, row0+nrows) of a dense/affine matrix against every token's x
@@ -291,15 +318,18 @@ __device__ __forceinline__ void rows_block(unsigned char *smem, uint32_t kind, c
     }
     pdl_wait();
     pdl_launch_dependents();
+    trace_mark(p.trace, 0);
     __half *xs = reinterpret_cast<__half *>(smem + L.xs);
     float *wsum = reinterpret_cast<float *>(smem + L.wsum);
     bool ready = false;
     for (uint32_t tok = tok_begin; tok < tok_end; ++tok) {
         stage_x<OUT>(p.xsrc, tok, p.D, xs, wsum, write_back);
+        trace_mark(p.trace, 1);
         if (!ready) {
             ready = __syncthreads_and(mbar_wait(bar, 0, p.status));
             if (!ready) return;
         }
+        trace_mark(p.trace, 2);
         if (warp < nrows) {
             const float v = router_row_logit<META, true>(kind, smem + L.rows,
                                                          reinterpret_cast<const uint16_t *>(smem + L.meta(0)),
@@ -308,6 +338,7 @@ __device__ __forceinline__ void rows_block(unsigned char *smem, uint32_t kind, c
             if (lane == 0) emit(tok, row0 + warp, v);
         }
         __syncthreads();
+        trace_mark(p.trace, 3);
     }
 }
 
@@ -317,6 +348,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage1_kernel(Stage1Params 
     __shared__ bool is_last;
     const int warp = threadIdx.x >> 5;
     const uint32_t b = blockIdx.x;
+    trace_begin(p.trace);
     if (b < p.n_router_blocks) {
         const uint32_t chunk = b / p.router_row_blocks, rb = b % p.router_row_blocks;
         const uint32_t tok_begin = chunk * p.tokens_per_chunk, tok_end = min(tok_begin + p.tokens_per_chunk, p.tokens);
@@ -325,6 +357,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage1_kernel(Stage1Params 
         rows_block<META, OUT>(smem, p.router_kind, p.rW, p.rS, p.rB, row0, nrows, p, tok_begin, tok_end,
                               rb == 0 && p.xsrc.x_out != nullptr,
                               [&](uint32_t tok, int row, float v) { p.logits[(size_t)tok * p.E + row] = v; });
+        if (p.defer_topk) { trace_end(p.trace); return; }
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -333,10 +366,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage1_kernel(Stage1Params 
         }
         __syncthreads();
         if (is_last) {      // every logit of this token chunk is visible: select (moe.metal:233-285)
+            if (p.trace != nullptr && threadIdx.x == 0) p.trace[2 + 4] = global_timer_ns();
             __threadfence();
-            for (uint32_t tok = tok_begin + warp; tok < tok_end; tok += kDecodeWarps)
-                topk_softmax_warp(p.logits + (size_t)tok * p.E, p.E, p.K, p.pes,
-                                  p.out_idx + (size_t)tok * p.K, p.out_w + (size_t)tok * p.K);
+            // the x row and the staged weights are dead by now: their shared memory is the scratch
+            for (uint32_t tok = tok_begin; tok < tok_end; ++tok)
+                topk_softmax_block(p.logits + (size_t)tok * p.E, p.E, p.K, p.pes, p.out_idx + (size_t)tok * p.K,
+                                   p.out_w + (size_t)tok * p.K, reinterpret_cast<float *>(smem + 16));
+            if (p.trace != nullptr && threadIdx.x == 0) p.trace[2 + 5] = global_timer_ns();
             if (threadIdx.x == 0) p.counter[chunk] = 0;
         }
     } else if (b < p.n_router_blocks + p.n_shared_blocks) {
@@ -363,6 +399,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage1_kernel(Stage1Params 
         rows_block<META, OUT>(smem, p.gate_kind, p.gW, p.gS, p.gB, 0, 1, p, tok_begin, tok_end, false,
                               [&](uint32_t tok, int, float v) { p.gate_val[tok] = round_mid<OUT>(v); });
     }
+    trace_end(p.trace);
 }
 
 // ---------------------------------------------------------------------------
@@ -377,6 +414,7 @@ struct Stage2Params {
     const uint32_t *active_slots;       // device, or nullptr = identity
     uint32_t D, F, top_k, act;
     unsigned int *status;
+    unsigned long long *trace;   // optional {start, end} timestamps of this launch
 };
 
 template <int BITS, int META, int OUT>
@@ -387,14 +425,32 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage2_kernel(Stage2Params 
     const uint32_t tok = blockIdx.z;
     const int f0 = blockIdx.x * kBlockFeatures;
     const int n_tiles = min(kTilesPerBlock, (int)(p.F - f0) / kTileFeatures);
+    trace_begin(p.trace);
     init_tile_barriers(smem);
     pdl_wait();                 // the expert indices come from stage 1
     pdl_launch_dependents();
+    trace_mark(p.trace, 0);
     uint32_t slot = blockIdx.y;
     if (p.active_slots != nullptr) slot = p.active_slots[slot];
     if (slot >= p.top_k) return;        // moe.metal:720
+    // deferred selection (see RoutedSource); the scratch is the red area, unused until the reduction
+    uint32_t *sel_idx = reinterpret_cast<uint32_t *>(smem + L.red);
+    float *sel_score = reinterpret_cast<float *>(smem + L.red) + 32;
+    if (p.src.logits != nullptr) {
+        topk_select_block(p.src.logits + (size_t)tok * p.src.num_experts, p.src.num_experts, p.top_k, sel_idx, sel_score,
+                          reinterpret_cast<float *>(smem + L.red) + 64);
+        trace_mark(p.trace, 1);
+    }
     if (warp == 0) {
-        const uint8_t *blob = routed_blob(p.src, tok, slot, p.top_k);
+        const uint8_t *blob;
+        if (p.src.logits != nullptr) {
+            blob = expert_blob(p.src, sel_idx[slot]);
+            if (blockIdx.x == 0 && blockIdx.y == 0)
+                routing_weights_warp(sel_idx, sel_score, p.top_k, p.src.pes, p.src.publish_idx + (size_t)tok * p.top_k,
+                                     p.src.publish_w + (size_t)tok * p.top_k);
+        } else {
+            blob = routed_blob(p.src, tok, slot, p.top_k);
+        }
         const AffineMat gate = {blob + p.off.o[0], reinterpret_cast<const uint16_t *>(blob + p.off.o[1]),
                                 reinterpret_cast<const uint16_t *>(blob + p.off.o[2])};
         const AffineMat up = {blob + p.off.o[3], reinterpret_cast<const uint16_t *>(blob + p.off.o[4]),
@@ -403,9 +459,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage2_kernel(Stage2Params 
         if (lane == 0) bulk_g2s(smem + L.xs, p.x + (size_t)tok * p.x_stride, p.D * 2, reinterpret_cast<uint64_t *>(smem));
         for (int tile = 1; tile < n_tiles; ++tile)
             issue_gate_up_copies<BITS>(smem, L, tile, gate, up, f0 + tile * kTileFeatures, p.D, 0);
+        // warm the L2 with this block's share of the expert's down projection (stage 3 reads it next)
+        l2_prefetch_slice(blob + p.off.o[6], (size_t)p.D * p.F * BITS / 8, blockIdx.x, gridDim.x, lane);
+        l2_prefetch_slice(blob + p.off.o[7], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
+        l2_prefetch_slice(blob + p.off.o[8], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
     }
     gate_up_compute<BITS, META, OUT>(smem, L, f0, n_tiles, p.D, p.act, false, p.acts,
                                      ((size_t)tok * p.top_k + slot) * p.F, p.status);
+    trace_end(p.trace);
 }
 
 // ---------------------------------------------------------------------------
@@ -428,8 +489,12 @@ struct Stage3Params {
     void *h1_out;                       // optional out_dtype[tokens][D]
     void *y;                            // out_dtype[tokens][D]  (block output h2)
     void *hidden;                       // optional out_dtype[tokens][D], hidden += y
+    // ranges the next launch will read (the next layer's router and shared-expert
+    // weights): each block asks the L2 for its share
+    const void *next_ptr[6]; unsigned long long next_bytes[6];
     uint32_t D, F, top_k;
     unsigned int *status;
+    unsigned long long *trace;   // optional {start, end} timestamps of this launch
 };
 
 // one warp: bulk-copy a 16-row down tile (+ scales, biases) into its region
@@ -460,8 +525,20 @@ __device__ __forceinline__ const __half *stage_row_part(const void *rows, size_t
     if (OUT == OUT_F16) return reinterpret_cast<const __half *>(rows) + row_offset;
     const int lane = threadIdx.x & 31;
     const float *src = reinterpret_cast<const float *>(rows) + row_offset;
+    // one trip to memory: up to 1024 values stay in registers between the maximum
+    // (a property of the whole row) and the conversion; longer rows are re-read
+    constexpr int kKeep = 8;
+    float4 keep[kKeep];
     float m = 0.0f;
-    for (int i = lane * 4; i < n; i += 128) {        // the scale is a property of the whole row
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+        const int i = lane * 4 + j * 128;
+        keep[j] = i < n ? *reinterpret_cast<const float4 *>(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j)
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(keep[j].x), fabsf(keep[j].y)), fmaxf(fabsf(keep[j].z), fabsf(keep[j].w))));
+    for (int i = lane * 4 + kKeep * 128; i < n; i += 128) {
         const float4 v = *reinterpret_cast<const float4 *>(src + i);
         m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
     }
@@ -473,13 +550,19 @@ __device__ __forceinline__ const __half *stage_row_part(const void *rows, size_t
         scale_down = __uint_as_float((268u - ebits) << 23);
         scale_up = __uint_as_float((ebits - 14u) << 23);
     }
-    for (int i = begin + lane * 4; i < begin + count; i += 128) {
-        const float4 v = *reinterpret_cast<const float4 *>(src + i);
+    auto put = [&](int i, const float4 &v) {
         __half2 lo = __floats2half2_rn(v.x * scale_down, v.y * scale_down);
         __half2 hi = __floats2half2_rn(v.z * scale_down, v.w * scale_down);
         *reinterpret_cast<uint2 *>(smem_row + i) =
             make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+    };
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+        const int i = lane * 4 + j * 128;
+        if (i >= begin && i < begin + count) put(i, keep[j]);
     }
+    for (int i = lane * 4 + kKeep * 128; i < begin + count; i += 128)
+        if (i >= begin) put(i, *reinterpret_cast<const float4 *>(src + i));
     __syncwarp();
     return smem_row;
 }
@@ -490,7 +573,6 @@ __device__ __forceinline__ bool down_warp(unsigned char *region, const DownLayou
                                           const void *act_rows, size_t act_offset, unsigned int *status,
                                           float (&out)[2]) {
     const int lane = threadIdx.x & 31;
-    const int g = lane >> 2;
     const int groups = n / kGroup;
     const int gpw = (groups + kDownSplit - 1) / kDownSplit;
     const int g_begin = min(half * gpw, groups), g_end = min(g_begin + gpw, groups);
@@ -518,7 +600,14 @@ __device__ __forceinline__ bool down_warp(unsigned char *region, const DownLayou
     const SmemTile tiles[1] = {{region + L.w, reinterpret_cast<const uint16_t *>(region + L.meta(0)),
                                 reinterpret_cast<const uint16_t *>(region + L.meta(1))}};
     float acc[1][4] = {};
-    tile_accumulate_auto<BITS, META, 1, true>(tiles, n, g_begin, g_end - g_begin, g == 0 ? arow : nullptr, xsum, acc);
+    if (g_end - g_begin == 4 && (g_begin & 3) == 0 && (groups & 3) == 0) {
+        uint32_t xb[4][8];
+        const float xs4[4] = {xsum[g_begin], xsum[g_begin + 1], xsum[g_begin + 2], xsum[g_begin + 3]};
+        load_x_fragments<BITS, 4>(arow, g_begin, xb);
+        tile_accumulate_prepared<BITS, META, 4>(tiles[0], n, g_begin, xb, xs4, acc);
+    } else {
+        tile_accumulate_auto<BITS, META, 1, true>(tiles, n, g_begin, g_end - g_begin, arow, xsum, acc);
+    }
     out[0] = acc[0][0] * scale_up;
     out[1] = acc[0][2] * scale_up;
     return true;
@@ -539,11 +628,18 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
     uint64_t *bar = reinterpret_cast<uint64_t *>(region);
     const bool routed = unit < (int)p.top_k;
     const bool shared = unit == (int)p.top_k && p.shared_f != 0;
+    trace_begin(p.trace);
     // expert tiles depend only on stage 1's indices, which are complete before this
     // kernel can start: request them before waiting for stage 2's activations
+    if (p.src.logits != nullptr) {
+        // select here (see RoutedSource): this runs while stage 2 is still working
+        topk_select_block(p.src.logits + (size_t)tok * p.src.num_experts, p.src.num_experts, p.top_k,
+                          reinterpret_cast<uint32_t *>(part), part + 32, part + 64);
+    }
     if (half == 0) {
         if (routed) {
-            const uint8_t *blob = routed_blob(p.src, tok, unit, p.top_k);
+            const uint8_t *blob = p.src.logits != nullptr ? expert_blob(p.src, reinterpret_cast<uint32_t *>(part)[unit])
+                                                          : routed_blob(p.src, tok, unit, p.top_k);
             const AffineMat mat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
                                 reinterpret_cast<const uint16_t *>(blob + p.off.o[8])};
             issue_down_copies<BITS>(region, L, mat, row0, p.F, bar);
@@ -552,9 +648,19 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
             else issue_down_copies<8>(region, L, p.sdown, row0, p.shared_f, bar);
         }
     }
+    if (warp == (int)(blockDim.x >> 5) - 1) {
+#pragma unroll
+        for (int i = 0; i < 6; ++i)
+            if (p.next_ptr[i] != nullptr) l2_prefetch_slice(p.next_ptr[i], p.next_bytes[i], blockIdx.x, gridDim.x, lane);
+    }
     __syncthreads();        // the barrier of each unit is initialised before its second warp waits on it
     pdl_wait();
     pdl_launch_dependents();
+    trace_mark(p.trace, 0);
+    // routing weights for the final sum: fetched now, in parallel, instead of one dependent load per slot later
+    float *wk_s = part + (kMaxTopK + 1) * kDownSplit * 16;
+    if (threadIdx.x < p.top_k) wk_s[threadIdx.x] = __half2float(p.routing_w[(size_t)tok * p.top_k + threadIdx.x]);
+    const float gate_v = (p.gate_val != nullptr && threadIdx.x < 16) ? p.gate_val[tok] : 0.0f;
     bool ok = true;
     float v[2] = {0.0f, 0.0f};
     if (routed) {
@@ -569,7 +675,9 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
         part[(unit * kDownSplit + half) * 16 + g] = v[0];
         part[(unit * kDownSplit + half) * 16 + g + 8] = v[1];
     }
+    trace_mark(p.trace, 1);
     if (!__syncthreads_and(ok)) return;
+    trace_mark(p.trace, 2);
     if (threadIdx.x < 16) {
         const size_t i = (size_t)tok * p.D + row0 + threadIdx.x;
         auto unit_sum = [&](int u) {
@@ -582,18 +690,19 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
         if (p.shared_f != 0) {
             // h1 = out(down) then out(h1 * sigmoid(g))  (dequant_int*_gemv_simd store; utility.metal:60-70)
             float h1 = round_out<OUT>(unit_sum(p.top_k));
-            if (p.gate_val != nullptr) h1 = round_out<OUT>(sigmoid_div(h1, p.gate_val[tok]));
+            if (p.gate_val != nullptr) h1 = round_out<OUT>(sigmoid_div(h1, gate_v));
             if (p.h1_out != nullptr) store_out<OUT>(p.h1_out, i, h1);
             acc = h1;
         } else {
             acc = p.residual != nullptr ? load_out<OUT>(p.residual, i) : 0.0f;
         }
         for (uint32_t k = 0; k < p.top_k; ++k)      // slot order, moe.metal:802-808
-            acc += __half2float(p.routing_w[(size_t)tok * p.top_k + k]) * unit_sum(k);
+            acc += wk_s[k] * unit_sum(k);
         const float yv = round_out<OUT>(acc);
         if (p.y != nullptr) store_out<OUT>(p.y, i, yv);
         if (p.hidden != nullptr) store_out<OUT>(p.hidden, i, load_out<OUT>(p.hidden, i) + yv);   // utility.metal:94-103
     }
+    trace_end(p.trace);
 }
 
 }  // namespace nvmai

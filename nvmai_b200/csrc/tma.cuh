@@ -34,6 +34,26 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
                  : "memory");
 }
 
+// Asks the L2 to fetch [p, p + bytes) (16-byte multiples); nothing waits on it.
+// Used by a stage to warm the L2 with the weights the NEXT stage will stage in
+// shared memory, so that stage's copies hit the L2 instead of going to HBM.
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// this block's share of a contiguous range, cut into pieces one lane issues each
+__device__ __forceinline__ void l2_prefetch_slice(const void *base, size_t total_bytes, uint32_t part, uint32_t parts,
+                                                  int lane) {
+    const size_t per = ((total_bytes + parts - 1) / parts + 15) & ~(size_t)15;
+    const size_t begin = (size_t)part * per;
+    if (begin >= total_bytes) return;
+    const size_t end = begin + per < total_bytes ? begin + per : total_bytes;
+    constexpr size_t kPiece = 4096;
+    for (size_t o = begin + (size_t)lane * kPiece; o < end; o += 32 * kPiece) {
+        const size_t n = (end - o < kPiece ? end - o : kPiece) & ~(size_t)15;
+        if (n) l2_prefetch(static_cast<const unsigned char *>(base) + o, (uint32_t)n);
+    }
+}
+
 __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -73,5 +93,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsign
 // independent prologue now / wait for everything the previous kernel wrote.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Kernel-level timeline for the optional trace: slot[0] = time block 0 started,
+// slot[1] = latest time any block finished (GPU global timer, ns).
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void trace_begin(unsigned long long *slot) {
+    if (slot != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+        slot[0] = global_timer_ns();
+}
+__device__ __forceinline__ void trace_end(unsigned long long *slot) {
+    if (slot != nullptr && threadIdx.x == 0) atomicMax(slot + 1, global_timer_ns());
+}
+// slot[2 + i]: phase marks of block 0 (i < kTraceMarks)
+constexpr int kTraceMarks = 6;
+constexpr int kTraceWords = 2 + kTraceMarks;
+__device__ __forceinline__ void trace_mark(unsigned long long *slot, int i) {
+    if (slot != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+        slot[2 + i] = global_timer_ns();
+}
 
 }  // namespace nvmai

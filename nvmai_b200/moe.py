@@ -160,6 +160,17 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_stack_decode_host(self._h, _ptr(x0_host), tokens, _ptr(y_last_host),
                                                          _stream(stream)), "stack_decode_host")
 
+    def set_trace(self, enable: bool) -> None:
+        check(self._lib.nvmai_cuda_moe_set_trace(self._h, int(enable)), "set_trace")
+
+    def read_trace(self, layers: int | None = None):
+        """-> uint64 array [layers, 3, 8]: {start, end, six phase marks of block 0} GPU-timer ns per stage launch."""
+        import numpy as np
+        n = self.config.num_layers if layers is None else layers
+        out = np.zeros((n, 3, 8), dtype=np.uint64)
+        check(self._lib.nvmai_cuda_moe_read_trace(self._h, out.ctypes.data, n), "read_trace")
+        return out
+
     def synchronize(self, stream=None) -> None:
         check(self._lib.nvmai_cuda_moe_synchronize(self._h, _stream(stream)), "synchronize")
 
