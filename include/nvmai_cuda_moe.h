@@ -126,6 +126,29 @@ NVMAI_API int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, c
 NVMAI_API int nvmai_cuda_moe_router(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride,
                           uint32_t tokens, uint32_t *out_idx, void *out_w_f16, void *stream);
 
+/* The same router for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference.  Meant for hosts that gave all of HBM to their own
+ * arena before the first token (resident experts, KV state), where a cudaMalloc at
+ * this point can fail, and for decode loops that cannot afford the device-wide
+ * serialisation of cudaMalloc / cudaFree.  No handle: the logits and block
+ * counters live in a fixed 64.5 KiB array inside the library image (every GPU that
+ * loads the library holds it until the process exits), so the batch is limited to
+ * NVMAI_CUDA_NOALLOC_MAX_TOKENS rows; more returns NVMAI_CUDA_ERANGE.  `config`
+ * supplies d, num_experts, top_k, router_kind, meta_dtype; `router`,
+ * `effective_scale`, `per_expert_scale` as in nvmai_cuda_moe_layer.  The call
+ * makes no cudaMalloc / cudaFree and calls no allocating routine; it clears the
+ * counters with a memset on `stream` and launches one kernel.  The first call on
+ * a device looks up the array's device address (cudaGetSymbolAddress with that
+ * device current) and should therefore happen before any stream capture.  All
+ * calls share the one array: two calls that overlap on the GPU (different
+ * streams, no ordering) race on it; order them.  Results are bit-identical to
+ * nvmai_cuda_moe_router. */
+#define NVMAI_CUDA_NOALLOC_MAX_TOKENS 64u
+NVMAI_API int nvmai_cuda_moe_router_noalloc(const nvmai_cuda_moe_config *config, const nvmai_affine_tensor *router,
+                                  const void *effective_scale, const void *per_expert_scale, const void *x_f16,
+                                  uint32_t x_stride, uint32_t tokens, uint32_t *out_idx, void *out_w_f16,
+                                  void *stream);
+
 /* `SharedExpertRuntime.encode` + scalar gate GEMV + `sigmoid_scalar_mul_fp16`
  * (RealForwardRunner.swift:3866-3905): h1 = sigmoid(g.x) * down(act(gate.x)*up.x).
  * h1 is out_dtype[tokens][d]. */

@@ -7,4 +7,5 @@ helpers.  Importing it does not load the library; the first call does, and fails
 loudly when the library is absent.
 """
 from . import format, synthetic  # noqa: F401
-from .moe import Elementwise, MoE, MoEConfig, NvmaiError, affine_gemv, dequant, launch_count  # noqa: F401
+from .moe import (Elementwise, MoE, MoEConfig, NvmaiError, affine_gemv, dequant, launch_count,  # noqa: F401
+                  router_noalloc)

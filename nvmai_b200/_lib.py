@@ -49,6 +49,7 @@ PROTOTYPES = {
     "nvmai_cuda_moe_destroy": (None, [vp]),
     "nvmai_cuda_moe_register_layer": (C.c_int, [vp, u32, C.POINTER(Layer)]),
     "nvmai_cuda_moe_router": (C.c_int, [vp, u32, vp, u32, u32, vp, vp, vp]),
+    "nvmai_cuda_moe_router_noalloc": (C.c_int, [C.POINTER(Config), C.POINTER(AffineTensor), vp, vp, vp, u32, u32, vp, vp, vp]),
     "nvmai_cuda_moe_shared_expert": (C.c_int, [vp, u32, vp, u32, u32, vp, vp]),
     "nvmai_cuda_moe_routed_phase1": (C.c_int, [vp, C.POINTER(vp), C.POINTER(ExpertOffsets), vp, vp,
                                                 C.POINTER(u32), u32, vp]),

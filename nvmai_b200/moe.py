@@ -188,6 +188,21 @@ def affine_gemv(bits: int, meta: int, w, scales, biases, x, y, m: int, n: int, s
                                                 m, n, _stream(stream)), "affine_gemv")
 
 
+NOALLOC_MAX_TOKENS = 64
+
+
+def router_noalloc(config: MoEConfig, router, x, out_idx, out_w, *, tokens: int = 1, x_stride: int | None = None,
+                   effective_scale=None, per_expert_scale=None, stream=None) -> None:
+    """Router for callers that must not allocate device memory (no handle; the
+    scratch is a fixed array inside the library, at most NOALLOC_MAX_TOKENS rows).
+    Calls that overlap on the GPU race on that array: keep them ordered."""
+    cfg = config.to_c()
+    t = _tensor(router)
+    check(_lib.lib().nvmai_cuda_moe_router_noalloc(C.byref(cfg), C.byref(t), _ptr(effective_scale),
+                                                   _ptr(per_expert_scale), _ptr(x), x_stride or config.d, tokens,
+                                                   _ptr(out_idx), _ptr(out_w), _stream(stream)), "router_noalloc")
+
+
 class Elementwise:
     """`Elementwise` (sources/NVMAI/Kernels/Primitives/Elementwise.swift), the three MoE-side kernels."""
 
