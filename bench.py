@@ -253,6 +253,9 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     tokens = args.tokens
+    if world > 1:
+        run_ours_ep(args, torch, dist, rank, world, local)
+        return
     cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
                     router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16,
                     meta_dtype=fmt.META_BF16, activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32,
@@ -318,8 +321,8 @@ def run_ours(args) -> None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(times[0]), float(times[1])
     ms_per_step = ms / args.steps
-    value = world * tokens / (ms_per_step / 1e3)       # interim multi-GPU mode: independent replicas
-    e2e_value = world * tokens / (e2e_ms / args.steps / 1e3)
+    value = tokens / (ms_per_step / 1e3)
+    e2e_value = tokens / (e2e_ms / args.steps / 1e3)
 
     rec = None
     if rank == 0:
@@ -345,6 +348,126 @@ def run_ours(args) -> None:
         print(json.dumps(rec), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
+    """Expert-parallel stack: 256/world experts per rank, every rank decodes its own
+    `--tokens` rows (weak scaling: one more GPU brings one more decode stream); per layer
+    an all-gather of the rows (dispatch) and an all-to-all of the share rows (combine)
+    over NCCL.  The step, collectives included, is captured as one CUDA graph."""
+    from nvmai_b200 import MoE, MoEConfig, launch_count, synthetic
+    from nvmai_b200 import format as fmt
+    from nvmai_b200.ep import ExpertPlacement, LibraryBackend, ep_stack_step
+    tokens = args.tokens
+    pl = ExpertPlacement(E, world, args.placement)
+    cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
+                    router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16,
+                    meta_dtype=fmt.META_BF16, activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32,
+                    max_tokens=world * tokens, num_layers=args.layers)
+    moe = MoE(cfg)
+    devs = []
+    for l in range(args.layers):
+        # same seed on every rank: router / shared expert / gate are replicas; the local
+        # expert blobs are random bytes whose values do not matter for the timing
+        dev = synthetic.device_layer(1000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits,
+                                     meta=fmt.META_BF16, expert_ids=pl.local_experts(rank))
+        synthetic.register_device_layer(moe, l, dev)
+        devs.append(dev)
+    moe.set_expert_map(pl.expert_map(rank))
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    backend = LibraryBackend(moe, stream=stream)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(42 + rank)
+    n_inputs = 16
+    xs = torch.randn(n_inputs, tokens, D, device="cuda", generator=gen).to(torch.float16)
+    x_in = torch.empty(tokens, D, dtype=torch.float16, device="cuda")
+    y_out = torch.empty(tokens, D, dtype=torch.float32, device="cuda")
+    xs_host = [xs[i].cpu().pin_memory() for i in range(n_inputs)]
+    y_host = torch.empty(tokens, D, dtype=torch.float32).pin_memory()
+
+    def eager_step():
+        y = ep_stack_step(backend, dist, None, x_in, world=world, layers=args.layers)
+        y_out.copy_(y, non_blocking=True)
+
+    graph = None
+    with torch.cuda.stream(stream):
+        x_in.copy_(xs[0])
+        for _ in range(2):
+            eager_step()
+        stream.synchronize()
+        dist.barrier()
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                eager_step()
+            graph = g
+        except Exception as exc:      # capture of the collectives refused: plain launches instead
+            if rank == 0:
+                print(f"[bench] CUDA-graph capture of the expert-parallel step failed ({exc}); running eagerly",
+                      file=sys.stderr)
+            torch.cuda.synchronize()
+
+        def step(i):
+            x_in.copy_(xs[i % n_inputs], non_blocking=True)
+            if graph is not None:
+                graph.replay()
+            else:
+                eager_step()
+
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local) if rank == 0 else None
+        l0 = launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(args.steps):
+            step(i)
+        end.record(stream)
+        dist.barrier()
+        torch.cuda.synchronize()
+        launches = launch_count() - l0
+        ms = start.elapsed_time(end)
+        assert torch.isfinite(y_out).all(), "non-finite output"
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            x_in.copy_(xs_host[i % n_inputs], non_blocking=True)
+            if graph is not None:
+                graph.replay()
+            else:
+                eager_step()
+            y_host.copy_(y_out, non_blocking=True)
+            stream.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        clocks = sampler.stop() if sampler else None
+    times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_per_step = float(times[0]) / args.steps
+    if rank == 0:
+        peak, which = measured_peaks()
+        rec = base_record(args, world)
+        # kernels per layer on the expert-parallel path: router, group, gate/up, down, combine, shared gate/up,
+        # shared down, finalize (+ renorm between layers); graph replays do not pass the library's counter
+        per_step = args.layers * 9 - 1
+        rec.update({"value": world * tokens / (ms_per_step / 1e3), "ms_per_step": ms_per_step, "scaling": "weak",
+                    "dtype": "f16xu%d->f32" % args.bits, "clocks": clocks,
+                    "gpu_launches": int(launches) if graph is None else per_step * args.steps,
+                    "e2e": {"value": world * tokens / (float(times[1]) / args.steps / 1e3), "unit": UNIT,
+                            "h2d_bytes_per_step": tokens * D * 2, "d2h_bytes_per_step": tokens * D * 4},
+                    "roofline": {"bound": "hbm", "kernel": "expert-parallel step (all kernels + 2 collectives per layer)",
+                                 "achieved": args.layers * layer_bytes(args.bits) * tokens / (ms_per_step / 1e3) / 1e9,
+                                 "peak": peak, "peak_source": which, "unit": "GB/s",
+                                 "frac": args.layers * layer_bytes(args.bits) * tokens / (ms_per_step / 1e3) / 1e9 / peak,
+                                 "traffic": None}})
+        rec["config"].update({"parallelism": f"ep{world}", "experts_per_gpu": E // world, "placement": args.placement,
+                              "tokens_per_step": world * tokens, "graph": graph is not None,
+                              "collectives_per_layer": "all_gather(x) + all_to_all(share rows), NCCL"})
+        print(json.dumps(rec), flush=True)
+    dist.destroy_process_group()
 
 
 def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> dict:
@@ -400,6 +523,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -189,6 +189,29 @@ NVMAI_API int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, con
 NVMAI_API int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const void *w_f16, uint32_t tokens,
                                void *sorted_pairs, uint32_t *expert_offsets, uint32_t *expert_counts, void *stream);
 
+/* ---- expert parallelism (no counterpart in the reference, which runs on one GPU) ----
+ * A rank holds n_local of the layer's expert blobs, contiguous at `experts` in
+ * local-index order; map_host[e] = local index of global expert e or 0xFFFFFFFF.
+ * The map is validated (every local index used exactly once). NULL resets. */
+NVMAI_API int nvmai_cuda_moe_set_expert_map(nvmai_cuda_moe *h, const uint32_t *map_host, uint32_t n_local);
+
+/* This rank's share of the routed experts for `tokens` rows that every rank holds:
+ * share[t] = sum over the token's (expert, weight) pairs whose expert is local of
+ * float(w) * down_e(act(gate_e.x) * up_e.x), fp32 rows [tokens][d]; idx / w as the
+ * router wrote them (global expert ids).  Rows of a token with no local expert are
+ * zero.  The shared expert and the residual are the token owner's business. */
+NVMAI_API int nvmai_cuda_moe_routed_partial(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
+                                  const uint32_t *idx, const void *w_f16, float *share_f32, void *stream);
+
+/* Owner side: y = out(h1 + sum_r shares[r]) with the ranks' shares added in rank
+ * order (bitwise reproducible), hidden += y.  shares fp32 [ranks][tokens][d]. */
+NVMAI_API int nvmai_cuda_moe_ep_finalize(nvmai_cuda_moe *h, const float *shares_f32, uint32_t ranks, const void *h1,
+                               uint32_t tokens, void *y, void *hidden_inout, void *stream);
+
+/* x = half(y * rsqrt(mean(y^2) + 1e-6)) per row: the stand-in for the attention +
+ * rmsnorm between two MoE blocks that the stack benchmark uses. */
+NVMAI_API int nvmai_cuda_moe_rms_renorm(nvmai_cuda_moe *h, const void *y, uint32_t tokens, void *x_f16_out, void *stream);
+
 /* Benchmark driver for an FFN-only stack: runs layers 0..num_layers-1 on one
  * token batch; between layers the block output is renormalised to unit RMS in
  * fp32 and rounded to fp16 (a stand-in for the attention + rmsnorm the real model

@@ -56,6 +56,10 @@ PROTOTYPES = {
     "nvmai_cuda_moe_routed_phase2": (C.c_int, [vp, C.POINTER(vp), C.POINTER(ExpertOffsets), vp, vp, vp, vp, vp]),
     "nvmai_cuda_moe_layer_decode": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, vp, vp]),
     "nvmai_cuda_moe_group_pairs": (C.c_int, [vp, vp, vp, u32, vp, vp, vp, vp]),
+    "nvmai_cuda_moe_set_expert_map": (C.c_int, [vp, vp, u32]),
+    "nvmai_cuda_moe_routed_partial": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, vp]),
+    "nvmai_cuda_moe_ep_finalize": (C.c_int, [vp, vp, u32, vp, u32, vp, vp, vp]),
+    "nvmai_cuda_moe_rms_renorm": (C.c_int, [vp, vp, u32, vp, vp]),
     "nvmai_cuda_moe_stack_decode": (C.c_int, [vp, vp, u32, vp, vp]),
     "nvmai_cuda_moe_stack_decode_host": (C.c_int, [vp, vp, u32, vp, vp]),
     "nvmai_cuda_moe_dequant": (C.c_int, [u32, u32, vp, vp, vp, u32, u32, vp, vp]),

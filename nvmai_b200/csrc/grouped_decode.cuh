@@ -35,7 +35,13 @@ struct GroupParams {
     WorkItem *work;               // optional work list
     uint32_t *n_work;             // [2]: routed items, then routed + shared items
     uint32_t shared_chunks;       // ceil(tokens / 8) when a shared expert rides along, else 0
+    // Expert parallelism: global expert id -> index of its blob among the experts this
+    // rank holds, or kNotLocal.  Pairs routed to experts held elsewhere are left out
+    // (inv = kNotLocal).  nullptr: every expert is local and ids are used as they are.
+    const uint32_t *expert_map;
+    uint32_t n_local;             // number of local blobs (E when there is no map)
 };
+constexpr uint32_t kNotLocal = 0xFFFFFFFFu;
 
 constexpr int kGroupThreads = 1024;
 
@@ -49,7 +55,14 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
     pdl_launch_dependents();
     for (int e = tid; e < kMaxExperts; e += kGroupThreads) { hist[e] = 0; running[e] = 0; }
     __syncthreads();
-    for (uint32_t i = tid; i < P; i += kGroupThreads) atomicAdd(&hist[min(p.idx[i], p.E - 1u)], 1u);
+    auto local_of = [&](uint32_t i) -> uint32_t {
+        const uint32_t e = min(p.idx[i], p.E - 1u);
+        return p.expert_map ? p.expert_map[e] : e;
+    };
+    for (uint32_t i = tid; i < P; i += kGroupThreads) {
+        const uint32_t e = local_of(i);
+        if (e != kNotLocal) atomicAdd(&hist[e], 1u);
+    }
     __syncthreads();
     // exclusive scans (pair offsets, work-item offsets) by one warp, 8 experts per lane
     if (warp == 0) {
@@ -75,7 +88,7 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
         }
     }
     __syncthreads();
-    for (uint32_t e = tid; e < p.E; e += kGroupThreads) {
+    for (uint32_t e = tid; e < p.n_local; e += kGroupThreads) {
         p.expert_counts[e] = hist[e];
         p.expert_offsets[e] = hist[e] ? offs[e] : 0xFFFFFFFFu;
         if (p.work != nullptr) {
@@ -97,8 +110,9 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
         for (int i = tid; i < (kGroupThreads / 32) * kMaxExperts; i += kGroupThreads) (&cnt[0][0])[i] = 0;
         __syncthreads();
         const uint32_t i = base + tid;
-        const bool live = i < P;
-        const uint32_t e = live ? min(p.idx[i], p.E - 1u) : 0xFFFFFFFFu;
+        const uint32_t e = i < P ? local_of(i) : kNotLocal;
+        const bool live = e != kNotLocal;
+        if (i < P && !live) p.inv[i] = kNotLocal;
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         const uint32_t rank_in_warp = __popc(peers & ((1u << lane) - 1u));
         if (live && rank_in_warp == 0) cnt[warp][e] = (uint16_t)__popc(peers);
@@ -115,7 +129,7 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
             }
         }
         __syncthreads();
-        for (uint32_t ee = tid; ee < p.E; ee += kGroupThreads) {
+        for (uint32_t ee = tid; ee < p.n_local; ee += kGroupThreads) {
             uint32_t tot = 0;
             for (int w = 0; w < kGroupThreads / 32; ++w) tot += cnt[w][ee];
             running[ee] += tot;
@@ -412,6 +426,7 @@ struct CombineParams {
     const uint32_t *inv; const __half *routing_w; const float *gate_val;
     const void *residual;
     void *y; void *hidden;
+    float *partial_y;      // expert parallelism: this rank's share sum_r w[t,r]*partial (local pairs only), fp32, nothing else
     uint32_t D, K;
 };
 
@@ -427,6 +442,15 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
         wk[threadIdx.x] = __half2float(p.routing_w[tok * p.K + threadIdx.x]);
     }
     __syncthreads();
+    if (p.partial_y != nullptr) {
+        for (uint32_t d = threadIdx.x; d < p.D; d += blockDim.x) {
+            float acc = 0.0f;
+            for (uint32_t r = 0; r < p.K; ++r)
+                if (pos[r] != kNotLocal) acc += wk[r] * p.partial[(size_t)pos[r] * p.D + d];
+            p.partial_y[(size_t)tok * p.D + d] = acc;
+        }
+        return;
+    }
     for (uint32_t d = threadIdx.x; d < p.D; d += blockDim.x) {
         const size_t i = (size_t)tok * p.D + d;
         float acc;
@@ -438,6 +462,27 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
             acc = p.residual != nullptr ? load_out<OUT>(p.residual, i) : 0.0f;
         }
         for (uint32_t r = 0; r < p.K; ++r) acc += wk[r] * p.partial[(size_t)pos[r] * p.D + d];
+        const float yv = round_out<OUT>(acc);
+        if (p.y != nullptr) store_out<OUT>(p.y, i, yv);
+        if (p.hidden != nullptr) store_out<OUT>(p.hidden, i, load_out<OUT>(p.hidden, i) + yv);
+    }
+}
+
+// Expert parallelism, owner side: y[t] = out(h1[t] + sum over ranks of that rank's
+// share, in rank order), hidden += y.  shares: [ranks][tokens][D] fp32.
+struct EpFinalizeParams {
+    const float *shares; uint32_t ranks;
+    const void *h1;        // out dtype [tokens][D] or nullptr
+    void *y; void *hidden;
+    uint32_t tokens, D;
+};
+
+template <int OUT>
+__global__ void __launch_bounds__(256) ep_finalize_kernel(EpFinalizeParams p) {
+    const size_t n = (size_t)p.tokens * p.D;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = p.h1 != nullptr ? load_out<OUT>(p.h1, i) : 0.0f;
+        for (uint32_t r = 0; r < p.ranks; ++r) acc += p.shares[(size_t)r * n + i];
         const float yv = round_out<OUT>(acc);
         if (p.y != nullptr) store_out<OUT>(p.y, i, yv);
         if (p.hidden != nullptr) store_out<OUT>(p.hidden, i, load_out<OUT>(p.hidden, i) + yv);

@@ -56,6 +56,8 @@ struct nvmai_cuda_moe {
     float *partial = nullptr;        // [T*K][D]
     float *shared_partial = nullptr; // [T][D]
     uint32_t max_work = 0;
+    uint32_t *expert_map = nullptr;  // expert parallelism: global id -> local blob index (device), or null
+    uint32_t n_local = 0;
     // optional kernel timeline (the counterpart of the reference's NVMAI_KERNEL_STATS)
     unsigned long long *trace = nullptr;   // [num_layers][3 stages][start, end]
     bool trace_on = false;
@@ -285,7 +287,7 @@ constexpr uint32_t kGroupedMinTokens = 4;   // below this every token runs its o
 
 int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, uint32_t tokens,
                        TokenExpertPair *pairs_out, uint32_t *offsets_out, uint32_t *counts_out, bool with_work,
-                       bool pdl, cudaStream_t st) {
+                       bool pdl, cudaStream_t st, bool with_shared = true, bool use_map = false) {
     const auto &c = h->cfg;
     GroupParams g{};
     g.idx = idx; g.weights = w; g.tokens = tokens; g.K = c.top_k; g.E = c.num_experts;
@@ -295,20 +297,24 @@ int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, 
     g.pairs_out = pairs_out;
     g.work = with_work ? h->work : nullptr;
     g.n_work = h->n_work;
-    g.shared_chunks = (with_work && c.shared_f) ? (tokens + kPairsPerItem - 1) / kPairsPerItem : 0;
+    g.shared_chunks = (with_work && with_shared && c.shared_f) ? (tokens + kPairsPerItem - 1) / kPairsPerItem : 0;
+    g.expert_map = use_map ? h->expert_map : nullptr;
+    g.n_local = (use_map && h->expert_map) ? h->n_local : c.num_experts;
     return launch_kernel(h, group_pairs_kernel, dim3(1), dim3(kGroupThreads), 0, st, pdl, g);
 }
 
 // Batched tail of a layer: group pairs by expert, gate/up and down per (tile, work
 // item), then the per-token weighted sum in rank order.
+// partial_y != nullptr: expert-parallel share (local experts only, no shared expert, fp32 rows out).
 int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, uint32_t tokens, const uint32_t *idx,
-                 const __half *w, void *hidden, void *y, cudaStream_t st) {
+                 const __half *w, void *hidden, void *y, cudaStream_t st, float *partial_y = nullptr) {
     const auto &c = h->cfg;
-    int rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st);
+    const bool ep = partial_y != nullptr;
+    int rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, !ep, st, !ep, ep);
     if (rc) return rc;
     const uint32_t P = tokens * c.top_k;
     const uint32_t routed_bound = std::min(P, c.num_experts + P / kPairsPerItem);
-    const uint32_t shared_chunks = c.shared_f ? (tokens + kPairsPerItem - 1) / kPairsPerItem : 0;
+    const uint32_t shared_chunks = (c.shared_f && !ep) ? (tokens + kPairsPerItem - 1) / kPairsPerItem : 0;
     GroupedStage2Params p2{};
     p2.experts = static_cast<const uint8_t *>(lv.w.experts); p2.stride = lv.w.expert_stride; p2.num_experts = c.num_experts;
     p2.off = to_offsets(lv.w.offsets);
@@ -344,10 +350,11 @@ int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, 
     });
     if (rc) return rc;
     CombineParams pc{};
-    pc.partial = h->partial; pc.shared_partial = c.shared_f ? h->shared_partial : nullptr;
+    pc.partial = h->partial; pc.shared_partial = (c.shared_f && !ep) ? h->shared_partial : nullptr;
     pc.inv = h->inv; pc.routing_w = w;
     pc.gate_val = (c.shared_f && c.shared_gate_kind != NVMAI_GATE_NONE) ? h->gate_val : nullptr;
     pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
+    pc.partial_y = partial_y;
     return dispatch_out(c.out_dtype, [&](auto O) {
         return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
     });
@@ -472,7 +479,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
         if (c.shared_f) need = std::max(need, GateUpLayout(c.d, c.shared_bits).total);
         const uint32_t warps = (c.top_k < (uint32_t)kMaxTopK ? c.top_k : (uint32_t)kMaxTopK) + (c.shared_f ? 1 : 0);
         need = std::max(need, DownLayout(c.f, c.shared_f, c.routed_bits, c.shared_bits, warps).total);
-        if (c.max_tokens >= kGroupedMinTokens) {
+        {
             need = std::max(need, GroupedGateUpLayout(c.d, c.routed_bits).total);
             if (c.shared_f) need = std::max(need, GroupedGateUpLayout(c.d, c.shared_bits).total);
             need = std::max(need, GroupedDownLayout(c.f, c.shared_f, c.routed_bits, c.shared_bits).total);
@@ -505,7 +512,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
                      alloc(&h->expert_counts, kMaxExperts * 4) && alloc(&h->work, (size_t)h->max_work * sizeof(WorkItem)) &&
                      alloc(&h->n_work, 16) && alloc(&h->trace, (size_t)c.num_layers * 3 * kTraceWords * sizeof(unsigned long long));
         // per-pair partial rows are only needed by the batched path
-        if (ok && T >= kGroupedMinTokens)
+        if (ok)
             ok = alloc(&h->partial, P * c.d * sizeof(float)) && alloc(&h->shared_partial, T * c.d * sizeof(float));
     }
     if (!ok) {
@@ -525,7 +532,7 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y);
     cudaFree(h->sorted_pair); cudaFree(h->inv); cudaFree(h->expert_offsets); cudaFree(h->expert_counts);
-    cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->trace); cudaFree(h->partial); cudaFree(h->shared_partial);
+    cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->trace); cudaFree(h->expert_map); cudaFree(h->partial); cudaFree(h->shared_partial);
     delete h;
 }
 
@@ -661,6 +668,64 @@ int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const voi
     return launch_group_pairs(h, idx, static_cast<const __half *>(w_f16), tokens,
                               static_cast<TokenExpertPair *>(sorted_pairs), expert_offsets, expert_counts, false, false,
                               static_cast<cudaStream_t>(stream));
+}
+
+int nvmai_cuda_moe_set_expert_map(nvmai_cuda_moe *h, const uint32_t *map_host, uint32_t n_local) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    const auto &c = h->cfg;
+    if (map_host == nullptr) {              // back to "every expert is local"
+        cudaFree(h->expert_map);
+        h->expert_map = nullptr;
+        h->n_local = 0;
+        return NVMAI_CUDA_OK;
+    }
+    if (n_local == 0 || n_local > c.num_experts) return NVMAI_CUDA_ERANGE;
+    uint32_t seen = 0;
+    for (uint32_t e = 0; e < c.num_experts; ++e) {
+        if (map_host[e] == kNotLocal) continue;
+        if (map_host[e] >= n_local) return NVMAI_CUDA_ERANGE;
+        ++seen;
+    }
+    if (seen != n_local) return NVMAI_CUDA_EINVAL;     // a bad placement map is rejected, not trusted
+    if (!h->expert_map) {
+        int rc = record(h, cudaMalloc(reinterpret_cast<void **>(&h->expert_map), kMaxExperts * sizeof(uint32_t)));
+        if (rc) return NVMAI_CUDA_ENOMEM;
+    }
+    h->n_local = n_local;
+    return record(h, cudaMemcpy(h->expert_map, map_host, c.num_experts * sizeof(uint32_t), cudaMemcpyHostToDevice));
+}
+
+int nvmai_cuda_moe_routed_partial(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
+                                  const uint32_t *idx, const void *w_f16, float *share_f32, void *stream) {
+    int rc = check_layer(h, layer);
+    if (rc) return rc;
+    if (!x_f16 || !idx || !w_f16 || !share_f32 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
+    if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
+    return grouped_tail(h, h->layers[layer], static_cast<const __half *>(x_f16), tokens, idx,
+                        static_cast<const __half *>(w_f16), nullptr, nullptr, static_cast<cudaStream_t>(stream),
+                        share_f32);
+}
+
+int nvmai_cuda_moe_ep_finalize(nvmai_cuda_moe *h, const float *shares_f32, uint32_t ranks, const void *h1,
+                               uint32_t tokens, void *y, void *hidden_inout, void *stream) {
+    if (!h || !shares_f32 || ranks == 0 || tokens == 0) return NVMAI_CUDA_EINVAL;
+    EpFinalizeParams p{shares_f32, ranks, h1, y, hidden_inout, tokens, h->cfg.d};
+    const size_t n = (size_t)tokens * h->cfg.d;
+    const unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 1184);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dispatch_out(h->cfg.out_dtype, [&](auto O) {
+        return launch_kernel(h, ep_finalize_kernel<decltype(O)::value>, dim3(blocks), dim3(256), 0, st, false, p);
+    });
+}
+
+int nvmai_cuda_moe_rms_renorm(nvmai_cuda_moe *h, const void *y, uint32_t tokens, void *x_f16_out, void *stream) {
+    if (!h || !y || !x_f16_out || tokens == 0) return NVMAI_CUDA_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (h->cfg.out_dtype == NVMAI_OUT_FP16)
+        rms_renorm_kernel<OUT_F16><<<tokens, 256, 0, st>>>(y, static_cast<__half *>(x_f16_out), h->cfg.d);
+    else
+        rms_renorm_kernel<OUT_F32><<<tokens, 256, 0, st>>>(y, static_cast<__half *>(x_f16_out), h->cfg.d);
+    return check_launch(h);
 }
 
 static int stack_enqueue(nvmai_cuda_moe *h, const __half *x0, uint32_t tokens, void *y_last, cudaStream_t st) {

@@ -145,6 +145,27 @@ class MoE:
                                                    _ptr(expert_offsets), _ptr(expert_counts), _stream(stream)),
               "group_pairs")
 
+    # -- expert parallelism --------------------------------------------------------------
+    def set_expert_map(self, expert_map) -> None:
+        """expert_map[e] = index of global expert e among this rank's blobs, or 0xFFFFFFFF."""
+        if expert_map is None:
+            check(self._lib.nvmai_cuda_moe_set_expert_map(self._h, None, 0), "set_expert_map")
+            return
+        arr = (C.c_uint32 * len(expert_map))(*[int(v) for v in expert_map])
+        n_local = sum(1 for v in expert_map if int(v) != 0xFFFFFFFF)
+        check(self._lib.nvmai_cuda_moe_set_expert_map(self._h, arr, n_local), "set_expert_map")
+
+    def routed_partial(self, layer: int, x, tokens: int, idx, w, share, *, stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_routed_partial(self._h, layer, _ptr(x), tokens, _ptr(idx), _ptr(w), _ptr(share),
+                                                      _stream(stream)), "routed_partial")
+
+    def ep_finalize(self, shares, ranks: int, h1, tokens: int, *, y=None, hidden=None, stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_ep_finalize(self._h, _ptr(shares), ranks, _ptr(h1), tokens, _ptr(y), _ptr(hidden),
+                                                   _stream(stream)), "ep_finalize")
+
+    def rms_renorm(self, y, tokens: int, x_out, *, stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_rms_renorm(self._h, _ptr(y), tokens, _ptr(x_out), _stream(stream)), "rms_renorm")
+
     # -- fused paths ----------------------------------------------------------------
     def layer_decode(self, layer: int, x, tokens: int, *, hidden=None, h2_out=None, out_idx=None, out_w=None,
                      stream=None) -> None:

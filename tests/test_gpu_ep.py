@@ -1,0 +1,92 @@
+"""Expert-parallel layer on 2 GPUs (NCCL) through the C ABI against the single-rank
+oracle.  Needs two devices; skipped on a one-GPU box."""
+import os
+import sys
+import traceback
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+for p_ in (ROOT, ROOT / "tests"):
+    if str(p_) not in sys.path:
+        sys.path.insert(0, str(p_))
+
+pytestmark = pytest.mark.gpu
+
+D, F, E, K, B_OWN = 256, 128, 32, 8, 3
+
+
+def _cfg(tokens):
+    from nvmai_b200 import MoEConfig
+    from nvmai_b200 import format as fmt
+    return MoEConfig(d=D, f=F, shared_f=F, num_experts=E, top_k=K, routed_bits=8, shared_bits=8,
+                     router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16, meta_dtype=fmt.META_FP16,
+                     out_dtype=fmt.OUT_FP32, max_tokens=tokens)
+
+
+def _rank_main(rank, world, port, out_dir):
+    try:
+        import torch
+        import torch.distributed as dist
+        import gpu_util as gu
+        from nvmai_b200 import MoE, synthetic
+        from nvmai_b200 import format as fmt
+        from nvmai_b200.ep import ExpertPlacement, LibraryBackend, ep_layer_step
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        host = synthetic.layer(901, d=D, f=F, shared_f=F, num_experts=E, routed_bits=8, meta=fmt.META_FP16)
+        pl = ExpertPlacement(E, world, "strided")
+        local = dict(host)
+        local["experts"] = np.ascontiguousarray(host["experts"][pl.local_experts(rank)])   # only this rank's blobs
+        moe = MoE(_cfg(world * B_OWN))
+        dl = gu.DeviceLayer(local)
+        dl.register(moe, 0)
+        moe.set_expert_map(pl.expert_map(rank))
+        x_all = synthetic.hidden_rows(902, world * B_OWN, D)
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            x_own = gu.to_dev(x_all[rank * B_OWN:(rank + 1) * B_OWN].copy()).view(torch.float16)
+            y = ep_layer_step(LibraryBackend(moe, stream=st), dist, None, 0, x_own, world=world)
+            st.synchronize()
+        np.save(os.path.join(out_dir, f"y{rank}.npy"), y.cpu().numpy())
+        dist.destroy_process_group()
+    except Exception:
+        with open(os.path.join(out_dir, f"err{rank}.txt"), "w") as f:
+            f.write(traceback.format_exc())
+        sys.exit(3)
+
+
+def test_two_gpu_expert_parallel_layer_matches_oracle(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    import gpu_util as gu
+    from nvmai_b200 import synthetic
+    from nvmai_b200 import format as fmt
+    from oracle import oracle as orc
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, 29561, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        if p.is_alive():
+            p.kill()
+            p.join()
+    errs = [p.read_text() for p in tmp_path.glob("err*.txt")]
+    assert [p.exitcode for p in procs] == [0, 0], errs
+    host = synthetic.layer(901, d=D, f=F, shared_f=F, num_experts=E, routed_bits=8, meta=fmt.META_FP16)
+    cfg = _cfg(2 * B_OWN)
+    L, keep = gu.oracle_layer(host, cfg)
+    x_all = synthetic.hidden_rows(902, 2 * B_OWN, D)
+    for rank in range(2):
+        y = np.load(tmp_path / f"y{rank}.npy")
+        for j in range(B_OWN):
+            o_idx, _, want, _, cpu = gu.oracle_decode(L, cfg, np.ascontiguousarray(x_all[rank * B_OWN + j]))
+            assert orc.rel_error(y[j], cpu) < 1e-3
+            assert orc.rel_error(y[j], want) < 5e-4
