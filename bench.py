@@ -254,7 +254,12 @@ def run_ours(args) -> None:
 
     tokens = args.tokens
     if world > 1:
+        # a stuck collective would otherwise hold the GPUs until someone kills the job
+        killer = threading.Timer(args.deadline, lambda: os._exit(2))
+        killer.daemon = True
+        killer.start()
         run_ours_ep(args, torch, dist, rank, world, local)
+        killer.cancel()
         return
     cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
                     router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16,
@@ -397,16 +402,12 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
             eager_step()
         stream.synchronize()
         dist.barrier()
-        try:
+        if args.ep_graph:
+            # thread-local capture mode: NCCL's watchdog thread may touch CUDA while this thread captures
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
                 eager_step()
             graph = g
-        except Exception as exc:      # capture of the collectives refused: plain launches instead
-            if rank == 0:
-                print(f"[bench] CUDA-graph capture of the expert-parallel step failed ({exc}); running eagerly",
-                      file=sys.stderr)
-            torch.cuda.synchronize()
 
         def step(i):
             x_in.copy_(xs[i % n_inputs], non_blocking=True)
@@ -524,6 +525,10 @@ def main() -> None:
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
+    ap.add_argument("--ep-graph", action="store_true",
+                    help="expert-parallel runs: capture the step (kernels + NCCL collectives) as one CUDA graph")
+    ap.add_argument("--deadline", type=float, default=600.0,
+                    help="multi-GPU runs: give up (exit 2) after this many seconds instead of waiting on a stuck collective")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
