@@ -359,7 +359,8 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
     """Expert-parallel stack: 256/world experts per rank, every rank decodes its own
     `--tokens` rows (weak scaling: one more GPU brings one more decode stream); per layer
     an all-gather of the rows (dispatch) and an all-to-all of the share rows (combine)
-    over NCCL.  The step, collectives included, is captured as one CUDA graph."""
+    over NCCL, issued by the library on its own communicator and replayed with the
+    kernels as one CUDA graph."""
     from nvmai_b200 import MoE, MoEConfig, launch_count, synthetic
     from nvmai_b200 import format as fmt
     from nvmai_b200.ep import ExpertPlacement, LibraryBackend, ep_stack_step
@@ -391,30 +392,39 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
     xs_host = [xs[i].cpu().pin_memory() for i in range(n_inputs)]
     y_host = torch.empty(tokens, D, dtype=torch.float32).pin_memory()
 
-    def eager_step():
-        y = ep_stack_step(backend, dist, None, x_in, world=world, layers=args.layers)
-        y_out.copy_(y, non_blocking=True)
+    t_begin = time.perf_counter()
 
-    graph = None
+    def note(msg):      # progress on stderr: tells where a stuck multi-GPU run stopped
+        if args.verbose:
+            print(f"[rank {rank} +{time.perf_counter() - t_begin:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
+    native = args.ep_driver == "native"
+    note("weights resident")
+    if native:
+        # the library's own communicator: compute and both collectives of all layers replay as one CUDA graph
+        ids = [moe.ep_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        moe.ep_init(ids[0], rank, world, tokens)
+
+        def run_step():
+            moe.ep_stack_decode(x_in, tokens, y_out, stream=stream)
+    else:
+        # torch.distributed collectives around the library's per-stage calls, plain launches
+        def run_step():
+            y = ep_stack_step(backend, dist, None, x_in, world=world, layers=args.layers)
+            y_out.copy_(y, non_blocking=True)
+
     with torch.cuda.stream(stream):
         x_in.copy_(xs[0])
-        for _ in range(2):
-            eager_step()
-        stream.synchronize()
+        for call in range(3):       # plain launches, graph capture, first replay
+            run_step()
+            stream.synchronize()
+            note(f"step call {call} done")
         dist.barrier()
-        if args.ep_graph:
-            # thread-local capture mode: NCCL's watchdog thread may touch CUDA while this thread captures
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
-                eager_step()
-            graph = g
 
         def step(i):
             x_in.copy_(xs[i % n_inputs], non_blocking=True)
-            if graph is not None:
-                graph.replay()
-            else:
-                eager_step()
+            run_step()
 
         for i in range(max(args.warmup, 3)):
             step(i)
@@ -431,14 +441,12 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
         torch.cuda.synchronize()
         launches = launch_count() - l0
         ms = start.elapsed_time(end)
+        note(f"timed region done: {ms / args.steps:.3f} ms/step")
         assert torch.isfinite(y_out).all(), "non-finite output"
         t0 = time.perf_counter()
         for i in range(args.steps):
             x_in.copy_(xs_host[i % n_inputs], non_blocking=True)
-            if graph is not None:
-                graph.replay()
-            else:
-                eager_step()
+            run_step()
             y_host.copy_(y_out, non_blocking=True)
             stream.synchronize()
         dist.barrier()
@@ -452,11 +460,10 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
         peak, which = measured_peaks()
         rec = base_record(args, world)
         # kernels per layer on the expert-parallel path: router, group, gate/up, down, combine, shared gate/up,
-        # shared down, finalize (+ renorm between layers); graph replays do not pass the library's counter
-        per_step = args.layers * 9 - 1
+        # shared down, finalize (+ renorm between layers); the library counts them, replays included
         rec.update({"value": world * tokens / (ms_per_step / 1e3), "ms_per_step": ms_per_step, "scaling": "weak",
                     "dtype": "f16xu%d->f32" % args.bits, "clocks": clocks,
-                    "gpu_launches": int(launches) if graph is None else per_step * args.steps,
+                    "gpu_launches": int(launches),
                     "e2e": {"value": world * tokens / (float(times[1]) / args.steps / 1e3), "unit": UNIT,
                             "h2d_bytes_per_step": tokens * D * 2, "d2h_bytes_per_step": tokens * D * 4},
                     "roofline": {"bound": "hbm", "kernel": "expert-parallel step (all kernels + 2 collectives per layer)",
@@ -465,10 +472,18 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
                                  "frac": args.layers * layer_bytes(args.bits) * tokens / (ms_per_step / 1e3) / 1e9 / peak,
                                  "traffic": None}})
         rec["config"].update({"parallelism": f"ep{world}", "experts_per_gpu": E // world, "placement": args.placement,
-                              "tokens_per_step": world * tokens, "graph": graph is not None,
+                              "tokens_per_step": world * tokens, "graph": native,
+                              "ep_driver": args.ep_driver,
                               "collectives_per_layer": "all_gather(x) + all_to_all(share rows), NCCL"})
         print(json.dumps(rec), flush=True)
+    note("end-to-end region done")
+    dist.barrier()
+    torch.cuda.synchronize()
+    if native:
+        moe.ep_shutdown()       # every rank, with nothing in flight
+    note("communicator closed")
     dist.destroy_process_group()
+    note("process group closed")
 
 
 def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> dict:
@@ -525,8 +540,10 @@ def main() -> None:
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
-    ap.add_argument("--ep-graph", action="store_true",
-                    help="expert-parallel runs: capture the step (kernels + NCCL collectives) as one CUDA graph")
+    ap.add_argument("--ep-driver", default="native", choices=["native", "torch"],
+                    help="expert-parallel runs: the library's own communicator and CUDA graph (native), or "
+                         "torch.distributed collectives around per-stage calls with plain launches (torch)")
+    ap.add_argument("--verbose", action="store_true", help="progress lines on stderr")
     ap.add_argument("--deadline", type=float, default=600.0,
                     help="multi-GPU runs: give up (exit 2) after this many seconds instead of waiting on a stuck collective")
     args = ap.parse_args()

@@ -212,6 +212,28 @@ NVMAI_API int nvmai_cuda_moe_ep_finalize(nvmai_cuda_moe *h, const float *shares_
  * rmsnorm between two MoE blocks that the stack benchmark uses. */
 NVMAI_API int nvmai_cuda_moe_rms_renorm(nvmai_cuda_moe *h, const void *y, uint32_t tokens, void *x_f16_out, void *stream);
 
+/* Expert parallelism with the exchange inside the library (no counterpart in the
+ * reference, which runs on one GPU): the library opens its own NCCL communicator
+ * (libnccl.so.2, resolved at run time; NVMAI_CUDA_ENCCL when it is missing or a call
+ * fails).  One rank obtains an id, the host's launcher hands the 128 bytes to every
+ * rank, and every rank calls ep_init (collective, blocking) after set_expert_map and
+ * before ep_stack_decode.  world * rows_own must fit max_tokens. */
+#define NVMAI_CUDA_EP_ID_BYTES 128
+NVMAI_API int nvmai_cuda_moe_ep_unique_id(void *id_out_host);
+NVMAI_API int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank, uint32_t world,
+                                     uint32_t rows_own);
+NVMAI_API int nvmai_cuda_moe_ep_shutdown(nvmai_cuda_moe *h);
+
+/* The FFN-only stack of the benchmark, sharded by experts: this rank's rows in
+ * (fp16 [rows_own][d]), the last layer's block output for them out (out_dtype).
+ * Per layer: shared expert on the own rows, all-gather of the rows, router on all
+ * rows, local experts' shares, all-to-all of the shares to the rows' owners, rank-
+ * ordered sum + shared expert, RMS renormalisation.  Every rank must call it with the
+ * same rows_own, the same number of times.  The first call per (x, y, rows, stream)
+ * issues plain launches, the second captures a CUDA graph, later ones replay it. */
+NVMAI_API int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uint32_t rows_own, void *y_own,
+                                             void *stream);
+
 /* Benchmark driver for an FFN-only stack: runs layers 0..num_layers-1 on one
  * token batch; between layers the block output is renormalised to unit RMS in
  * fp32 and rounded to fp16 (a stand-in for the attention + rmsnorm the real model

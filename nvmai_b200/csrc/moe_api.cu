@@ -15,6 +15,7 @@
 #include <tuple>
 #include <vector>
 
+#include "ep_comm.cuh"
 #include "grouped_decode.cuh"
 #include "misc_kernels.cuh"
 
@@ -66,7 +67,16 @@ struct nvmai_cuda_moe {
     void *stage_x = nullptr;        // host-call staging: [T][D] fp16
     void *stage_y = nullptr;        // host-call staging: [T][D] out_dtype
     std::map<StackGraphKey, cudaGraphExec_t> stack_graphs;
-    bool graphs_stale = false;
+    bool graphs_stale = false, ep_graphs_stale = false;
+    // expert parallelism over NCCL: communicator and exchange buffers
+    NcclComm ep_comm = nullptr;
+    uint32_t ep_rank = 0, ep_world = 0, ep_rows_own = 0;
+    __half *ep_x_all = nullptr;      // [world * rows_own][D]: every rank's rows, in rank order
+    float *ep_share = nullptr;       // [world * rows_own][D]: this rank's share of every row
+    float *ep_recv = nullptr;        // [world][rows_own][D]: every rank's share of this rank's rows
+    void *ep_h1 = nullptr;           // [rows_own][D] out_dtype: shared expert of this rank's rows
+    struct EpGraph { cudaGraphExec_t exec = nullptr; uint32_t calls = 0; };
+    std::map<StackGraphKey, EpGraph> ep_graphs;
 };
 
 namespace {
@@ -281,6 +291,32 @@ int check_layer(const nvmai_cuda_moe *h, uint32_t layer) {
     if (layer >= h->layers.size()) return NVMAI_CUDA_ERANGE;
     if (!h->layers[layer].registered) return NVMAI_CUDA_EINVAL;
     return NVMAI_CUDA_OK;
+}
+
+// The shared expert alone: gate/up tiles + gate row, then its down projection.
+int shared_expert_impl(nvmai_cuda_moe *h, const LayerViews &lv, const XSource &xsrc, uint32_t tokens, void *h1,
+                       cudaStream_t st) {
+    const auto &c = h->cfg;
+    int rc = launch_stage1(h, lv, xsrc, tokens, nullptr, nullptr, false, true, true, false, st);
+    if (rc) return rc;
+    Stage3Params p{};
+    p.sdown = to_mat(lv.w.shared_down_proj);
+    p.shared_f = c.shared_f;
+    p.shared_bits = c.shared_bits;
+    p.shared_act = h->shared_act;
+    p.gate_val = c.shared_gate_kind != NVMAI_GATE_NONE ? h->gate_val : nullptr;
+    p.y = h1;
+    p.top_k = 0;
+    return launch_stage3(h, p, tokens, false, st);
+}
+
+void ep_release(nvmai_cuda_moe *h) {
+    for (auto &kv : h->ep_graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    h->ep_graphs.clear();
+    if (h->ep_comm) { nccl_api().CommDestroy(h->ep_comm); h->ep_comm = nullptr; }
+    cudaFree(h->ep_x_all); cudaFree(h->ep_share); cudaFree(h->ep_recv); cudaFree(h->ep_h1);
+    h->ep_x_all = nullptr; h->ep_share = nullptr; h->ep_recv = nullptr; h->ep_h1 = nullptr;
+    h->ep_world = h->ep_rows_own = 0;
 }
 
 constexpr uint32_t kGroupedMinTokens = 4;   // below this every token runs its own blocks
@@ -528,6 +564,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
 void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     if (!h) return;
     for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
+    ep_release(h);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y);
@@ -558,7 +595,7 @@ int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, const nvmai
     if (wts->effective_scale && !aligned16(wts->effective_scale)) return NVMAI_CUDA_EINVAL;
     h->layers[layer].w = *wts;
     h->layers[layer].registered = true;
-    h->graphs_stale = true;
+    h->graphs_stale = h->ep_graphs_stale = true;
     return NVMAI_CUDA_OK;
 }
 
@@ -582,20 +619,8 @@ int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *
     if (c.shared_f == 0 || !x_f16 || !h1 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
     if (x_stride < c.d || (x_stride % 8) != 0) return NVMAI_CUDA_EINVAL;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const LayerViews &lv = h->layers[layer];
     const XSource xsrc{static_cast<const __half *>(x_f16), x_stride, nullptr, nullptr};
-    rc = launch_stage1(h, lv, xsrc, tokens, nullptr, nullptr, false, true, true, false, st);
-    if (rc) return rc;
-    Stage3Params p{};
-    p.sdown = to_mat(lv.w.shared_down_proj);
-    p.shared_f = c.shared_f;
-    p.shared_bits = c.shared_bits;
-    p.shared_act = h->shared_act;
-    p.gate_val = c.shared_gate_kind != NVMAI_GATE_NONE ? h->gate_val : nullptr;
-    p.y = h1;
-    p.top_k = 0;
-    return launch_stage3(h, p, tokens, false, st);
+    return shared_expert_impl(h, h->layers[layer], xsrc, tokens, h1, static_cast<cudaStream_t>(stream));
 }
 
 int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_host,
@@ -801,6 +826,130 @@ int nvmai_cuda_moe_stack_decode_host(nvmai_cuda_moe *h, const void *x0_f16_host,
                                    cudaMemcpyDeviceToHost, st));
     if (rc) return rc;
     return record(h, cudaStreamSynchronize(st));
+}
+
+// ---- expert parallelism: the whole step inside the library -------------------
+// The exchange runs on a communicator of the library's own, so that the compute
+// launches and both collectives of all layers sit in one stream and replay as one
+// CUDA graph (NCCL supports stream capture of its own calls).
+
+int nvmai_cuda_moe_ep_unique_id(void *id_out_host) {
+    if (!id_out_host) return NVMAI_CUDA_EINVAL;
+    const NcclApi &nccl = nccl_api();
+    if (!nccl.ok) return NVMAI_CUDA_ENCCL;
+    NcclUniqueId id;
+    if (nccl.GetUniqueId(&id) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
+    std::memcpy(id_out_host, &id, sizeof(id));
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank, uint32_t world, uint32_t rows_own) {
+    if (!h || !id_host || world == 0 || rank >= world || rows_own == 0) return NVMAI_CUDA_EINVAL;
+    const auto &c = h->cfg;
+    if ((uint64_t)world * rows_own > c.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (c.num_experts % world != 0) return NVMAI_CUDA_EINVAL;
+    const NcclApi &nccl = nccl_api();
+    if (!nccl.ok) return NVMAI_CUDA_ENCCL;
+    ep_release(h);
+    const size_t rows = (size_t)world * rows_own;
+    auto alloc = [&](auto **ptr, size_t bytes) { return cudaMalloc(reinterpret_cast<void **>(ptr), bytes) == cudaSuccess; };
+    if (!(alloc(&h->ep_x_all, rows * c.d * 2) && alloc(&h->ep_share, rows * c.d * 4) &&
+          alloc(&h->ep_recv, rows * c.d * 4) && alloc(&h->ep_h1, (size_t)rows_own * c.d * out_size(c.out_dtype)))) {
+        cudaGetLastError();
+        ep_release(h);
+        return NVMAI_CUDA_ENOMEM;
+    }
+    NcclUniqueId id;
+    std::memcpy(&id, id_host, sizeof(id));
+    if (nccl.CommInitRank(&h->ep_comm, (int)world, id, (int)rank) != kNcclSuccess) {
+        h->ep_comm = nullptr;
+        ep_release(h);
+        return NVMAI_CUDA_ENCCL;
+    }
+    h->ep_rank = rank; h->ep_world = world; h->ep_rows_own = rows_own;
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_ep_shutdown(nvmai_cuda_moe *h) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    ep_release(h);
+    return NVMAI_CUDA_OK;
+}
+
+static int ep_stack_enqueue(nvmai_cuda_moe *h, const __half *x_own, uint32_t rows_own, void *y_own, cudaStream_t st) {
+    const auto &c = h->cfg;
+    const NcclApi &nccl = nccl_api();
+    const uint32_t world = h->ep_world, rows = world * rows_own;
+    const size_t own_elems = (size_t)rows_own * c.d;
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+        const LayerViews &lv = h->layers[l];
+        const bool last = l + 1 == c.num_layers;
+        const __half *x = l == 0 ? x_own : h->xnorm;
+        int rc;
+        if (c.shared_f) {      // needs this rank's rows only
+            const XSource own{x, c.d, nullptr, nullptr};
+            if ((rc = shared_expert_impl(h, lv, own, rows_own, h->ep_h1, st))) return rc;
+        }
+        if (nccl.AllGather(x, h->ep_x_all, own_elems, kNcclFloat16, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
+        const XSource all{h->ep_x_all, c.d, nullptr, nullptr};
+        if ((rc = launch_stage1(h, lv, all, rows, h->idx, h->w, true, false, false, false, st))) return rc;
+        if ((rc = grouped_tail(h, lv, h->ep_x_all, rows, h->idx, h->w, nullptr, nullptr, st, h->ep_share))) return rc;
+        bool ok = nccl.GroupStart() == kNcclSuccess;      // all-to-all: block r of my shares -> rank r
+        for (uint32_t r = 0; r < world && ok; ++r) {
+            ok = nccl.Send(h->ep_share + r * own_elems, own_elems, kNcclFloat32, (int)r, h->ep_comm, st) == kNcclSuccess &&
+                 nccl.Recv(h->ep_recv + r * own_elems, own_elems, kNcclFloat32, (int)r, h->ep_comm, st) == kNcclSuccess;
+        }
+        const bool ended = nccl.GroupEnd() == kNcclSuccess;
+        if (!ok || !ended) return NVMAI_CUDA_ENCCL;
+        void *y = last ? y_own : h->y;
+        if ((rc = nvmai_cuda_moe_ep_finalize(h, h->ep_recv, world, c.shared_f ? h->ep_h1 : nullptr, rows_own, y, nullptr, st)))
+            return rc;
+        if (!last && (rc = nvmai_cuda_moe_rms_renorm(h, y, rows_own, h->xnorm, st))) return rc;
+    }
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uint32_t rows_own, void *y_own, void *stream) {
+    if (!h || !x_own_f16 || !y_own || !aligned16(x_own_f16)) return NVMAI_CUDA_EINVAL;
+    if (!h->ep_comm || !h->expert_map) return NVMAI_CUDA_EINVAL;    // ep_init and set_expert_map come first
+    if (rows_own == 0 || rows_own > h->ep_rows_own) return NVMAI_CUDA_ERANGE;
+    const auto &c = h->cfg;
+    for (uint32_t l = 0; l < c.num_layers; ++l)
+        if (!h->layers[l].registered) return NVMAI_CUDA_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half *x = static_cast<const __half *>(x_own_f16);
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (st != nullptr) cudaStreamIsCapturing(st, &cs);
+    if (st == nullptr || cs != cudaStreamCaptureStatusNone) return ep_stack_enqueue(h, x, rows_own, y_own, st);
+    if (h->ep_graphs_stale) {
+        for (auto &kv : h->ep_graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+        h->ep_graphs.clear();
+        h->ep_graphs_stale = false;
+    }
+    auto &g = h->ep_graphs[StackGraphKey{x_own_f16, y_own, rows_own, st}];
+    // First call per key: plain launches (NCCL sets up its channels on first use).
+    // Second call: capture.  Every rank takes the same branch, since all count alike.
+    if (g.calls++ == 0) return ep_stack_enqueue(h, x, rows_own, y_own, st);
+    if (!g.exec) {
+        int rc = record(h, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        if (rc) return rc;
+        const uint64_t launches_before = g_launches.load();
+        rc = ep_stack_enqueue(h, x, rows_own, y_own, st);
+        g_launches.store(launches_before);
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamEndCapture(st, &graph);
+        if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+        if ((rc = record(h, e))) return rc;
+        e = cudaGraphInstantiate(&g.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if ((rc = record(h, e))) { g.exec = nullptr; return rc; }
+    }
+    int rc = record(h, cudaGraphLaunch(g.exec, st));
+    if (rc == NVMAI_CUDA_OK) {
+        const uint64_t per_layer = 6 + (c.shared_f ? 2 : 0) + 1;     // router, group, 2 grouped, combine, finalize (+shared 2, +renorm)
+        g_launches.fetch_add((uint64_t)c.num_layers * per_layer - 1, std::memory_order_relaxed);
+    }
+    return rc;
 }
 
 int nvmai_cuda_moe_dequant(uint32_t bits, uint32_t meta_dtype, const void *w, const void *scales, const void *biases,

@@ -163,6 +163,28 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_ep_finalize(self._h, _ptr(shares), ranks, _ptr(h1), tokens, _ptr(y), _ptr(hidden),
                                                    _stream(stream)), "ep_finalize")
 
+    def ep_unique_id(self) -> bytes:
+        """The 128-byte id one rank makes and the launcher hands to every rank."""
+        import ctypes
+        buf = ctypes.create_string_buffer(128)
+        check(self._lib.nvmai_cuda_moe_ep_unique_id(buf), "ep_unique_id")
+        return buf.raw
+
+    def ep_init(self, unique_id: bytes, rank: int, world: int, rows_own: int) -> None:
+        """Collective over the ranks: opens the library's own communicator."""
+        import ctypes
+        if len(unique_id) != 128:
+            raise ValueError("the communicator id is 128 bytes")
+        buf = ctypes.create_string_buffer(unique_id, 128)
+        check(self._lib.nvmai_cuda_moe_ep_init(self._h, buf, rank, world, rows_own), "ep_init")
+
+    def ep_shutdown(self) -> None:
+        check(self._lib.nvmai_cuda_moe_ep_shutdown(self._h), "ep_shutdown")
+
+    def ep_stack_decode(self, x_own, rows_own: int, y_own, *, stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_ep_stack_decode(self._h, _ptr(x_own), rows_own, _ptr(y_own), _stream(stream)),
+              "ep_stack_decode")
+
     def rms_renorm(self, y, tokens: int, x_out, *, stream=None) -> None:
         check(self._lib.nvmai_cuda_moe_rms_renorm(self._h, _ptr(y), tokens, _ptr(x_out), _stream(stream)), "rms_renorm")
 

@@ -53,11 +53,49 @@ def _rank_main(rank, world, port, out_dir):
             y = ep_layer_step(LibraryBackend(moe, stream=st), dist, None, 0, x_own, world=world)
             st.synchronize()
         np.save(os.path.join(out_dir, f"y{rank}.npy"), y.cpu().numpy())
+        _native_stack(rank, world, out_dir, dist, pl, x_all, st)
         dist.destroy_process_group()
     except Exception:
         with open(os.path.join(out_dir, f"err{rank}.txt"), "w") as f:
             f.write(traceback.format_exc())
         sys.exit(3)
+
+
+def _native_stack(rank, world, out_dir, dist, pl, x_all, st):
+    """Two layers through the library's own communicator (plain launches, then the
+    captured graph, then a replay) against the torch.distributed-driven step."""
+    import torch
+    import gpu_util as gu
+    from nvmai_b200 import MoE, synthetic
+    from nvmai_b200 import format as fmt
+    from nvmai_b200.ep import LibraryBackend, ep_stack_step
+    cfg = _cfg(world * B_OWN)
+    cfg.num_layers = 2
+    moe = MoE(cfg)
+    keep = []
+    for layer in range(2):
+        host = synthetic.layer(910 + layer, d=D, f=F, shared_f=F, num_experts=E, routed_bits=8, meta=fmt.META_FP16)
+        local = dict(host)
+        local["experts"] = np.ascontiguousarray(host["experts"][pl.local_experts(rank)])
+        dl = gu.DeviceLayer(local)
+        dl.register(moe, layer)
+        keep.append(dl)
+    moe.set_expert_map(pl.expert_map(rank))
+    ids = [moe.ep_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    moe.ep_init(ids[0], rank, world, B_OWN)
+    with torch.cuda.stream(st):
+        x_own = gu.to_dev(x_all[rank * B_OWN:(rank + 1) * B_OWN].copy()).view(torch.float16)
+        want = ep_stack_step(LibraryBackend(moe, stream=st), dist, None, x_own, world=world, layers=2).clone()
+        st.synchronize()
+        y = torch.empty_like(want)
+        for call in range(3):
+            y.zero_()
+            moe.ep_stack_decode(x_own, B_OWN, y, stream=st)
+            moe.synchronize(stream=st)
+            assert torch.equal(y, want), f"native expert-parallel stack, call {call}"
+    np.save(os.path.join(out_dir, f"native{rank}.npy"), y.cpu().numpy())
+    moe.ep_shutdown()
 
 
 def test_two_gpu_expert_parallel_layer_matches_oracle(tmp_path):
@@ -90,3 +128,4 @@ def test_two_gpu_expert_parallel_layer_matches_oracle(tmp_path):
             o_idx, _, want, _, cpu = gu.oracle_decode(L, cfg, np.ascontiguousarray(x_all[rank * B_OWN + j]))
             assert orc.rel_error(y[j], cpu) < 1e-3
             assert orc.rel_error(y[j], want) < 5e-4
+        assert (tmp_path / f"native{rank}.npy").exists()
