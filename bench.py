@@ -486,6 +486,80 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
     note("process group closed")
 
 
+def run_prefill(args) -> None:
+    """configs[2]: one layer, `--tokens` rows (4096 by default), 4-bit: router, pair grouping, the grouped
+    gate/up and down GEMMs on the tensor cores, ordered combine.  Rotates over `--layers` independently seeded
+    layers (453 MB of experts each, larger than L2).  Not the headline line: its own metric."""
+    import torch
+    from nvmai_b200 import MoE, MoEConfig, launch_count, synthetic
+    from nvmai_b200 import format as fmt
+    torch.cuda.set_device(0)
+    tokens, n_layers = args.tokens, args.layers
+    cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
+                    router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16,
+                    meta_dtype=fmt.META_BF16, activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32,
+                    max_tokens=tokens, num_layers=n_layers)
+    moe = MoE(cfg)
+    devs = []
+    for l in range(n_layers):
+        dev = synthetic.device_layer(2000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits,
+                                     meta=fmt.META_BF16)
+        synthetic.register_device_layer(moe, l, dev)
+        devs.append(dev)
+    stream = torch.cuda.Stream()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    x = torch.randn(tokens, D, device="cuda", generator=gen).to(torch.float16)
+    y = torch.empty(tokens, D, dtype=torch.float32, device="cuda")
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty(tokens, D, dtype=torch.float32).pin_memory()
+    x_in = torch.empty_like(x)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            moe.layer_prefill(i % n_layers, x, tokens, y_out=y, stream=stream)
+        stream.synchronize()
+        sampler = ClockSampler(0)
+        l0 = launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(args.steps):
+            moe.layer_prefill(i % n_layers, x, tokens, y_out=y, stream=stream)
+        end.record(stream)
+        stream.synchronize()
+        launches = launch_count() - l0
+        ms = start.elapsed_time(end) / args.steps
+        assert torch.isfinite(y).all(), "non-finite output"
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            x_in.copy_(x_host, non_blocking=True)
+            moe.layer_prefill(i % n_layers, x_in, tokens, y_out=y, stream=stream)
+            y_host.copy_(y, non_blocking=True)
+            stream.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        clocks = sampler.stop()
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    flops_routed = tokens * K * 3 * 2 * D * F
+    flops_shared = tokens * 3 * 2 * D * FS
+    flops_router = tokens * 2 * D * E
+    tf = (flops_routed + flops_shared) / (ms * 1e-3) / 1e12
+    rec = {"metric": "moe_ffn_prefill_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+           "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+           "scaling": "weak", "dtype": "f16xu%d->f32" % args.bits, "value": tokens / (ms * 1e-3), "ms_per_step": ms,
+           "clocks": clocks, "gpu_launches": int(launches),
+           "config": {"workload": f"configs[2]: prefill chunk of {tokens} rows, one MoE layer, 35B-A3B shape, {args.bits}-bit",
+                      "d": D, "f": F, "experts": E, "top_k": K, "layers_rotated": n_layers, "bits": args.bits,
+                      "l2": "each layer's experts (453 MB at 4-bit) exceed the 126 MB L2; layers rotate"},
+           "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": tokens * D * 2,
+                   "d2h_bytes_per_step": tokens * D * 4},
+           "roofline": {"bound": "tensor", "kernel": "whole prefill block (router, grouping, packing, 4 GEMM launches, combine)",
+                        "achieved": tf, "peak": peak, "peak_source": "measured (sustained)" if peaks else "fallback",
+                        "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                        "flops": {"routed": flops_routed, "shared": flops_shared, "router_not_counted": flops_router}}}
+    print(json.dumps(rec), flush=True)
+
+
 def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> dict:
     """Times the dominant kernel (routed gate/up + activation) alone: one launch per
     layer with that layer's own experts (40 x 9.4 MB at 4-bit, larger than L2),
@@ -540,6 +614,9 @@ def main() -> None:
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
+    ap.add_argument("--prefill", action="store_true",
+                    help="measure configs[2] (a prefill chunk through the tensor-core grouped GEMMs) instead of the "
+                         "decode stack; --tokens defaults to 4096 and --layers to 2 here")
     ap.add_argument("--ep-driver", default="native", choices=["native", "torch"],
                     help="expert-parallel runs: the library's own communicator and CUDA graph (native), or "
                          "torch.distributed collectives around per-stage calls with plain launches (torch)")
@@ -547,7 +624,13 @@ def main() -> None:
     ap.add_argument("--deadline", type=float, default=600.0,
                     help="multi-GPU runs: give up (exit 2) after this many seconds instead of waiting on a stuck collective")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.prefill:
+        if args.tokens == 1:
+            args.tokens = 4096
+        if args.layers == LAYERS:
+            args.layers = 2
+        run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -212,6 +212,19 @@ NVMAI_API int nvmai_cuda_moe_ep_finalize(nvmai_cuda_moe *h, const float *shares_
  * rmsnorm between two MoE blocks that the stack benchmark uses. */
 NVMAI_API int nvmai_cuda_moe_rms_renorm(nvmai_cuda_moe *h, const void *y, uint32_t tokens, void *x_f16_out, void *stream);
 
+/* The whole MoE block for a prefill chunk (RealForwardRunner.swift:3244-3591:
+ * PrefillRouter.encodeBlock, pair grouping, prefill_grouped_routed_moe_batched_phase1 /
+ * _down, prefill_moe_reduce_token_major, PrefillSharedExpert.encodeBlock, the tail at
+ * :3560-3569) as grouped GEMMs on the tensor cores: x fp16 [tokens][d] (dense rows),
+ * hidden_inout = out(out(hidden + h1) + h2) in place, y_out (optional) = out(h1 + h2),
+ * out_idx / out_w (optional) the routing.  The tile shapes want f % 128 == 0,
+ * d % 256 == 0 and shared_f % 128 == 0 (NVMAI_CUDA_EINVAL otherwise).  Weights reach the
+ * tensor cores as fp16(q*s + b); scales and biases pass through fp16, which is exact
+ * for magnitudes in fp16's normal range. */
+NVMAI_API int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
+                                           void *hidden_inout, void *y_out, uint32_t *out_idx, void *out_w_f16,
+                                           void *stream);
+
 /* Expert parallelism with the exchange inside the library (no counterpart in the
  * reference, which runs on one GPU): the library opens its own NCCL communicator
  * (libnccl.so.2, resolved at run time; NVMAI_CUDA_ENCCL when it is missing or a call

@@ -60,6 +60,7 @@ PROTOTYPES = {
     "nvmai_cuda_moe_routed_partial": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, vp]),
     "nvmai_cuda_moe_ep_finalize": (C.c_int, [vp, vp, u32, vp, u32, vp, vp, vp]),
     "nvmai_cuda_moe_rms_renorm": (C.c_int, [vp, vp, u32, vp, vp]),
+    "nvmai_cuda_moe_layer_prefill": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, vp, vp]),
     "nvmai_cuda_moe_ep_unique_id": (C.c_int, [vp]),
     "nvmai_cuda_moe_ep_init": (C.c_int, [vp, vp, u32, u32, u32]),
     "nvmai_cuda_moe_ep_shutdown": (C.c_int, [vp]),

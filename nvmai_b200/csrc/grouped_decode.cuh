@@ -35,6 +35,10 @@ struct GroupParams {
     WorkItem *work;               // optional work list
     uint32_t *n_work;             // [2]: routed items, then routed + shared items
     uint32_t shared_chunks;       // ceil(tokens / 8) when a shared expert rides along, else 0
+    // Rows per work item: 8 for the batched decode kernels.  The prefill GEMMs take up to
+    // 128 and want an expert's rows split evenly over its items (140 rows = 70 + 70, not
+    // 128 + 12: every item pays for the whole expert's weights).
+    uint32_t pairs_per_item, even_split;
     // Expert parallelism: global expert id -> index of its blob among the experts this
     // rank holds, or kNotLocal.  Pairs routed to experts held elsewhere are left out
     // (inv = kNotLocal).  nullptr: every expert is local and ids are used as they are.
@@ -51,6 +55,7 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
     __shared__ uint32_t n_routed;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t P = p.tokens * p.K;
+    const uint32_t ppi = p.pairs_per_item ? p.pairs_per_item : (uint32_t)kPairsPerItem;
     pdl_wait();
     pdl_launch_dependents();
     for (int e = tid; e < kMaxExperts; e += kGroupThreads) { hist[e] = 0; running[e] = 0; }
@@ -68,7 +73,7 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
     if (warp == 0) {
         uint32_t c[kMaxExperts / 32], sum = 0, isum = 0;
 #pragma unroll
-        for (int j = 0; j < kMaxExperts / 32; ++j) { c[j] = hist[lane * (kMaxExperts / 32) + j]; sum += c[j]; isum += (c[j] + kPairsPerItem - 1) / kPairsPerItem; }
+        for (int j = 0; j < kMaxExperts / 32; ++j) { c[j] = hist[lane * (kMaxExperts / 32) + j]; sum += c[j]; isum += (c[j] + ppi - 1) / ppi; }
         uint32_t pre = sum, ipre = isum;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -80,7 +85,7 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
         for (int j = 0; j < kMaxExperts / 32; ++j) {
             const int e = lane * (kMaxExperts / 32) + j;
             offs[e] = run; item_base[e] = irun;
-            run += c[j]; irun += (c[j] + kPairsPerItem - 1) / kPairsPerItem;
+            run += c[j]; irun += (c[j] + ppi - 1) / ppi;
         }
         if (lane == 31) {
             n_routed = ipre;
@@ -92,18 +97,22 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
         p.expert_counts[e] = hist[e];
         p.expert_offsets[e] = hist[e] ? offs[e] : 0xFFFFFFFFu;
         if (p.work != nullptr) {
-            const uint32_t n_items = (hist[e] + kPairsPerItem - 1) / kPairsPerItem;
+            const uint32_t n_items = (hist[e] + ppi - 1) / ppi;
+            const uint32_t even = n_items ? hist[e] / n_items : 0, extra = n_items ? hist[e] % n_items : 0;
             for (uint32_t j = 0; j < n_items; ++j) {
-                const uint32_t s = j * kPairsPerItem;
-                p.work[item_base[e] + j] = WorkItem{e, offs[e] + s, min((uint32_t)kPairsPerItem, hist[e] - s), 0};
+                if (p.even_split) {
+                    p.work[item_base[e] + j] = WorkItem{e, offs[e] + j * even + min(j, extra), even + (j < extra ? 1u : 0u), 0};
+                } else {
+                    const uint32_t s = j * ppi;
+                    p.work[item_base[e] + j] = WorkItem{e, offs[e] + s, min(ppi, hist[e] - s), 0};
+                }
             }
         }
     }
     if (p.work != nullptr && p.shared_chunks != 0) {
         // the shared expert sees every token: items of 8 consecutive tokens, after the routed ones
         for (uint32_t j = tid; j < p.shared_chunks; j += kGroupThreads)
-            p.work[n_routed + j] = WorkItem{kSharedExpertId, j * kPairsPerItem,
-                                            min((uint32_t)kPairsPerItem, p.tokens - j * kPairsPerItem), 0};
+            p.work[n_routed + j] = WorkItem{kSharedExpertId, j * ppi, min(ppi, p.tokens - j * ppi), 0};
     }
     // stable scatter, 1024 pair ids at a time in increasing order
     for (uint32_t base = 0; base < P; base += kGroupThreads) {
@@ -428,6 +437,10 @@ struct CombineParams {
     void *y; void *hidden;
     float *partial_y;      // expert parallelism: this rank's share sum_r w[t,r]*partial (local pairs only), fp32, nothing else
     uint32_t D, K;
+    // Prefill rounding (prefill.metal:437-458, RealForwardRunner.swift:3560-3569): every
+    // partial is rounded to the output type, h2 = out(sum_r fma(w, partial)) on its own,
+    // and the residual takes two steps: hidden = out(out(hidden + h1) + h2).
+    uint32_t prefill;
 };
 
 template <int OUT>
@@ -460,6 +473,15 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
             acc = h1;
         } else {
             acc = p.residual != nullptr ? load_out<OUT>(p.residual, i) : 0.0f;
+        }
+        if (p.prefill) {
+            const float h1 = acc;
+            float h2 = 0.0f;
+            for (uint32_t r = 0; r < p.K; ++r) h2 = fmaf(wk[r], round_out<OUT>(p.partial[(size_t)pos[r] * p.D + d]), h2);
+            h2 = round_out<OUT>(h2);
+            if (p.y != nullptr) store_out<OUT>(p.y, i, h1 + h2);
+            if (p.hidden != nullptr) store_out<OUT>(p.hidden, i, round_out<OUT>(load_out<OUT>(p.hidden, i) + h1) + h2);
+            continue;
         }
         for (uint32_t r = 0; r < p.K; ++r) acc += wk[r] * p.partial[(size_t)pos[r] * p.D + d];
         const float yv = round_out<OUT>(acc);

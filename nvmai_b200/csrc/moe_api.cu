@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <new>
@@ -18,6 +19,7 @@
 #include "ep_comm.cuh"
 #include "grouped_decode.cuh"
 #include "misc_kernels.cuh"
+#include "prefill_gemm.cuh"
 
 using namespace nvmai;
 
@@ -68,6 +70,15 @@ struct nvmai_cuda_moe {
     void *stage_y = nullptr;        // host-call staging: [T][D] out_dtype
     std::map<StackGraphKey, cudaGraphExec_t> stack_graphs;
     bool graphs_stale = false, ep_graphs_stale = false;
+    // L2 prefetch of the next stage's weights in the fused layer chain: off unless
+    // NVMAI_CUDA_L2_PREFETCH=1 (measured slower on B200: the prefetch competes with the
+    // running stage's own copies); in_layer_chain: stage 3 follows this stage 2
+    bool l2_prefetch = false, in_layer_chain = false;
+    // prefill GEMMs: fp16 operand copies (allocated by the first prefill call)
+    __half *pf_x = nullptr;          // [T][D] x rows in the 4-bit unpack's K order
+    __half *pf_acts16 = nullptr;     // [T*K][F] routed activations as the down GEMM reads them
+    __half *pf_sacts16 = nullptr;    // [T][Fs] the shared expert's
+    float *pf_rowscale = nullptr, *pf_srowscale = nullptr;   // per row: power of two taken out of a wide-range row
     // expert parallelism over NCCL: communicator and exchange buffers
     NcclComm ep_comm = nullptr;
     uint32_t ep_rank = 0, ep_world = 0, ep_rows_own = 0;
@@ -257,6 +268,7 @@ int launch_stage2(nvmai_cuda_moe *h, const RoutedSource &src, const ExpertOffset
     p.src = src; p.off = off; p.x = x; p.x_stride = x_stride; p.acts = acts;
     p.active_slots = active_slots_dev;
     p.D = c.d; p.F = c.f; p.top_k = c.top_k; p.act = c.activation;
+    p.prefetch_down = (h->l2_prefetch && h->in_layer_chain) ? 1u : 0u;
     p.status = h->status;
     p.trace = h->cur_trace;
     dim3 grid((c.f + kBlockFeatures - 1) / kBlockFeatures, n_slots, tokens);
@@ -323,7 +335,8 @@ constexpr uint32_t kGroupedMinTokens = 4;   // below this every token runs its o
 
 int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, uint32_t tokens,
                        TokenExpertPair *pairs_out, uint32_t *offsets_out, uint32_t *counts_out, bool with_work,
-                       bool pdl, cudaStream_t st, bool with_shared = true, bool use_map = false) {
+                       bool pdl, cudaStream_t st, bool with_shared = true, bool use_map = false,
+                       uint32_t pairs_per_item = 0, bool even_split = false) {
     const auto &c = h->cfg;
     GroupParams g{};
     g.idx = idx; g.weights = w; g.tokens = tokens; g.K = c.top_k; g.E = c.num_experts;
@@ -336,6 +349,7 @@ int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, 
     g.shared_chunks = (with_work && with_shared && c.shared_f) ? (tokens + kPairsPerItem - 1) / kPairsPerItem : 0;
     g.expert_map = use_map ? h->expert_map : nullptr;
     g.n_local = (use_map && h->expert_map) ? h->n_local : c.num_experts;
+    g.pairs_per_item = pairs_per_item; g.even_split = even_split ? 1u : 0u;
     return launch_kernel(h, group_pairs_kernel, dim3(1), dim3(kGroupThreads), 0, st, pdl, g);
 }
 
@@ -391,6 +405,7 @@ int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, 
     pc.gate_val = (c.shared_f && c.shared_gate_kind != NVMAI_GATE_NONE) ? h->gate_val : nullptr;
     pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
     pc.partial_y = partial_y;
+    pc.prefill = 0;
     return dispatch_out(c.out_dtype, [&](auto O) {
         return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
     });
@@ -424,7 +439,9 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
         src.publish_idx = idx;
         src.publish_w = w;
     }
+    h->in_layer_chain = true;
     rc = launch_stage2(h, src, to_offsets(lv.w.offsets), x_rows, c.d, tokens, h->acts, nullptr, c.top_k, true, st);
+    h->in_layer_chain = false;
     h->cur_trace = nullptr;
     if (rc) return rc;
     h->cur_trace = slot(2);
@@ -443,7 +460,7 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
     p.y = h2_out ? h2_out : h->y;
     p.hidden = hidden;
     p.top_k = c.top_k;
-    if (next_layer != nullptr) {    // stack driver: warm the L2 with what the next layer's first stage reads
+    if (next_layer != nullptr && h->l2_prefetch) {    // stack driver: warm the L2 with what the next layer's first stage reads
         const auto &nw = next_layer->w;
         const size_t router_bytes = c.router_kind == 0 ? (size_t)c.num_experts * c.d * 2
                                                        : (size_t)c.num_experts * c.d * c.router_kind / 8;
@@ -463,6 +480,112 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
     rc = launch_stage3(h, p, tokens, true, st);
     h->cur_trace = nullptr;
     return rc;
+}
+
+// ---- prefill: grouped GEMMs on the tensor cores ----------------------------------
+int ensure_prefill_scratch(nvmai_cuda_moe *h) {
+    if (h->pf_acts16) return NVMAI_CUDA_OK;
+    const auto &c = h->cfg;
+    const size_t T = c.max_tokens, P = T * c.top_k;
+    auto alloc = [&](auto **ptr, size_t bytes) { return cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16) == cudaSuccess; };
+    if (alloc(&h->pf_x, T * c.d * 2) && alloc(&h->pf_acts16, P * c.f * 2) && alloc(&h->pf_sacts16, T * c.shared_f * 2) &&
+        alloc(&h->pf_rowscale, P * 4) && alloc(&h->pf_srowscale, T * 4))
+        return NVMAI_CUDA_OK;
+    cudaGetLastError();
+    cudaFree(h->pf_x); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
+    h->pf_x = h->pf_acts16 = h->pf_sacts16 = nullptr; h->pf_rowscale = h->pf_srowscale = nullptr;
+    return NVMAI_CUDA_ENOMEM;
+}
+
+template <int PHASE>
+int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParams &p, dim3 grid, cudaStream_t st) {
+    const auto &c = h->cfg;
+    return dispatch_bits_meta(bits, c.meta_dtype, [&](auto B, auto M) {
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            return launch_kernel(h, prefill_gemm_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value, PHASE>,
+                                 grid, dim3(kPfThreads), kPfSmemBytes, st, true, p);
+        });
+    });
+}
+
+// rows of src (out_dtype for intermediates, fp16 for x) -> fp16 rows in the K order the
+// weights of `bits` unpack in; returns the buffer the GEMM should read and its row scales
+int launch_pack_rows(nvmai_cuda_moe *h, const void *src, bool src_f32, __half *dst, float *row_scale, uint32_t rows,
+                     uint32_t n, uint32_t bits, cudaStream_t st) {
+    PackRowsParams p{src, dst, src_f32 ? row_scale : nullptr, rows, n, bits == 4 ? 1u : 0u};
+    const dim3 grid((rows + 7) / 8), block(256);
+    if (src_f32) return launch_kernel(h, pack_rows_kernel<1>, grid, block, 0, st, true, p);
+    return launch_kernel(h, pack_rows_kernel<0>, grid, block, 0, st, true, p);
+}
+
+// The whole block for `tokens` rows: router, grouping, gate/up GEMMs + activation,
+// down GEMMs, rank-ordered weighted sum with the shared expert and the two-step
+// residual of the prefill path (RealForwardRunner.swift:3244-3591).
+int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint32_t tokens, void *hidden, void *y,
+                       uint32_t *out_idx, __half *out_w, cudaStream_t st) {
+    const auto &c = h->cfg;
+    const LayerViews &lv = h->layers[layer];
+    int rc = ensure_prefill_scratch(h);
+    if (rc) return rc;
+    uint32_t *idx = out_idx ? out_idx : h->idx;
+    __half *w = out_w ? out_w : h->w;
+    const bool wide = c.out_dtype == NVMAI_OUT_FP32;
+    const XSource xsrc{x, c.d, nullptr, nullptr};
+    if ((rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, false, c.shared_f != 0, false, st))) return rc;
+    if ((rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st, false, false, kPfTileN, true)))
+        return rc;
+    const uint32_t P = tokens * c.top_k;
+    const uint32_t max_items = std::min(P, c.num_experts + P / kPfTileN);
+    const uint32_t shared_items = (tokens + kPfTileN - 1) / kPfTileN;
+    const bool need_perm = c.routed_bits == 4 || (c.shared_f && c.shared_bits == 4);
+    if (need_perm && (rc = launch_pack_rows(h, x, false, h->pf_x, nullptr, tokens, c.d, 4, st))) return rc;
+
+    PrefillGemmParams g{};
+    g.experts = static_cast<const uint8_t *>(lv.w.experts); g.stride = lv.w.expert_stride; g.num_experts = c.num_experts;
+    g.off = to_offsets(lv.w.offsets);
+    g.work = h->work; g.n_work = h->n_work; g.sorted_pair = h->sorted_pair;
+    g.tokens = tokens; g.top_k = c.top_k; g.act = c.activation; g.status = h->status;
+    // gate/up, routed then shared
+    g.shared = 0; g.b_rows = c.routed_bits == 4 ? h->pf_x : x; g.b_stride = c.d; g.kdim = c.d;
+    g.out = h->acts; g.out_stride = c.f; g.round_gate_up = 0;
+    if ((rc = launch_prefill_gemm<0>(h, c.routed_bits, g, dim3(c.f / kPfTileM, max_items), st))) return rc;
+    if (c.shared_f) {
+        PrefillGemmParams s = g;
+        s.shared = 1; s.s0 = to_mat(lv.w.shared_gate_proj); s.s1 = to_mat(lv.w.shared_up_proj);
+        s.b_rows = c.shared_bits == 4 ? h->pf_x : x; s.out = h->shared_act; s.out_stride = c.shared_f; s.round_gate_up = 1;
+        if ((rc = launch_prefill_gemm<0>(h, c.shared_bits, s, dim3(c.shared_f / kPfTileM, shared_items), st))) return rc;
+    }
+    // activation rows as the down GEMMs read them
+    const __half *acts16 = static_cast<const __half *>(h->acts), *sacts16 = static_cast<const __half *>(h->shared_act);
+    if (wide || c.routed_bits == 4) {
+        if ((rc = launch_pack_rows(h, h->acts, wide, h->pf_acts16, h->pf_rowscale, P, c.f, c.routed_bits, st))) return rc;
+        acts16 = h->pf_acts16;
+    }
+    if (c.shared_f && (wide || c.shared_bits == 4)) {
+        if ((rc = launch_pack_rows(h, h->shared_act, wide, h->pf_sacts16, h->pf_srowscale, tokens, c.shared_f, c.shared_bits, st)))
+            return rc;
+        sacts16 = h->pf_sacts16;
+    }
+    // down, routed then shared
+    g.b_rows = acts16; g.b_stride = c.f; g.kdim = c.f; g.row_scale = wide ? h->pf_rowscale : nullptr;
+    g.out = h->partial; g.out_stride = c.d;
+    if ((rc = launch_prefill_gemm<1>(h, c.routed_bits, g, dim3(c.d / (2 * kPfTileM), max_items), st))) return rc;
+    if (c.shared_f) {
+        PrefillGemmParams s = g;
+        s.shared = 1; s.s0 = to_mat(lv.w.shared_down_proj); s.s1 = s.s0;
+        s.b_rows = sacts16; s.b_stride = c.shared_f; s.kdim = c.shared_f; s.row_scale = wide ? h->pf_srowscale : nullptr;
+        s.out = h->shared_partial;
+        if ((rc = launch_prefill_gemm<1>(h, c.shared_bits, s, dim3(c.d / (2 * kPfTileM), shared_items), st))) return rc;
+    }
+    CombineParams pc{};
+    pc.partial = h->partial; pc.shared_partial = c.shared_f ? h->shared_partial : nullptr;
+    pc.inv = h->inv; pc.routing_w = w;
+    pc.gate_val = (c.shared_f && c.shared_gate_kind != NVMAI_GATE_NONE) ? h->gate_val : nullptr;
+    pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
+    pc.partial_y = nullptr; pc.prefill = 1;
+    return dispatch_out(c.out_dtype, [&](auto O) {
+        return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
+    });
 }
 
 }  // namespace
@@ -527,6 +650,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
     if (!h) return fail(NVMAI_CUDA_ENOMEM);
     h->cfg = c;
     h->layers.resize(c.num_layers);
+    if (const char *env = std::getenv("NVMAI_CUDA_L2_PREFETCH")) h->l2_prefetch = env[0] == '1';
     const size_t T = c.max_tokens;
     auto alloc = [&](auto **ptr, size_t bytes) -> bool {
         cudaError_t e = cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16);
@@ -565,6 +689,7 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     if (!h) return;
     for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
     ep_release(h);
+    cudaFree(h->pf_x); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y);
@@ -686,6 +811,21 @@ int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x
 // Layer l > 0 reads the previous layer's block output and renormalises it inside
 // its own stage 1 (every block derives the same rows; block 0 stores them for
 // stage 2), so a layer is exactly three launches.
+int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
+                                 void *hidden_inout, void *y_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    int rc = check_layer(h, layer);
+    if (rc) return rc;
+    const auto &c = h->cfg;
+    if (!x_f16 || !aligned16(x_f16) || (!hidden_inout && !y_out)) return NVMAI_CUDA_EINVAL;
+    if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (c.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
+    // tile shapes of the tensor-core kernels: 128 weight rows per accumulator, two accumulators per CTA
+    if (c.f % kPfTileM != 0 || c.d % (2 * kPfTileM) != 0 || c.shared_f % kPfTileM != 0) return NVMAI_CUDA_EINVAL;
+    if (h->expert_map) return NVMAI_CUDA_EINVAL;      // prefill runs on one GPU's full expert set
+    return layer_prefill_impl(h, layer, static_cast<const __half *>(x_f16), tokens, hidden_inout, y_out, out_idx,
+                              static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
+}
+
 int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const void *w_f16, uint32_t tokens,
                                void *sorted_pairs, uint32_t *expert_offsets, uint32_t *expert_counts, void *stream) {
     if (!h || !idx || !sorted_pairs || !expert_offsets || !expert_counts) return NVMAI_CUDA_EINVAL;

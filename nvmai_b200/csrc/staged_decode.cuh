@@ -413,6 +413,7 @@ struct Stage2Params {
     void *acts;                         // [tokens][top_k][F], fp16 or fp32 (see round_mid)
     const uint32_t *active_slots;       // device, or nullptr = identity
     uint32_t D, F, top_k, act;
+    uint32_t prefetch_down;             // also ask the L2 for the experts' down projections
     unsigned int *status;
     unsigned long long *trace;   // optional {start, end} timestamps of this launch
 };
@@ -459,10 +460,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage2_kernel(Stage2Params 
         if (lane == 0) bulk_g2s(smem + L.xs, p.x + (size_t)tok * p.x_stride, p.D * 2, reinterpret_cast<uint64_t *>(smem));
         for (int tile = 1; tile < n_tiles; ++tile)
             issue_gate_up_copies<BITS>(smem, L, tile, gate, up, f0 + tile * kTileFeatures, p.D, 0);
-        // warm the L2 with this block's share of the expert's down projection (stage 3 reads it next)
-        l2_prefetch_slice(blob + p.off.o[6], (size_t)p.D * p.F * BITS / 8, blockIdx.x, gridDim.x, lane);
-        l2_prefetch_slice(blob + p.off.o[7], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
-        l2_prefetch_slice(blob + p.off.o[8], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
+        if (p.prefetch_down) {
+            // warm the L2 with this block's share of the expert's down projection (stage 3 reads it next)
+            l2_prefetch_slice(blob + p.off.o[6], (size_t)p.D * p.F * BITS / 8, blockIdx.x, gridDim.x, lane);
+            l2_prefetch_slice(blob + p.off.o[7], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
+            l2_prefetch_slice(blob + p.off.o[8], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
+        }
     }
     gate_up_compute<BITS, META, OUT>(smem, L, f0, n_tiles, p.D, p.act, false, p.acts,
                                      ((size_t)tok * p.top_k + slot) * p.F, p.status);

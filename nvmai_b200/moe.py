@@ -163,6 +163,14 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_ep_finalize(self._h, _ptr(shares), ranks, _ptr(h1), tokens, _ptr(y), _ptr(hidden),
                                                    _stream(stream)), "ep_finalize")
 
+    def layer_prefill(self, layer: int, x, tokens: int, *, hidden=None, y_out=None, out_idx=None, out_w=None,
+                      stream=None) -> None:
+        """The block for a prefill chunk (encodeRoutedMoEPrefill, RealForwardRunner.swift:3244-3591):
+        x fp16 [tokens][d]; hidden updated in place with the prefill path's two-step residual;
+        y_out = out(h1 + h2)."""
+        check(self._lib.nvmai_cuda_moe_layer_prefill(self._h, layer, _ptr(x), tokens, _ptr(hidden), _ptr(y_out),
+                                                     _ptr(out_idx), _ptr(out_w), _stream(stream)), "layer_prefill")
+
     def ep_unique_id(self) -> bytes:
         """The 128-byte id one rank makes and the launcher hands to every rank."""
         import ctypes

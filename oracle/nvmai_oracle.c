@@ -756,11 +756,10 @@ static float orc_dense_row_dot_f16(const uint16_t *w, const uint16_t *x, size_t 
  *   h2 = out(h1 + sum_k w_k down_k(acts_k));  hidden = out(hidden + h2).
  * out() is half() for out_dtype fp16 and the identity for fp32.
  * hidden_inout may be NULL (h2 only).  idx_out/w_out/h2_out optional. */
-void orc_gpu_layer_decode(const orc_layer *L, const uint16_t *x_f16, void *hidden_inout,
-                          uint32_t *idx_out, uint16_t *w_out, void *h2_out, float *margin_out) {
-    const size_t D = L->D, F = L->F, K = L->K, E = L->E;
+static void orc_layer_route(const orc_layer *L, const uint16_t *x_f16, uint32_t *idx, uint16_t *w16,
+                            float *margin_out) {
+    const size_t D = L->D, K = L->K, E = L->E;
     float *logits = (float *)malloc(E * sizeof(float));
-    uint32_t idx[64]; uint16_t w16[64];
     if (L->router_kind == 0)
         orc_router_logits_dense_f16((const uint16_t *)L->router_W, x_f16, L->eff_scale, E, D, logits, NULL);
     else
@@ -768,34 +767,44 @@ void orc_gpu_layer_decode(const orc_layer *L, const uint16_t *x_f16, void *hidde
                                  x_f16, L->eff_scale, E, D, logits, NULL);
     orc_topk_softmax(logits, E, K, L->per_expert_scale, idx, w16, NULL, margin_out);
     free(logits);
+}
 
+/* h1 = the gated shared expert's output for one row (zeros without a shared expert), out_dtype elements. */
+static void orc_layer_h1(const orc_layer *L, const uint16_t *x_f16, void *h1) {
+    const size_t D = L->D;
+    const size_t esz = L->out_dtype == ORC_OUT_FP16 ? 2 : 4;
+    if (!L->shared[0]) { memset(h1, 0, D * esz); return; }
+    if (L->shared_gate_kind == 0) {
+        /* dense fp16 gate row: same rounding points, g = half(w.x) */
+        orc_gpu_shared_expert(L->shared, L->shared_bits, L->meta, L->act, NULL, NULL, NULL, 0,
+                              x_f16, D, L->Fs, L->out_dtype, h1);
+        float g = orc_round_mid(orc_dense_row_dot_f16((const uint16_t *)L->sgate_W, x_f16, D), L->out_dtype);
+        for (size_t d = 0; d < D; ++d) {
+            if (L->out_dtype == ORC_OUT_FP16) {
+                float v = orc_f16_to_f32(((uint16_t *)h1)[d]);
+                ((uint16_t *)h1)[d] = orc_f32_to_f16(v / (1.0f + expf(-g)));
+            } else {
+                ((float *)h1)[d] = ((float *)h1)[d] / (1.0f + expf(-g));
+            }
+        }
+    } else if (L->shared_gate_kind > 0) {
+        orc_gpu_shared_expert(L->shared, L->shared_bits, L->meta, L->act, L->sgate_W,
+                              L->sgate_S, L->sgate_B, L->shared_gate_kind, x_f16, D, L->Fs,
+                              L->out_dtype, h1);
+    } else {
+        orc_gpu_shared_expert(L->shared, L->shared_bits, L->meta, L->act, NULL, NULL, NULL, 0,
+                              x_f16, D, L->Fs, L->out_dtype, h1);
+    }
+}
+
+void orc_gpu_layer_decode(const orc_layer *L, const uint16_t *x_f16, void *hidden_inout,
+                          uint32_t *idx_out, uint16_t *w_out, void *h2_out, float *margin_out) {
+    const size_t D = L->D, F = L->F, K = L->K, E = L->E;
+    uint32_t idx[64]; uint16_t w16[64];
+    orc_layer_route(L, x_f16, idx, w16, margin_out);
     const size_t esz = L->out_dtype == ORC_OUT_FP16 ? 2 : 4;
     void *h1 = malloc(D * esz);
-    if (L->shared[0]) {
-        if (L->shared_gate_kind == 0) {
-            /* dense fp16 gate row: same rounding points, g = half(w.x) */
-            orc_gpu_shared_expert(L->shared, L->shared_bits, L->meta, L->act, NULL, NULL, NULL, 0,
-                                  x_f16, D, L->Fs, L->out_dtype, h1);
-            float g = orc_round_mid(orc_dense_row_dot_f16((const uint16_t *)L->sgate_W, x_f16, D), L->out_dtype);
-            for (size_t d = 0; d < D; ++d) {
-                if (L->out_dtype == ORC_OUT_FP16) {
-                    float v = orc_f16_to_f32(((uint16_t *)h1)[d]);
-                    ((uint16_t *)h1)[d] = orc_f32_to_f16(v / (1.0f + expf(-g)));
-                } else {
-                    ((float *)h1)[d] = ((float *)h1)[d] / (1.0f + expf(-g));
-                }
-            }
-        } else if (L->shared_gate_kind > 0) {
-            orc_gpu_shared_expert(L->shared, L->shared_bits, L->meta, L->act, L->sgate_W,
-                                  L->sgate_S, L->sgate_B, L->shared_gate_kind, x_f16, D, L->Fs,
-                                  L->out_dtype, h1);
-        } else {
-            orc_gpu_shared_expert(L->shared, L->shared_bits, L->meta, L->act, NULL, NULL, NULL, 0,
-                                  x_f16, D, L->Fs, L->out_dtype, h1);
-        }
-    } else {
-        memset(h1, 0, D * esz);
-    }
+    orc_layer_h1(L, x_f16, h1);
 
     const uint8_t *blobs[64];
     for (size_t k = 0; k < K; ++k) {
@@ -811,6 +820,66 @@ void orc_gpu_layer_decode(const orc_layer *L, const uint16_t *x_f16, void *hidde
     if (idx_out) memcpy(idx_out, idx, K * 4);
     if (w_out) memcpy(w_out, w16, K * 2);
     free(acts); free(h1); free(h2);
+}
+
+/* One row of a prefill chunk with the prefill path's rounding points
+ * (prefill.metal:499-500, 531-533, 457; RealForwardRunner.swift:3560-3569):
+ * act = half(act(gate.x) * (up.x)); partial_r = half(down_r.act_r);
+ * h2 = half(sum_r fma(float(w_r), float(partial_r), acc)), r ascending;
+ * hidden = half(half(hidden + h1) + h2).  y_out (optional) = half(h1 + h2).
+ * out_dtype 1: the same with every "half" above an fp32 no-op except the
+ * activations (11 significant bits, orc_round11). */
+void orc_gpu_layer_prefill_row(const orc_layer *L, const uint16_t *x_f16, void *hidden_inout, void *y_out,
+                               uint32_t *idx_out, uint16_t *w_out, void *acts_out) {
+    const size_t D = L->D, F = L->F, K = L->K, E = L->E;
+    const int f16 = L->out_dtype == ORC_OUT_FP16;
+    uint32_t idx[64]; uint16_t w16[64];
+    orc_layer_route(L, x_f16, idx, w16, NULL);
+    const size_t esz = f16 ? 2 : 4;
+    void *h1 = malloc(D * esz);
+    orc_layer_h1(L, x_f16, h1);
+    const uint8_t *blobs[64];
+    for (size_t k = 0; k < K; ++k) {
+        uint32_t e = idx[k] < E ? idx[k] : (uint32_t)E - 1;
+        blobs[k] = L->experts + (uint64_t)e * L->stride;
+    }
+    void *acts = malloc(K * F * 4);
+    orc_gpu_phase1(blobs, L->off, L->routed_bits, L->meta, L->act, x_f16, D, F, K, NULL, 0, L->out_dtype, acts);
+    float *a = (float *)malloc(F * sizeof(float));
+    float *h2 = (float *)calloc(D, sizeof(float));
+    const size_t groups = F / ORC_GROUP, row_bytes = F * (size_t)L->routed_bits / 8;
+    for (size_t k = 0; k < K; ++k) {
+        for (size_t i = 0; i < F; ++i)
+            a[i] = f16 ? orc_f16_to_f32(((const uint16_t *)acts)[k * F + i]) : ((const float *)acts)[k * F + i];
+        const uint8_t *base = blobs[k];
+        const float wk = orc_f16_to_f32(w16[k]);
+        for (size_t d = 0; d < D; ++d) {
+            float v = (float)orc_row_dot64(L->routed_bits, L->meta, base + L->off[6] + d * row_bytes,
+                                           (const uint16_t *)(base + L->off[7]) + d * groups,
+                                           (const uint16_t *)(base + L->off[8]) + d * groups, a, F);
+            if (f16) v = orc_round_f16(v);
+            h2[d] = fmaf(wk, v, h2[d]);
+        }
+    }
+    for (size_t d = 0; d < D; ++d) {
+        if (f16) {
+            const float h2v = orc_round_f16(h2[d]);
+            const float h1v = orc_f16_to_f32(((const uint16_t *)h1)[d]);
+            if (y_out) ((uint16_t *)y_out)[d] = orc_f32_to_f16(h1v + h2v);
+            if (hidden_inout) {
+                uint16_t *hid = (uint16_t *)hidden_inout;
+                hid[d] = orc_f32_to_f16(orc_round_f16(orc_f16_to_f32(hid[d]) + h1v) + h2v);
+            }
+        } else {
+            const float h1v = ((const float *)h1)[d];
+            if (y_out) ((float *)y_out)[d] = h1v + h2[d];
+            if (hidden_inout) ((float *)hidden_inout)[d] = (((float *)hidden_inout)[d] + h1v) + h2[d];
+        }
+    }
+    if (idx_out) memcpy(idx_out, idx, K * 4);
+    if (w_out) memcpy(w_out, w16, K * 2);
+    if (acts_out) memcpy(acts_out, acts, K * F * esz);
+    free(a); free(h2); free(acts); free(h1);
 }
 
 /* The same block on the reference CPU path: fp32 x (the fp16 input widened),

@@ -145,6 +145,8 @@ def _declare(L: C.CDLL) -> None:
     L.orc_gpu_prefill_reduce.argtypes = [vp, vp, sz, sz, sz, vp]; L.orc_gpu_prefill_reduce.restype = None
     L.orc_gpu_layer_decode.argtypes = [C.POINTER(Layer), vp, vp, vp, vp, vp, vp]
     L.orc_gpu_layer_decode.restype = None
+    L.orc_gpu_layer_prefill_row.argtypes = [C.POINTER(Layer), vp, vp, vp, vp, vp, vp]
+    L.orc_gpu_layer_prefill_row.restype = None
     L.orc_cpu_layer_decode.argtypes = [C.POINTER(Layer), vp, vp, vp, vp, GEMV4_FN]
     L.orc_cpu_layer_decode.restype = None
     L.orc_rel_error.argtypes = [vp, vp, sz]; L.orc_rel_error.restype = C.c_float

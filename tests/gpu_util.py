@@ -93,3 +93,18 @@ def oracle_decode(L, cfg: MoEConfig, x_f16_row: np.ndarray):
                              orc.ref_gemv4_ptr())
     h2f = orc.f16_bits_to_f32(h2) if cfg.out_dtype == fmt.OUT_FP16 else h2
     return idx, w16, h2f, float(margin[0]), cpu
+
+
+def oracle_prefill_row(L, cfg: MoEConfig, x_f16_row: np.ndarray, hidden_row: np.ndarray | None = None):
+    """One row with the prefill path's rounding points -> (idx, w16, y as fp32, hidden out as fp32 or None)."""
+    lib = orc.lib()
+    import ctypes as C
+    f16 = cfg.out_dtype == fmt.OUT_FP16
+    idx = np.zeros(cfg.top_k, dtype=np.uint32)
+    w16 = np.zeros(cfg.top_k, dtype=np.uint16)
+    y = np.zeros(cfg.d, dtype=np.uint16 if f16 else np.float32)
+    hid = None if hidden_row is None else np.ascontiguousarray(hidden_row).copy()
+    lib.orc_gpu_layer_prefill_row(C.byref(L), orc.ptr(x_f16_row), orc.ptr(hid), orc.ptr(y), orc.ptr(idx), orc.ptr(w16),
+                                  None)
+    to32 = (lambda a: orc.f16_bits_to_f32(a)) if f16 else (lambda a: a)
+    return idx, w16, to32(y), (None if hid is None else to32(hid))
