@@ -531,7 +531,27 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     __half *w = out_w ? out_w : h->w;
     const bool wide = c.out_dtype == NVMAI_OUT_FP32;
     const XSource xsrc{x, c.d, nullptr, nullptr};
-    if ((rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, false, c.shared_f != 0, false, st))) return rc;
+    // A dense fp16 router without an input scale is a plain GEMM (products of two fp16 values are
+    // exact in fp32, so only the order of the fp32 additions differs from the decode router's);
+    // affine routers keep the exact code-times-activation kernel.
+    const bool gemm_router = c.router_kind == NVMAI_ROUTER_DENSE_F16 && lv.w.effective_scale == nullptr &&
+                             c.num_experts % (2 * kPfTileM) == 0;
+    if (gemm_router) {
+        PrefillGemmParams r{};
+        r.shared = 1;
+        r.s0 = AffineMat{static_cast<const uint8_t *>(lv.w.router.w), nullptr, nullptr};
+        r.s1 = r.s0;
+        r.tokens = tokens; r.top_k = c.top_k; r.b_rows = x; r.b_stride = c.d; r.kdim = c.d;
+        r.out = h->logits; r.out_stride = c.num_experts; r.status = h->status;
+        const dim3 grid(c.num_experts / (2 * kPfTileM), (tokens + kPfTileN - 1) / kPfTileN);
+        if ((rc = launch_kernel(h, prefill_gemm_kernel<16, 0, 0, 2>, grid, dim3(kPfThreads), kPfSmemBytes, st, false, r)))
+            return rc;
+        TopkRowsParams tk{h->logits, static_cast<const uint16_t *>(lv.w.per_expert_scale), idx, w, c.num_experts, c.top_k};
+        if ((rc = launch_kernel(h, topk_rows_kernel, dim3(tokens), dim3(256), 0, st, true, tk))) return rc;
+        if (c.shared_f && (rc = launch_stage1(h, lv, xsrc, tokens, nullptr, nullptr, false, false, true, false, st))) return rc;
+    } else if ((rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, false, c.shared_f != 0, false, st))) {
+        return rc;
+    }
     if ((rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st, false, false, kPfTileN, true)))
         return rc;
     const uint32_t P = tokens * c.top_k;

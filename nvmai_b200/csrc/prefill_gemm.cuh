@@ -45,8 +45,10 @@ namespace nvmai {
 constexpr int kPfTileM = 128;                 // weight rows per accumulator
 constexpr int kPfTileN = 128;                 // most token rows per work item
 constexpr int kPfKBlock = 64;                 // K values per pipeline stage
-constexpr int kPfStages = 2;
-constexpr int kPfProducerWarps = 8;
+constexpr int kPfStages = 4;
+constexpr int kPfProducerWarps = 16;
+constexpr int kPfAhead = 3;                   // K blocks of packed codes a producer holds in registers
+constexpr int kPfDefer = 2;                   // iterations between issuing a stage's copies and announcing it
 constexpr int kPfProducers = kPfProducerWarps * 32;
 constexpr int kPfThreads = kPfProducers + 32;
 constexpr uint32_t kPfTmemCols = 256;         // two fp32 accumulators of up to 128 columns
@@ -91,7 +93,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // 32 lanes x 32 consecutive columns of 32-bit accumulators: register i = column i
 // of the lane this thread owns (lane quarter of the warp = warp index mod 4).
@@ -136,73 +139,60 @@ template <int META> __device__ __forceinline__ __half2 meta_half2(uint16_t bits)
     return __float2half2_rn(__uint_as_float(((uint32_t)bits) << 16));
 }
 
-// 32 codes (one producer thread's share of a K block) -> 4 swizzled 16-byte chunks.
+// 16 codes (one producer thread's share of a K block) -> 2 swizzled 16-byte chunks.
 template <int BITS>
-struct PackedCodes { uint4 v[BITS == 4 ? 1 : 2]; };
+struct PackedCodes { uint32_t v[BITS == 4 ? 2 : 4]; };
 
 template <int BITS>
 __device__ __forceinline__ PackedCodes<BITS> pf_load_codes(const uint8_t *p) {
     PackedCodes<BITS> c;
-    c.v[0] = ldg_stream_u4(p);
-    if (BITS == 8) c.v[1] = ldg_stream_u4(p + 16);
+    if (BITS == 4) { const uint2 q = ldg_stream_u2(p); c.v[0] = q.x; c.v[1] = q.y; }
+    else { const uint4 q = ldg_stream_u4(p); c.v[0] = q.x; c.v[1] = q.y; c.v[2] = q.z; c.v[3] = q.w; }
     return c;
 }
 
 template <int BITS>
-__device__ __forceinline__ void dequant_store(uint32_t tile_smem, uint32_t row, uint32_t half, const PackedCodes<BITS> &c,
-                                              __half2 s2, __half2 b2) {
+__device__ __forceinline__ void dequant_store(uint32_t tile_smem, uint32_t row, uint32_t quarter,
+                                              const PackedCodes<BITS> &c, __half2 s2, __half2 b2) {
     const __half2 k1024 = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
-    if (BITS == 4) {
-        const uint32_t w[4] = {c.v[0].x, c.v[0].y, c.v[0].z, c.v[0].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {        // word j = codes 8j .. 8j+7 = chunk j of this half row
-            uint32_t o[4];
+    for (int j = 0; j < 2; ++j) {            // chunk j of this quarter row = codes 8j .. 8j+7 of the thread's 16
+        uint32_t o[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t t = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;      // (1024 + q_i, 1024 + q_{i+4})
-                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
-                const __half2 v = __hfma2(q, s2, b2);
-                o[i] = *reinterpret_cast<const uint32_t *>(&v);
-            }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_smem + sw128_offset(row, half * 4 + j)),
-                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        for (int i = 0; i < 4; ++i) {
+            uint32_t t;
+            if (BITS == 4) t = ((c.v[j] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;      // (1024 + q_i, 1024 + q_{i+4})
+            else t = __byte_perm(c.v[2 * j + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342 : 0x4140);   // (1024 + q_2i, 1024 + q_2i+1)
+            const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
+            const __half2 v = __hfma2(q, s2, b2);
+            o[i] = *reinterpret_cast<const uint32_t *>(&v);
         }
-    } else {
-        const uint32_t w[8] = {c.v[0].x, c.v[0].y, c.v[0].z, c.v[0].w, c.v[1].x, c.v[1].y, c.v[1].z, c.v[1].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {        // words 2j, 2j+1 = codes 8j .. 8j+7
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t t = __byte_perm(w[2 * j + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342 : 0x4140);
-                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
-                const __half2 v = __hfma2(q, s2, b2);
-                o[i] = *reinterpret_cast<const uint32_t *>(&v);
-            }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_smem + sw128_offset(row, half * 4 + j)),
-                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-        }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_smem + sw128_offset(row, quarter * 2 + j)),
+                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
     }
 }
 
 struct PrefillGemmParams {
-    // routed items: blobs + offsets; shared items: the tensors themselves
+    // routed items: blobs + offsets; shared / router items: the tensors themselves
     const uint8_t *experts; unsigned long long stride; uint32_t num_experts; ExpertOffsets off;
-    AffineMat s0, s1;              // shared items: phase 0 gate, up; phase 1 down (s0 only)
+    AffineMat s0, s1;              // direct tensors: phase 0 gate, up; phase 1 down; phase 2 the router matrix (s0)
     uint32_t shared;               // 1: item y = token rows [128 y, 128 y + 128), weights from s0/s1
     const WorkItem *work; const uint32_t *n_work; const uint32_t *sorted_pair;
     uint32_t tokens, top_k;
-    const __half *b_rows; uint32_t b_stride;   // phase 0: x rows by token; phase 1: packed activation rows by position
+    const __half *b_rows; uint32_t b_stride;   // phase 0, 2: x rows by token; phase 1: packed activation rows by position
     const float *row_scale;        // phase 1: factor per row undone in the epilogue, or nullptr
-    void *out; uint32_t out_stride;            // phase 0: acts [row][F] (fp16 / fp32 by OUT); phase 1: partial fp32 [row][D]
-    uint32_t kdim;                 // D (phase 0) / F (phase 1)
+    void *out; uint32_t out_stride;            // phase 0: acts [row][F] (fp16 / fp32 by OUT); phase 1: partial fp32 [row][D];
+                                               // phase 2: logits fp32 [token][E]
+    uint32_t kdim;                 // D (phase 0, 2) / F (phase 1)
     uint32_t act;                  // activation kind (phase 0)
     uint32_t round_gate_up;        // phase 0: round gate and up before the activation (the shared expert does)
     unsigned int *status;
 };
 
+// BITS: 4 / 8 = affine codes dequantised by the producers, 16 = dense fp16 rows copied as they are.
+// PHASE: 0 gate/up + activation, 1 down, 2 router logits (A0, A1 = rows 0-127, 128-255 of a 256-row block).
 template <int BITS, int META, int OUT, int PHASE>
-__global__ void __launch_bounds__(kPfThreads, 2) prefill_gemm_kernel(PrefillGemmParams p) {
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemmParams p) {
     extern __shared__ unsigned char pf_smem_raw[];
     const uint32_t raw = smem_addr(pf_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // shared-window address of the aligned area
@@ -236,7 +226,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_gemm_kernel(PrefillGemm
         mbar_init(accum, 1);
         mbar_fence_init();
     }
-    // B rows past the item's count are never written: clear both stages' B tiles once
+    // B rows past the item's count are never written: clear every stage's B tile once
     for (int i = tid; i < kPfStages * kPfTileBytes / 16; i += kPfThreads) {
         const int s = i / (kPfTileBytes / 16), o = i % (kPfTileBytes / 16);
         *reinterpret_cast<uint4 *>(gen + 1024 + (size_t)s * kPfStageBytes + 2 * kPfTileBytes + (size_t)o * 16) = make_uint4(0, 0, 0, 0);
@@ -254,11 +244,11 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_gemm_kernel(PrefillGemm
 
     if (warp < kPfProducerWarps) {
         // ---------------- producers ----------------
-        const uint32_t row = tid >> 1, half = tid & 1;
+        const uint32_t row = tid >> 2, quarter = tid & 3;       // 16 K values of one row per matrix and K block
         const size_t row_bytes = (size_t)p.kdim * BITS / 8;
         const uint32_t groups = p.kdim / kGroup;
         AffineMat m0, m1;
-        uint32_t r0, r1;          // matrix rows this thread dequantises
+        uint32_t r0, r1;          // matrix rows this thread converts
         if (PHASE == 0) {
             r0 = r1 = blockIdx.x * kPfTileM + row;
             if (p.shared) { m0 = p.s0; m1 = p.s1; }
@@ -280,58 +270,93 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_gemm_kernel(PrefillGemm
             }
             m1 = m0;
         }
-        const uint8_t *w0 = m0.w + (size_t)r0 * row_bytes + half * (BITS * 4);     // 32 codes = BITS*4 bytes
-        const uint8_t *w1 = m1.w + (size_t)r1 * row_bytes + half * (BITS * 4);
-        const uint16_t *s0 = m0.s + (size_t)r0 * groups, *b0 = m0.b + (size_t)r0 * groups;
-        const uint16_t *s1 = m1.s + (size_t)r1 * groups, *b1 = m1.b + (size_t)r1 * groups;
-        // B: chunk c of rows (tid >> 3) + 32 j
+        const uint8_t *w0 = m0.w + (size_t)r0 * row_bytes + quarter * (BITS * 2);     // 16 values = BITS*2 bytes
+        const uint8_t *w1 = m1.w + (size_t)r1 * row_bytes + quarter * (BITS * 2);
+        const uint16_t *s0 = nullptr, *b0 = nullptr, *s1 = nullptr, *b1 = nullptr;
+        if (BITS != 16) {
+            s0 = m0.s + (size_t)r0 * groups; b0 = m0.b + (size_t)r0 * groups;
+            s1 = m1.s + (size_t)r1 * groups; b1 = m1.b + (size_t)r1 * groups;
+        }
+        // B: chunk c of rows (tid >> 3) + 64 j
         const uint32_t bc = tid & 7;
-        const __half *bsrc[4];
-        uint32_t bdst[4];
+        const __half *bsrc[2];
+        uint32_t bdst[2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t r = (tid >> 3) + 32 * j;
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t r = (tid >> 3) + 64 * j;
             bdst[j] = sw128_offset(r, bc);
             if (r < count) {
                 size_t src_row;
-                if (PHASE == 0) src_row = p.shared ? item.start + r : p.sorted_pair[item.start + r] / p.top_k;
-                else src_row = item.start + r;
+                if (PHASE == 1) src_row = item.start + r;
+                else src_row = p.shared ? item.start + r : p.sorted_pair[item.start + r] / p.top_k;
                 bsrc[j] = p.b_rows + src_row * p.b_stride + bc * 8;
             } else {
                 bsrc[j] = nullptr;
             }
         }
-        PackedCodes<BITS> c0 = pf_load_codes<BITS>(w0), c1 = pf_load_codes<BITS>(w1);
-        uint16_t ms0 = s0[0], mb0 = b0[0], ms1 = s1[0], mb1 = b1[0];
-        for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
-            const uint32_t s = kb % kPfStages, ph = (kb / kPfStages) & 1u;
-            const PackedCodes<BITS> cur0 = c0, cur1 = c1;
-            const __half2 sc0 = meta_half2<META>(ms0), bi0 = meta_half2<META>(mb0);
-            const __half2 sc1 = meta_half2<META>(ms1), bi1 = meta_half2<META>(mb1);
-            if (kb + 1 < n_kb) {            // next K block's codes fly while this one is converted
-                c0 = pf_load_codes<BITS>(w0 + (size_t)(kb + 1) * (kPfKBlock * BITS / 8));
-                c1 = pf_load_codes<BITS>(w1 + (size_t)(kb + 1) * (kPfKBlock * BITS / 8));
-                ms0 = s0[kb + 1]; mb0 = b0[kb + 1]; ms1 = s1[kb + 1]; mb1 = b1[kb + 1];
-            }
-            // the stage is free once the MMAs that read it have finished
-            {
-                bool done = false;
-                for (uint32_t it = 0; it < kPfWaitTries && !done; ++it) done = mbar_try_wait(&empty[s], ph ^ 1u);
-                if (!done) { atomicExch(p.status, 1u); ok = false; }
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const uint32_t st = stage0 + s * kPfStageBytes;
+        // codes of the next kPfAhead K blocks wait in registers (the loads fly while earlier blocks are converted)
+        constexpr int CB = BITS == 16 ? 4 : BITS;
+        PackedCodes<CB> c0[kPfAhead], c1[kPfAhead];
+        uint16_t ms0[kPfAhead], mb0[kPfAhead], ms1[kPfAhead], mb1[kPfAhead];
+        auto fetch = [&](int slot, uint32_t kb) {
+            if (BITS == 16 || kb >= n_kb) return;
+            c0[slot] = pf_load_codes<CB>(w0 + (size_t)kb * (kPfKBlock * BITS / 8));
+            c1[slot] = pf_load_codes<CB>(w1 + (size_t)kb * (kPfKBlock * BITS / 8));
+            ms0[slot] = s0[kb]; mb0[slot] = b0[kb]; ms1[slot] = s1[kb]; mb1[slot] = b1[kb];
+        };
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (bsrc[j] != nullptr) cp_async16(st + 2 * kPfTileBytes + bdst[j], bsrc[j] + (size_t)kb * kPfKBlock);
-            dequant_store<BITS>(st, row, half, cur0, sc0, bi0);
-            dequant_store<BITS>(st + kPfTileBytes, row, half, cur1, sc1, bi1);
-            cp_async_wait_all();
-            fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full[s]);
+        for (int i = 0; i < kPfAhead; ++i) fetch(i, i);
+        // The arrival for K block kb is made kPfDefer iterations later, once the cp.async
+        // group of that block has landed: the copies get that long to complete.
+        for (uint32_t it = 0; it < n_kb + kPfDefer && ok; ++it) {
+            if (it < n_kb) {
+                const uint32_t kb = it, s = kb % kPfStages, ph = (kb / kPfStages) & 1u;
+                const PackedCodes<CB> cur0 = c0[0], cur1 = c1[0];
+                __half2 sc0, bi0, sc1, bi1;
+                if (BITS != 16) {
+                    sc0 = meta_half2<META>(ms0[0]); bi0 = meta_half2<META>(mb0[0]);
+                    sc1 = meta_half2<META>(ms1[0]); bi1 = meta_half2<META>(mb1[0]);
+                }
+#pragma unroll
+                for (int i = 0; i + 1 < kPfAhead; ++i) {
+                    c0[i] = c0[i + 1]; c1[i] = c1[i + 1];
+                    ms0[i] = ms0[i + 1]; mb0[i] = mb0[i + 1]; ms1[i] = ms1[i + 1]; mb1[i] = mb1[i + 1];
+                }
+                fetch(kPfAhead - 1, kb + kPfAhead);
+                // the stage is free once the MMAs that read it have finished
+                {
+                    bool done = false;
+                    for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = mbar_try_wait(&empty[s], ph ^ 1u);
+                    if (!done) { atomicExch(p.status, 1u); ok = false; }
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) {
+                    const uint32_t st = stage0 + s * kPfStageBytes;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        if (bsrc[j] != nullptr) cp_async16(st + 2 * kPfTileBytes + bdst[j], bsrc[j] + (size_t)kb * kPfKBlock);
+                    if (BITS == 16) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            cp_async16(st + sw128_offset(row, quarter * 2 + j), w0 + (size_t)kb * (kPfKBlock * 2) + j * 16);
+                            cp_async16(st + kPfTileBytes + sw128_offset(row, quarter * 2 + j),
+                                       w1 + (size_t)kb * (kPfKBlock * 2) + j * 16);
+                        }
+                    } else {
+                        dequant_store<CB>(st, row, quarter, cur0, sc0, bi0);
+                        dequant_store<CB>(st + kPfTileBytes, row, quarter, cur1, sc1, bi1);
+                    }
+                }
+            }
+            cp_async_commit();
+            if (it >= kPfDefer && ok) {
+                cp_async_wait_group<kPfDefer>();
+                fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[(it - kPfDefer) % kPfStages]);
+            }
         }
+        cp_async_wait_group<0>();
     } else if (lane == 0) {
         // ---------------- MMA issue: one thread ----------------
         const uint32_t idesc = umma_idesc_f16(kPfTileM, n_cols);
@@ -363,37 +388,35 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_gemm_kernel(PrefillGemm
             if (!done) { atomicExch(p.status, 1u); ok = false; }
         }
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+        const uint32_t q = warp & 3u, cb = (warp >> 2) * 32u;       // lane quarter, 32 columns per warp
+        if (ok && cb < n_cols) {
             tc_fence_after_sync();
-            const uint32_t q = warp & 3u, col_half = warp >> 2;
             const uint32_t lane_addr = tmem + ((q * 32u) << 16);
-            for (uint32_t cb = col_half * 64u; cb < col_half * 64u + 64u && cb < n_cols; cb += 32u) {
-                uint32_t a0[32], a1[32];
-                tmem_ld32(lane_addr + cb, a0);
-                tmem_ld32(lane_addr + kPfTileN + cb, a1);
-                tmem_ld_wait();
-                if (PHASE == 0) {
-                    const uint32_t f = blockIdx.x * kPfTileM + q * 32u + lane;
+            uint32_t a0[32], a1[32];
+            tmem_ld32(lane_addr + cb, a0);
+            tmem_ld32(lane_addr + kPfTileN + cb, a1);
+            tmem_ld_wait();
+            if (PHASE == 0) {
+                const uint32_t f = blockIdx.x * kPfTileM + q * 32u + lane;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t n = cb + i;
-                        if (n < count) {
-                            float g = __uint_as_float(a0[i]), u = __uint_as_float(a1[i]);
-                            if (p.round_gate_up) { g = round_mid<OUT>(g); u = round_mid<OUT>(u); }
-                            store_mid<OUT>(p.out, (size_t)(item.start + n) * p.out_stride + f, hidden_act(g, p.act) * u);
-                        }
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t n = cb + i;
+                    if (n < count) {
+                        float g = __uint_as_float(a0[i]), u = __uint_as_float(a1[i]);
+                        if (p.round_gate_up) { g = round_mid<OUT>(g); u = round_mid<OUT>(u); }
+                        store_mid<OUT>(p.out, (size_t)(item.start + n) * p.out_stride + f, hidden_act(g, p.act) * u);
                     }
-                } else {
-                    const uint32_t d = blockIdx.x * 2 * kPfTileM + q * 32u + lane;
-                    float *out = static_cast<float *>(p.out);
+                }
+            } else {
+                const uint32_t d = blockIdx.x * 2 * kPfTileM + q * 32u + lane;
+                float *out = static_cast<float *>(p.out);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t n = cb + i;
-                        if (n < count) {
-                            const float sc = p.row_scale != nullptr ? p.row_scale[item.start + n] : 1.0f;
-                            out[(size_t)(item.start + n) * p.out_stride + d] = __uint_as_float(a0[i]) * sc;
-                            out[(size_t)(item.start + n) * p.out_stride + d + kPfTileM] = __uint_as_float(a1[i]) * sc;
-                        }
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t n = cb + i;
+                    if (n < count) {
+                        const float sc = (PHASE == 1 && p.row_scale != nullptr) ? p.row_scale[item.start + n] : 1.0f;
+                        out[(size_t)(item.start + n) * p.out_stride + d] = __uint_as_float(a0[i]) * sc;
+                        out[(size_t)(item.start + n) * p.out_stride + d + kPfTileM] = __uint_as_float(a1[i]) * sc;
                     }
                 }
             }
@@ -405,6 +428,19 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_gemm_kernel(PrefillGemm
         __syncwarp();
         tmem_dealloc(tmem, kPfTmemCols);
     }
+}
+
+// Router for a prefill chunk from the logits the GEMM wrote: one block per token
+// (router_topk_select_k8 semantics, moe.metal:233-285; prefill_router_block :402-417).
+struct TopkRowsParams {
+    const float *logits; const uint16_t *pes; uint32_t *out_idx; __half *out_w; uint32_t E, K;
+};
+__global__ void __launch_bounds__(256) topk_rows_kernel(TopkRowsParams p) {
+    __shared__ __align__(16) float work[kMaxExperts + 64];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t tok = blockIdx.x;
+    topk_softmax_block(p.logits + tok * p.E, (int)p.E, (int)p.K, p.pes, p.out_idx + tok * p.K, p.out_w + tok * p.K, work);
 }
 
 // ---- operand packing ---------------------------------------------------------------
