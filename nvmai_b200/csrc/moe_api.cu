@@ -568,11 +568,13 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     // gate/up, routed then shared
     g.shared = 0; g.b_rows = c.routed_bits == 4 ? h->pf_x : x; g.b_stride = c.d; g.kdim = c.d;
     g.out = h->acts; g.out_stride = c.f; g.round_gate_up = 0;
+    g.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 0) * kTraceWords : nullptr;
     if ((rc = launch_prefill_gemm<0>(h, c.routed_bits, g, dim3(c.f / kPfTileM, max_items), st))) return rc;
     if (c.shared_f) {
         PrefillGemmParams s = g;
         s.shared = 1; s.s0 = to_mat(lv.w.shared_gate_proj); s.s1 = to_mat(lv.w.shared_up_proj);
         s.b_rows = c.shared_bits == 4 ? h->pf_x : x; s.out = h->shared_act; s.out_stride = c.shared_f; s.round_gate_up = 1;
+        s.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 2) * kTraceWords : nullptr;
         if ((rc = launch_prefill_gemm<0>(h, c.shared_bits, s, dim3(c.shared_f / kPfTileM, shared_items), st))) return rc;
     }
     // activation rows as the down GEMMs read them
@@ -589,12 +591,13 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     // down, routed then shared
     g.b_rows = acts16; g.b_stride = c.f; g.kdim = c.f; g.row_scale = wide ? h->pf_rowscale : nullptr;
     g.out = h->partial; g.out_stride = c.d;
+    g.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 1) * kTraceWords : nullptr;
     if ((rc = launch_prefill_gemm<1>(h, c.routed_bits, g, dim3(c.d / (2 * kPfTileM), max_items), st))) return rc;
     if (c.shared_f) {
         PrefillGemmParams s = g;
         s.shared = 1; s.s0 = to_mat(lv.w.shared_down_proj); s.s1 = s.s0;
         s.b_rows = sacts16; s.b_stride = c.shared_f; s.kdim = c.shared_f; s.row_scale = wide ? h->pf_srowscale : nullptr;
-        s.out = h->shared_partial;
+        s.out = h->shared_partial; s.trace = nullptr;
         if ((rc = launch_prefill_gemm<1>(h, c.shared_bits, s, dim3(c.d / (2 * kPfTileM), shared_items), st))) return rc;
     }
     CombineParams pc{};

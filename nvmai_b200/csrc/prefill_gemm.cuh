@@ -40,20 +40,23 @@
 #include "grouped_decode.cuh"
 #include "tma.cuh"
 
+#include <type_traits>
+
 namespace nvmai {
 
 constexpr int kPfTileM = 128;                 // weight rows per accumulator
-constexpr int kPfTileN = 128;                 // most token rows per work item
+constexpr int kPfTileN = 256;                 // most token rows per work item
 constexpr int kPfKBlock = 64;                 // K values per pipeline stage
-constexpr int kPfStages = 4;
+constexpr int kPfStages = 3;
 constexpr int kPfProducerWarps = 16;
 constexpr int kPfAhead = 3;                   // K blocks of packed codes a producer holds in registers
-constexpr int kPfDefer = 2;                   // iterations between issuing a stage's copies and announcing it
+constexpr int kPfDefer = 1;                   // steps between issuing a stage's copies and announcing it
 constexpr int kPfProducers = kPfProducerWarps * 32;
 constexpr int kPfThreads = kPfProducers + 32;
-constexpr uint32_t kPfTmemCols = 256;         // two fp32 accumulators of up to 128 columns
-constexpr int kPfTileBytes = 128 * 128;       // 128 rows x 64 fp16
-constexpr int kPfStageBytes = 3 * kPfTileBytes;
+constexpr uint32_t kPfTmemCols = 512;         // two fp32 accumulators of up to 256 columns: all of an SM's tensor memory
+constexpr int kPfTileBytes = 128 * 128;       // an A tile: 128 rows x 64 fp16
+constexpr int kPfBTileBytes = kPfTileN * 128; // the B tile: up to 256 rows x 64 fp16
+constexpr int kPfStageBytes = 2 * kPfTileBytes + kPfBTileBytes;
 constexpr size_t kPfSmemBytes = 1024 /* alignment slack */ + 1024 /* barriers */ + (size_t)kPfStages * kPfStageBytes;
 constexpr uint32_t kPfWaitTries = 1u << 16;
 
@@ -139,36 +142,51 @@ template <int META> __device__ __forceinline__ __half2 meta_half2(uint16_t bits)
     return __float2half2_rn(__uint_as_float(((uint32_t)bits) << 16));
 }
 
-// 16 codes (one producer thread's share of a K block) -> 2 swizzled 16-byte chunks.
+// 32 codes of one matrix row (one producer thread's share of a K block) -> 4 swizzled 16-byte chunks.
 template <int BITS>
-struct PackedCodes { uint32_t v[BITS == 4 ? 2 : 4]; };
+struct PackedCodes { uint32_t v[BITS]; };
 
 template <int BITS>
-__device__ __forceinline__ PackedCodes<BITS> pf_load_codes(const uint8_t *p) {
-    PackedCodes<BITS> c;
-    if (BITS == 4) { const uint2 q = ldg_stream_u2(p); c.v[0] = q.x; c.v[1] = q.y; }
-    else { const uint4 q = ldg_stream_u4(p); c.v[0] = q.x; c.v[1] = q.y; c.v[2] = q.z; c.v[3] = q.w; }
-    return c;
+__device__ __forceinline__ void pf_load_codes(PackedCodes<BITS> &c, const uint8_t *p) {
+#pragma unroll
+    for (int i = 0; i < BITS / 4; ++i) {
+        const uint4 q = ldg_stream_u4(p + 16 * i);
+        c.v[4 * i] = q.x; c.v[4 * i + 1] = q.y; c.v[4 * i + 2] = q.z; c.v[4 * i + 3] = q.w;
+    }
 }
 
+// dst[j]: shared-window address of the thread's j-th chunk in the stage's tile.
+// 4-bit: the nibbles of a word are masked where they lie, (1024 + q) for nibbles 0, 4, 2, 6 (after one
+// shift by 8 for the latter two) and (1024 + 16 q) for nibbles 1, 5, 3, 7; the second kind is multiplied
+// by s / 16 (s16, exact unless s / 16 is an fp16 subnormal), so that one shift serves a whole word.
 template <int BITS>
-__device__ __forceinline__ void dequant_store(uint32_t tile_smem, uint32_t row, uint32_t quarter,
-                                              const PackedCodes<BITS> &c, __half2 s2, __half2 b2) {
+__device__ __forceinline__ void dequant_store(const uint32_t (&dst)[4], const PackedCodes<BITS> &c, __half2 s2, __half2 s16,
+                                              __half2 b2) {
     const __half2 k1024 = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {            // chunk j of this quarter row = codes 8j .. 8j+7 of the thread's 16
+    for (int j = 0; j < 4; ++j) {            // chunk j = codes 8j .. 8j+7 of the thread's 32
         uint32_t o[4];
+        if (BITS == 4) {
+            const uint32_t w = c.v[j], w8 = w >> 8;
+            const uint32_t t[4] = {(w & 0x000F000Fu) | 0x64006400u, (w & 0x00F000F0u) | 0x64006400u,
+                                   (w8 & 0x000F000Fu) | 0x64006400u, (w8 & 0x00F000F0u) | 0x64006400u};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t t;
-            if (BITS == 4) t = ((c.v[j] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;      // (1024 + q_i, 1024 + q_{i+4})
-            else t = __byte_perm(c.v[2 * j + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342 : 0x4140);   // (1024 + q_2i, 1024 + q_2i+1)
-            const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
-            const __half2 v = __hfma2(q, s2, b2);
-            o[i] = *reinterpret_cast<const uint32_t *>(&v);
+            for (int i = 0; i < 4; ++i) {    // (q_i, q_{i+4})
+                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t[i]), k1024);
+                const __half2 v = __hfma2(q, (i & 1) ? s16 : s2, b2);
+                o[i] = *reinterpret_cast<const uint32_t *>(&v);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {    // (q_2i, q_2i+1)
+                const uint32_t t = __byte_perm(c.v[2 * j + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342 : 0x4140);
+                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
+                const __half2 v = __hfma2(q, s2, b2);
+                o[i] = *reinterpret_cast<const uint32_t *>(&v);
+            }
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_smem + sw128_offset(row, quarter * 2 + j)),
-                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst[j]), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                     : "memory");
     }
 }
 
@@ -176,7 +194,7 @@ struct PrefillGemmParams {
     // routed items: blobs + offsets; shared / router items: the tensors themselves
     const uint8_t *experts; unsigned long long stride; uint32_t num_experts; ExpertOffsets off;
     AffineMat s0, s1;              // direct tensors: phase 0 gate, up; phase 1 down; phase 2 the router matrix (s0)
-    uint32_t shared;               // 1: item y = token rows [128 y, 128 y + 128), weights from s0/s1
+    uint32_t shared;               // 1: item y = token rows [256 y, 256 y + 256), weights from s0/s1
     const WorkItem *work; const uint32_t *n_work; const uint32_t *sorted_pair;
     uint32_t tokens, top_k;
     const __half *b_rows; uint32_t b_stride;   // phase 0, 2: x rows by token; phase 1: packed activation rows by position
@@ -187,6 +205,7 @@ struct PrefillGemmParams {
     uint32_t act;                  // activation kind (phase 0)
     uint32_t round_gate_up;        // phase 0: round gate and up before the activation (the shared expert does)
     unsigned int *status;
+    unsigned long long *trace;     // optional timeline of block (0, 0): start, end, marks (setup, loop, MMAs done, epilogue)
 };
 
 // BITS: 4 / 8 = affine codes dequantised by the producers, 16 = dense fp16 rows copied as they are.
@@ -208,6 +227,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
     pdl_wait();
     pdl_launch_dependents();
     if (*reinterpret_cast<volatile unsigned int *>(p.status) != 0u) return;    // an earlier wait gave up: do not pile on
+    trace_begin(p.trace);
     WorkItem item;
     if (p.shared) {
         item.expert = kSharedExpertId;
@@ -227,8 +247,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
         mbar_fence_init();
     }
     // B rows past the item's count are never written: clear every stage's B tile once
-    for (int i = tid; i < kPfStages * kPfTileBytes / 16; i += kPfThreads) {
-        const int s = i / (kPfTileBytes / 16), o = i % (kPfTileBytes / 16);
+    for (int i = tid; i < kPfStages * kPfBTileBytes / 16; i += kPfThreads) {
+        const int s = i / (kPfBTileBytes / 16), o = i % (kPfBTileBytes / 16);
         *reinterpret_cast<uint4 *>(gen + 1024 + (size_t)s * kPfStageBytes + 2 * kPfTileBytes + (size_t)o * 16) = make_uint4(0, 0, 0, 0);
     }
     fence_proxy_async_smem();
@@ -241,122 +261,115 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
     tc_fence_after_sync();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     bool ok = true;
+    trace_mark(p.trace, 0);
 
     if (warp < kPfProducerWarps) {
         // ---------------- producers ----------------
-        const uint32_t row = tid >> 2, quarter = tid & 3;       // 16 K values of one row per matrix and K block
+        // thread -> (matrix, row, half row): 32 K values of one row of one of the two A tiles per K block
+        const uint32_t mat = tid >> 8, row = (tid & 255) >> 1, half = tid & 1;
         const size_t row_bytes = (size_t)p.kdim * BITS / 8;
         const uint32_t groups = p.kdim / kGroup;
-        AffineMat m0, m1;
-        uint32_t r0, r1;          // matrix rows this thread converts
+        AffineMat m;
+        uint32_t r;               // matrix row this thread converts
         if (PHASE == 0) {
-            r0 = r1 = blockIdx.x * kPfTileM + row;
-            if (p.shared) { m0 = p.s0; m1 = p.s1; }
+            r = blockIdx.x * kPfTileM + row;
+            if (p.shared) m = mat ? p.s1 : p.s0;
             else {
                 const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
-                m0 = AffineMat{blob + p.off.o[0], reinterpret_cast<const uint16_t *>(blob + p.off.o[1]),
-                               reinterpret_cast<const uint16_t *>(blob + p.off.o[2])};
-                m1 = AffineMat{blob + p.off.o[3], reinterpret_cast<const uint16_t *>(blob + p.off.o[4]),
-                               reinterpret_cast<const uint16_t *>(blob + p.off.o[5])};
+                const int o = mat ? 3 : 0;
+                m = AffineMat{blob + p.off.o[o], reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 1]),
+                              reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 2])};
             }
         } else {
-            r0 = blockIdx.x * 2 * kPfTileM + row;
-            r1 = r0 + kPfTileM;
-            if (p.shared) { m0 = p.s0; }
+            r = blockIdx.x * 2 * kPfTileM + mat * kPfTileM + row;
+            if (p.shared) m = p.s0;
             else {
                 const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
-                m0 = AffineMat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
-                               reinterpret_cast<const uint16_t *>(blob + p.off.o[8])};
+                m = AffineMat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
+                              reinterpret_cast<const uint16_t *>(blob + p.off.o[8])};
             }
-            m1 = m0;
         }
-        const uint8_t *w0 = m0.w + (size_t)r0 * row_bytes + quarter * (BITS * 2);     // 16 values = BITS*2 bytes
-        const uint8_t *w1 = m1.w + (size_t)r1 * row_bytes + quarter * (BITS * 2);
-        const uint16_t *s0 = nullptr, *b0 = nullptr, *s1 = nullptr, *b1 = nullptr;
-        if (BITS != 16) {
-            s0 = m0.s + (size_t)r0 * groups; b0 = m0.b + (size_t)r0 * groups;
-            s1 = m1.s + (size_t)r1 * groups; b1 = m1.b + (size_t)r1 * groups;
-        }
+        const uint8_t *wsrc = m.w + (size_t)r * row_bytes + half * (BITS * 4);      // 32 values = BITS*4 bytes
+        const uint16_t *ssrc = nullptr, *bsrc_meta = nullptr;
+        if (BITS != 16) { ssrc = m.s + (size_t)r * groups; bsrc_meta = m.b + (size_t)r * groups; }
+        uint32_t adst[4];          // offsets of the thread's four chunks inside a stage
+#pragma unroll
+        for (int j = 0; j < 4; ++j) adst[j] = mat * kPfTileBytes + sw128_offset(row, half * 4 + j);
         // B: chunk c of rows (tid >> 3) + 64 j
         const uint32_t bc = tid & 7;
-        const __half *bsrc[2];
-        uint32_t bdst[2];
+        const __half *bsrc[4];
+        uint32_t bdst[4];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const uint32_t r = (tid >> 3) + 64 * j;
-            bdst[j] = sw128_offset(r, bc);
-            if (r < count) {
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t br = (tid >> 3) + 64 * j;
+            bdst[j] = 2 * kPfTileBytes + sw128_offset(br, bc);
+            if (br < count) {
                 size_t src_row;
-                if (PHASE == 1) src_row = item.start + r;
-                else src_row = p.shared ? item.start + r : p.sorted_pair[item.start + r] / p.top_k;
+                if (PHASE == 1) src_row = item.start + br;
+                else src_row = p.shared ? item.start + br : p.sorted_pair[item.start + br] / p.top_k;
                 bsrc[j] = p.b_rows + src_row * p.b_stride + bc * 8;
             } else {
                 bsrc[j] = nullptr;
             }
         }
-        // codes of the next kPfAhead K blocks wait in registers (the loads fly while earlier blocks are converted)
+        // The codes of K block kb + kPfAhead are requested while block kb is converted (slot kb % kPfAhead,
+        // compile-time because the K loop is unrolled by the number of stages); the B rows go straight to
+        // shared memory with cp.async, and the stage is announced one step later, when that group has landed.
         constexpr int CB = BITS == 16 ? 4 : BITS;
-        PackedCodes<CB> c0[kPfAhead], c1[kPfAhead];
-        uint16_t ms0[kPfAhead], mb0[kPfAhead], ms1[kPfAhead], mb1[kPfAhead];
-        auto fetch = [&](int slot, uint32_t kb) {
+        PackedCodes<CB> codes[kPfAhead];
+        uint16_t ms[kPfAhead], mb[kPfAhead];
+        auto fetch = [&](PackedCodes<CB> &c, uint16_t &s_, uint16_t &b_, uint32_t kb) {
             if (BITS == 16 || kb >= n_kb) return;
-            c0[slot] = pf_load_codes<CB>(w0 + (size_t)kb * (kPfKBlock * BITS / 8));
-            c1[slot] = pf_load_codes<CB>(w1 + (size_t)kb * (kPfKBlock * BITS / 8));
-            ms0[slot] = s0[kb]; mb0[slot] = b0[kb]; ms1[slot] = s1[kb]; mb1[slot] = b1[kb];
+            pf_load_codes<CB>(c, wsrc + (size_t)kb * (kPfKBlock * BITS / 8));
+            s_ = ssrc[kb]; b_ = bsrc_meta[kb];
         };
 #pragma unroll
-        for (int i = 0; i < kPfAhead; ++i) fetch(i, i);
-        // The arrival for K block kb is made kPfDefer iterations later, once the cp.async
-        // group of that block has landed: the copies get that long to complete.
-        for (uint32_t it = 0; it < n_kb + kPfDefer && ok; ++it) {
-            if (it < n_kb) {
-                const uint32_t kb = it, s = kb % kPfStages, ph = (kb / kPfStages) & 1u;
-                const PackedCodes<CB> cur0 = c0[0], cur1 = c1[0];
-                __half2 sc0, bi0, sc1, bi1;
-                if (BITS != 16) {
-                    sc0 = meta_half2<META>(ms0[0]); bi0 = meta_half2<META>(mb0[0]);
-                    sc1 = meta_half2<META>(ms1[0]); bi1 = meta_half2<META>(mb1[0]);
-                }
-#pragma unroll
-                for (int i = 0; i + 1 < kPfAhead; ++i) {
-                    c0[i] = c0[i + 1]; c1[i] = c1[i + 1];
-                    ms0[i] = ms0[i + 1]; mb0[i] = mb0[i + 1]; ms1[i] = ms1[i + 1]; mb1[i] = mb1[i + 1];
-                }
-                fetch(kPfAhead - 1, kb + kPfAhead);
-                // the stage is free once the MMAs that read it have finished
-                {
-                    bool done = false;
-                    for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = mbar_try_wait(&empty[s], ph ^ 1u);
-                    if (!done) { atomicExch(p.status, 1u); ok = false; }
-                }
+        for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], mb[i], i);
+        // One step = one K block into stage S (compile-time), using code slot C (compile-time).
+        auto step = [&](auto S, auto C, uint32_t kb) {
+            constexpr uint32_t s = decltype(S)::value;
+            constexpr int cs = decltype(C)::value;
+            const uint32_t ph = (kb / kPfStages) & 1u;
+            if (kb < n_kb) {
+                bool done = false;      // the stage is free once the MMAs that read it have finished
+                for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = mbar_try_wait(&empty[s], ph ^ 1u);
+                if (!done) { atomicExch(p.status, 1u); ok = false; }
                 ok = __all_sync(0xffffffffu, ok);
                 if (ok) {
                     const uint32_t st = stage0 + s * kPfStageBytes;
 #pragma unroll
-                    for (int j = 0; j < 2; ++j)
-                        if (bsrc[j] != nullptr) cp_async16(st + 2 * kPfTileBytes + bdst[j], bsrc[j] + (size_t)kb * kPfKBlock);
+                    for (int j = 0; j < 4; ++j)
+                        if (bsrc[j] != nullptr) cp_async16(st + bdst[j], bsrc[j] + (size_t)kb * kPfKBlock);
                     if (BITS == 16) {
 #pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            cp_async16(st + sw128_offset(row, quarter * 2 + j), w0 + (size_t)kb * (kPfKBlock * 2) + j * 16);
-                            cp_async16(st + kPfTileBytes + sw128_offset(row, quarter * 2 + j),
-                                       w1 + (size_t)kb * (kPfKBlock * 2) + j * 16);
-                        }
+                        for (int j = 0; j < 4; ++j) cp_async16(st + adst[j], wsrc + (size_t)kb * (kPfKBlock * 2) + j * 16);
                     } else {
-                        dequant_store<CB>(st, row, quarter, cur0, sc0, bi0);
-                        dequant_store<CB>(st + kPfTileBytes, row, quarter, cur1, sc1, bi1);
+                        const __half2 sc = meta_half2<META>(ms[cs]), bi = meta_half2<META>(mb[cs]);
+                        const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f));
+                        const uint32_t d4[4] = {st + adst[0], st + adst[1], st + adst[2], st + adst[3]};
+                        dequant_store<CB>(d4, codes[cs], sc, sc16, bi);
+                        fetch(codes[cs], ms[cs], mb[cs], kb + kPfAhead);      // the slot is free again
                     }
                 }
             }
             cp_async_commit();
-            if (it >= kPfDefer && ok) {
+            // the arrival for K block kb - kPfDefer: its cp.async group has had kPfDefer steps to land
+            if (kb >= (uint32_t)kPfDefer && kb < n_kb + kPfDefer && ok) {
                 cp_async_wait_group<kPfDefer>();
                 fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's reads
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full[(it - kPfDefer) % kPfStages]);
+                constexpr uint32_t sa = (s + kPfStages - kPfDefer) % kPfStages;
+                if (lane == 0) mbar_arrive(&full[sa]);
             }
+        };
+        static_assert(kPfStages == 3 && kPfAhead == 3, "the unrolled body below is written for 3 stages and 3 code slots");
+        for (uint32_t kb = 0; kb < n_kb + kPfDefer && ok; kb += 3) {
+            step(std::integral_constant<uint32_t, 0>{}, std::integral_constant<int, 0>{}, kb);
+            step(std::integral_constant<uint32_t, 1>{}, std::integral_constant<int, 1>{}, kb + 1);
+            step(std::integral_constant<uint32_t, 2>{}, std::integral_constant<int, 2>{}, kb + 2);
         }
         cp_async_wait_group<0>();
+        trace_mark(p.trace, 1);
     } else if (lane == 0) {
         // ---------------- MMA issue: one thread ----------------
         const uint32_t idesc = umma_idesc_f16(kPfTileM, n_cols);
@@ -388,9 +401,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
             if (!done) { atomicExch(p.status, 1u); ok = false; }
         }
         ok = __all_sync(0xffffffffu, ok);
-        const uint32_t q = warp & 3u, cb = (warp >> 2) * 32u;       // lane quarter, 32 columns per warp
-        if (ok && cb < n_cols) {
-            tc_fence_after_sync();
+        const uint32_t q = warp & 3u;                               // lane quarter of the accumulator this warp may read
+        if (ok) tc_fence_after_sync();
+        trace_mark(p.trace, 2);
+        for (uint32_t cb = (warp >> 2) * 64u; ok && cb < (warp >> 2) * 64u + 64u && cb < n_cols; cb += 32u) {
             const uint32_t lane_addr = tmem + ((q * 32u) << 16);
             uint32_t a0[32], a1[32];
             tmem_ld32(lane_addr + cb, a0);
@@ -404,7 +418,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
                     if (n < count) {
                         float g = __uint_as_float(a0[i]), u = __uint_as_float(a1[i]);
                         if (p.round_gate_up) { g = round_mid<OUT>(g); u = round_mid<OUT>(u); }
-                        store_mid<OUT>(p.out, (size_t)(item.start + n) * p.out_stride + f, hidden_act(g, p.act) * u);
+                        // exp and the quotient through the fast intrinsics (2 ulp): far below the fp16 operand rounding
+                        const float a = p.act == ACT_SILU ? __fdividef(g, 1.0f + __expf(-g)) : act_gelu_tanh(g);
+                        store_mid<OUT>(p.out, (size_t)(item.start + n) * p.out_stride + f, a * u);
                     }
                 }
             } else {
@@ -422,12 +438,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
             }
         }
     }
+    trace_mark(p.trace, 3);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == kPfProducerWarps) {
         __syncwarp();
         tmem_dealloc(tmem, kPfTmemCols);
     }
+    trace_end(p.trace);
 }
 
 // Router for a prefill chunk from the logits the GEMM wrote: one block per token
