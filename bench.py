@@ -560,6 +560,11 @@ def run_prefill(args) -> None:
     print(json.dumps(rec), flush=True)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one stage2_kernel launch from the ncu capture summarised in
+# profiles/decode_stage_kernels_4bit_ncu_full.md (the 8-bit kernel has not been captured)
+STAGE2_DRAM_BYTES_PER_LAUNCH = {4: 9508352, 8: None}
+
+
 def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> dict:
     """Times the dominant kernel (routed gate/up + activation) alone: one launch per
     layer with that layer's own experts (40 x 9.4 MB at 4-bit, larger than L2),
@@ -593,10 +598,7 @@ def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> di
     us = start.elapsed_time(end) * 1e3 / (reps * len(plans))
     nbytes = stage2_bytes(args.bits, 4)
     achieved = nbytes / (us * 1e-6) / 1e9
-    traffic = None
-    tp = ROOT / "profiles" / "stage2_traffic.json"
-    if tp.exists():
-        traffic = json.loads(tp.read_text()).get(f"{args.bits}bit_bytes_per_launch")
+    traffic = STAGE2_DRAM_BYTES_PER_LAUNCH.get(args.bits)
     return {"bound": "hbm", "kernel": "stage2_kernel (routed gate/up + activation)", "achieved": achieved, "peak": peak,
             "peak_source": which, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
             "bytes_per_launch": nbytes, "us_per_launch": us}
