@@ -159,7 +159,10 @@ NVMAI_API int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, co
  * (MoE.swift:295-392; moe.metal:642-727, 812-861):
  * acts[slot*f + j] = half(act(gate_slot[j].x) * (up_slot[j].x)) for the 8 blobs
  * in `blobs_host` (host array of 8 device pointers, the argument-buffer of
- * MoE.swift:215-227).  active_slots_host NULL = all slots. */
+ * MoE.swift:215-227).  active_slots_host NULL = all slots.  The acts buffer holds
+ * fp16 values with out_dtype = NVMAI_OUT_FP16 and fp32 values rounded to 11
+ * significant bits with NVMAI_OUT_FP32 (top_k * f elements either way); phase 2
+ * reads the same type. */
 NVMAI_API int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_host,
                                  const nvmai_expert_offsets *offsets, const void *x_f16, void *acts_f16,
                                  const uint32_t *active_slots_host, uint32_t active_count, void *stream);
