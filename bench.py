@@ -486,6 +486,97 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
     note("process group closed")
 
 
+def run_batch_layer(args) -> None:
+    """configs[1] / configs[4]: ONE layer, a batch of `--tokens` independent rows through the batched decode
+    kernels (rows that picked the same expert share one read of its weights).  Rotates over 16 independently
+    seeded layers so that the working set exceeds L2.  `--zipf S` replaces the router's choice by expert ids
+    drawn with popularity ~ rank^-S over a seeded permutation (configs[4]); the routed kernels then run from
+    the given ids (`nvmai_cuda_moe_routed_partial`), router and shared expert left out."""
+    import torch
+    from nvmai_b200 import MoE, MoEConfig, launch_count, synthetic
+    from nvmai_b200 import format as fmt
+    from nvmai_b200.ep import ExpertPlacement
+    torch.cuda.set_device(0)
+    tokens, n_layers = args.tokens, 16
+    cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
+                    router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16,
+                    meta_dtype=fmt.META_BF16, activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32,
+                    max_tokens=tokens, num_layers=n_layers)
+    moe = MoE(cfg)
+    devs = []
+    for l in range(n_layers):
+        dev = synthetic.device_layer(3000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits,
+                                     meta=fmt.META_BF16)
+        synthetic.register_device_layer(moe, l, dev)
+        devs.append(dev)
+    stream = torch.cuda.Stream()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11)
+    x = torch.randn(tokens, D, device="cuda", generator=gen).to(torch.float16)
+    y = torch.empty(tokens, D, dtype=torch.float32, device="cuda")
+    idx = torch.empty(tokens, K, dtype=torch.int32, device="cuda")
+    w = torch.empty(tokens, K, dtype=torch.float16, device="cuda")
+    zipf = args.zipf > 0
+    if zipf:
+        rng = np.random.default_rng(4)
+        perm = rng.permutation(E)
+        p = (np.arange(1, E + 1, dtype=np.float64) ** -args.zipf)
+        p /= p.sum()
+        ids = np.stack([perm[rng.choice(E, size=K, replace=False, p=p)] for _ in range(tokens)]).astype(np.int32)
+        idx.copy_(torch.from_numpy(ids))
+        w.fill_(1.0 / K)
+
+    def step(i: int) -> None:
+        if zipf:
+            moe.routed_partial(i % n_layers, x, tokens, idx, w, y, stream=stream)
+        else:
+            moe.layer_decode(i % n_layers, x, tokens, h2_out=y, out_idx=idx, out_w=w, stream=stream)
+
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        stream.synchronize()
+        sampler = ClockSampler(0)
+        l0 = launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(args.steps):
+            step(i)
+        end.record(stream)
+        stream.synchronize()
+        launches = launch_count() - l0
+        ms = start.elapsed_time(end) / args.steps
+        clocks = sampler.stop()
+    assert torch.isfinite(y).all(), "non-finite output"
+    ids = idx.cpu().numpy()
+    distinct = int(np.unique(ids).size)
+    blob = expert_bytes(args.bits)
+    nbytes = distinct * blob + tokens * (D * 2 + D * 4)
+    if not zipf:
+        nbytes += blob + E * D * 2 + D * 2           # shared expert, fp16 router, gate row
+    peak, which = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    load = {}
+    counts = np.bincount(ids.ravel(), minlength=E)
+    for n in (2, 4, 8):
+        for mode in ("contiguous", "strided"):
+            per = ExpertPlacement(E, n, mode).pairs_per_rank(ids.ravel())
+            load[f"{mode}{n}"] = round(max(per) / (sum(per) / n), 3)
+    rec = {"metric": "moe_ffn_layer_batch_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+           "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "data": "synthetic", "scaling": "weak",
+           "dtype": "f16xu%d->f32" % args.bits, "value": tokens / (ms * 1e-3), "ms_per_step": ms, "clocks": clocks,
+           "gpu_launches": int(launches),
+           "config": {"workload": ("configs[4]: one layer, %d rows, Zipf(%.1f) routing, routed experts only" % (tokens, args.zipf))
+                      if zipf else ("configs[1]: one layer, %d independent rows, router + routed + shared" % tokens),
+                      "d": D, "f": F, "experts": E, "top_k": K, "bits": args.bits, "layers_rotated": n_layers,
+                      "distinct_experts": distinct, "hottest_expert_rows": int(counts.max()),
+                      "max_over_mean_pairs_per_gpu": load},
+           "roofline": {"bound": "hbm", "kernel": "whole layer call (each distinct expert's bytes counted once)",
+                        "achieved": gbs, "peak": peak, "peak_source": which, "unit": "GB/s", "frac": gbs / peak,
+                        "traffic": None, "bytes_per_step": nbytes}}
+    print(json.dumps(rec), flush=True)
+
+
 def run_prefill(args) -> None:
     """configs[2]: one layer, `--tokens` rows (4096 by default), 4-bit: router, pair grouping, the grouped
     gate/up and down GEMMs on the tensor cores, ordered combine.  Rotates over `--layers` independently seeded
@@ -616,6 +707,10 @@ def main() -> None:
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
+    ap.add_argument("--batch-layer", action="store_true",
+                    help="measure configs[1] (one layer, --tokens independent rows, batched decode kernels) or, with "
+                         "--zipf, configs[4] instead of the decode stack")
+    ap.add_argument("--zipf", type=float, default=0.0, help="with --batch-layer: Zipf exponent of the expert popularity")
     ap.add_argument("--prefill", action="store_true",
                     help="measure configs[2] (a prefill chunk through the tensor-core grouped GEMMs) instead of the "
                          "decode stack; --tokens defaults to 4096 and --layers to 2 here")
@@ -626,7 +721,9 @@ def main() -> None:
     ap.add_argument("--deadline", type=float, default=600.0,
                     help="multi-GPU runs: give up (exit 2) after this many seconds instead of waiting on a stuck collective")
     args = ap.parse_args()
-    if args.prefill:
+    if args.batch_layer:
+        run_batch_layer(args)
+    elif args.prefill:
         if args.tokens == 1:
             args.tokens = 4096
         if args.layers == LAYERS:
