@@ -74,6 +74,10 @@ struct nvmai_cuda_moe {
     // NVMAI_CUDA_L2_PREFETCH=1 (measured slower on B200: the prefetch competes with the
     // running stage's own copies); in_layer_chain: stage 3 follows this stage 2
     bool l2_prefetch = false, in_layer_chain = false;
+    // Batches below this run every token's blocks separately; from here on rows are grouped by expert.  Measured on
+    // B200 (8-bit layer): 4 rows 60 us separate / 102 us grouped, 16 rows 190 / 265, 64 rows 697 / 570.
+    // NVMAI_CUDA_GROUPED_MIN overrides it.
+    uint32_t grouped_min_tokens = 24;
     // prefill GEMMs: fp16 operand copies (allocated by the first prefill call)
     __half *pf_x = nullptr;          // [T][D] x rows in the 4-bit unpack's K order
     __half *pf_acts16 = nullptr;     // [T*K][F] routed activations as the down GEMM reads them
@@ -331,7 +335,6 @@ void ep_release(nvmai_cuda_moe *h) {
     h->ep_world = h->ep_rows_own = 0;
 }
 
-constexpr uint32_t kGroupedMinTokens = 4;   // below this every token runs its own blocks
 
 int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, uint32_t tokens,
                        TokenExpertPair *pairs_out, uint32_t *offsets_out, uint32_t *counts_out, bool with_work,
@@ -420,7 +423,7 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
     const LayerViews &lv = h->layers[layer];
     uint32_t *idx = out_idx ? out_idx : h->idx;
     __half *w = out_w ? out_w : h->w;
-    const bool grouped = tokens >= kGroupedMinTokens;
+    const bool grouped = tokens >= h->grouped_min_tokens;
     auto slot = [&](int stage) { return (h->trace_on && !grouped) ? h->trace + ((size_t)layer * 3 + stage) * kTraceWords : nullptr; };
     h->cur_trace = slot(0);
     // single-token path: the expert stages select the experts themselves from the logits
@@ -674,6 +677,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
     h->cfg = c;
     h->layers.resize(c.num_layers);
     if (const char *env = std::getenv("NVMAI_CUDA_L2_PREFETCH")) h->l2_prefetch = env[0] == '1';
+    if (const char *env = std::getenv("NVMAI_CUDA_GROUPED_MIN")) h->grouped_min_tokens = (uint32_t)std::max(1, std::atoi(env));
     const size_t T = c.max_tokens;
     auto alloc = [&](auto **ptr, size_t bytes) -> bool {
         cudaError_t e = cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16);

@@ -180,10 +180,15 @@ __device__ __forceinline__ float sum8_halves(const uint4 &q) {
 // thread ends up with both sums of a feature.  round_gate_up: the shared expert
 // rounds gate and up before the activation (SharedExpertInt4.swift:61-96;
 // dequant_int8.metal:159-163); the routed experts do not (moe.metal:682).
-template <int BITS, int META, int OUT>
+struct NoLateWork { __device__ __forceinline__ void operator()() const {} };
+
+// after_first_tile: called by every thread once the block's first tile has landed (the
+// place for requests that must not compete with the block's own copies).
+template <int BITS, int META, int OUT, typename Late = NoLateWork>
 __device__ __forceinline__ void gate_up_compute(unsigned char *smem, const GateUpLayout &L, int f0, int n_tiles,
                                                 int D, uint32_t act, bool round_gate_up, void *out_base,
-                                                size_t out_row_offset, unsigned int *status) {
+                                                size_t out_row_offset, unsigned int *status,
+                                                Late after_first_tile = Late()) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int groups = D / kGroup;
@@ -192,6 +197,7 @@ __device__ __forceinline__ void gate_up_compute(unsigned char *smem, const GateU
     float *red = reinterpret_cast<float *>(smem + L.red);        // [tile][warp][16]
     const __half *xs = reinterpret_cast<const __half *>(smem + L.xs);
     bool ok = mbar_wait(reinterpret_cast<uint64_t *>(smem), 0, status);      // tile 0 (and x, when it was copied)
+    after_first_tile();
     const bool fast = gpw == 4 && g_end - g_begin == 4 && (groups & 3) == 0;
     if (fast) {
         // x fragments and group sums once, reused by every tile
@@ -460,15 +466,20 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage2_kernel(Stage2Params 
         if (lane == 0) bulk_g2s(smem + L.xs, p.x + (size_t)tok * p.x_stride, p.D * 2, reinterpret_cast<uint64_t *>(smem));
         for (int tile = 1; tile < n_tiles; ++tile)
             issue_gate_up_copies<BITS>(smem, L, tile, gate, up, f0 + tile * kTileFeatures, p.D, 0);
-        if (p.prefetch_down) {
-            // warm the L2 with this block's share of the expert's down projection (stage 3 reads it next)
-            l2_prefetch_slice(blob + p.off.o[6], (size_t)p.D * p.F * BITS / 8, blockIdx.x, gridDim.x, lane);
-            l2_prefetch_slice(blob + p.off.o[7], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
-            l2_prefetch_slice(blob + p.off.o[8], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
-        }
     }
+    const uint8_t *pf_blob = nullptr;
+    if (p.prefetch_down && warp == 0) {
+        pf_blob = p.src.logits != nullptr ? expert_blob(p.src, sel_idx[slot]) : routed_blob(p.src, tok, slot, p.top_k);
+    }
+    // once this block's own tile is in: warm the L2 with its share of the expert's down projection (stage 3 reads it next)
+    auto late = [&]() {
+        if (pf_blob == nullptr) return;
+        l2_prefetch_slice(pf_blob + p.off.o[6], (size_t)p.D * p.F * BITS / 8, blockIdx.x, gridDim.x, lane);
+        l2_prefetch_slice(pf_blob + p.off.o[7], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
+        l2_prefetch_slice(pf_blob + p.off.o[8], (size_t)p.D * (p.F / kGroup) * 2, blockIdx.x, gridDim.x, lane);
+    };
     gate_up_compute<BITS, META, OUT>(smem, L, f0, n_tiles, p.D, p.act, false, p.acts,
-                                     ((size_t)tok * p.top_k + slot) * p.F, p.status);
+                                     ((size_t)tok * p.top_k + slot) * p.F, p.status, late);
     trace_end(p.trace);
 }
 

@@ -304,23 +304,27 @@ def test_layer_decode_reference_format_fp16_out():
     _check_layer(host, cfg, 1, seed=78, tol_gpu_oracle=2e-3)     # one fp16 ulp of the output
 
 
-@pytest.mark.parametrize("tokens", [2, 4, 16, 64])
-def test_layer_decode_batch(tokens):
-    """configs[1]: independent rows, 8-bit; from 4 rows on, rows that picked the same
-    expert are grouped and share one read of its weights"""
+@pytest.mark.parametrize("tokens,grouped_min", [(2, None), (4, None), (16, None), (64, None), (4, 4), (16, 4)])
+def test_layer_decode_batch(tokens, grouped_min, monkeypatch):
+    """configs[1]: independent rows, 8-bit.  Small batches run every row's blocks separately; from 24 rows on
+    (or from NVMAI_CUDA_GROUPED_MIN on) rows that picked the same expert are grouped and share one read of its weights"""
+    if grouped_min is not None:
+        monkeypatch.setenv("NVMAI_CUDA_GROUPED_MIN", str(grouped_min))
     host, cfg = _layer_case(8, fmt.META_FP16, fmt.OUT_FP32, tokens, seed=5)
     _check_layer(host, cfg, tokens, seed=6 + tokens, tol_gpu_oracle=5e-4)
 
 
-def test_layer_decode_batch_4bit_reference_rounding():
+def test_layer_decode_batch_4bit_reference_rounding(monkeypatch):
     """grouped path with the reference's fp16 rounding points and a ragged batch (11 rows)"""
+    monkeypatch.setenv("NVMAI_CUDA_GROUPED_MIN", "4")
     host, cfg = _layer_case(4, fmt.META_BF16, fmt.OUT_FP16, 11, seed=15, router_kind=fmt.ROUTER_AFFINE8,
                             gate_kind=fmt.ROUTER_AFFINE8)
     _check_layer(host, cfg, 11, seed=16, tol_gpu_oracle=2e-3)
 
 
-def test_batched_result_equals_row_by_row():
+def test_batched_result_equals_row_by_row(monkeypatch):
     """grouping must not change a row's result: batch of 9 == nine single-row calls, bitwise"""
+    monkeypatch.setenv("NVMAI_CUDA_GROUPED_MIN", "4")
     host, cfg = _layer_case(4, fmt.META_BF16, fmt.OUT_FP32, 9, seed=41, d=256, f=128, e=32)
     moe = MoE(cfg)
     dl = gu.DeviceLayer(host)
