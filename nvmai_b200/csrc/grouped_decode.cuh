@@ -148,6 +148,113 @@ __global__ void __launch_bounds__(kGroupThreads) group_pairs_kernel(GroupParams 
 }
 
 // ---------------------------------------------------------------------------
+// The same grouping for large pair counts (prefill chunks: 32768 pairs at 4096 rows) as
+// three launches over ceil(P / 1024) blocks: per-block histograms, one block that scans
+// them (offsets, counts, work items, every block's first position per expert), and a
+// stable scatter of each block's 1024 pairs.  Output identical to group_pairs_kernel.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kGroupThreads) group_hist_kernel(GroupParams p, uint32_t *block_hist) {
+    __shared__ uint32_t hist[kMaxExperts];
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t P = p.tokens * p.K;
+    for (int e = threadIdx.x; e < kMaxExperts; e += kGroupThreads) hist[e] = 0;
+    __syncthreads();
+    const uint32_t i = blockIdx.x * kGroupThreads + threadIdx.x;
+    if (i < P) {
+        const uint32_t g = min(p.idx[i], p.E - 1u);
+        const uint32_t e = p.expert_map ? p.expert_map[g] : g;
+        if (e != kNotLocal) atomicAdd(&hist[e], 1u);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kMaxExperts; e += kGroupThreads) block_hist[(size_t)blockIdx.x * kMaxExperts + e] = hist[e];
+}
+
+// one block of kMaxExperts threads: thread e owns expert e.  block_hist[b][e] becomes the first sorted
+// position of block b's pairs of expert e.
+__global__ void __launch_bounds__(kMaxExperts) group_scan_kernel(GroupParams p, uint32_t *block_hist, uint32_t n_blocks) {
+    __shared__ uint32_t warp_tot[kMaxExperts / 32], warp_items[kMaxExperts / 32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+    const uint32_t ppi = p.pairs_per_item ? p.pairs_per_item : (uint32_t)kPairsPerItem;
+    uint32_t total = 0;
+    for (uint32_t b = 0; b < n_blocks; ++b) total += block_hist[(size_t)b * kMaxExperts + e];
+    const uint32_t items = (total + ppi - 1) / ppi;
+    uint32_t pre = total, ipre = items;            // inclusive scans inside the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, pre, o), iv = __shfl_up_sync(0xffffffffu, ipre, o);
+        if (lane >= o) { pre += v; ipre += iv; }
+    }
+    if (lane == 31) { warp_tot[warp] = pre; warp_items[warp] = ipre; }
+    __syncthreads();
+    uint32_t off = pre - total, item_base = ipre - items, all_items = 0;
+    for (int w = 0; w < kMaxExperts / 32; ++w) {
+        if (w < warp) { off += warp_tot[w]; item_base += warp_items[w]; }
+        all_items += warp_items[w];
+    }
+    if ((uint32_t)e < p.n_local) {
+        p.expert_counts[e] = total;
+        p.expert_offsets[e] = total ? off : 0xFFFFFFFFu;
+        if (p.work != nullptr) {
+            const uint32_t even = items ? total / items : 0, extra = items ? total % items : 0;
+            for (uint32_t j = 0; j < items; ++j) {
+                if (p.even_split) {
+                    p.work[item_base + j] = WorkItem{(uint32_t)e, off + j * even + min(j, extra), even + (j < extra ? 1u : 0u), 0};
+                } else {
+                    const uint32_t s = j * ppi;
+                    p.work[item_base + j] = WorkItem{(uint32_t)e, off + s, min(ppi, total - s), 0};
+                }
+            }
+        }
+    }
+    if (e == 0 && p.n_work != nullptr) { p.n_work[0] = all_items; p.n_work[1] = all_items + p.shared_chunks; }
+    if (p.work != nullptr && p.shared_chunks != 0)
+        for (uint32_t j = e; j < p.shared_chunks; j += kMaxExperts)
+            p.work[all_items + j] = WorkItem{kSharedExpertId, j * ppi, min(ppi, p.tokens - j * ppi), 0};
+    uint32_t run = off;
+    for (uint32_t b = 0; b < n_blocks; ++b) {
+        const uint32_t c = block_hist[(size_t)b * kMaxExperts + e];
+        block_hist[(size_t)b * kMaxExperts + e] = run;
+        run += c;
+    }
+}
+
+__global__ void __launch_bounds__(kGroupThreads) group_scatter_kernel(GroupParams p, const uint32_t *block_base) {
+    __shared__ uint16_t cnt[kGroupThreads / 32][kMaxExperts];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t P = p.tokens * p.K;
+    for (int i = tid; i < (kGroupThreads / 32) * kMaxExperts; i += kGroupThreads) (&cnt[0][0])[i] = 0;
+    __syncthreads();
+    const uint32_t i = blockIdx.x * kGroupThreads + tid;
+    uint32_t e = kNotLocal;
+    if (i < P) {
+        const uint32_t g = min(p.idx[i], p.E - 1u);
+        e = p.expert_map ? p.expert_map[g] : g;
+    }
+    const bool live = e != kNotLocal;
+    if (i < P && !live) p.inv[i] = kNotLocal;
+    const uint32_t peers = __match_any_sync(0xffffffffu, e);
+    const uint32_t rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (live && rank_in_warp == 0) cnt[warp][e] = (uint16_t)__popc(peers);
+    __syncthreads();
+    if (live) {
+        uint32_t before = 0;
+        for (int w = 0; w < warp; ++w) before += cnt[w][e];
+        const uint32_t pos = block_base[(size_t)blockIdx.x * kMaxExperts + e] + before + rank_in_warp;
+        p.sorted_pair[pos] = i;
+        p.inv[i] = pos;
+        if (p.pairs_out != nullptr) {
+            const uint32_t wb = p.weights ? (uint32_t)__half_as_ushort(p.weights[i]) : 0u;
+            p.pairs_out[pos] = TokenExpertPair{i / p.K, p.idx[i], i % p.K, wb};
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // grouped gate/up: block = (8-feature tile, work item)
 // ---------------------------------------------------------------------------
 struct GroupedGateUpLayout {

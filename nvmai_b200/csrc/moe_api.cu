@@ -59,6 +59,7 @@ struct nvmai_cuda_moe {
     float *partial = nullptr;        // [T*K][D]
     float *shared_partial = nullptr; // [T][D]
     uint32_t max_work = 0;
+    uint32_t *group_hist = nullptr;  // [ceil(T*K / 1024)][256]: per-block expert histograms of the large grouping path
     uint32_t *expert_map = nullptr;  // expert parallelism: global id -> local blob index (device), or null
     uint32_t n_local = 0;
     // optional kernel timeline (the counterpart of the reference's NVMAI_KERNEL_STATS)
@@ -79,7 +80,8 @@ struct nvmai_cuda_moe {
     // NVMAI_CUDA_GROUPED_MIN overrides it.
     uint32_t grouped_min_tokens = 24;
     // prefill GEMMs: fp16 operand copies (allocated by the first prefill call)
-    __half *pf_x = nullptr;          // [T][D] x rows in the 4-bit unpack's K order
+    __half *pf_x = nullptr;          // [T*K][D] x rows gathered into sorted pair order, in the weights' K order
+    __half *pf_xn = nullptr;         // [T][D] x rows in token order (shared expert), in its weights' K order
     __half *pf_acts16 = nullptr;     // [T*K][F] routed activations as the down GEMM reads them
     __half *pf_sacts16 = nullptr;    // [T][Fs] the shared expert's
     float *pf_rowscale = nullptr, *pf_srowscale = nullptr;   // per row: power of two taken out of a wide-range row
@@ -189,9 +191,9 @@ cudaError_t ensure_smem(Kern kern, size_t bytes) {
 
 // pdl: launch with programmatic stream serialization, so that the kernel's
 // prologue (its weight copies) may overlap the previous kernel's tail.
-template <typename Kern, typename Params>
+template <typename Kern, typename... Params>
 int launch_kernel(nvmai_cuda_moe *h, Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
-                  const Params &p) {
+                  const Params &...p) {
     cudaError_t e = ensure_smem(kern, smem);
     if (e != cudaSuccess) return record(h, e);
     cudaLaunchConfig_t cfg{};
@@ -204,7 +206,7 @@ int launch_kernel(nvmai_cuda_moe *h, Kern kern, dim3 grid, dim3 block, size_t sm
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, kern, p);
+    e = cudaLaunchKernelEx(&cfg, kern, p...);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return record(h, e);
 }
@@ -353,6 +355,15 @@ int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, 
     g.expert_map = use_map ? h->expert_map : nullptr;
     g.n_local = (use_map && h->expert_map) ? h->n_local : c.num_experts;
     g.pairs_per_item = pairs_per_item; g.even_split = even_split ? 1u : 0u;
+    const uint32_t P = tokens * c.top_k;
+    if (P > 4 * kGroupThreads) {          // large pair counts: histogram / scan / scatter over P / 1024 blocks
+        const uint32_t n_blocks = (P + kGroupThreads - 1) / kGroupThreads;
+        int rc = launch_kernel(h, group_hist_kernel, dim3(n_blocks), dim3(kGroupThreads), 0, st, pdl, g, h->group_hist);
+        if (rc) return rc;
+        if ((rc = launch_kernel(h, group_scan_kernel, dim3(1), dim3(kMaxExperts), 0, st, true, g, h->group_hist, n_blocks))) return rc;
+        return launch_kernel(h, group_scatter_kernel, dim3(n_blocks), dim3(kGroupThreads), 0, st, true, g,
+                             static_cast<const uint32_t *>(h->group_hist));
+    }
     return launch_kernel(h, group_pairs_kernel, dim3(1), dim3(kGroupThreads), 0, st, pdl, g);
 }
 
@@ -491,31 +502,73 @@ int ensure_prefill_scratch(nvmai_cuda_moe *h) {
     const auto &c = h->cfg;
     const size_t T = c.max_tokens, P = T * c.top_k;
     auto alloc = [&](auto **ptr, size_t bytes) { return cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16) == cudaSuccess; };
-    if (alloc(&h->pf_x, T * c.d * 2) && alloc(&h->pf_acts16, P * c.f * 2) && alloc(&h->pf_sacts16, T * c.shared_f * 2) &&
-        alloc(&h->pf_rowscale, P * 4) && alloc(&h->pf_srowscale, T * 4))
+    if (alloc(&h->pf_x, P * c.d * 2) && alloc(&h->pf_xn, T * c.d * 2) && alloc(&h->pf_acts16, P * c.f * 2) &&
+        alloc(&h->pf_sacts16, T * c.shared_f * 2) && alloc(&h->pf_rowscale, P * 4) && alloc(&h->pf_srowscale, T * 4))
         return NVMAI_CUDA_OK;
     cudaGetLastError();
-    cudaFree(h->pf_x); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
-    h->pf_x = h->pf_acts16 = h->pf_sacts16 = nullptr; h->pf_rowscale = h->pf_srowscale = nullptr;
+    cudaFree(h->pf_x); cudaFree(h->pf_xn); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale);
+    cudaFree(h->pf_srowscale);
+    h->pf_x = h->pf_xn = h->pf_acts16 = h->pf_sacts16 = nullptr; h->pf_rowscale = h->pf_srowscale = nullptr;
     return NVMAI_CUDA_ENOMEM;
 }
 
+// cuTensorMapEncodeTiled, looked up through the runtime (the library does not link libcuda)
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Tensor map over fp16 rows [rows][cols] (row stride in elements), box = 64 values x box_rows rows, 128-byte
+// swizzle, zero fill outside.  Base and row stride must be 16-byte multiples.
+int make_rows_tmap(nvmai_cuda_moe *h, CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t stride_elems,
+                   uint32_t box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return NVMAI_CUDA_ECUDA;
+    if (!aligned16(base) || (stride_elems * 2) % 16 != 0 || cols % kPfKBlock != 0) return NVMAI_CUDA_EINVAL;
+    const cuuint64_t gdim[2] = {cols, rows};
+    const cuuint64_t gstride[1] = {stride_elems * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kPfKBlock, box_rows};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), gdim, gstride, box, estride,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { h->last_cuda_error = (int)r; return NVMAI_CUDA_ECUDA; }
+    return NVMAI_CUDA_OK;
+}
+
+// b_rows: fp16 [b_count][kdim] in work-item order
 template <int PHASE>
-int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParams &p, dim3 grid, cudaStream_t st) {
+int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParams &p, const void *b_rows, uint64_t b_count,
+                        dim3 grid, cudaStream_t st) {
     const auto &c = h->cfg;
+    PrefillGemmArgs args{};
+    args.p = p;
+    int rc = make_rows_tmap(h, &args.tmap_b, b_rows, b_count, p.kdim, p.kdim, kPfBoxRows);
+    if (rc) return rc;
+    args.tmap_a = args.tmap_b;
     return dispatch_bits_meta(bits, c.meta_dtype, [&](auto B, auto M) {
         return dispatch_out(c.out_dtype, [&](auto O) {
             return launch_kernel(h, prefill_gemm_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value, PHASE>,
-                                 grid, dim3(kPfThreads), kPfSmemBytes, st, true, p);
+                                 grid, dim3(kPfThreads), kPfSmemBytes, st, true, args);
         });
     });
 }
 
-// rows of src (out_dtype for intermediates, fp16 for x) -> fp16 rows in the K order the
-// weights of `bits` unpack in; returns the buffer the GEMM should read and its row scales
+// rows of src (out_dtype for intermediates, fp16 for x) -> fp16 rows in the K order the weights of `bits` unpack
+// in; gather != nullptr: output row r comes from source row gather[r] / gather_div
 int launch_pack_rows(nvmai_cuda_moe *h, const void *src, bool src_f32, __half *dst, float *row_scale, uint32_t rows,
-                     uint32_t n, uint32_t bits, cudaStream_t st) {
-    PackRowsParams p{src, dst, src_f32 ? row_scale : nullptr, rows, n, bits == 4 ? 1u : 0u};
+                     uint32_t n, uint32_t bits, cudaStream_t st, const uint32_t *gather = nullptr, uint32_t gather_div = 1) {
+    PackRowsParams p{src, dst, src_f32 ? row_scale : nullptr, rows, n, bits == 4 ? 1u : 0u, gather, gather_div};
     const dim3 grid((rows + 7) / 8), block(256);
     if (src_f32) return launch_kernel(h, pack_rows_kernel<1>, grid, block, 0, st, true, p);
     return launch_kernel(h, pack_rows_kernel<0>, grid, block, 0, st, true, p);
@@ -540,17 +593,18 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     const bool gemm_router = c.router_kind == NVMAI_ROUTER_DENSE_F16 && lv.w.effective_scale == nullptr &&
                              c.num_experts % (2 * kPfTileM) == 0;
     if (gemm_router) {
-        PrefillGemmParams r{};
+        PrefillGemmArgs ra{};
+        PrefillGemmParams &r = ra.p;
         r.shared = 1;
-        r.s0 = AffineMat{static_cast<const uint8_t *>(lv.w.router.w), nullptr, nullptr};
-        r.s1 = r.s0;
-        r.tokens = tokens; r.top_k = c.top_k; r.b_rows = x; r.b_stride = c.d; r.kdim = c.d;
+        r.tokens = tokens; r.top_k = c.top_k; r.kdim = c.d;
         r.out = h->logits; r.out_stride = c.num_experts; r.status = h->status;
+        if ((rc = make_rows_tmap(h, &ra.tmap_b, x, tokens, c.d, c.d, kPfBoxRows))) return rc;
+        if ((rc = make_rows_tmap(h, &ra.tmap_a, lv.w.router.w, c.num_experts, c.d, c.d, kPfTileM))) return rc;
         const dim3 grid(c.num_experts / (2 * kPfTileM), (tokens + kPfTileN - 1) / kPfTileN);
-        if ((rc = launch_kernel(h, prefill_gemm_kernel<16, 0, 0, 2>, grid, dim3(kPfThreads), kPfSmemBytes, st, false, r)))
+        if ((rc = launch_kernel(h, prefill_gemm_kernel<16, 0, 0, 2>, grid, dim3(kPfThreads), kPfSmemBytes, st, false, ra)))
             return rc;
-        TopkRowsParams tk{h->logits, static_cast<const uint16_t *>(lv.w.per_expert_scale), idx, w, c.num_experts, c.top_k};
-        if ((rc = launch_kernel(h, topk_rows_kernel, dim3(tokens), dim3(256), 0, st, true, tk))) return rc;
+        TopkRowsParams tk{h->logits, static_cast<const uint16_t *>(lv.w.per_expert_scale), idx, w, c.num_experts, c.top_k, tokens};
+        if ((rc = launch_kernel(h, topk_rows_kernel, dim3((tokens + 7) / 8), dim3(256), 0, st, true, tk))) return rc;
         if (c.shared_f && (rc = launch_stage1(h, lv, xsrc, tokens, nullptr, nullptr, false, false, true, false, st))) return rc;
     } else if ((rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, false, c.shared_f != 0, false, st))) {
         return rc;
@@ -560,8 +614,10 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     const uint32_t P = tokens * c.top_k;
     const uint32_t max_items = std::min(P, c.num_experts + P / kPfTileN);
     const uint32_t shared_items = (tokens + kPfTileN - 1) / kPfTileN;
-    const bool need_perm = c.routed_bits == 4 || (c.shared_f && c.shared_bits == 4);
-    if (need_perm && (rc = launch_pack_rows(h, x, false, h->pf_x, nullptr, tokens, c.d, 4, st))) return rc;
+    // x rows as the GEMMs read them: gathered into sorted pair order for the routed items (an item's rows are then
+    // one row range of the tensor map), token order for the shared expert; each in its weights' K order
+    if ((rc = launch_pack_rows(h, x, false, h->pf_x, nullptr, P, c.d, c.routed_bits, st, h->sorted_pair, c.top_k))) return rc;
+    if (c.shared_f && (rc = launch_pack_rows(h, x, false, h->pf_xn, nullptr, tokens, c.d, c.shared_bits, st))) return rc;
 
     PrefillGemmParams g{};
     g.experts = static_cast<const uint8_t *>(lv.w.experts); g.stride = lv.w.expert_stride; g.num_experts = c.num_experts;
@@ -569,16 +625,17 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     g.work = h->work; g.n_work = h->n_work; g.sorted_pair = h->sorted_pair;
     g.tokens = tokens; g.top_k = c.top_k; g.act = c.activation; g.status = h->status;
     // gate/up, routed then shared
-    g.shared = 0; g.b_rows = c.routed_bits == 4 ? h->pf_x : x; g.b_stride = c.d; g.kdim = c.d;
+    g.shared = 0; g.kdim = c.d;
     g.out = h->acts; g.out_stride = c.f; g.round_gate_up = 0;
     g.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 0) * kTraceWords : nullptr;
-    if ((rc = launch_prefill_gemm<0>(h, c.routed_bits, g, dim3(c.f / kPfTileM, max_items), st))) return rc;
+    if ((rc = launch_prefill_gemm<0>(h, c.routed_bits, g, h->pf_x, P, dim3(c.f / kPfTileM, max_items), st))) return rc;
     if (c.shared_f) {
         PrefillGemmParams s = g;
         s.shared = 1; s.s0 = to_mat(lv.w.shared_gate_proj); s.s1 = to_mat(lv.w.shared_up_proj);
-        s.b_rows = c.shared_bits == 4 ? h->pf_x : x; s.out = h->shared_act; s.out_stride = c.shared_f; s.round_gate_up = 1;
+        s.out = h->shared_act; s.out_stride = c.shared_f; s.round_gate_up = 1;
         s.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 2) * kTraceWords : nullptr;
-        if ((rc = launch_prefill_gemm<0>(h, c.shared_bits, s, dim3(c.shared_f / kPfTileM, shared_items), st))) return rc;
+        if ((rc = launch_prefill_gemm<0>(h, c.shared_bits, s, h->pf_xn, tokens, dim3(c.shared_f / kPfTileM, shared_items), st)))
+            return rc;
     }
     // activation rows as the down GEMMs read them
     const __half *acts16 = static_cast<const __half *>(h->acts), *sacts16 = static_cast<const __half *>(h->shared_act);
@@ -592,16 +649,17 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
         sacts16 = h->pf_sacts16;
     }
     // down, routed then shared
-    g.b_rows = acts16; g.b_stride = c.f; g.kdim = c.f; g.row_scale = wide ? h->pf_rowscale : nullptr;
+    g.kdim = c.f; g.row_scale = wide ? h->pf_rowscale : nullptr;
     g.out = h->partial; g.out_stride = c.d;
     g.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 1) * kTraceWords : nullptr;
-    if ((rc = launch_prefill_gemm<1>(h, c.routed_bits, g, dim3(c.d / (2 * kPfTileM), max_items), st))) return rc;
+    if ((rc = launch_prefill_gemm<1>(h, c.routed_bits, g, acts16, P, dim3(c.d / (2 * kPfTileM), max_items), st))) return rc;
     if (c.shared_f) {
         PrefillGemmParams s = g;
         s.shared = 1; s.s0 = to_mat(lv.w.shared_down_proj); s.s1 = s.s0;
-        s.b_rows = sacts16; s.b_stride = c.shared_f; s.kdim = c.shared_f; s.row_scale = wide ? h->pf_srowscale : nullptr;
+        s.kdim = c.shared_f; s.row_scale = wide ? h->pf_srowscale : nullptr;
         s.out = h->shared_partial; s.trace = nullptr;
-        if ((rc = launch_prefill_gemm<1>(h, c.shared_bits, s, dim3(c.d / (2 * kPfTileM), shared_items), st))) return rc;
+        if ((rc = launch_prefill_gemm<1>(h, c.shared_bits, s, sacts16, tokens, dim3(c.d / (2 * kPfTileM), shared_items), st)))
+            return rc;
     }
     CombineParams pc{};
     pc.partial = h->partial; pc.shared_partial = c.shared_f ? h->shared_partial : nullptr;
@@ -697,7 +755,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
         h->max_work = (uint32_t)(std::min(P, c.num_experts + P / kPairsPerItem) + (T + kPairsPerItem - 1) / kPairsPerItem);
         if (ok) ok = alloc(&h->sorted_pair, P * 4) && alloc(&h->inv, P * 4) && alloc(&h->expert_offsets, kMaxExperts * 4) &&
                      alloc(&h->expert_counts, kMaxExperts * 4) && alloc(&h->work, (size_t)h->max_work * sizeof(WorkItem)) &&
-                     alloc(&h->n_work, 16) && alloc(&h->trace, (size_t)c.num_layers * 3 * kTraceWords * sizeof(unsigned long long));
+                     alloc(&h->n_work, 16) && alloc(&h->group_hist, ((P + kGroupThreads - 1) / kGroupThreads) * kMaxExperts * 4) && alloc(&h->trace, (size_t)c.num_layers * 3 * kTraceWords * sizeof(unsigned long long));
         // per-pair partial rows are only needed by the batched path
         if (ok)
             ok = alloc(&h->partial, P * c.d * sizeof(float)) && alloc(&h->shared_partial, T * c.d * sizeof(float));
@@ -721,7 +779,7 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y);
     cudaFree(h->sorted_pair); cudaFree(h->inv); cudaFree(h->expert_offsets); cudaFree(h->expert_counts);
-    cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->trace); cudaFree(h->expert_map); cudaFree(h->partial); cudaFree(h->shared_partial);
+    cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->group_hist); cudaFree(h->trace); cudaFree(h->expert_map); cudaFree(h->partial); cudaFree(h->shared_partial);
     delete h;
 }
 

@@ -1,5 +1,5 @@
-// Prefill: the routed and shared experts as grouped GEMMs on the 5th-generation
-// tensor cores (tcgen05.mma, accumulators in tensor memory).
+// Prefill: the routed and shared experts (and a dense router) as grouped GEMMs on
+// the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
 // What it replaces: prefill_grouped_routed_moe_batched_phase1/_down
 // (prefill.metal:460-534), which evaluate every (pair, feature) dot product on its
@@ -7,30 +7,38 @@
 // PrefillSharedExpert.encodeBlock (PrefillSharedExpert.swift:13-60), which repeats
 // the decode GEMVs once per token row.
 //
-// One CTA = one work item (an expert and up to 128 of the token rows routed to it,
-// consecutive in the sorted pair order) x one tile of 2 x 128 weight rows:
+// One CTA = one work item (an expert and up to 256 of the token rows routed to it,
+// consecutive in the sorted pair order) x one pair of 128-row weight tiles:
 //   phase 0:  A0 = 128 gate rows, A1 = the same 128 up rows, B = the item's token rows
 //             of x;  epilogue act(gate) * up -> acts[row][feature]
 //   phase 1:  A0, A1 = two 128-row tiles of the down projection, B = the item's packed
 //             activation rows;  epilogue -> partial[row][d] (fp32)
+//   phase 2:  A0, A1 = two 128-row tiles of a dense fp16 router matrix, B = token rows;
+//             epilogue -> logits[token][expert]
 // D[128 x N] (+)= A[128 x 16] * B[N x 16]^T per instruction, N = the item's row
 // count rounded up to 16: the weights are the M operand, so a short item costs a
-// narrow instruction instead of a padded tile.
+// narrow instruction instead of a padded tile.  Two accumulators of up to 256
+// columns take the SM's 512 tensor-memory columns.
 //
 // Operands in shared memory are fp16, K-major, in the 128-byte swizzle layout the
 // tensor core reads through matrix descriptors: row r of a tile at byte r*128
 // (8-row groups 1024 bytes apart), its eight 16-byte chunks XORed with r % 8.  One
 // K block = 64 values = one quantisation group = one such 128-byte row.
 //
-// Eight producer warps build the operands: the packed codes of the K block come
-// from global memory into registers, become fp16 w = q*s + b (one rounding: the
-// fp16 fused multiply-add of the exact code, scale and bias; scale and bias are
-// converted from their 16-bit storage type to fp16, exact for magnitudes in fp16's
-// normal range) and are stored swizzled; the token rows come with 16-byte
-// cp.async.  A ninth warp's elected lane issues the MMAs and commits them to the
-// mbarriers that hand the stage back.  4-bit codes unpack in the order
-// (0,4,1,5,2,6,3,7) within each 8; the B operand's rows are stored in the same order
-// (the sum over k does not care, as long as both operands agree).
+// B rows (and a dense A) arrive by TMA: tiled tensor-map loads with the 128-byte
+// swizzle mode write a 64 x 64 box in exactly that layout and complete on the
+// stage's mbarrier by byte count; one thread issues them.  No multicast.  The host
+// hands B in work-item order (x rows gathered into sorted pair order by
+// pack_rows_kernel), so an item's rows are one contiguous row range of the map.
+// Sixteen producer warps build the quantised A operand: each thread holds the 32
+// packed codes of one row three K blocks ahead in registers, turns them into fp16
+// w = q*s + b (one rounding: the fp16 fused multiply-add of the exact code, scale and
+// bias; scale and bias are converted from their 16-bit storage type to fp16, exact
+// for magnitudes in fp16's normal range) and stores them swizzled.  A seventeenth
+// warp's elected lane issues the MMAs and commits them to the mbarriers that hand
+// the stage back.  4-bit codes unpack in the order (0,4,1,5,2,6,3,7) within each 8;
+// the B rows are stored in the same K order (the sum over k does not care, as long as
+// both operands agree).
 //
 // Every wait is bounded; on expiry the status word is set, the CTA still frees its
 // tensor memory and returns, and CTAs that start later return at once.
@@ -39,6 +47,8 @@
 #include "decode_kernels.cuh"
 #include "grouped_decode.cuh"
 #include "tma.cuh"
+
+#include <cuda.h>          // CUtensorMap (the type only: the encoder is looked up at run time by the host code)
 
 #include <type_traits>
 
@@ -50,7 +60,7 @@ constexpr int kPfKBlock = 64;                 // K values per pipeline stage
 constexpr int kPfStages = 3;
 constexpr int kPfProducerWarps = 16;
 constexpr int kPfAhead = 3;                   // K blocks of packed codes a producer holds in registers
-constexpr int kPfDefer = 1;                   // steps between issuing a stage's copies and announcing it
+constexpr uint32_t kPfBoxRows = 64;           // rows of one TMA box of the B operand
 constexpr int kPfProducers = kPfProducerWarps * 32;
 constexpr int kPfThreads = kPfProducers + 32;
 constexpr uint32_t kPfTmemCols = 512;         // two fp32 accumulators of up to 256 columns: all of an SM's tensor memory
@@ -58,7 +68,7 @@ constexpr int kPfTileBytes = 128 * 128;       // an A tile: 128 rows x 64 fp16
 constexpr int kPfBTileBytes = kPfTileN * 128; // the B tile: up to 256 rows x 64 fp16
 constexpr int kPfStageBytes = 2 * kPfTileBytes + kPfBTileBytes;
 constexpr size_t kPfSmemBytes = 1024 /* alignment slack */ + 1024 /* barriers */ + (size_t)kPfStages * kPfStageBytes;
-constexpr uint32_t kPfWaitTries = 1u << 16;
+constexpr uint32_t kPfWaitTries = 1u << 22;    // bounded: a few seconds at the hardware's default try_wait limit
 
 // ---- tcgen05 / async-proxy primitives ---------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t cols) {
@@ -93,11 +103,25 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+// Pipeline waits here are short (a stage turns over in well under a microsecond), so the wait must wake
+// promptly: try_wait without a suspend-time hint (the hardware's own short limit), retried up to kPfWaitTries.
+__device__ __forceinline__ bool pf_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return done != 0;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Tiled TMA load of one box of a 2-D tensor map into shared memory, completing (by bytes) on an mbarrier.
+// c0 = element index along the contiguous dimension (its byte offset must be a multiple of 16), c1 = row.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst_smem), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar))
+                 : "memory");
+}
 
 // 32 lanes x 32 consecutive columns of 32-bit accumulators: register i = column i
 // of the lane this thread owns (lane quarter of the warp = warp index mod 4).
@@ -197,7 +221,6 @@ struct PrefillGemmParams {
     uint32_t shared;               // 1: item y = token rows [256 y, 256 y + 256), weights from s0/s1
     const WorkItem *work; const uint32_t *n_work; const uint32_t *sorted_pair;
     uint32_t tokens, top_k;
-    const __half *b_rows; uint32_t b_stride;   // phase 0, 2: x rows by token; phase 1: packed activation rows by position
     const float *row_scale;        // phase 1: factor per row undone in the epilogue, or nullptr
     void *out; uint32_t out_stride;            // phase 0: acts [row][F] (fp16 / fp32 by OUT); phase 1: partial fp32 [row][D];
                                                // phase 2: logits fp32 [token][E]
@@ -208,10 +231,21 @@ struct PrefillGemmParams {
     unsigned long long *trace;     // optional timeline of block (0, 0): start, end, marks (setup, loop, MMAs done, epilogue)
 };
 
+// Kernel argument: the B operand's rows as a tensor map ([rows][K] fp16, box 64 values x 64 rows, 128-byte
+// swizzle: a box lands in exactly the layout the MMA descriptor reads), for BITS = 16 also the dense A matrix
+// (box 64 x 128), then the plain parameters.  Row i of B = row item.start + i of that tensor: the host hands in
+// rows already in work-item order (sorted pair order, or token order for the shared expert and the router).
+struct alignas(64) PrefillGemmArgs {
+    CUtensorMap tmap_b;
+    CUtensorMap tmap_a;
+    PrefillGemmParams p;
+};
+
 // BITS: 4 / 8 = affine codes dequantised by the producers, 16 = dense fp16 rows copied as they are.
 // PHASE: 0 gate/up + activation, 1 down, 2 router logits (A0, A1 = rows 0-127, 128-255 of a 256-row block).
 template <int BITS, int META, int OUT, int PHASE>
-__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemmParams p) {
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __grid_constant__ PrefillGemmArgs args) {
+    const PrefillGemmParams &p = args.p;
     extern __shared__ unsigned char pf_smem_raw[];
     const uint32_t raw = smem_addr(pf_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // shared-window address of the aligned area
@@ -242,16 +276,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
     const uint32_t n_kb = p.kdim / kPfKBlock;
 
     if (tid == 0) {
-        for (int s = 0; s < kPfStages; ++s) { mbar_init(&full[s], kPfProducerWarps); mbar_init(&empty[s], 1); }
+        // a stage is full when every producer warp has arrived and the issuing thread's TMA bytes have landed
+        for (int s = 0; s < kPfStages; ++s) { mbar_init(&full[s], kPfProducerWarps + 1); mbar_init(&empty[s], 1); }
         mbar_init(accum, 1);
         mbar_fence_init();
     }
-    // B rows past the item's count are never written: clear every stage's B tile once
-    for (int i = tid; i < kPfStages * kPfBTileBytes / 16; i += kPfThreads) {
-        const int s = i / (kPfBTileBytes / 16), o = i % (kPfBTileBytes / 16);
-        *reinterpret_cast<uint4 *>(gen + 1024 + (size_t)s * kPfStageBytes + 2 * kPfTileBytes + (size_t)o * 16) = make_uint4(0, 0, 0, 0);
-    }
-    fence_proxy_async_smem();
     if (warp == kPfProducerWarps) {
         tmem_alloc(tmem_slot, kPfTmemCols);
         tmem_relinquish();
@@ -295,26 +324,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
         uint32_t adst[4];          // offsets of the thread's four chunks inside a stage
 #pragma unroll
         for (int j = 0; j < 4; ++j) adst[j] = mat * kPfTileBytes + sw128_offset(row, half * 4 + j);
-        // B: chunk c of rows (tid >> 3) + 64 j
-        const uint32_t bc = tid & 7;
-        const __half *bsrc[4];
-        uint32_t bdst[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t br = (tid >> 3) + 64 * j;
-            bdst[j] = 2 * kPfTileBytes + sw128_offset(br, bc);
-            if (br < count) {
-                size_t src_row;
-                if (PHASE == 1) src_row = item.start + br;
-                else src_row = p.shared ? item.start + br : p.sorted_pair[item.start + br] / p.top_k;
-                bsrc[j] = p.b_rows + src_row * p.b_stride + bc * 8;
-            } else {
-                bsrc[j] = nullptr;
-            }
-        }
         // The codes of K block kb + kPfAhead are requested while block kb is converted (slot kb % kPfAhead,
-        // compile-time because the K loop is unrolled by the number of stages); the B rows go straight to
-        // shared memory with cp.async, and the stage is announced one step later, when that group has landed.
+        // compile-time because the K loop is unrolled by the number of stages).  The B rows (and a dense A)
+        // are TMA boxes issued by one thread; they complete on the stage's barrier by byte count.
         constexpr int CB = BITS == 16 ? 4 : BITS;
         PackedCodes<CB> codes[kPfAhead];
         uint16_t ms[kPfAhead], mb[kPfAhead];
@@ -325,50 +337,48 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
         };
 #pragma unroll
         for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], mb[i], i);
+        const uint32_t n_box = (n_cols + kPfBoxRows - 1) / kPfBoxRows;
+        const uint32_t stage_tx = n_box * (kPfBoxRows * 128u) + (BITS == 16 ? 2u * kPfTileBytes : 0u);
+        const uint32_t a_row0 = PHASE == 0 ? blockIdx.x * kPfTileM : blockIdx.x * 2 * kPfTileM;
         // One step = one K block into stage S (compile-time), using code slot C (compile-time).
         auto step = [&](auto S, auto C, uint32_t kb) {
             constexpr uint32_t s = decltype(S)::value;
             constexpr int cs = decltype(C)::value;
+            if (kb >= n_kb || !ok) return;
             const uint32_t ph = (kb / kPfStages) & 1u;
-            if (kb < n_kb) {
-                bool done = false;      // the stage is free once the MMAs that read it have finished
-                for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = mbar_try_wait(&empty[s], ph ^ 1u);
-                if (!done) { atomicExch(p.status, 1u); ok = false; }
-                ok = __all_sync(0xffffffffu, ok);
-                if (ok) {
-                    const uint32_t st = stage0 + s * kPfStageBytes;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (bsrc[j] != nullptr) cp_async16(st + bdst[j], bsrc[j] + (size_t)kb * kPfKBlock);
-                    if (BITS == 16) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) cp_async16(st + adst[j], wsrc + (size_t)kb * (kPfKBlock * 2) + j * 16);
-                    } else {
-                        const __half2 sc = meta_half2<META>(ms[cs]), bi = meta_half2<META>(mb[cs]);
-                        const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f));
-                        const uint32_t d4[4] = {st + adst[0], st + adst[1], st + adst[2], st + adst[3]};
-                        dequant_store<CB>(d4, codes[cs], sc, sc16, bi);
-                        fetch(codes[cs], ms[cs], mb[cs], kb + kPfAhead);      // the slot is free again
-                    }
+            bool done = false;      // the stage is free once the MMAs that read it have finished
+            for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = pf_try_wait(&empty[s], ph ^ 1u);
+            if (!done) { atomicExch(p.status, 1u); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            const uint32_t st = stage0 + s * kPfStageBytes;
+            if (tid == 0) {
+                mbar_expect_tx(&full[s], stage_tx);
+                for (uint32_t j = 0; j < n_box; ++j)
+                    tma_load_2d(st + 2 * kPfTileBytes + j * (kPfBoxRows * 128u), &args.tmap_b, kb * kPfKBlock,
+                                item.start + j * kPfBoxRows, &full[s]);
+                if (BITS == 16) {
+                    tma_load_2d(st, &args.tmap_a, kb * kPfKBlock, a_row0, &full[s]);
+                    tma_load_2d(st + kPfTileBytes, &args.tmap_a, kb * kPfKBlock, a_row0 + kPfTileM, &full[s]);
                 }
             }
-            cp_async_commit();
-            // the arrival for K block kb - kPfDefer: its cp.async group has had kPfDefer steps to land
-            if (kb >= (uint32_t)kPfDefer && kb < n_kb + kPfDefer && ok) {
-                cp_async_wait_group<kPfDefer>();
+            if (BITS != 16) {
+                const __half2 sc = meta_half2<META>(ms[cs]), bi = meta_half2<META>(mb[cs]);
+                const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f));
+                const uint32_t d4[4] = {st + adst[0], st + adst[1], st + adst[2], st + adst[3]};
+                dequant_store<CB>(d4, codes[cs], sc, sc16, bi);
+                fetch(codes[cs], ms[cs], mb[cs], kb + kPfAhead);      // the slot is free again
                 fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's reads
-                __syncwarp();
-                constexpr uint32_t sa = (s + kPfStages - kPfDefer) % kPfStages;
-                if (lane == 0) mbar_arrive(&full[sa]);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
         };
         static_assert(kPfStages == 3 && kPfAhead == 3, "the unrolled body below is written for 3 stages and 3 code slots");
-        for (uint32_t kb = 0; kb < n_kb + kPfDefer && ok; kb += 3) {
+        for (uint32_t kb = 0; kb < n_kb && ok; kb += 3) {
             step(std::integral_constant<uint32_t, 0>{}, std::integral_constant<int, 0>{}, kb);
             step(std::integral_constant<uint32_t, 1>{}, std::integral_constant<int, 1>{}, kb + 1);
             step(std::integral_constant<uint32_t, 2>{}, std::integral_constant<int, 2>{}, kb + 2);
         }
-        cp_async_wait_group<0>();
         trace_mark(p.trace, 1);
     } else if (lane == 0) {
         // ---------------- MMA issue: one thread ----------------
@@ -376,7 +386,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
         for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
             const uint32_t s = kb % kPfStages, ph = (kb / kPfStages) & 1u;
             bool done = false;
-            for (uint32_t it = 0; it < kPfWaitTries && !done; ++it) done = mbar_try_wait(&full[s], ph);
+            for (uint32_t it = 0; it < kPfWaitTries && !done; ++it) done = pf_try_wait(&full[s], ph);
             if (!done) { atomicExch(p.status, 1u); ok = false; break; }
             tc_fence_after_sync();
             const uint32_t st = stage0 + s * kPfStageBytes;
@@ -397,7 +407,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
         // ---------------- epilogue: producers turn consumers ----------------
         if (ok) {
             bool done = false;
-            for (uint32_t it = 0; it < kPfWaitTries && !done; ++it) done = mbar_try_wait(accum, 0u);
+            for (uint32_t it = 0; it < kPfWaitTries && !done; ++it) done = pf_try_wait(accum, 0u);
             if (!done) { atomicExch(p.status, 1u); ok = false; }
         }
         ok = __all_sync(0xffffffffu, ok);
@@ -451,14 +461,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(PrefillGemm
 // Router for a prefill chunk from the logits the GEMM wrote: one block per token
 // (router_topk_select_k8 semantics, moe.metal:233-285; prefill_router_block :402-417).
 struct TopkRowsParams {
-    const float *logits; const uint16_t *pes; uint32_t *out_idx; __half *out_w; uint32_t E, K;
+    const float *logits; const uint16_t *pes; uint32_t *out_idx; __half *out_w; uint32_t E, K, tokens;
 };
+// one warp per token row (8 rounds of arg-max over 8 logits per lane), 8 rows per block
 __global__ void __launch_bounds__(256) topk_rows_kernel(TopkRowsParams p) {
-    __shared__ __align__(16) float work[kMaxExperts + 64];
     pdl_wait();
     pdl_launch_dependents();
-    const size_t tok = blockIdx.x;
-    topk_softmax_block(p.logits + tok * p.E, (int)p.E, (int)p.K, p.pes, p.out_idx + tok * p.K, p.out_w + tok * p.K, work);
+    const size_t tok = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (tok >= p.tokens) return;
+    topk_softmax_warp(p.logits + tok * p.E, (int)p.E, (int)p.K, p.pes, p.out_idx + tok * p.K, p.out_w + tok * p.K);
 }
 
 // ---- operand packing ---------------------------------------------------------------
@@ -469,6 +480,7 @@ struct PackRowsParams {
     __half *dst;            // [rows][n] fp16
     float *row_scale;       // fp32 sources: per row, the power of two taken out (nullptr for fp16 sources)
     uint32_t rows, n, permute;
+    const uint32_t *gather; uint32_t gather_div;   // optional: source row = gather[row] / gather_div (pair id -> token)
 };
 
 // One warp per row.  fp32 rows ("wide range" intermediates) are scaled by a power
@@ -481,9 +493,10 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(PackRowsParams p) {
     pdl_launch_dependents();
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= p.rows) return;
+    const size_t srow = p.gather != nullptr ? p.gather[row] / p.gather_div : row;
     float mul = 1.0f;
     if (SRC_F32) {
-        const float *src = static_cast<const float *>(p.src) + (size_t)row * p.n;
+        const float *src = static_cast<const float *>(p.src) + srow * p.n;
         float m = 0.0f;
         for (uint32_t i = lane; i < p.n; i += 32) {
             const float v = fabsf(src[i]);
@@ -503,8 +516,8 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(PackRowsParams p) {
         for (int pos = 0; pos < 8; ++pos) {
             const uint32_t k = i8 + (p.permute ? pf_k_order(pos) : pos);
             float v;
-            if (SRC_F32) v = static_cast<const float *>(p.src)[(size_t)row * p.n + k] * mul;
-            else v = __half2float(static_cast<const __half *>(p.src)[(size_t)row * p.n + k]);
+            if (SRC_F32) v = static_cast<const float *>(p.src)[srow * p.n + k] * mul;
+            else v = __half2float(static_cast<const __half *>(p.src)[srow * p.n + k]);
             out[pos] = __float2half_rn(v);
         }
         *reinterpret_cast<uint4 *>(p.dst + (size_t)row * p.n + i8) = *reinterpret_cast<const uint4 *>(out);
