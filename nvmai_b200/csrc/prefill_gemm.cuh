@@ -57,17 +57,20 @@ namespace nvmai {
 constexpr int kPfTileM = 128;                 // weight rows per accumulator
 constexpr int kPfTileN = 256;                 // most token rows per work item
 constexpr int kPfKBlock = 64;                 // K values per pipeline stage
-constexpr int kPfStages = 3;
+constexpr int kPfStages = 3;                  // A stages (two converted 128 x 64 fp16 tiles each)
 constexpr int kPfProducerWarps = 16;
+constexpr int kPfMmaWarp = kPfProducerWarps;      // its lane 0 issues the MMAs; the warp owns the tensor-memory allocation
+constexpr int kPfTmaWarp = kPfProducerWarps + 1;  // its lane 0 issues the TMA loads
 constexpr int kPfAhead = 3;                   // K blocks of packed codes a producer holds in registers
 constexpr uint32_t kPfBoxRows = 64;           // rows of one TMA box of the B operand
 constexpr int kPfProducers = kPfProducerWarps * 32;
-constexpr int kPfThreads = kPfProducers + 32;
-constexpr uint32_t kPfTmemCols = 512;         // two fp32 accumulators of up to 256 columns: all of an SM's tensor memory
+constexpr int kPfThreads = kPfProducers + 64;
+constexpr uint32_t kPfTmemCols = 512;         // all of an SM's tensor memory: 2 x 256 or 4 x 128 fp32 accumulator columns
 constexpr int kPfTileBytes = 128 * 128;       // an A tile: 128 rows x 64 fp16
-constexpr int kPfBTileBytes = kPfTileN * 128; // the B tile: up to 256 rows x 64 fp16
-constexpr int kPfStageBytes = 2 * kPfTileBytes + kPfBTileBytes;
-constexpr size_t kPfSmemBytes = 1024 /* alignment slack */ + 1024 /* barriers */ + (size_t)kPfStages * kPfStageBytes;
+constexpr int kPfAStageBytes = 2 * kPfTileBytes;
+constexpr int kPfBRingBytes = 96 * 1024;      // B ring: 3 K blocks of 256 rows ... 8 of up to 64 rows
+constexpr int kPfBMaxDepth = 8;
+constexpr size_t kPfSmemBytes = 1024 /* alignment slack */ + 1024 /* barriers */ + (size_t)kPfStages * kPfAStageBytes + kPfBRingBytes;
 constexpr uint32_t kPfWaitTries = 1u << 22;    // bounded: a few seconds at the hardware's default try_wait limit
 
 // ---- tcgen05 / async-proxy primitives ---------------------------------------------
@@ -134,6 +137,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -250,11 +261,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     const uint32_t raw = smem_addr(pf_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // shared-window address of the aligned area
     unsigned char *gen = pf_smem_raw + (base - raw);              // the same place as a generic pointer
-    uint64_t *full = reinterpret_cast<uint64_t *>(gen);           // [kPfStages]
-    uint64_t *empty = full + kPfStages;                           // [kPfStages]
-    uint64_t *accum = empty + kPfStages;                          // [1]
+    uint64_t *a_full = reinterpret_cast<uint64_t *>(gen);         // [kPfStages]   A tiles of a K block converted
+    uint64_t *a_empty = a_full + kPfStages;                       // [kPfStages]   ... and read by their MMAs
+    uint64_t *b_full = a_empty + kPfStages;                       // [kPfBMaxDepth] B rows of a K block landed
+    uint64_t *b_empty = b_full + kPfBMaxDepth;                    // [kPfBMaxDepth] ... and read by their MMAs
+    uint64_t *accum = b_empty + kPfBMaxDepth;                     // [1]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum + 1);
-    const uint32_t stage0 = base + 1024u;
+    const uint32_t a_ring = base + 1024u, b_ring = a_ring + kPfStages * kPfAStageBytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // the work list was written by an earlier kernel in the stream
@@ -274,14 +287,23 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     const uint32_t count = min(item.count, (uint32_t)kPfTileN);
     const uint32_t n_cols = (count + 15u) & ~15u;
     const uint32_t n_kb = p.kdim / kPfKBlock;
+    // The B ring holds as many K blocks as fit: a narrow item keeps more blocks in flight, which is what
+    // hides the latency of its row fetches.
+    const uint32_t n_box = (n_cols + kPfBoxRows - 1) / kPfBoxRows;
+    const uint32_t b_slot = n_box * (kPfBoxRows * 128u);
+    const uint32_t b_depth = min((uint32_t)kPfBMaxDepth, (uint32_t)kPfBRingBytes / b_slot);
+    // Accumulators.  Dependent MMAs into one accumulator are spaced by the tensor pipe's latency, so a narrow
+    // item (<= 128 columns) alternates between two accumulators per A tile and adds them in the epilogue.
+    const bool split = n_cols <= 128u;
+    const uint32_t acc1 = split ? 128u : 256u;    // column of A1's accumulator; the second halves sit 256 columns on
 
     if (tid == 0) {
-        // a stage is full when every producer warp has arrived and the issuing thread's TMA bytes have landed
-        for (int s = 0; s < kPfStages; ++s) { mbar_init(&full[s], kPfProducerWarps + 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < kPfStages; ++s) { mbar_init(&a_full[s], BITS == 16 ? 1 : kPfProducerWarps); mbar_init(&a_empty[s], 1); }
+        for (int j = 0; j < kPfBMaxDepth; ++j) { mbar_init(&b_full[j], 1); mbar_init(&b_empty[j], 1); }
         mbar_init(accum, 1);
         mbar_fence_init();
     }
-    if (warp == kPfProducerWarps) {
+    if (warp == kPfMmaWarp) {
         tmem_alloc(tmem_slot, kPfTmemCols);
         tmem_relinquish();
     }
@@ -291,139 +313,163 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     bool ok = true;
     trace_mark(p.trace, 0);
+    auto wait = [&](uint64_t *bar, uint32_t parity) {
+        bool done = false;
+        for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = pf_try_wait(bar, parity);
+        if (!done) atomicExch(p.status, 1u);
+        return done;
+    };
 
     if (warp < kPfProducerWarps) {
-        // ---------------- producers ----------------
-        // thread -> (matrix, row, half row): 32 K values of one row of one of the two A tiles per K block
-        const uint32_t mat = tid >> 8, row = (tid & 255) >> 1, half = tid & 1;
-        const size_t row_bytes = (size_t)p.kdim * BITS / 8;
-        const uint32_t groups = p.kdim / kGroup;
-        AffineMat m;
-        uint32_t r;               // matrix row this thread converts
-        if (PHASE == 0) {
-            r = blockIdx.x * kPfTileM + row;
-            if (p.shared) m = mat ? p.s1 : p.s0;
-            else {
-                const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
-                const int o = mat ? 3 : 0;
-                m = AffineMat{blob + p.off.o[o], reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 1]),
-                              reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 2])};
-            }
-        } else {
-            r = blockIdx.x * 2 * kPfTileM + mat * kPfTileM + row;
-            if (p.shared) m = p.s0;
-            else {
-                const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
-                m = AffineMat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
-                              reinterpret_cast<const uint16_t *>(blob + p.off.o[8])};
-            }
-        }
-        const uint8_t *wsrc = m.w + (size_t)r * row_bytes + half * (BITS * 4);      // 32 values = BITS*4 bytes
-        const uint16_t *ssrc = nullptr, *bsrc_meta = nullptr;
-        if (BITS != 16) { ssrc = m.s + (size_t)r * groups; bsrc_meta = m.b + (size_t)r * groups; }
-        uint32_t adst[4];          // offsets of the thread's four chunks inside a stage
-#pragma unroll
-        for (int j = 0; j < 4; ++j) adst[j] = mat * kPfTileBytes + sw128_offset(row, half * 4 + j);
-        // The codes of K block kb + kPfAhead are requested while block kb is converted (slot kb % kPfAhead,
-        // compile-time because the K loop is unrolled by the number of stages).  The B rows (and a dense A)
-        // are TMA boxes issued by one thread; they complete on the stage's barrier by byte count.
-        constexpr int CB = BITS == 16 ? 4 : BITS;
-        PackedCodes<CB> codes[kPfAhead];
-        uint16_t ms[kPfAhead], mb[kPfAhead];
-        auto fetch = [&](PackedCodes<CB> &c, uint16_t &s_, uint16_t &b_, uint32_t kb) {
-            if (BITS == 16 || kb >= n_kb) return;
-            pf_load_codes<CB>(c, wsrc + (size_t)kb * (kPfKBlock * BITS / 8));
-            s_ = ssrc[kb]; b_ = bsrc_meta[kb];
-        };
-#pragma unroll
-        for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], mb[i], i);
-        const uint32_t n_box = (n_cols + kPfBoxRows - 1) / kPfBoxRows;
-        const uint32_t stage_tx = n_box * (kPfBoxRows * 128u) + (BITS == 16 ? 2u * kPfTileBytes : 0u);
-        const uint32_t a_row0 = PHASE == 0 ? blockIdx.x * kPfTileM : blockIdx.x * 2 * kPfTileM;
-        // One step = one K block into stage S (compile-time), using code slot C (compile-time).
-        auto step = [&](auto S, auto C, uint32_t kb) {
-            constexpr uint32_t s = decltype(S)::value;
-            constexpr int cs = decltype(C)::value;
-            if (kb >= n_kb || !ok) return;
-            const uint32_t ph = (kb / kPfStages) & 1u;
-            bool done = false;      // the stage is free once the MMAs that read it have finished
-            for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = pf_try_wait(&empty[s], ph ^ 1u);
-            if (!done) { atomicExch(p.status, 1u); ok = false; }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            const uint32_t st = stage0 + s * kPfStageBytes;
-            if (tid == 0) {
-                mbar_expect_tx(&full[s], stage_tx);
-                for (uint32_t j = 0; j < n_box; ++j)
-                    tma_load_2d(st + 2 * kPfTileBytes + j * (kPfBoxRows * 128u), &args.tmap_b, kb * kPfKBlock,
-                                item.start + j * kPfBoxRows, &full[s]);
-                if (BITS == 16) {
-                    tma_load_2d(st, &args.tmap_a, kb * kPfKBlock, a_row0, &full[s]);
-                    tma_load_2d(st + kPfTileBytes, &args.tmap_a, kb * kPfKBlock, a_row0 + kPfTileM, &full[s]);
+        // ---------------- producers: the quantised A operand ----------------
+        if (BITS != 16) {
+            // thread -> (matrix, row, half row): 32 K values of one row of one of the two A tiles per K block
+            const uint32_t mat = tid >> 8, row = (tid & 255) >> 1, half = tid & 1;
+            const size_t row_bytes = (size_t)p.kdim * BITS / 8;
+            const uint32_t groups = p.kdim / kGroup;
+            AffineMat m;
+            uint32_t r;               // matrix row this thread converts
+            if (PHASE == 0) {
+                r = blockIdx.x * kPfTileM + row;
+                if (p.shared) m = mat ? p.s1 : p.s0;
+                else {
+                    const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
+                    const int o = mat ? 3 : 0;
+                    m = AffineMat{blob + p.off.o[o], reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 1]),
+                                  reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 2])};
+                }
+            } else {
+                r = blockIdx.x * 2 * kPfTileM + mat * kPfTileM + row;
+                if (p.shared) m = p.s0;
+                else {
+                    const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
+                    m = AffineMat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
+                                  reinterpret_cast<const uint16_t *>(blob + p.off.o[8])};
                 }
             }
-            if (BITS != 16) {
+            const uint8_t *wsrc = m.w + (size_t)r * row_bytes + half * (BITS * 4);      // 32 values = BITS*4 bytes
+            const uint16_t *ssrc = m.s + (size_t)r * groups, *bsrc_meta = m.b + (size_t)r * groups;
+            uint32_t adst[4];          // offsets of the thread's four chunks inside an A stage
+#pragma unroll
+            for (int j = 0; j < 4; ++j) adst[j] = mat * kPfTileBytes + sw128_offset(row, half * 4 + j);
+            // The codes of K block kb + kPfAhead are requested while block kb is converted (slot kb % kPfAhead,
+            // compile-time because the K loop is unrolled by the number of stages).
+            constexpr int CB = BITS == 16 ? 4 : BITS;
+            PackedCodes<CB> codes[kPfAhead];
+            uint16_t ms[kPfAhead], mb[kPfAhead];
+            auto fetch = [&](PackedCodes<CB> &c, uint16_t &s_, uint16_t &b_, uint32_t kb) {
+                if (kb >= n_kb) return;
+                pf_load_codes<CB>(c, wsrc + (size_t)kb * (kPfKBlock * BITS / 8));
+                s_ = ssrc[kb]; b_ = bsrc_meta[kb];
+            };
+#pragma unroll
+            for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], mb[i], i);
+            // One step = one K block into stage S (compile-time), using code slot C (compile-time).
+            auto step = [&](auto S, auto C, uint32_t kb) {
+                constexpr uint32_t s = decltype(S)::value;
+                constexpr int cs = decltype(C)::value;
+                if (kb >= n_kb || !ok) return;
+                ok = wait(&a_empty[s], ((kb / kPfStages) & 1u) ^ 1u);      // free once the MMAs that read it have finished
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) return;
+                const uint32_t st = a_ring + s * kPfAStageBytes;
                 const __half2 sc = meta_half2<META>(ms[cs]), bi = meta_half2<META>(mb[cs]);
                 const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f));
                 const uint32_t d4[4] = {st + adst[0], st + adst[1], st + adst[2], st + adst[3]};
                 dequant_store<CB>(d4, codes[cs], sc, sc16, bi);
                 fetch(codes[cs], ms[cs], mb[cs], kb + kPfAhead);      // the slot is free again
                 fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[s]);
+            };
+            static_assert(kPfStages == 3 && kPfAhead == 3, "the unrolled body below is written for 3 stages and 3 code slots");
+            for (uint32_t kb = 0; kb < n_kb && ok; kb += 3) {
+                step(std::integral_constant<uint32_t, 0>{}, std::integral_constant<int, 0>{}, kb);
+                step(std::integral_constant<uint32_t, 1>{}, std::integral_constant<int, 1>{}, kb + 1);
+                step(std::integral_constant<uint32_t, 2>{}, std::integral_constant<int, 2>{}, kb + 2);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full[s]);
-        };
-        static_assert(kPfStages == 3 && kPfAhead == 3, "the unrolled body below is written for 3 stages and 3 code slots");
-        for (uint32_t kb = 0; kb < n_kb && ok; kb += 3) {
-            step(std::integral_constant<uint32_t, 0>{}, std::integral_constant<int, 0>{}, kb);
-            step(std::integral_constant<uint32_t, 1>{}, std::integral_constant<int, 1>{}, kb + 1);
-            step(std::integral_constant<uint32_t, 2>{}, std::integral_constant<int, 2>{}, kb + 2);
         }
         trace_mark(p.trace, 1);
+    } else if (warp == kPfTmaWarp) {
+        // ---------------- TMA issue: one thread, running ahead of everything else ----------------
+        if (lane == 0) {
+            const uint32_t a_row0 = blockIdx.x * 2 * kPfTileM;
+            uint32_t j = 0, jph = 0;
+            for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
+                ok = wait(&b_empty[j], jph ^ 1u);
+                if (!ok) break;
+                mbar_expect_tx(&b_full[j], b_slot);
+                for (uint32_t x = 0; x < n_box; ++x)
+                    tma_load_2d(b_ring + j * b_slot + x * (kPfBoxRows * 128u), &args.tmap_b, kb * kPfKBlock,
+                                item.start + x * kPfBoxRows, &b_full[j]);
+                if (BITS == 16) {                 // a dense A matrix comes the same way
+                    const uint32_t s = kb % kPfStages;
+                    ok = wait(&a_empty[s], ((kb / kPfStages) & 1u) ^ 1u);
+                    if (!ok) break;
+                    const uint32_t st = a_ring + s * kPfAStageBytes;
+                    mbar_expect_tx(&a_full[s], 2u * kPfTileBytes);
+                    tma_load_2d(st, &args.tmap_a, kb * kPfKBlock, a_row0, &a_full[s]);
+                    tma_load_2d(st + kPfTileBytes, &args.tmap_a, kb * kPfKBlock, a_row0 + kPfTileM, &a_full[s]);
+                }
+                if (++j == b_depth) { j = 0; jph ^= 1u; }
+            }
+        }
     } else if (lane == 0) {
         // ---------------- MMA issue: one thread ----------------
         const uint32_t idesc = umma_idesc_f16(kPfTileM, n_cols);
+        uint32_t j = 0, jph = 0;
         for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
-            const uint32_t s = kb % kPfStages, ph = (kb / kPfStages) & 1u;
-            bool done = false;
-            for (uint32_t it = 0; it < kPfWaitTries && !done; ++it) done = pf_try_wait(&full[s], ph);
-            if (!done) { atomicExch(p.status, 1u); ok = false; break; }
+            const uint32_t s = kb % kPfStages;
+            ok = wait(&a_full[s], (kb / kPfStages) & 1u) && wait(&b_full[j], jph);
+            if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t st = stage0 + s * kPfStageBytes;
+            const uint32_t st = a_ring + s * kPfAStageBytes;
             const uint64_t da0 = umma_desc_sw128(st), da1 = umma_desc_sw128(st + kPfTileBytes),
-                           db = umma_desc_sw128(st + 2 * kPfTileBytes);
+                           db = umma_desc_sw128(b_ring + j * b_slot);
 #pragma unroll
             for (uint32_t k = 0; k < kPfKBlock / 16; ++k) {        // 16 values = 32 bytes = +2 in the address field
-                const uint32_t accumulate = (kb | k) != 0u;
-                umma_f16_ss(tmem, da0 + 2 * k, db + 2 * k, idesc, accumulate);
-                umma_f16_ss(tmem + kPfTileN, da1 + 2 * k, db + 2 * k, idesc, accumulate);
+                // split: K steps alternate between the two accumulators of each A tile
+                const uint32_t second = split ? (k & 1u) * 256u : 0u;
+                const uint32_t accumulate = split ? ((kb | (k >> 1)) != 0u) : ((kb | k) != 0u);
+                umma_f16_ss(tmem + second, da0 + 2 * k, db + 2 * k, idesc, accumulate);
+                umma_f16_ss(tmem + acc1 + second, da1 + 2 * k, db + 2 * k, idesc, accumulate);
             }
-            umma_commit(&empty[s]);
+            umma_commit(&a_empty[s]);
+            umma_commit(&b_empty[j]);
+            if (++j == b_depth) { j = 0; jph ^= 1u; }
         }
         if (ok) umma_commit(accum);
     }
 
     if (warp < kPfProducerWarps) {
         // ---------------- epilogue: producers turn consumers ----------------
-        if (ok) {
-            bool done = false;
-            for (uint32_t it = 0; it < kPfWaitTries && !done; ++it) done = pf_try_wait(accum, 0u);
-            if (!done) { atomicExch(p.status, 1u); ok = false; }
-        }
+        if (ok) ok = wait(accum, 0u);
         ok = __all_sync(0xffffffffu, ok);
         const uint32_t q = warp & 3u;                               // lane quarter of the accumulator this warp may read
         if (ok) tc_fence_after_sync();
         trace_mark(p.trace, 2);
-        for (uint32_t cb = (warp >> 2) * 64u; ok && cb < (warp >> 2) * 64u + 64u && cb < n_cols; cb += 32u) {
+        const uint32_t span = split ? 32u : 64u;                    // columns per warp group
+        for (uint32_t cb = (warp >> 2) * span; ok && cb < (warp >> 2) * span + span && cb < n_cols; cb += 16u) {
             const uint32_t lane_addr = tmem + ((q * 32u) << 16);
-            uint32_t a0[32], a1[32];
-            tmem_ld32(lane_addr + cb, a0);
-            tmem_ld32(lane_addr + kPfTileN + cb, a1);
+            uint32_t a0[16], a1[16];
+            tmem_ld16(lane_addr + cb, a0);
+            tmem_ld16(lane_addr + acc1 + cb, a1);
             tmem_ld_wait();
+            if (split) {
+                uint32_t b0[16], b1[16];
+                tmem_ld16(lane_addr + 256u + cb, b0);
+                tmem_ld16(lane_addr + acc1 + 256u + cb, b1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    a0[i] = __float_as_uint(__uint_as_float(a0[i]) + __uint_as_float(b0[i]));
+                    a1[i] = __float_as_uint(__uint_as_float(a1[i]) + __uint_as_float(b1[i]));
+                }
+            }
             if (PHASE == 0) {
                 const uint32_t f = blockIdx.x * kPfTileM + q * 32u + lane;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const uint32_t n = cb + i;
                     if (n < count) {
                         float g = __uint_as_float(a0[i]), u = __uint_as_float(a1[i]);
@@ -437,7 +483,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 const uint32_t d = blockIdx.x * 2 * kPfTileM + q * 32u + lane;
                 float *out = static_cast<float *>(p.out);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const uint32_t n = cb + i;
                     if (n < count) {
                         const float sc = (PHASE == 1 && p.row_scale != nullptr) ? p.row_scale[item.start + n] : 1.0f;
@@ -451,7 +497,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     trace_mark(p.trace, 3);
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == kPfProducerWarps) {
+    if (warp == kPfMmaWarp) {
         __syncwarp();
         tmem_dealloc(tmem, kPfTmemCols);
     }
