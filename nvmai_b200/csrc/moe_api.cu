@@ -558,8 +558,8 @@ int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParam
     args.tmap_a = args.tmap_b;
     return dispatch_bits_meta(bits, c.meta_dtype, [&](auto B, auto M) {
         return dispatch_out(c.out_dtype, [&](auto O) {
-            return launch_kernel(h, prefill_gemm_ts_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value, PHASE>,
-                                 grid, dim3(kPfThreads), kTsSmemBytes, st, true, args);
+            return launch_kernel(h, prefill_gemm_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value, PHASE>,
+                                 grid, dim3(kPfThreads), kPfSmemBytes, st, true, args);
         });
     });
 }
@@ -609,11 +609,11 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     } else if ((rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, false, c.shared_f != 0, false, st))) {
         return rc;
     }
-    if ((rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st, false, false, kTsTileN, true)))
+    if ((rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st, false, false, kPfTileN, true)))
         return rc;
     const uint32_t P = tokens * c.top_k;
-    const uint32_t max_items = std::min(P, c.num_experts + P / kTsTileN);
-    const uint32_t shared_items = (tokens + kTsTileN - 1) / kTsTileN;
+    const uint32_t max_items = std::min(P, c.num_experts + P / kPfTileN);
+    const uint32_t shared_items = (tokens + kPfTileN - 1) / kPfTileN;
     // x rows as the GEMMs read them: gathered into sorted pair order for the routed items (an item's rows are then
     // one row range of the tensor map), token order for the shared expert; each in its weights' K order
     if ((rc = launch_pack_rows(h, x, false, h->pf_x, nullptr, P, c.d, c.routed_bits, st, h->sorted_pair, c.top_k))) return rc;

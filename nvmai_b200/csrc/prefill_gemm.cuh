@@ -98,16 +98,6 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, ui
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// The same with the A operand in tensor memory (128 lanes = rows, two 16-bit K values per 32-bit column).
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // The barrier gets one arrival when every MMA this thread issued so far has finished.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
@@ -157,16 +147,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
-// 16 consecutive 32-bit columns of the lane this thread owns <- registers
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major tile in the 128-byte swizzle layout, base
@@ -242,34 +222,6 @@ __device__ __forceinline__ void dequant_store(const uint32_t (&dst)[4], const Pa
         }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst[j]), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
                      : "memory");
-    }
-}
-
-// The same conversion into registers: o[4 j .. 4 j + 3] = the 8 values of word j, in unpack order.
-template <int BITS>
-__device__ __forceinline__ void dequant_regs(const PackedCodes<BITS> &c, __half2 s2, __half2 s16, __half2 b2, uint32_t (&o)[16]) {
-    const __half2 k1024 = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        if (BITS == 4) {
-            const uint32_t w = c.v[j], w8 = w >> 8;
-            const uint32_t t[4] = {(w & 0x000F000Fu) | 0x64006400u, (w & 0x00F000F0u) | 0x64006400u,
-                                   (w8 & 0x000F000Fu) | 0x64006400u, (w8 & 0x00F000F0u) | 0x64006400u};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t[i]), k1024);
-                const __half2 v = __hfma2(q, (i & 1) ? s16 : s2, b2);
-                o[4 * j + i] = *reinterpret_cast<const uint32_t *>(&v);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t t = __byte_perm(c.v[2 * j + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342 : 0x4140);
-                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
-                const __half2 v = __hfma2(q, s2, b2);
-                o[4 * j + i] = *reinterpret_cast<const uint32_t *>(&v);
-            }
-        }
     }
 }
 
@@ -535,241 +487,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                     const uint32_t n = cb + i;
                     if (n < count) {
                         const float sc = (PHASE == 1 && p.row_scale != nullptr) ? p.row_scale[item.start + n] : 1.0f;
-                        out[(size_t)(item.start + n) * p.out_stride + d] = __uint_as_float(a0[i]) * sc;
-                        out[(size_t)(item.start + n) * p.out_stride + d + kPfTileM] = __uint_as_float(a1[i]) * sc;
-                    }
-                }
-            }
-        }
-    }
-    trace_mark(p.trace, 3);
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == kPfMmaWarp) {
-        __syncwarp();
-        tmem_dealloc(tmem, kPfTmemCols);
-    }
-    trace_end(p.trace);
-}
-
-// ---------------------------------------------------------------------------------------------------
-// The quantised GEMMs with the A operand in tensor memory.  The converted weights never touch shared
-// memory: a producer thread owns one row of one A tile (tensor-memory lane = row), converts its 32 codes
-// of the K block in registers and writes them with tcgen05.st; the MMA reads A from tensor memory and only
-// B from shared memory.  That takes the A tiles' stores and the tensor core's reads of them (64 of the 112 KB
-// a K block moved through shared memory) off the shared-memory ports, and leaves all of shared memory to
-// the B ring.  Tensor-memory budget: two accumulators of up to 192 columns + two A stages of 64 columns
-// (2 matrices x 64 K values = 32 columns each) = 512.  Work items therefore hold up to 192 rows.
-// ---------------------------------------------------------------------------------------------------
-constexpr int kTsTileN = 192;
-constexpr uint32_t kTsAccCols = 192;
-constexpr uint32_t kTsAStageCols = 64;
-constexpr int kTsAStages = 2;
-constexpr uint32_t kTsABase = 2 * kTsAccCols;
-constexpr int kTsBDepth = 8;
-constexpr int kTsBRingBytes = kTsBDepth * 3 * (int)kPfBoxRows * 128;      // 8 K blocks of up to 192 rows
-constexpr size_t kTsSmemBytes = 1024 /* alignment slack */ + 1024 /* barriers */ + kTsBRingBytes;
-
-template <int BITS, int META, int OUT, int PHASE>
-__global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_ts_kernel(const __grid_constant__ PrefillGemmArgs args) {
-    static_assert(BITS == 4 || BITS == 8, "quantised A operands only");
-    const PrefillGemmParams &p = args.p;
-    extern __shared__ unsigned char pf_smem_raw[];
-    const uint32_t raw = smem_addr(pf_smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    unsigned char *gen = pf_smem_raw + (base - raw);
-    uint64_t *a_full = reinterpret_cast<uint64_t *>(gen);         // [kTsAStages]
-    uint64_t *a_empty = a_full + kTsAStages;                      // [kTsAStages]
-    uint64_t *b_full = a_empty + kTsAStages;                      // [kTsBDepth]
-    uint64_t *b_empty = b_full + kTsBDepth;                       // [kTsBDepth]
-    uint64_t *accum = b_empty + kTsBDepth;                        // [1]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum + 1);
-    const uint32_t b_ring = base + 1024u;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-    pdl_wait();
-    pdl_launch_dependents();
-    if (*reinterpret_cast<volatile unsigned int *>(p.status) != 0u) return;
-    trace_begin(p.trace);
-    WorkItem item;
-    if (p.shared) {
-        item.expert = kSharedExpertId;
-        item.start = blockIdx.y * kTsTileN;
-        item.count = min((uint32_t)kTsTileN, p.tokens - item.start);
-    } else {
-        if (blockIdx.y >= p.n_work[0]) return;
-        item = p.work[blockIdx.y];
-    }
-    const uint32_t count = min(item.count, (uint32_t)kTsTileN);
-    const uint32_t n_cols = (count + 15u) & ~15u;
-    const uint32_t n_kb = p.kdim / kPfKBlock;
-    const uint32_t n_box = (n_cols + kPfBoxRows - 1) / kPfBoxRows;
-    const uint32_t b_slot = n_box * (kPfBoxRows * 128u);
-
-    if (tid == 0) {
-        for (int s = 0; s < kTsAStages; ++s) { mbar_init(&a_full[s], kPfProducerWarps); mbar_init(&a_empty[s], 1); }
-        for (int j = 0; j < kTsBDepth; ++j) { mbar_init(&b_full[j], 1); mbar_init(&b_empty[j], 1); }
-        mbar_init(accum, 1);
-        mbar_fence_init();
-    }
-    if (warp == kPfMmaWarp) {
-        tmem_alloc(tmem_slot, kPfTmemCols);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
-    bool ok = true;
-    trace_mark(p.trace, 0);
-    auto wait = [&](uint64_t *bar, uint32_t parity) {
-        bool done = false;
-        for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = pf_try_wait(bar, parity);
-        if (!done) atomicExch(p.status, 1u);
-        return done;
-    };
-
-    if (warp < kPfProducerWarps) {
-        // ---------------- producers ----------------
-        // warp -> (lane quarter of tensor memory, matrix, half row); thread -> row = quarter * 32 + lane
-        const uint32_t q = warp & 3u, mat = (warp >> 2) >> 1, half = (warp >> 2) & 1u, row = q * 32u + lane;
-        const size_t row_bytes = (size_t)p.kdim * BITS / 8;
-        const uint32_t groups = p.kdim / kGroup;
-        AffineMat m;
-        uint32_t r;
-        if (PHASE == 0) {
-            r = blockIdx.x * kPfTileM + row;
-            if (p.shared) m = mat ? p.s1 : p.s0;
-            else {
-                const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
-                const int o = mat ? 3 : 0;
-                m = AffineMat{blob + p.off.o[o], reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 1]),
-                              reinterpret_cast<const uint16_t *>(blob + p.off.o[o + 2])};
-            }
-        } else {
-            r = blockIdx.x * 2 * kPfTileM + mat * kPfTileM + row;
-            if (p.shared) m = p.s0;
-            else {
-                const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
-                m = AffineMat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
-                              reinterpret_cast<const uint16_t *>(blob + p.off.o[8])};
-            }
-        }
-        const uint8_t *wsrc = m.w + (size_t)r * row_bytes + half * (BITS * 4);
-        const uint16_t *ssrc = m.s + (size_t)r * groups, *bsrc_meta = m.b + (size_t)r * groups;
-        // this thread's 16 columns inside an A stage: lane field = its quarter, column = matrix * 32 + half * 16
-        const uint32_t a_dst = tmem + ((q * 32u) << 16) + kTsABase + mat * 32u + half * 16u;
-        PackedCodes<BITS> codes[kPfAhead];
-        uint16_t ms[kPfAhead], mb[kPfAhead];
-        auto fetch = [&](PackedCodes<BITS> &c, uint16_t &s_, uint16_t &b_, uint32_t kb) {
-            if (kb >= n_kb) return;
-            pf_load_codes<BITS>(c, wsrc + (size_t)kb * (kPfKBlock * BITS / 8));
-            s_ = ssrc[kb]; b_ = bsrc_meta[kb];
-        };
-#pragma unroll
-        for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], mb[i], i);
-        auto step = [&](auto S, auto C, uint32_t kb) {
-            constexpr uint32_t s = decltype(S)::value;
-            constexpr int cs = decltype(C)::value;
-            if (kb >= n_kb || !ok) return;
-            const __half2 sc = meta_half2<META>(ms[cs]), bi = meta_half2<META>(mb[cs]);
-            const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f));
-            uint32_t o[16];
-            dequant_regs<BITS>(codes[cs], sc, sc16, bi, o);
-            fetch(codes[cs], ms[cs], mb[cs], kb + kPfAhead);      // the slot is free again
-            ok = wait(&a_empty[s], ((kb / kTsAStages) & 1u) ^ 1u);      // free once the MMAs that read it have finished
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            tc_fence_after_sync();
-            tmem_st16(a_dst + s * kTsAStageCols, o);
-            tmem_st_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&a_full[s]);
-        };
-        static_assert(kTsAStages == 2 && kPfAhead == 3, "the unrolled body below is written for 2 stages and 3 code slots");
-        using U0 = std::integral_constant<uint32_t, 0>; using U1 = std::integral_constant<uint32_t, 1>;
-        using I0 = std::integral_constant<int, 0>; using I1 = std::integral_constant<int, 1>; using I2 = std::integral_constant<int, 2>;
-        for (uint32_t kb = 0; kb < n_kb && ok; kb += 6) {
-            step(U0{}, I0{}, kb);
-            step(U1{}, I1{}, kb + 1);
-            step(U0{}, I2{}, kb + 2);
-            step(U1{}, I0{}, kb + 3);
-            step(U0{}, I1{}, kb + 4);
-            step(U1{}, I2{}, kb + 5);
-        }
-        trace_mark(p.trace, 1);
-    } else if (warp == kPfTmaWarp) {
-        if (lane == 0) {
-            uint32_t j = 0, jph = 0;
-            for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
-                ok = wait(&b_empty[j], jph ^ 1u);
-                if (!ok) break;
-                mbar_expect_tx(&b_full[j], b_slot);
-                for (uint32_t x = 0; x < n_box; ++x)
-                    tma_load_2d(b_ring + j * b_slot + x * (kPfBoxRows * 128u), &args.tmap_b, kb * kPfKBlock,
-                                item.start + x * kPfBoxRows, &b_full[j]);
-                if (++j == kTsBDepth) { j = 0; jph ^= 1u; }
-            }
-        }
-    } else if (lane == 0) {
-        // ---------------- MMA issue ----------------
-        const uint32_t idesc = umma_idesc_f16(kPfTileM, n_cols);
-        uint32_t j = 0, jph = 0;
-        for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
-            const uint32_t s = kb % kTsAStages;
-            ok = wait(&a_full[s], (kb / kTsAStages) & 1u) && wait(&b_full[j], jph);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t a0 = tmem + kTsABase + s * kTsAStageCols;          // matrix 0; matrix 1 is 32 columns on
-            const uint64_t db = umma_desc_sw128(b_ring + j * b_slot);
-#pragma unroll
-            for (uint32_t k = 0; k < kPfKBlock / 16; ++k) {        // 16 K values = 8 columns of A = +2 in B's address field
-                const uint32_t accumulate = (kb | k) != 0u;
-                umma_f16_ts(tmem, a0 + 8 * k, db + 2 * k, idesc, accumulate);
-                umma_f16_ts(tmem + kTsAccCols, a0 + 32 + 8 * k, db + 2 * k, idesc, accumulate);
-            }
-            umma_commit(&a_empty[s]);
-            umma_commit(&b_empty[j]);
-            if (++j == kTsBDepth) { j = 0; jph ^= 1u; }
-        }
-        if (ok) umma_commit(accum);
-    }
-
-    if (warp < kPfProducerWarps) {
-        // ---------------- epilogue ----------------
-        if (ok) ok = wait(accum, 0u);
-        ok = __all_sync(0xffffffffu, ok);
-        const uint32_t q = warp & 3u, g = warp >> 2;               // lane quarter; column group of 48
-        if (ok) tc_fence_after_sync();
-        trace_mark(p.trace, 2);
-        for (uint32_t cb = g * 48u; ok && cb < g * 48u + 48u && cb < n_cols; cb += 16u) {
-            const uint32_t lane_addr = tmem + ((q * 32u) << 16);
-            uint32_t a0[16], a1[16];
-            tmem_ld16(lane_addr + cb, a0);
-            tmem_ld16(lane_addr + kTsAccCols + cb, a1);
-            tmem_ld_wait();
-            if (PHASE == 0) {
-                const uint32_t f = blockIdx.x * kPfTileM + q * 32u + lane;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t n = cb + i;
-                    if (n < count) {
-                        float gv = __uint_as_float(a0[i]), u = __uint_as_float(a1[i]);
-                        if (p.round_gate_up) { gv = round_mid<OUT>(gv); u = round_mid<OUT>(u); }
-                        // exp and the quotient through the fast intrinsics (2 ulp): far below the fp16 operand rounding
-                        const float a = p.act == ACT_SILU ? __fdividef(gv, 1.0f + __expf(-gv)) : act_gelu_tanh(gv);
-                        store_mid<OUT>(p.out, (size_t)(item.start + n) * p.out_stride + f, a * u);
-                    }
-                }
-            } else {
-                const uint32_t d = blockIdx.x * 2 * kPfTileM + q * 32u + lane;
-                float *out = static_cast<float *>(p.out);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t n = cb + i;
-                    if (n < count) {
-                        const float sc = p.row_scale != nullptr ? p.row_scale[item.start + n] : 1.0f;
                         out[(size_t)(item.start + n) * p.out_stride + d] = __uint_as_float(a0[i]) * sc;
                         out[(size_t)(item.start + n) * p.out_stride + d + kPfTileM] = __uint_as_float(a1[i]) * sc;
                     }
