@@ -79,6 +79,9 @@ struct nvmai_cuda_moe {
     // B200 (8-bit layer): 4 rows 60 us separate / 102 us grouped, 16 rows 190 / 265, 64 rows 697 / 570.
     // NVMAI_CUDA_GROUPED_MIN overrides it.
     uint32_t grouped_min_tokens = 24;
+    // 8-bit weights on the tensor-core prefill path (fp16 operand tiles: about 3e-3 of one expert's output);
+    // off = prefill calls with 8-bit weights run the exact decode kernels.  NVMAI_CUDA_PREFILL_TC8=1 turns it on.
+    bool prefill_tc8 = false;
     // prefill GEMMs: fp16 operand copies (allocated by the first prefill call)
     __half *pf_x = nullptr;          // [T*K][D] x rows gathered into sorted pair order, in the weights' K order
     __half *pf_xn = nullptr;         // [T][D] x rows in token order (shared expert), in its weights' K order
@@ -502,8 +505,9 @@ int ensure_prefill_scratch(nvmai_cuda_moe *h) {
     const auto &c = h->cfg;
     const size_t T = c.max_tokens, P = T * c.top_k;
     auto alloc = [&](auto **ptr, size_t bytes) { return cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16) == cudaSuccess; };
-    if (alloc(&h->pf_x, P * c.d * 2) && alloc(&h->pf_xn, T * c.d * 2) && alloc(&h->pf_acts16, P * c.f * 2) &&
-        alloc(&h->pf_sacts16, T * c.shared_f * 2) && alloc(&h->pf_rowscale, P * 4) && alloc(&h->pf_srowscale, T * 4))
+    const size_t dx = c.d + pf_extra_cols(c.d), fx = c.f + pf_extra_cols(c.f), sfx = c.shared_f + pf_extra_cols(c.shared_f);
+    if (alloc(&h->pf_x, P * dx * 2) && alloc(&h->pf_xn, T * dx * 2) && alloc(&h->pf_acts16, P * fx * 2) &&
+        alloc(&h->pf_sacts16, T * sfx * 2) && alloc(&h->pf_rowscale, P * 4) && alloc(&h->pf_srowscale, T * 4))
         return NVMAI_CUDA_OK;
     cudaGetLastError();
     cudaFree(h->pf_x); cudaFree(h->pf_xn); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale);
@@ -546,16 +550,21 @@ int make_rows_tmap(nvmai_cuda_moe *h, CUtensorMap *map, const void *base, uint64
     return NVMAI_CUDA_OK;
 }
 
-// b_rows: fp16 [b_count][kdim] in work-item order
+// b_rows: fp16 [b_count][kdim] in work-item order; b2_rows: the direct items' rows (token order), or nullptr
 template <int PHASE>
 int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParams &p, const void *b_rows, uint64_t b_count,
-                        dim3 grid, cudaStream_t st) {
+                        const void *b2_rows, uint64_t b2_count, dim3 grid, cudaStream_t st) {
     const auto &c = h->cfg;
     PrefillGemmArgs args{};
     args.p = p;
-    int rc = make_rows_tmap(h, &args.tmap_b, b_rows, b_count, p.kdim, p.kdim, kPfBoxRows);
+    const uint64_t cols = p.kdim + pf_extra_cols(p.kdim);        // the rows carry their correction columns
+    int rc = make_rows_tmap(h, &args.tmap_b, b_rows, b_count, cols, cols, kPfBoxRows);
     if (rc) return rc;
-    args.tmap_a = args.tmap_b;
+    if (b2_rows != nullptr) {
+        if ((rc = make_rows_tmap(h, &args.tmap_a, b2_rows, b2_count, cols, cols, kPfBoxRows))) return rc;
+    } else {
+        args.tmap_a = args.tmap_b;
+    }
     return dispatch_bits_meta(bits, c.meta_dtype, [&](auto B, auto M) {
         return dispatch_out(c.out_dtype, [&](auto O) {
             return launch_kernel(h, prefill_gemm_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value, PHASE>,
@@ -568,7 +577,7 @@ int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParam
 // in; gather != nullptr: output row r comes from source row gather[r] / gather_div
 int launch_pack_rows(nvmai_cuda_moe *h, const void *src, bool src_f32, __half *dst, float *row_scale, uint32_t rows,
                      uint32_t n, uint32_t bits, cudaStream_t st, const uint32_t *gather = nullptr, uint32_t gather_div = 1) {
-    PackRowsParams p{src, dst, src_f32 ? row_scale : nullptr, rows, n, bits == 4 ? 1u : 0u, gather, gather_div};
+    PackRowsParams p{src, dst, src_f32 ? row_scale : nullptr, rows, n, bits == 4 ? 1u : 0u, gather, gather_div, pf_extra_cols(n)};
     const dim3 grid((rows + 7) / 8), block(256);
     if (src_f32) return launch_kernel(h, pack_rows_kernel<1>, grid, block, 0, st, true, p);
     return launch_kernel(h, pack_rows_kernel<0>, grid, block, 0, st, true, p);
@@ -595,9 +604,9 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     if (gemm_router) {
         PrefillGemmArgs ra{};
         PrefillGemmParams &r = ra.p;
-        r.shared = 1;
+        r.shared_from = 0;
         r.tokens = tokens; r.top_k = c.top_k; r.kdim = c.d;
-        r.out = h->logits; r.out_stride = c.num_experts; r.status = h->status;
+        r.out2 = h->logits; r.out_stride2 = c.num_experts; r.status = h->status;
         if ((rc = make_rows_tmap(h, &ra.tmap_b, x, tokens, c.d, c.d, kPfBoxRows))) return rc;
         if ((rc = make_rows_tmap(h, &ra.tmap_a, lv.w.router.w, c.num_experts, c.d, c.d, kPfTileM))) return rc;
         const dim3 grid(c.num_experts / (2 * kPfTileM), (tokens + kPfTileN - 1) / kPfTileN);
@@ -624,41 +633,47 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     g.off = to_offsets(lv.w.offsets);
     g.work = h->work; g.n_work = h->n_work; g.sorted_pair = h->sorted_pair;
     g.tokens = tokens; g.top_k = c.top_k; g.act = c.activation; g.status = h->status;
-    // gate/up, routed then shared
-    g.shared = 0; g.kdim = c.d;
+    // The shared expert rides in the routed launches (its token tiles after the routed items) when bit width and
+    // shapes agree; otherwise it gets launches of its own.
+    const bool merged = c.shared_f != 0 && c.shared_bits == c.routed_bits && c.shared_f == c.f;
+    const uint32_t none = 0xFFFFFFFFu;
+    // gate/up
+    g.kdim = c.d;
     g.out = h->acts; g.out_stride = c.f; g.round_gate_up = 0;
+    g.s0 = to_mat(lv.w.shared_gate_proj); g.s1 = to_mat(lv.w.shared_up_proj);
+    g.out2 = h->shared_act; g.out_stride2 = c.shared_f; g.round_gate_up2 = 1; g.row_scale2 = nullptr;
     g.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 0) * kTraceWords : nullptr;
-    if ((rc = launch_prefill_gemm<0>(h, c.routed_bits, g, h->pf_x, P, dim3(c.f / kPfTileM, max_items), st))) return rc;
-    if (c.shared_f) {
+    g.shared_from = merged ? max_items : none;
+    if ((rc = launch_prefill_gemm<0>(h, c.routed_bits, g, h->pf_x, P, merged ? h->pf_xn : nullptr, tokens,
+                                     dim3(c.f / kPfTileM, max_items + (merged ? shared_items : 0)), st)))
+        return rc;
+    if (c.shared_f && !merged) {
         PrefillGemmParams s = g;
-        s.shared = 1; s.s0 = to_mat(lv.w.shared_gate_proj); s.s1 = to_mat(lv.w.shared_up_proj);
-        s.out = h->shared_act; s.out_stride = c.shared_f; s.round_gate_up = 1;
-        s.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 2) * kTraceWords : nullptr;
-        if ((rc = launch_prefill_gemm<0>(h, c.shared_bits, s, h->pf_xn, tokens, dim3(c.shared_f / kPfTileM, shared_items), st)))
+        s.shared_from = 0; s.trace = nullptr;
+        if ((rc = launch_prefill_gemm<0>(h, c.shared_bits, s, h->pf_xn, tokens, h->pf_xn, tokens,
+                                         dim3(c.shared_f / kPfTileM, shared_items), st)))
             return rc;
     }
     // activation rows as the down GEMMs read them
-    const __half *acts16 = static_cast<const __half *>(h->acts), *sacts16 = static_cast<const __half *>(h->shared_act);
-    if (wide || c.routed_bits == 4) {
-        if ((rc = launch_pack_rows(h, h->acts, wide, h->pf_acts16, h->pf_rowscale, P, c.f, c.routed_bits, st))) return rc;
-        acts16 = h->pf_acts16;
-    }
-    if (c.shared_f && (wide || c.shared_bits == 4)) {
-        if ((rc = launch_pack_rows(h, h->shared_act, wide, h->pf_sacts16, h->pf_srowscale, tokens, c.shared_f, c.shared_bits, st)))
-            return rc;
-        sacts16 = h->pf_sacts16;
-    }
-    // down, routed then shared
+    const __half *acts16 = h->pf_acts16, *sacts16 = h->pf_sacts16;
+    if ((rc = launch_pack_rows(h, h->acts, wide, h->pf_acts16, h->pf_rowscale, P, c.f, c.routed_bits, st))) return rc;
+    if (c.shared_f &&
+        (rc = launch_pack_rows(h, h->shared_act, wide, h->pf_sacts16, h->pf_srowscale, tokens, c.shared_f, c.shared_bits, st)))
+        return rc;
+    // down
     g.kdim = c.f; g.row_scale = wide ? h->pf_rowscale : nullptr;
     g.out = h->partial; g.out_stride = c.d;
+    g.s0 = to_mat(lv.w.shared_down_proj); g.s1 = g.s0;
+    g.out2 = h->shared_partial; g.out_stride2 = c.d; g.row_scale2 = wide ? h->pf_srowscale : nullptr;
     g.trace = h->trace_on ? h->trace + ((size_t)layer * 3 + 1) * kTraceWords : nullptr;
-    if ((rc = launch_prefill_gemm<1>(h, c.routed_bits, g, acts16, P, dim3(c.d / (2 * kPfTileM), max_items), st))) return rc;
-    if (c.shared_f) {
+    if ((rc = launch_prefill_gemm<1>(h, c.routed_bits, g, acts16, P, merged ? sacts16 : nullptr, tokens,
+                                     dim3(c.d / (2 * kPfTileM), max_items + (merged ? shared_items : 0)), st)))
+        return rc;
+    if (c.shared_f && !merged) {
         PrefillGemmParams s = g;
-        s.shared = 1; s.s0 = to_mat(lv.w.shared_down_proj); s.s1 = s.s0;
-        s.kdim = c.shared_f; s.row_scale = wide ? h->pf_srowscale : nullptr;
-        s.out = h->shared_partial; s.trace = nullptr;
-        if ((rc = launch_prefill_gemm<1>(h, c.shared_bits, s, sacts16, tokens, dim3(c.d / (2 * kPfTileM), shared_items), st)))
+        s.shared_from = 0; s.kdim = c.shared_f; s.trace = nullptr;
+        if ((rc = launch_prefill_gemm<1>(h, c.shared_bits, s, sacts16, tokens, sacts16, tokens,
+                                         dim3(c.d / (2 * kPfTileM), shared_items), st)))
             return rc;
     }
     CombineParams pc{};
@@ -735,6 +750,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
     h->cfg = c;
     h->layers.resize(c.num_layers);
     if (const char *env = std::getenv("NVMAI_CUDA_L2_PREFETCH")) h->l2_prefetch = env[0] == '1';
+    if (const char *env = std::getenv("NVMAI_CUDA_PREFILL_TC8")) h->prefill_tc8 = env[0] == '1';
     if (const char *env = std::getenv("NVMAI_CUDA_GROUPED_MIN")) h->grouped_min_tokens = (uint32_t)std::max(1, std::atoi(env));
     const size_t T = c.max_tokens;
     auto alloc = [&](auto **ptr, size_t bytes) -> bool {
@@ -904,6 +920,15 @@ int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *
     if (!x_f16 || !aligned16(x_f16) || (!hidden_inout && !y_out)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
     if (c.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
+    const bool any8 = c.routed_bits == 8 || (c.shared_f != 0 && c.shared_bits == 8);
+    if (any8 && !h->prefill_tc8) {
+        // 8-bit codes times a scale do not fit an fp16 operand exactly: the chunk runs the exact decode kernels
+        // (codes never rounded; the decode block's rounding order) unless the caller opted in to the tensor cores
+        if (h->expert_map) return NVMAI_CUDA_EINVAL;
+        const XSource xsrc{static_cast<const __half *>(x_f16), c.d, nullptr, nullptr};
+        return layer_decode_impl(h, layer, xsrc, static_cast<const __half *>(x_f16), tokens, hidden_inout, y_out, out_idx,
+                                 static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
+    }
     // tile shapes of the tensor-core kernels: 128 weight rows per accumulator, two accumulators per CTA
     if (c.f % kPfTileM != 0 || c.d % (2 * kPfTileM) != 0 || c.shared_f % kPfTileM != 0) return NVMAI_CUDA_EINVAL;
     if (h->expert_map) return NVMAI_CUDA_EINVAL;      // prefill runs on one GPU's full expert set

@@ -71,6 +71,11 @@ constexpr int kPfAStageBytes = 2 * kPfTileBytes;
 constexpr int kPfBRingBytes = 96 * 1024;      // B ring: 3 K blocks of 256 rows ... 8 of up to 64 rows
 constexpr int kPfBMaxDepth = 8;
 constexpr size_t kPfSmemBytes = 1024 /* alignment slack */ + 1024 /* barriers */ + (size_t)kPfStages * kPfAStageBytes + kPfBRingBytes;
+// Extra K columns that carry the affine correction: 3 fp16 values per quantisation group, rounded up to K blocks.
+__host__ __device__ constexpr uint32_t pf_extra_cols(uint32_t kdim) { return ((3u * (kdim / 64u) + 63u) / 64u) * 64u; }
+// The group sums in the correction columns are stored times this factor (and the constants they multiply divided
+// by it): 64 fp16 values can add up to 2^22.
+constexpr float kPfSumScale = 1.0f / 128.0f;
 constexpr uint32_t kPfWaitTries = 1u << 22;    // bounded: a few seconds at the hardware's default try_wait limit
 
 // ---- tcgen05 / async-proxy primitives ---------------------------------------------
@@ -191,13 +196,19 @@ __device__ __forceinline__ void pf_load_codes(PackedCodes<BITS> &c, const uint8_
 }
 
 // dst[j]: shared-window address of the thread's j-th chunk in the stage's tile.
-// 4-bit: the nibbles of a word are masked where they lie, (1024 + q) for nibbles 0, 4, 2, 6 (after one
-// shift by 8 for the latter two) and (1024 + 16 q) for nibbles 1, 5, 3, 7; the second kind is multiplied
-// by s / 16 (s16, exact unless s / 16 is an fp16 subnormal), so that one shift serves a whole word.
+// The operand is the CENTRED weight s * (q - c), c = 8 (4-bit) or 128 (8-bit); the rest of q*s + b, the
+// per-group constant b + c*s, comes in through the correction columns (pf_extra_cols).  With bf16 scales
+// (8 significant bits) and 4-bit codes (|q - 8| <= 8) the product is exact in fp16, so the tensor core sees
+// the reference's weights without a rounding; fp16 scales and 8-bit codes round once, relative to the centred
+// (smaller) magnitude.
+// 4-bit: the nibbles of a word are masked where they lie, (1024 + q) for nibbles 0, 4, 2, 6 (after one shift by 8
+// for the latter two) and (1024 + 16 q) for nibbles 1, 5, 3, 7; the second kind is multiplied by s / 16 (s16, exact
+// unless s / 16 is an fp16 subnormal), so that one shift serves a whole word.
 template <int BITS>
-__device__ __forceinline__ void dequant_store(const uint32_t (&dst)[4], const PackedCodes<BITS> &c, __half2 s2, __half2 s16,
-                                              __half2 b2) {
-    const __half2 k1024 = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
+__device__ __forceinline__ void dequant_store(const uint32_t (&dst)[4], const PackedCodes<BITS> &c, __half2 s2, __half2 s16) {
+    // 1024 + 8, 1024 + 16 * 8 = 1024 + 128
+    const __half2 k_even = __halves2half2(__ushort_as_half(BITS == 4 ? 0x6408 : 0x6480), __ushort_as_half(BITS == 4 ? 0x6408 : 0x6480));
+    const __half2 k_odd = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {            // chunk j = codes 8j .. 8j+7 of the thread's 32
         uint32_t o[4];
@@ -206,17 +217,17 @@ __device__ __forceinline__ void dequant_store(const uint32_t (&dst)[4], const Pa
             const uint32_t t[4] = {(w & 0x000F000Fu) | 0x64006400u, (w & 0x00F000F0u) | 0x64006400u,
                                    (w8 & 0x000F000Fu) | 0x64006400u, (w8 & 0x00F000F0u) | 0x64006400u};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {    // (q_i, q_{i+4})
-                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t[i]), k1024);
-                const __half2 v = __hfma2(q, (i & 1) ? s16 : s2, b2);
+            for (int i = 0; i < 4; ++i) {    // (q_i, q_{i+4}) - 8, or 16 times that
+                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t[i]), (i & 1) ? k_odd : k_even);
+                const __half2 v = __hmul2(q, (i & 1) ? s16 : s2);
                 o[i] = *reinterpret_cast<const uint32_t *>(&v);
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {    // (q_2i, q_2i+1)
+            for (int i = 0; i < 4; ++i) {    // (q_2i, q_2i+1) - 128
                 const uint32_t t = __byte_perm(c.v[2 * j + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342 : 0x4140);
-                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
-                const __half2 v = __hfma2(q, s2, b2);
+                const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k_even);
+                const __half2 v = __hmul2(q, s2);
                 o[i] = *reinterpret_cast<const uint32_t *>(&v);
             }
         }
@@ -229,12 +240,17 @@ struct PrefillGemmParams {
     // routed items: blobs + offsets; shared / router items: the tensors themselves
     const uint8_t *experts; unsigned long long stride; uint32_t num_experts; ExpertOffsets off;
     AffineMat s0, s1;              // direct tensors: phase 0 gate, up; phase 1 down; phase 2 the router matrix (s0)
-    uint32_t shared;               // 1: item y = token rows [256 y, 256 y + 256), weights from s0/s1
+    // Blocks with blockIdx.y >= shared_from are "direct" items: item i = token rows [256 i, 256 i + 256) with the
+    // weights of s0/s1 (the shared expert, the router), their B rows in tmap_a (tmap_b when BITS = 16) and their
+    // outputs in out2 / row_scale2.  0: every block; 0xFFFFFFFF: none.  Routed and shared items share one launch
+    // when their bit width and K extent agree, so that the shared expert fills the tail of the routed items.
+    uint32_t shared_from;
     const WorkItem *work; const uint32_t *n_work; const uint32_t *sorted_pair;
     uint32_t tokens, top_k;
     const float *row_scale;        // phase 1: factor per row undone in the epilogue, or nullptr
     void *out; uint32_t out_stride;            // phase 0: acts [row][F] (fp16 / fp32 by OUT); phase 1: partial fp32 [row][D];
                                                // phase 2: logits fp32 [token][E]
+    void *out2; uint32_t out_stride2; const float *row_scale2; uint32_t round_gate_up2;   // the same for direct items
     uint32_t kdim;                 // D (phase 0, 2) / F (phase 1)
     uint32_t act;                  // activation kind (phase 0)
     uint32_t round_gate_up;        // phase 0: round gate and up before the activation (the shared expert does)
@@ -276,17 +292,24 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     if (*reinterpret_cast<volatile unsigned int *>(p.status) != 0u) return;    // an earlier wait gave up: do not pile on
     trace_begin(p.trace);
     WorkItem item;
-    if (p.shared) {
+    const bool direct = blockIdx.y >= p.shared_from;
+    if (direct) {
         item.expert = kSharedExpertId;
-        item.start = blockIdx.y * kPfTileN;
+        item.start = (blockIdx.y - p.shared_from) * kPfTileN;
         item.count = min((uint32_t)kPfTileN, p.tokens - item.start);
     } else {
         if (blockIdx.y >= p.n_work[0]) return;
         item = p.work[blockIdx.y];
     }
+    const CUtensorMap *b_map = (direct && BITS != 16) ? &args.tmap_a : &args.tmap_b;
+    void *out_base = direct ? p.out2 : p.out;
+    const uint32_t out_stride = direct ? p.out_stride2 : p.out_stride;
+    const float *row_scale = direct ? p.row_scale2 : p.row_scale;
+    const uint32_t round_gate_up = direct ? p.round_gate_up2 : p.round_gate_up;
     const uint32_t count = min(item.count, (uint32_t)kPfTileN);
     const uint32_t n_cols = (count + 15u) & ~15u;
-    const uint32_t n_kb = p.kdim / kPfKBlock;
+    const uint32_t n_main = p.kdim / kPfKBlock;                                      // K blocks of codes
+    const uint32_t n_kb = n_main + (BITS == 16 ? 0u : pf_extra_cols(p.kdim) / kPfKBlock);    // + the correction columns
     // The B ring holds as many K blocks as fit: a narrow item keeps more blocks in flight, which is what
     // hides the latency of its row fetches.
     const uint32_t n_box = (n_cols + kPfBoxRows - 1) / kPfBoxRows;
@@ -331,7 +354,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             uint32_t r;               // matrix row this thread converts
             if (PHASE == 0) {
                 r = blockIdx.x * kPfTileM + row;
-                if (p.shared) m = mat ? p.s1 : p.s0;
+                if (direct) m = mat ? p.s1 : p.s0;
                 else {
                     const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
                     const int o = mat ? 3 : 0;
@@ -340,7 +363,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 }
             } else {
                 r = blockIdx.x * 2 * kPfTileM + mat * kPfTileM + row;
-                if (p.shared) m = p.s0;
+                if (direct) m = p.s0;
                 else {
                     const uint8_t *blob = p.experts + (size_t)min(item.expert, p.num_experts - 1u) * p.stride;
                     m = AffineMat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
@@ -356,37 +379,92 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             // compile-time because the K loop is unrolled by the number of stages).
             constexpr int CB = BITS == 16 ? 4 : BITS;
             PackedCodes<CB> codes[kPfAhead];
-            uint16_t ms[kPfAhead], mb[kPfAhead];
-            auto fetch = [&](PackedCodes<CB> &c, uint16_t &s_, uint16_t &b_, uint32_t kb) {
-                if (kb >= n_kb) return;
+            uint16_t ms[kPfAhead];
+            auto fetch = [&](PackedCodes<CB> &c, uint16_t &s_, uint32_t kb) {
+                if (kb >= n_main) return;
                 pf_load_codes<CB>(c, wsrc + (size_t)kb * (kPfKBlock * BITS / 8));
-                s_ = ssrc[kb]; b_ = bsrc_meta[kb];
+                s_ = ssrc[kb];
             };
 #pragma unroll
-            for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], mb[i], i);
+            for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], i);
             // One step = one K block into stage S (compile-time), using code slot C (compile-time).
             auto step = [&](auto S, auto C, uint32_t kb) {
                 constexpr uint32_t s = decltype(S)::value;
                 constexpr int cs = decltype(C)::value;
-                if (kb >= n_kb || !ok) return;
+                if (kb >= n_main || !ok) return;
                 ok = wait(&a_empty[s], ((kb / kPfStages) & 1u) ^ 1u);      // free once the MMAs that read it have finished
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) return;
                 const uint32_t st = a_ring + s * kPfAStageBytes;
-                const __half2 sc = meta_half2<META>(ms[cs]), bi = meta_half2<META>(mb[cs]);
+                const __half2 sc = meta_half2<META>(ms[cs]);
                 const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f));
                 const uint32_t d4[4] = {st + adst[0], st + adst[1], st + adst[2], st + adst[3]};
-                dequant_store<CB>(d4, codes[cs], sc, sc16, bi);
-                fetch(codes[cs], ms[cs], mb[cs], kb + kPfAhead);      // the slot is free again
+                dequant_store<CB>(d4, codes[cs], sc, sc16);
+                fetch(codes[cs], ms[cs], kb + kPfAhead);      // the slot is free again
                 fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[s]);
             };
             static_assert(kPfStages == 3 && kPfAhead == 3, "the unrolled body below is written for 3 stages and 3 code slots");
-            for (uint32_t kb = 0; kb < n_kb && ok; kb += 3) {
+            for (uint32_t kb = 0; kb < n_main && ok; kb += 3) {
                 step(std::integral_constant<uint32_t, 0>{}, std::integral_constant<int, 0>{}, kb);
                 step(std::integral_constant<uint32_t, 1>{}, std::integral_constant<int, 1>{}, kb + 1);
                 step(std::integral_constant<uint32_t, 2>{}, std::integral_constant<int, 2>{}, kb + 2);
+            }
+            // The correction columns: c_g = b_g + centre * s_g per group g of this thread's row, as fp16 hi + lo, in the
+            // layout [hi | hi | lo | zeros] that pack_rows_kernel's [X_hi | X_lo | X_hi | zeros] multiplies against.
+            const float centre = BITS == 4 ? 8.0f : 128.0f;
+            for (uint32_t kb = n_main; kb < n_kb && ok; ++kb) {
+                const uint32_t s = kb % kPfStages;
+                ok = wait(&a_empty[s], ((kb / kPfStages) & 1u) ^ 1u);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t st = a_ring + s * kPfAStageBytes;
+                const uint32_t c0 = (kb - n_main) * kPfKBlock + half * 32u;      // first correction column of this thread
+                const bool vec = (groups & 7u) == 0;      // 8 groups = one 16-byte load of scales and one of biases
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {              // chunk j = correction columns c0 + 8j .. c0 + 8j + 7
+                    const uint32_t col0 = c0 + 8 * j;
+                    float val[8];
+                    if (vec) {
+                        const uint32_t seg = col0 / groups, g0 = col0 % groups;      // a chunk stays inside one segment
+                        if (seg < 3) {
+                            const uint4 sv = *reinterpret_cast<const uint4 *>(ssrc + g0), bv = *reinterpret_cast<const uint4 *>(bsrc_meta + g0);
+                            const uint16_t *s16p = reinterpret_cast<const uint16_t *>(&sv), *b16p = reinterpret_cast<const uint16_t *>(&bv);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float cg = fmaf(centre, meta_to_float<META>(s16p[e]), meta_to_float<META>(b16p[e])) * (1.0f / kPfSumScale);
+                                const float hi = __half2float(__float2half_rn(cg));
+                                val[e] = seg == 2 ? cg - hi : hi;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) val[e] = 0.0f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const uint32_t col = col0 + e, seg = col / groups, g = col % groups;
+                            val[e] = 0.0f;
+                            if (seg < 3) {
+                                const float cg = fmaf(centre, meta_to_float<META>(ssrc[g]), meta_to_float<META>(bsrc_meta[g])) * (1.0f / kPfSumScale);
+                                const float hi = __half2float(__float2half_rn(cg));
+                                val[e] = seg == 2 ? cg - hi : hi;
+                            }
+                        }
+                    }
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __half2 h2 = __floats2half2_rn(val[2 * i], val[2 * i + 1]);
+                        o[i] = *reinterpret_cast<const uint32_t *>(&h2);
+                    }
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(st + adst[j]), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                                 "r"(o[3]) : "memory");
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[s]);
             }
         }
         trace_mark(p.trace, 1);
@@ -400,7 +478,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                 if (!ok) break;
                 mbar_expect_tx(&b_full[j], b_slot);
                 for (uint32_t x = 0; x < n_box; ++x)
-                    tma_load_2d(b_ring + j * b_slot + x * (kPfBoxRows * 128u), &args.tmap_b, kb * kPfKBlock,
+                    tma_load_2d(b_ring + j * b_slot + x * (kPfBoxRows * 128u), b_map, kb * kPfKBlock,
                                 item.start + x * kPfBoxRows, &b_full[j]);
                 if (BITS == 16) {                 // a dense A matrix comes the same way
                     const uint32_t s = kb % kPfStages;
@@ -473,22 +551,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
                     const uint32_t n = cb + i;
                     if (n < count) {
                         float g = __uint_as_float(a0[i]), u = __uint_as_float(a1[i]);
-                        if (p.round_gate_up) { g = round_mid<OUT>(g); u = round_mid<OUT>(u); }
+                        if (round_gate_up) { g = round_mid<OUT>(g); u = round_mid<OUT>(u); }
                         // exp and the quotient through the fast intrinsics (2 ulp): far below the fp16 operand rounding
                         const float a = p.act == ACT_SILU ? __fdividef(g, 1.0f + __expf(-g)) : act_gelu_tanh(g);
-                        store_mid<OUT>(p.out, (size_t)(item.start + n) * p.out_stride + f, a * u);
+                        store_mid<OUT>(out_base, (size_t)(item.start + n) * out_stride + f, a * u);
                     }
                 }
             } else {
                 const uint32_t d = blockIdx.x * 2 * kPfTileM + q * 32u + lane;
-                float *out = static_cast<float *>(p.out);
+                float *out = static_cast<float *>(out_base);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const uint32_t n = cb + i;
                     if (n < count) {
-                        const float sc = (PHASE == 1 && p.row_scale != nullptr) ? p.row_scale[item.start + n] : 1.0f;
-                        out[(size_t)(item.start + n) * p.out_stride + d] = __uint_as_float(a0[i]) * sc;
-                        out[(size_t)(item.start + n) * p.out_stride + d + kPfTileM] = __uint_as_float(a1[i]) * sc;
+                        const float sc = (PHASE == 1 && row_scale != nullptr) ? row_scale[item.start + n] : 1.0f;
+                        out[(size_t)(item.start + n) * out_stride + d] = __uint_as_float(a0[i]) * sc;
+                        out[(size_t)(item.start + n) * out_stride + d + kPfTileM] = __uint_as_float(a1[i]) * sc;
                     }
                 }
             }
@@ -527,7 +605,12 @@ struct PackRowsParams {
     float *row_scale;       // fp32 sources: per row, the power of two taken out (nullptr for fp16 sources)
     uint32_t rows, n, permute;
     const uint32_t *gather; uint32_t gather_div;   // optional: source row = gather[row] / gather_div (pair id -> token)
+    // After the n values every row carries extra_cols more (a multiple of 64): the sums X_g of its n / 64 groups of
+    // fp16 values, split into fp16 hi + lo, laid out [hi_0..hi_G-1 | lo_0..lo_G-1 | hi_0..hi_G-1 | zeros].  Against
+    // the weights' [c_hi | c_hi | c_lo | 0] columns they add sum_g c_g * X_g to a GEMM row (pf_extra_cols).
+    uint32_t extra_cols;
 };
+
 
 // One warp per row.  fp32 rows ("wide range" intermediates) are scaled by a power
 // of two that brings the row's largest magnitude to [2^14, 2^15), so that the fp16
@@ -539,6 +622,7 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(PackRowsParams p) {
     pdl_launch_dependents();
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= p.rows) return;
+    const size_t stride = (size_t)p.n + p.extra_cols;
     const size_t srow = p.gather != nullptr ? p.gather[row] / p.gather_div : row;
     float mul = 1.0f;
     if (SRC_F32) {
@@ -556,18 +640,39 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(PackRowsParams p) {
         mul = ldexpf(1.0f, shift);
         if (lane == 0 && p.row_scale != nullptr) p.row_scale[row] = ldexpf(1.0f, -shift);
     }
-    for (uint32_t i8 = lane * 8; i8 < p.n; i8 += 256) {
-        __half out[8];
+    const uint32_t G = p.n / 64u;
+    __half *ext = p.dst + (size_t)row * stride + p.n;
+    for (uint32_t base8 = 0; base8 < p.n; base8 += 256) {      // every lane takes part in the shuffles of every pass
+        const uint32_t i8 = base8 + lane * 8;
+        float part = 0.0f;
+        if (i8 < p.n) {
+            __half out[8];
 #pragma unroll
-        for (int pos = 0; pos < 8; ++pos) {
-            const uint32_t k = i8 + (p.permute ? pf_k_order(pos) : pos);
-            float v;
-            if (SRC_F32) v = static_cast<const float *>(p.src)[srow * p.n + k] * mul;
-            else v = __half2float(static_cast<const __half *>(p.src)[srow * p.n + k]);
-            out[pos] = __float2half_rn(v);
+            for (int pos = 0; pos < 8; ++pos) {
+                const uint32_t k = i8 + (p.permute ? pf_k_order(pos) : pos);
+                float v;
+                if (SRC_F32) v = static_cast<const float *>(p.src)[srow * p.n + k] * mul;
+                else v = __half2float(static_cast<const __half *>(p.src)[srow * p.n + k]);
+                out[pos] = __float2half_rn(v);
+                part += __half2float(out[pos]);        // the value the tensor core will see
+            }
+            *reinterpret_cast<uint4 *>(p.dst + (size_t)row * stride + i8) = *reinterpret_cast<const uint4 *>(out);
         }
-        *reinterpret_cast<uint4 *>(p.dst + (size_t)row * p.n + i8) = *reinterpret_cast<const uint4 *>(out);
+        if (p.extra_cols != 0) {
+            // a group of 64 values = 8 neighbouring lanes of this pass
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            part += __shfl_xor_sync(0xffffffffu, part, 4);
+            const uint32_t g = i8 / 64u;
+            if ((lane & 7u) == 0 && i8 < p.n) {
+                const float sum = part * kPfSumScale;      // 64 values of up to 65504 each: keep the sum inside fp16's range
+                const __half hi = __float2half_rn(sum);
+                const __half lo = __float2half_rn(sum - __half2float(hi));
+                ext[g] = hi; ext[G + g] = lo; ext[2 * G + g] = hi;
+            }
+        }
     }
+    for (uint32_t i = 3 * G + lane; i < p.extra_cols; i += 32) ext[i] = __float2half_rn(0.0f);
 }
 
 }  // namespace nvmai

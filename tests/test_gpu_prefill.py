@@ -71,22 +71,34 @@ def _check_rows(host, cfg, x, got, got_idx, rows, tol_gpu, hid0=None, got_hid=No
         assert margin > 1e-5, f"row {t}: router decision margin {margin} too small for an exact-index test"
         assert got_idx[t].tolist() == o_idx.tolist(), f"row {t}"
         assert np.all(np.isfinite(got[t]))
-        assert orc.rel_error(got[t], cpu) < tol_cpu, f"row {t} vs the reference CPU path"
+        # The bound against the fp32 CPU path is 1e-3.  On a few cancellation-heavy rows the reference's OWN shader
+        # semantics (activations rounded to half) sit further than that from its CPU path; there the CUDA path is
+        # held to the shader semantics' distance plus 2e-4 instead.
+        own = orc.rel_error(o_y, cpu)
+        assert orc.rel_error(got[t], cpu) < max(tol_cpu, own + 2e-4), f"row {t} vs the reference CPU path"
         assert orc.rel_error(got[t], o_y) < tol_gpu, f"row {t} vs the shader-semantics oracle"
         if got_hid is not None:
             assert orc.rel_error(got_hid[t], o_hid) < tol_gpu, f"row {t}: hidden"
 
 
-@pytest.mark.parametrize("bits,meta", [(4, fmt.META_BF16), (8, fmt.META_FP16)])
-def test_prefill_small_shape_every_row(bits, meta):
+# 8-bit weights on the tensor cores are an opt-in (NVMAI_CUDA_PREFILL_TC8=1): 8-bit codes times a scale need more
+# than fp16's 11 bits, so that path is held to 5e-3 here; by default 8-bit prefill calls run the exact kernels.
+TC8_TOL = 5e-3
+
+
+@pytest.mark.parametrize("bits,meta,tc8", [(4, fmt.META_BF16, False), (4, fmt.META_FP16, False), (8, fmt.META_FP16, False),
+                                           (8, fmt.META_FP16, True)])
+def test_prefill_small_shape_every_row(bits, meta, tc8, monkeypatch):
     """D 256, F 128, 32 experts, 40 rows (ragged items: about 10 rows per expert)"""
+    if tc8:
+        monkeypatch.setenv("NVMAI_CUDA_PREFILL_TC8", "1")
     host, cfg = _case(bits, meta, fmt.OUT_FP32, 40, seed=300 + bits)
     moe, dl, x, got, got_idx, got_w, _, _ = _run_prefill(host, cfg, 40, seed=310 + bits)
-    # The tensor-core operands are fp16(q*s + b).  With 4-bit codes the result stays inside the 1e-3 bound; with
-    # 8-bit codes (|w| up to 5, one fp16 ulp = 2^-11 of that) and only 4 groups per row to average over, single
-    # rows reach 1.5e-3, so this small 8-bit case is held to 2e-3 (the benchmark shape below is held to 1e-3).
-    _check_rows(host, cfg, x, got, got_idx, range(40), tol_gpu=1e-3 if bits == 4 else 2e-3,
-                tol_cpu=FFN_TOL if bits == 4 else 2e-3)
+    tol = TC8_TOL if tc8 else FFN_TOL
+    # bf16 scales times the centred 4-bit code are exact in fp16; fp16 scales (11 bits) round once more, which shows
+    # against the shader-semantics oracle (1.05e-3 on one row of this case) but stays inside 1e-3 of the CPU path
+    tol_gpu = 1.5e-3 if (bits == 4 and meta == fmt.META_FP16) else tol
+    _check_rows(host, cfg, x, got, got_idx, range(40), tol_gpu=tol_gpu, tol_cpu=tol)
 
 
 def test_prefill_reference_rounding_with_residual():
@@ -99,21 +111,37 @@ def test_prefill_reference_rounding_with_residual():
     _check_rows(host, cfg, x, got, got_idx, range(24), tol_gpu=3e-3, hid0=hid0, got_hid=got_hid, tol_cpu=2e-3)
 
 
+def test_prefill_shared_expert_with_its_own_bit_width(monkeypatch):
+    """4-bit routed experts, 8-bit shared expert on the tensor cores: the shared expert cannot ride in the routed
+    launches and gets its own"""
+    monkeypatch.setenv("NVMAI_CUDA_PREFILL_TC8", "1")
+    d, f, e, rows = 256, 128, 32, 20
+    host = synthetic.layer(390, d=d, f=f, shared_f=f, num_experts=e, routed_bits=4, shared_bits=8, meta=fmt.META_BF16)
+    cfg = MoEConfig(d=d, f=f, shared_f=f, num_experts=e, top_k=8, routed_bits=4, shared_bits=8,
+                    router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16, meta_dtype=fmt.META_BF16,
+                    activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32, max_tokens=rows)
+    moe, dl, x, got, got_idx, got_w, _, _ = _run_prefill(host, cfg, rows, seed=391)
+    _check_rows(host, cfg, x, got, got_idx, range(rows), tol_gpu=TC8_TOL, tol_cpu=TC8_TOL)
+
+
 def test_prefill_items_longer_than_one_tile():
-    """8 experts and 300 rows: every expert gets all 300 rows, split evenly over 3 work items"""
-    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, 300, seed=330, e=8)
-    moe, dl, x, got, got_idx, got_w, _, _ = _run_prefill(host, cfg, 300, seed=331)
-    _check_rows(host, cfg, x, got, got_idx, list(range(0, 300, 7)), tol_gpu=1e-3)
+    """8 experts and 600 rows: every expert gets all 600 rows, split evenly over 3 work items of 200"""
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, 600, seed=330, e=8)
+    moe, dl, x, got, got_idx, got_w, _, _ = _run_prefill(host, cfg, 600, seed=331)
+    _check_rows(host, cfg, x, got, got_idx, list(range(0, 600, 13)), tol_gpu=1e-3)
 
 
-@pytest.mark.parametrize("bits", [4, 8])
-def test_prefill_benchmark_shape(bits):
+@pytest.mark.parametrize("bits,tc8", [(4, False), (8, False), (8, True)])
+def test_prefill_benchmark_shape(bits, tc8, monkeypatch):
     """the 35B-A3B layer shape, 512 rows (16 rows per expert on average); sampled rows against the oracle;
     the 8-bit distribution exercises the wide-range activation rows"""
+    if tc8:
+        monkeypatch.setenv("NVMAI_CUDA_PREFILL_TC8", "1")
     host, cfg = _case(bits, fmt.META_BF16, fmt.OUT_FP32, 512, seed=340 + bits, d=2048, f=512, e=256)
     moe, dl, x, got, got_idx, got_w, _, _ = _run_prefill(host, cfg, 512, seed=350 + bits)
     assert np.all(np.isfinite(got))
-    _check_rows(host, cfg, x, got, got_idx, [0, 1, 17, 255, 256, 511], tol_gpu=1e-3 if bits == 4 else 2e-3)
+    tol = TC8_TOL if tc8 else FFN_TOL
+    _check_rows(host, cfg, x, got, got_idx, [0, 1, 17, 255, 256, 511], tol_gpu=tol, tol_cpu=tol)
 
 
 def test_prefill_equals_decode_path_within_tolerance():
