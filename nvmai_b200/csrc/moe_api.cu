@@ -95,6 +95,10 @@ struct nvmai_cuda_moe {
     float *ep_share = nullptr;       // [world * rows_own][D]: this rank's share of every row
     float *ep_recv = nullptr;        // [world][rows_own][D]: every rank's share of this rank's rows
     void *ep_h1 = nullptr;           // [rows_own][D] out_dtype: shared expert of this rank's rows
+    // the shared expert runs beside the exchange + routed experts on a second stream (forked and joined per layer,
+    // also inside the captured graph)
+    cudaStream_t ep_side = nullptr;
+    cudaEvent_t ep_fork = nullptr, ep_join = nullptr;
     struct EpGraph { cudaGraphExec_t exec = nullptr; uint32_t calls = 0; };
     std::map<StackGraphKey, EpGraph> ep_graphs;
 };
@@ -335,6 +339,9 @@ void ep_release(nvmai_cuda_moe *h) {
     for (auto &kv : h->ep_graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     h->ep_graphs.clear();
     if (h->ep_comm) { nccl_api().CommDestroy(h->ep_comm); h->ep_comm = nullptr; }
+    if (h->ep_side) { cudaStreamDestroy(h->ep_side); h->ep_side = nullptr; }
+    if (h->ep_fork) { cudaEventDestroy(h->ep_fork); h->ep_fork = nullptr; }
+    if (h->ep_join) { cudaEventDestroy(h->ep_join); h->ep_join = nullptr; }
     cudaFree(h->ep_x_all); cudaFree(h->ep_share); cudaFree(h->ep_recv); cudaFree(h->ep_h1);
     h->ep_x_all = nullptr; h->ep_share = nullptr; h->ep_recv = nullptr; h->ep_h1 = nullptr;
     h->ep_world = h->ep_rows_own = 0;
@@ -1109,6 +1116,13 @@ int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank
         ep_release(h);
         return NVMAI_CUDA_ENOMEM;
     }
+    if (cudaStreamCreateWithFlags(&h->ep_side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&h->ep_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&h->ep_join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        ep_release(h);
+        return NVMAI_CUDA_ECUDA;
+    }
     NcclUniqueId id;
     std::memcpy(&id, id_host, sizeof(id));
     if (nccl.CommInitRank(&h->ep_comm, (int)world, id, (int)rank) != kNcclSuccess) {
@@ -1136,9 +1150,12 @@ static int ep_stack_enqueue(nvmai_cuda_moe *h, const __half *x_own, uint32_t row
         const bool last = l + 1 == c.num_layers;
         const __half *x = l == 0 ? x_own : h->xnorm;
         int rc;
-        if (c.shared_f) {      // needs this rank's rows only
+        if (c.shared_f) {      // needs this rank's rows only: runs beside the exchange and the routed experts
             const XSource own{x, c.d, nullptr, nullptr};
-            if ((rc = shared_expert_impl(h, lv, own, rows_own, h->ep_h1, st))) return rc;
+            if ((rc = record(h, cudaEventRecord(h->ep_fork, st)))) return rc;
+            if ((rc = record(h, cudaStreamWaitEvent(h->ep_side, h->ep_fork, 0)))) return rc;
+            if ((rc = shared_expert_impl(h, lv, own, rows_own, h->ep_h1, h->ep_side))) return rc;
+            if ((rc = record(h, cudaEventRecord(h->ep_join, h->ep_side)))) return rc;
         }
         if (nccl.AllGather(x, h->ep_x_all, own_elems, kNcclFloat16, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
         const XSource all{h->ep_x_all, c.d, nullptr, nullptr};
@@ -1152,6 +1169,7 @@ static int ep_stack_enqueue(nvmai_cuda_moe *h, const __half *x_own, uint32_t row
         const bool ended = nccl.GroupEnd() == kNcclSuccess;
         if (!ok || !ended) return NVMAI_CUDA_ENCCL;
         void *y = last ? y_own : h->y;
+        if (c.shared_f && (rc = record(h, cudaStreamWaitEvent(st, h->ep_join, 0)))) return rc;
         if ((rc = nvmai_cuda_moe_ep_finalize(h, h->ep_recv, world, c.shared_f ? h->ep_h1 : nullptr, rows_own, y, nullptr, st)))
             return rc;
         if (!last && (rc = nvmai_cuda_moe_rms_renorm(h, y, rows_own, h->xnorm, st))) return rc;
