@@ -221,9 +221,12 @@ NVMAI_API int nvmai_cuda_moe_rms_renorm(nvmai_cuda_moe *h, const void *y, uint32
  * :3560-3569) as grouped GEMMs on the tensor cores: x fp16 [tokens][d] (dense rows),
  * hidden_inout = out(out(hidden + h1) + h2) in place, y_out (optional) = out(h1 + h2),
  * out_idx / out_w (optional) the routing.  The tile shapes want f % 128 == 0,
- * d % 256 == 0 and shared_f % 128 == 0 (NVMAI_CUDA_EINVAL otherwise).  Weights reach the
- * tensor cores as fp16(q*s + b); scales and biases pass through fp16, which is exact
- * for magnitudes in fp16's normal range. */
+ * d % 256 == 0 and shared_f % 128 == 0 (NVMAI_CUDA_EINVAL otherwise).  The tensor cores
+ * multiply the centred weight s*(q - c) in fp16 (exact for 4-bit codes with bf16 scales)
+ * and the per-group constant b + c*s enters through correction columns, so 4-bit results
+ * stay within 1e-3 of the CPU path.  8-bit weights do not fit an fp16 operand (about 3e-3
+ * of one expert's output): such calls run the exact decode kernels (decode rounding
+ * order) unless the environment has NVMAI_CUDA_PREFILL_TC8=1. */
 NVMAI_API int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
                                            void *hidden_inout, void *y_out, uint32_t *out_idx, void *out_w_f16,
                                            void *stream);
