@@ -42,6 +42,9 @@ struct RoutedSource {
     const uint16_t *pes;      // per-expert scale (bf16) for the routing weights, or nullptr
     uint32_t *publish_idx;    // [tokens][top_k]: one block per token stores what it selected
     __half *publish_w;
+    // Expert parallelism (deferred selection only): global expert id -> index of the blob this rank holds, or
+    // 0xFFFFFFFF.  Experts held elsewhere yield no blob: their blocks do nothing, their slots add nothing.
+    const uint32_t *expert_map;
 };
 
 struct ExpertOffsets { uint32_t o[9]; };
@@ -54,7 +57,12 @@ __device__ __forceinline__ const uint8_t *routed_blob(const RoutedSource &src, u
     return src.base + (size_t)e * src.stride;
 }
 __device__ __forceinline__ const uint8_t *expert_blob(const RoutedSource &src, uint32_t e) {
-    return src.base + (size_t)min(e, src.num_experts - 1u) * src.stride;
+    e = min(e, src.num_experts - 1u);
+    if (src.expert_map != nullptr) {
+        e = src.expert_map[e];
+        if (e == 0xFFFFFFFFu) return nullptr;
+    }
+    return src.base + (size_t)e * src.stride;
 }
 
 // ---------------------------------------------------------------------------

@@ -1110,8 +1110,9 @@ int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank
     ep_release(h);
     const size_t rows = (size_t)world * rows_own;
     auto alloc = [&](auto **ptr, size_t bytes) { return cudaMalloc(reinterpret_cast<void **>(ptr), bytes) == cudaSuccess; };
+    // the replicated mode gathers every rank's share of EVERY row and keeps h1 for every row
     if (!(alloc(&h->ep_x_all, rows * c.d * 2) && alloc(&h->ep_share, rows * c.d * 4) &&
-          alloc(&h->ep_recv, rows * c.d * 4) && alloc(&h->ep_h1, (size_t)rows_own * c.d * out_size(c.out_dtype)))) {
+          alloc(&h->ep_recv, (size_t)world * rows * c.d * 4) && alloc(&h->ep_h1, rows * c.d * out_size(c.out_dtype)))) {
         cudaGetLastError();
         ep_release(h);
         return NVMAI_CUDA_ENOMEM;
@@ -1177,6 +1178,62 @@ static int ep_stack_enqueue(nvmai_cuda_moe *h, const __half *x_own, uint32_t row
     return NVMAI_CUDA_OK;
 }
 
+// Small batches (fewer rows in total than the grouping threshold): every rank keeps ALL rows.  One all-gather of
+// x per step, then per layer the three decode kernels over all rows, with the expert stages skipping the slots
+// whose expert another rank holds, ONE all-gather of the fp32 shares, and the rank-ordered sum on every rank (all
+// ranks stay bitwise identical, so the next layer needs no exchange of activations).  4 kernels + 1 collective per
+// layer instead of 9 + 2; the router, the shared expert and the sum are computed redundantly, which is cheap at
+// these sizes.
+static int ep_stack_enqueue_replicated(nvmai_cuda_moe *h, const __half *x_own, uint32_t rows_own, void *y_own, cudaStream_t st) {
+    const auto &c = h->cfg;
+    const NcclApi &nccl = nccl_api();
+    const uint32_t world = h->ep_world, rows = world * rows_own;
+    const size_t own_elems = (size_t)rows_own * c.d, all_elems = (size_t)rows * c.d;
+    if (nccl.AllGather(x_own, h->ep_x_all, own_elems, kNcclFloat16, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+        const LayerViews &lv = h->layers[l];
+        XSource xsrc{};
+        const __half *x_rows;
+        if (l == 0) { xsrc.x = h->ep_x_all; xsrc.x_stride = c.d; x_rows = h->ep_x_all; }
+        else { xsrc.y_prev = h->y; xsrc.x_out = h->xnorm; x_rows = h->xnorm; }
+        int rc = launch_stage1(h, lv, xsrc, rows, h->idx, h->w, true, c.shared_f != 0, c.shared_f != 0, true, st, true);
+        if (rc) return rc;
+        RoutedSource src = source_from_layer(h, lv, h->idx);
+        src.logits = h->logits;
+        src.pes = static_cast<const uint16_t *>(lv.w.per_expert_scale);
+        src.publish_idx = h->idx;
+        src.publish_w = h->w;
+        src.expert_map = h->expert_map;
+        if ((rc = launch_stage2(h, src, to_offsets(lv.w.offsets), x_rows, c.d, rows, h->acts, nullptr, c.top_k, true, st))) return rc;
+        Stage3Params p{};
+        p.src = src;
+        p.off = to_offsets(lv.w.offsets);
+        p.acts = h->acts;
+        p.routing_w = h->w;
+        p.sdown = to_mat(lv.w.shared_down_proj);
+        p.shared_f = c.shared_f;
+        p.shared_bits = c.shared_bits;
+        p.shared_act = h->shared_act;
+        p.gate_val = c.shared_gate_kind != NVMAI_GATE_NONE ? h->gate_val : nullptr;
+        p.h1_out = h->ep_h1;
+        p.share_out = h->ep_share;
+        p.top_k = c.top_k;
+        if ((rc = launch_stage3(h, p, rows, true, st))) return rc;
+        if (nccl.AllGather(h->ep_share, h->ep_recv, all_elems, kNcclFloat32, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
+        if ((rc = nvmai_cuda_moe_ep_finalize(h, h->ep_recv, world, c.shared_f ? h->ep_h1 : nullptr, rows, h->y, nullptr, st)))
+            return rc;
+    }
+    return record(h, cudaMemcpyAsync(y_own, static_cast<const char *>(h->y) + (size_t)h->ep_rank * own_elems * out_size(c.out_dtype),
+                                     own_elems * out_size(c.out_dtype), cudaMemcpyDeviceToDevice, st));
+}
+
+static bool ep_replicated_mode(const nvmai_cuda_moe *h, uint32_t rows_own) {
+    const auto &c = h->cfg;
+    const uint32_t rows = h->ep_world * rows_own;
+    return rows < h->grouped_min_tokens && c.top_k <= (uint32_t)kMaxTopK &&
+           (c.top_k + (c.shared_f ? 1 : 0)) * kDownSplit * 32 >= (uint32_t)kMaxExperts;
+}
+
 int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uint32_t rows_own, void *y_own, void *stream) {
     if (!h || !x_own_f16 || !y_own || !aligned16(x_own_f16)) return NVMAI_CUDA_EINVAL;
     if (!h->ep_comm || !h->expert_map) return NVMAI_CUDA_EINVAL;    // ep_init and set_expert_map come first
@@ -1188,7 +1245,7 @@ int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uin
     const __half *x = static_cast<const __half *>(x_own_f16);
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     if (st != nullptr) cudaStreamIsCapturing(st, &cs);
-    if (st == nullptr || cs != cudaStreamCaptureStatusNone) return ep_stack_enqueue(h, x, rows_own, y_own, st);
+    if (st == nullptr || cs != cudaStreamCaptureStatusNone) return (ep_replicated_mode(h, rows_own) ? ep_stack_enqueue_replicated(h, x, rows_own, y_own, st) : ep_stack_enqueue(h, x, rows_own, y_own, st));
     if (h->ep_graphs_stale) {
         for (auto &kv : h->ep_graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
         h->ep_graphs.clear();
@@ -1197,12 +1254,12 @@ int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uin
     auto &g = h->ep_graphs[StackGraphKey{x_own_f16, y_own, rows_own, st}];
     // First call per key: plain launches (NCCL sets up its channels on first use).
     // Second call: capture.  Every rank takes the same branch, since all count alike.
-    if (g.calls++ == 0) return ep_stack_enqueue(h, x, rows_own, y_own, st);
+    if (g.calls++ == 0) return (ep_replicated_mode(h, rows_own) ? ep_stack_enqueue_replicated(h, x, rows_own, y_own, st) : ep_stack_enqueue(h, x, rows_own, y_own, st));
     if (!g.exec) {
         int rc = record(h, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         if (rc) return rc;
         const uint64_t launches_before = g_launches.load();
-        rc = ep_stack_enqueue(h, x, rows_own, y_own, st);
+        rc = (ep_replicated_mode(h, rows_own) ? ep_stack_enqueue_replicated(h, x, rows_own, y_own, st) : ep_stack_enqueue(h, x, rows_own, y_own, st));
         g_launches.store(launches_before);
         cudaGraph_t graph = nullptr;
         cudaError_t e = cudaStreamEndCapture(st, &graph);
@@ -1214,8 +1271,12 @@ int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uin
     }
     int rc = record(h, cudaGraphLaunch(g.exec, st));
     if (rc == NVMAI_CUDA_OK) {
-        const uint64_t per_layer = 6 + (c.shared_f ? 2 : 0) + 1;     // router, group, 2 grouped, combine, finalize (+shared 2, +renorm)
-        g_launches.fetch_add((uint64_t)c.num_layers * per_layer - 1, std::memory_order_relaxed);
+        if (ep_replicated_mode(h, rows_own)) {
+            g_launches.fetch_add((uint64_t)c.num_layers * 4, std::memory_order_relaxed);     // 3 stages + finalize per layer
+        } else {
+            const uint64_t per_layer = 6 + (c.shared_f ? 2 : 0) + 1;     // router, group, 2 grouped, combine, finalize (+shared 2, +renorm)
+            g_launches.fetch_add((uint64_t)c.num_layers * per_layer - 1, std::memory_order_relaxed);
+        }
     }
     return rc;
 }

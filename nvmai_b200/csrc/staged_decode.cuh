@@ -448,6 +448,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage2_kernel(Stage2Params 
                           reinterpret_cast<float *>(smem + L.red) + 64);
         trace_mark(p.trace, 1);
     }
+    // an expert held by another rank (expert parallelism): nothing to do here beyond block (0, 0)'s publication
+    const bool local = p.src.logits == nullptr || expert_blob(p.src, sel_idx[slot]) != nullptr;
     if (warp == 0) {
         const uint8_t *blob;
         if (p.src.logits != nullptr) {
@@ -458,6 +460,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage2_kernel(Stage2Params 
         } else {
             blob = routed_blob(p.src, tok, slot, p.top_k);
         }
+        if (!local) blob = nullptr;
+        if (blob != nullptr) {
         const AffineMat gate = {blob + p.off.o[0], reinterpret_cast<const uint16_t *>(blob + p.off.o[1]),
                                 reinterpret_cast<const uint16_t *>(blob + p.off.o[2])};
         const AffineMat up = {blob + p.off.o[3], reinterpret_cast<const uint16_t *>(blob + p.off.o[4]),
@@ -466,7 +470,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) stage2_kernel(Stage2Params 
         if (lane == 0) bulk_g2s(smem + L.xs, p.x + (size_t)tok * p.x_stride, p.D * 2, reinterpret_cast<uint64_t *>(smem));
         for (int tile = 1; tile < n_tiles; ++tile)
             issue_gate_up_copies<BITS>(smem, L, tile, gate, up, f0 + tile * kTileFeatures, p.D, 0);
+        }
     }
+    if (!local) { trace_end(p.trace); return; }
     const uint8_t *pf_blob = nullptr;
     if (p.prefetch_down && warp == 0) {
         pf_blob = p.src.logits != nullptr ? expert_blob(p.src, sel_idx[slot]) : routed_blob(p.src, tok, slot, p.top_k);
@@ -501,6 +507,8 @@ struct Stage3Params {
     const void *shared_act;             // [tokens][shared_f], fp16 or fp32
     const float *gate_val;              // [tokens] or nullptr (ungated)
     void *h1_out;                       // optional out_dtype[tokens][D]
+    float *share_out;                   // expert parallelism: fp32 [tokens][D] = sum over this rank's slots of w_k * down_k;
+                                        // when set, y and hidden are not written (the shares are summed elsewhere)
     void *y;                            // out_dtype[tokens][D]  (block output h2)
     void *hidden;                       // optional out_dtype[tokens][D], hidden += y
     // ranges the next launch will read (the next layer's router and shared-expert
@@ -650,8 +658,11 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
         topk_select_block(p.src.logits + (size_t)tok * p.src.num_experts, p.src.num_experts, p.top_k,
                           reinterpret_cast<uint32_t *>(part), part + 32, part + 64);
     }
+    // a slot whose expert another rank holds (expert parallelism) loads nothing and adds nothing
+    bool local = true;
+    if (routed && p.src.logits != nullptr) local = expert_blob(p.src, reinterpret_cast<uint32_t *>(part)[unit]) != nullptr;
     if (half == 0) {
-        if (routed) {
+        if (routed && local) {
             const uint8_t *blob = p.src.logits != nullptr ? expert_blob(p.src, reinterpret_cast<uint32_t *>(part)[unit])
                                                           : routed_blob(p.src, tok, unit, p.top_k);
             const AffineMat mat{blob + p.off.o[6], reinterpret_cast<const uint16_t *>(blob + p.off.o[7]),
@@ -677,7 +688,7 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
     const float gate_v = (p.gate_val != nullptr && threadIdx.x < 16) ? p.gate_val[tok] : 0.0f;
     bool ok = true;
     float v[2] = {0.0f, 0.0f};
-    if (routed) {
+    if (routed && local) {
         ok = down_warp<BITS, META, OUT>(region, L, p.F, half, p.acts, ((size_t)tok * p.top_k + unit) * p.F, p.status, v);
     } else if (shared) {
         if (p.shared_bits == 4)
@@ -709,6 +720,13 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
             acc = h1;
         } else {
             acc = p.residual != nullptr ? load_out<OUT>(p.residual, i) : 0.0f;
+        }
+        if (p.share_out != nullptr) {               // expert parallelism: this rank's share only, h1 went to h1_out
+            float share = 0.0f;
+            for (uint32_t k = 0; k < p.top_k; ++k) share += wk_s[k] * unit_sum(k);
+            p.share_out[i] = share;
+            trace_end(p.trace);
+            return;
         }
         for (uint32_t k = 0; k < p.top_k; ++k)      // slot order, moe.metal:802-808
             acc += wk_s[k] * unit_sum(k);

@@ -18,10 +18,10 @@ pytestmark = pytest.mark.gpu
 D, F, E, K, B_OWN = 256, 128, 32, 8, 3
 
 
-def _cfg(tokens):
+def _cfg(tokens, bits=8):
     from nvmai_b200 import MoEConfig
     from nvmai_b200 import format as fmt
-    return MoEConfig(d=D, f=F, shared_f=F, num_experts=E, top_k=K, routed_bits=8, shared_bits=8,
+    return MoEConfig(d=D, f=F, shared_f=F, num_experts=E, top_k=K, routed_bits=bits, shared_bits=bits,
                      router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16, meta_dtype=fmt.META_FP16,
                      out_dtype=fmt.OUT_FP32, max_tokens=tokens)
 
@@ -69,12 +69,14 @@ def _native_stack(rank, world, out_dir, dist, pl, x_all, st):
     from nvmai_b200 import MoE, synthetic
     from nvmai_b200 import format as fmt
     from nvmai_b200.ep import LibraryBackend, ep_stack_step
-    cfg = _cfg(world * B_OWN)
+    # 4-bit weights: with the benchmark's all-positive 8-bit weights a renormalised all-negative row drives every
+    # gate to silu(-400) = 0 and the second layer's output is exactly zero (in the oracle too), which tests nothing
+    cfg = _cfg(world * B_OWN, bits=4)
     cfg.num_layers = 2
     moe = MoE(cfg)
     keep = []
     for layer in range(2):
-        host = synthetic.layer(910 + layer, d=D, f=F, shared_f=F, num_experts=E, routed_bits=8, meta=fmt.META_FP16)
+        host = synthetic.layer(910 + layer, d=D, f=F, shared_f=F, num_experts=E, routed_bits=4, meta=fmt.META_FP16)
         local = dict(host)
         local["experts"] = np.ascontiguousarray(host["experts"][pl.local_experts(rank)])
         dl = gu.DeviceLayer(local)
@@ -89,11 +91,14 @@ def _native_stack(rank, world, out_dir, dist, pl, x_all, st):
         want = ep_stack_step(LibraryBackend(moe, stream=st), dist, None, x_own, world=world, layers=2).clone()
         st.synchronize()
         y = torch.empty_like(want)
-        for call in range(3):
+        outs = []
+        for call in range(3):       # no assertion between the collective calls: a rank that stopped here would hang its peer
             y.zero_()
             moe.ep_stack_decode(x_own, B_OWN, y, stream=st)
             moe.synchronize(stream=st)
-            assert torch.equal(y, want), f"native expert-parallel stack, call {call}"
+            outs.append(y.cpu().numpy().copy())
+    np.save(os.path.join(out_dir, f"want{rank}.npy"), want.cpu().numpy())
+    np.save(os.path.join(out_dir, f"calls{rank}.npy"), np.stack(outs))
     np.save(os.path.join(out_dir, f"native{rank}.npy"), y.cpu().numpy())
     moe.ep_shutdown()
 
@@ -128,4 +133,14 @@ def test_two_gpu_expert_parallel_layer_matches_oracle(tmp_path):
             o_idx, _, want, _, cpu = gu.oracle_decode(L, cfg, np.ascontiguousarray(x_all[rank * B_OWN + j]))
             assert orc.rel_error(y[j], cpu) < 1e-3
             assert orc.rel_error(y[j], want) < 5e-4
-        assert (tmp_path / f"native{rank}.npy").exists()
+        # the library's own communicator: plain launches, graph capture, replay.  Small batches run the replicated mode
+        # (per-row kernels, shares all-gathered): the same arithmetic as the torch-driven grouped kernels up to the
+        # association of a few fp32 additions
+        want_s = np.load(tmp_path / f"want{rank}.npy")
+        calls = np.load(tmp_path / f"calls{rank}.npy")
+        assert np.all(np.isfinite(want_s)) and np.abs(want_s).max() > 0, "torch-driven reference stack"
+        for c in range(3):
+            assert np.all(np.isfinite(calls[c])), f"rank {rank} call {c}: non-finite values ({int((~np.isfinite(calls[c])).sum())})"
+            err = np.abs(calls[c] - want_s).max() / np.abs(want_s).max()
+            assert err < 1e-5, f"rank {rank} call {c}: {err}"
+            assert np.array_equal(calls[c].view(np.uint32), calls[0].view(np.uint32)), "plain launches, capture and replay agree bitwise"
