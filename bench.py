@@ -474,7 +474,9 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
         rec["config"].update({"parallelism": f"ep{world}", "experts_per_gpu": E // world, "placement": args.placement,
                               "tokens_per_step": world * tokens, "graph": native,
                               "ep_driver": args.ep_driver,
-                              "collectives_per_layer": "all_gather(x) + all_to_all(share rows), NCCL"})
+                              "collectives_per_layer": ("all_gather(fp32 share rows), NCCL; every rank keeps all rows (replicated mode)"
+                                                        if native and world * tokens < 24 else
+                                                        "all_gather(x) + all_to_all(share rows), NCCL")})
         print(json.dumps(rec), flush=True)
     note("end-to-end region done")
     dist.barrier()
