@@ -243,6 +243,17 @@ NVMAI_API int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uin
                                      uint32_t rows_own);
 NVMAI_API int nvmai_cuda_moe_ep_shutdown(nvmai_cuda_moe *h);
 
+/* Optional, after ep_init: exchange the ranks' shares through peer memory instead of NCCL
+ * (small batches, where every rank keeps all rows).  Every rank exports the handle of its
+ * receive area (a CUDA IPC handle, 64 bytes), the launcher collects the handles of all
+ * ranks in rank order and gives the array to every rank's attach.  Afterwards the down
+ * stage stores its share rows straight into every rank's receive area over NVLink (plain
+ * peer stores, no multicast) and the sum waits, with a bounded wait, for the per-layer
+ * arrival counter; one process per GPU on one node.  Every rank must attach (or none). */
+#define NVMAI_CUDA_EP_PEER_HANDLE_BYTES 64
+NVMAI_API int nvmai_cuda_moe_ep_peer_export(nvmai_cuda_moe *h, void *handle_out_host);
+NVMAI_API int nvmai_cuda_moe_ep_peer_attach(nvmai_cuda_moe *h, const void *handles_host);
+
 /* The FFN-only stack of the benchmark, sharded by experts: this rank's rows in
  * (fp16 [rows_own][d]), the last layer's block output for them out (out_dtype).
  * Per layer: shared expert on the own rows, all-gather of the rows, router on all

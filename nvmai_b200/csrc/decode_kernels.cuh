@@ -381,4 +381,24 @@ template <int OUT> __device__ __forceinline__ void store_mid(void *p, size_t i, 
     else reinterpret_cast<float *>(p)[i] = round11(v);
 }
 
+// Expert parallelism over peer memory (see ep_finalize_peer_kernel): where the ranks' receive buffers and
+// arrival counters live.
+constexpr int kEpMaxRanks = 8;
+constexpr int kEpMaxLayers = 128;
+
+struct EpPeerView {
+    float *recv[kEpMaxRanks];                    // every rank's receive area: [2][world][rows][D] fp32
+    unsigned long long *arrive[kEpMaxRanks];     // every rank's counters: [kEpMaxLayers]
+    const unsigned long long *step;              // this rank's step number (device)
+    unsigned long long *local_count;             // this rank's own block counters: [kEpMaxLayers]
+    uint32_t world, rank, layer, layers;
+    unsigned long long buf_elems;                // world * rows * D
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 }  // namespace nvmai

@@ -618,4 +618,55 @@ __global__ void __launch_bounds__(256) ep_finalize_kernel(EpFinalizeParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Peer-memory exchange of the shares (replicated expert-parallel mode): the down
+// stage of every rank stores its share rows straight into every rank's receive
+// buffer over NVLink (plain peer stores, no multicast) and counts its finished
+// blocks on a per-layer counter in the receiver's memory; the receiver's sum
+// waits for the counter.  Counters only grow: the step number (a device word the
+// step's first kernel increments, so a replayed CUDA graph sees it change) times
+// the arrivals per step is what a layer waits for, and the same step number picks
+// one of two receive buffers per layer parity, so that a rank one layer ahead never
+// writes what a slower rank still reads.
+// ---------------------------------------------------------------------------
+__global__ void ep_step_kernel(unsigned long long *step) { *step += 1ull; }
+
+struct EpFinalizePeerParams {
+    const float *recv;                   // this rank's receive area
+    const unsigned long long *arrive;    // this rank's counter of the layer
+    const unsigned long long *step;
+    unsigned long long arrivals_per_step, buf_elems;
+    uint32_t ranks, layer, layers;
+    const void *h1; void *y;
+    uint32_t tokens, D;
+    unsigned int *status;
+};
+
+// y = out(h1 + sum over ranks, in rank order) once every rank's shares of this layer have arrived
+template <int OUT>
+__global__ void __launch_bounds__(256) ep_finalize_peer_kernel(EpFinalizePeerParams p) {
+    __shared__ int ok_s;
+    const unsigned long long step = *p.step;
+    if (threadIdx.x == 0) {
+        const unsigned long long want = step * p.arrivals_per_step;
+        int ok = 0;
+        for (uint32_t it = 0; it < (1u << 22); ++it) {            // bounded: about a second
+            if (ld_acquire_sys_u64(p.arrive) >= want) { ok = 1; break; }
+            __nanosleep(200);
+        }
+        if (!ok) atomicExch(p.status, 1u);
+        ok_s = ok;
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    const unsigned long long buf = (step * p.layers + p.layer) & 1ull;
+    const float *shares = p.recv + buf * p.buf_elems;
+    const size_t n = (size_t)p.tokens * p.D;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = p.h1 != nullptr ? load_out<OUT>(p.h1, i) : 0.0f;
+        for (uint32_t r = 0; r < p.ranks; ++r) acc += __ldcg(shares + (size_t)r * n + i);     // written by peers: not through L1
+        store_out<OUT>(p.y, i, round_out<OUT>(acc));
+    }
+}
+
 }  // namespace nvmai

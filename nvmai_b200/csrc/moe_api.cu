@@ -99,6 +99,14 @@ struct nvmai_cuda_moe {
     // also inside the captured graph)
     cudaStream_t ep_side = nullptr;
     cudaEvent_t ep_fork = nullptr, ep_join = nullptr;
+    // peer-memory exchange of the shares (replicated mode): own area = [counters, 4 KB][receive buffers 2 x world*rows*D fp32],
+    // exported to the other ranks as a CUDA IPC handle; ep_peer_base[r] = rank r's area as mapped here
+    unsigned char *ep_xchg = nullptr;
+    unsigned char *ep_peer_base[kEpMaxRanks] = {};
+    bool ep_peers_attached = false;
+    unsigned long long *ep_step = nullptr;      // device: [0] number of steps enqueued (incremented by the step's first kernel),
+                                                // [2 ..] this rank's block counters per layer
+    size_t ep_buf_elems = 0;
     struct EpGraph { cudaGraphExec_t exec = nullptr; uint32_t calls = 0; };
     std::map<StackGraphKey, EpGraph> ep_graphs;
 };
@@ -339,6 +347,13 @@ void ep_release(nvmai_cuda_moe *h) {
     for (auto &kv : h->ep_graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     h->ep_graphs.clear();
     if (h->ep_comm) { nccl_api().CommDestroy(h->ep_comm); h->ep_comm = nullptr; }
+    for (uint32_t r = 0; r < (uint32_t)kEpMaxRanks; ++r) {
+        if (h->ep_peer_base[r] && h->ep_peer_base[r] != h->ep_xchg) cudaIpcCloseMemHandle(h->ep_peer_base[r]);
+        h->ep_peer_base[r] = nullptr;
+    }
+    h->ep_peers_attached = false;
+    cudaFree(h->ep_xchg); h->ep_xchg = nullptr;
+    cudaFree(h->ep_step); h->ep_step = nullptr;
     if (h->ep_side) { cudaStreamDestroy(h->ep_side); h->ep_side = nullptr; }
     if (h->ep_fork) { cudaEventDestroy(h->ep_fork); h->ep_fork = nullptr; }
     if (h->ep_join) { cudaEventDestroy(h->ep_join); h->ep_join = nullptr; }
@@ -1117,6 +1132,19 @@ int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank
         ep_release(h);
         return NVMAI_CUDA_ENOMEM;
     }
+    h->ep_buf_elems = (size_t)world * rows * c.d;
+    {
+        const size_t xbytes = 4096 + 2 * rows * c.d * sizeof(float) * world;
+        if (world > (uint32_t)kEpMaxRanks || c.num_layers > (uint32_t)kEpMaxLayers ||
+            cudaMalloc(reinterpret_cast<void **>(&h->ep_xchg), xbytes) != cudaSuccess ||
+            cudaMemset(h->ep_xchg, 0, xbytes) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void **>(&h->ep_step), (2 + kEpMaxLayers) * 8) != cudaSuccess ||
+            cudaMemset(h->ep_step, 0, (2 + kEpMaxLayers) * 8) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(h->ep_xchg); h->ep_xchg = nullptr;       // the exchange stays on NCCL then
+            cudaFree(h->ep_step); h->ep_step = nullptr;
+        }
+    }
     if (cudaStreamCreateWithFlags(&h->ep_side, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&h->ep_fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&h->ep_join, cudaEventDisableTiming) != cudaSuccess) {
@@ -1138,6 +1166,33 @@ int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank
 int nvmai_cuda_moe_ep_shutdown(nvmai_cuda_moe *h) {
     if (!h) return NVMAI_CUDA_EINVAL;
     ep_release(h);
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_ep_peer_export(nvmai_cuda_moe *h, void *handle_out_host) {
+    if (!h || !handle_out_host) return NVMAI_CUDA_EINVAL;
+    if (!h->ep_xchg) return NVMAI_CUDA_EINVAL;           // ep_init comes first
+    cudaIpcMemHandle_t mh;
+    int rc = record(h, cudaIpcGetMemHandle(&mh, h->ep_xchg));
+    if (rc) return rc;
+    static_assert(sizeof(mh) == NVMAI_CUDA_EP_PEER_HANDLE_BYTES, "IPC handle size");
+    std::memcpy(handle_out_host, &mh, sizeof(mh));
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_ep_peer_attach(nvmai_cuda_moe *h, const void *handles_host) {
+    if (!h || !handles_host || !h->ep_xchg || h->ep_world == 0) return NVMAI_CUDA_EINVAL;
+    for (uint32_t r = 0; r < h->ep_world; ++r) {
+        if (r == h->ep_rank) { h->ep_peer_base[r] = h->ep_xchg; continue; }
+        cudaIpcMemHandle_t mh;
+        std::memcpy(&mh, static_cast<const unsigned char *>(handles_host) + (size_t)r * sizeof(mh), sizeof(mh));
+        void *base = nullptr;
+        int rc = record(h, cudaIpcOpenMemHandle(&base, mh, cudaIpcMemLazyEnablePeerAccess));
+        if (rc) return rc;
+        h->ep_peer_base[r] = static_cast<unsigned char *>(base);
+    }
+    h->ep_peers_attached = true;
+    h->ep_graphs_stale = true;
     return NVMAI_CUDA_OK;
 }
 
@@ -1190,6 +1245,20 @@ static int ep_stack_enqueue_replicated(nvmai_cuda_moe *h, const __half *x_own, u
     const uint32_t world = h->ep_world, rows = world * rows_own;
     const size_t own_elems = (size_t)rows_own * c.d, all_elems = (size_t)rows * c.d;
     if (nccl.AllGather(x_own, h->ep_x_all, own_elems, kNcclFloat16, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
+    // with the peers' receive areas mapped, the shares travel by peer stores from the down stage itself
+    const bool p2p = h->ep_peers_attached;
+    EpPeerView view{};
+    if (p2p) {
+        for (uint32_t r = 0; r < world; ++r) {
+            view.arrive[r] = reinterpret_cast<unsigned long long *>(h->ep_peer_base[r]);
+            view.recv[r] = reinterpret_cast<float *>(h->ep_peer_base[r] + 4096);
+        }
+        view.step = h->ep_step; view.local_count = h->ep_step + 2; view.world = world; view.rank = h->ep_rank; view.layers = c.num_layers;
+        view.buf_elems = h->ep_buf_elems;
+        ep_step_kernel<<<1, 1, 0, st>>>(h->ep_step);
+        int rc = check_launch(h);
+        if (rc) return rc;
+    }
     for (uint32_t l = 0; l < c.num_layers; ++l) {
         const LayerViews &lv = h->layers[l];
         XSource xsrc{};
@@ -1216,8 +1285,24 @@ static int ep_stack_enqueue_replicated(nvmai_cuda_moe *h, const __half *x_own, u
         p.shared_act = h->shared_act;
         p.gate_val = c.shared_gate_kind != NVMAI_GATE_NONE ? h->gate_val : nullptr;
         p.h1_out = h->ep_h1;
-        p.share_out = h->ep_share;
         p.top_k = c.top_k;
+        if (p2p) {
+            view.layer = l;
+            p.peers = view;
+            if ((rc = launch_stage3(h, p, rows, true, st))) return rc;
+            EpFinalizePeerParams f{};
+            f.recv = view.recv[h->ep_rank]; f.arrive = view.arrive[h->ep_rank] + l; f.step = h->ep_step;
+            f.arrivals_per_step = world;          // one announcement per source rank and step
+            f.buf_elems = h->ep_buf_elems; f.ranks = world; f.layer = l; f.layers = c.num_layers;
+            f.h1 = c.shared_f ? h->ep_h1 : nullptr; f.y = h->y; f.tokens = rows; f.D = c.d; f.status = h->status;
+            const unsigned blocks = (unsigned)std::min<size_t>((all_elems + 255) / 256, 148);
+            rc = dispatch_out(c.out_dtype, [&](auto O) {
+                return launch_kernel(h, ep_finalize_peer_kernel<decltype(O)::value>, dim3(blocks), dim3(256), 0, st, false, f);
+            });
+            if (rc) return rc;
+            continue;
+        }
+        p.share_out = h->ep_share;
         if ((rc = launch_stage3(h, p, rows, true, st))) return rc;
         if (nccl.AllGather(h->ep_share, h->ep_recv, all_elems, kNcclFloat32, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
         if ((rc = nvmai_cuda_moe_ep_finalize(h, h->ep_recv, world, c.shared_f ? h->ep_h1 : nullptr, rows, h->y, nullptr, st)))

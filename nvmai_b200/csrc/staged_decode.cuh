@@ -509,6 +509,8 @@ struct Stage3Params {
     void *h1_out;                       // optional out_dtype[tokens][D]
     float *share_out;                   // expert parallelism: fp32 [tokens][D] = sum over this rank's slots of w_k * down_k;
                                         // when set, y and hidden are not written (the shares are summed elsewhere)
+    EpPeerView peers;                   // or (peers.world != 0): store the share into every rank's receive buffer
+                                        // and count the block there
     void *y;                            // out_dtype[tokens][D]  (block output h2)
     void *hidden;                       // optional out_dtype[tokens][D], hidden += y
     // ranges the next launch will read (the next layer's router and shared-expert
@@ -721,10 +723,30 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
         } else {
             acc = p.residual != nullptr ? load_out<OUT>(p.residual, i) : 0.0f;
         }
-        if (p.share_out != nullptr) {               // expert parallelism: this rank's share only, h1 went to h1_out
+        if (p.share_out != nullptr || p.peers.world != 0) {     // expert parallelism: this rank's share only, h1 went to h1_out
             float share = 0.0f;
             for (uint32_t k = 0; k < p.top_k; ++k) share += wk_s[k] * unit_sum(k);
-            p.share_out[i] = share;
+            if (p.peers.world != 0) {
+                const EpPeerView &v = p.peers;
+                const unsigned long long buf = (*v.step * v.layers + v.layer) & 1ull;
+                const size_t at = buf * v.buf_elems + (size_t)v.rank * gridDim.y * p.D + i;     // [buf][source rank][row][d]
+                for (uint32_t r = 0; r < v.world; ++r) v.recv[r][at] = share;
+                __threadfence_system();              // the 16 writers of this block: stores visible system-wide ...
+                __syncwarp(0x0000ffffu);
+                if (threadIdx.x == 0) {
+                    // ... before the block is counted.  Blocks count on a local word (it only grows); the block
+                    // that completes the layer's set announces the rank once at every receiver, so a layer costs one
+                    // system-scope atomic per peer instead of one per block.
+                    const unsigned long long blocks = (unsigned long long)gridDim.x * gridDim.y;
+                    const unsigned long long seen = atomicAdd(v.local_count + v.layer, 1ull) + 1ull;
+                    if (seen % blocks == 0) {
+                        __threadfence_system();
+                        for (uint32_t r = 0; r < v.world; ++r) atomicAdd_system(v.arrive[r] + v.layer, 1ull);
+                    }
+                }
+            } else {
+                p.share_out[i] = share;
+            }
             trace_end(p.trace);
             return;
         }

@@ -186,6 +186,20 @@ class MoE:
         buf = ctypes.create_string_buffer(unique_id, 128)
         check(self._lib.nvmai_cuda_moe_ep_init(self._h, buf, rank, world, rows_own), "ep_init")
 
+    def ep_peer_export(self) -> bytes:
+        """The 64-byte handle of this rank's receive area for the peer-memory exchange."""
+        import ctypes
+        buf = ctypes.create_string_buffer(64)
+        check(self._lib.nvmai_cuda_moe_ep_peer_export(self._h, buf), "ep_peer_export")
+        return buf.raw
+
+    def ep_peer_attach(self, handles: list[bytes]) -> None:
+        """handles: every rank's exported handle, in rank order."""
+        import ctypes
+        blob = b"".join(handles)
+        buf = ctypes.create_string_buffer(blob, len(blob))
+        check(self._lib.nvmai_cuda_moe_ep_peer_attach(self._h, buf), "ep_peer_attach")
+
     def ep_shutdown(self) -> None:
         check(self._lib.nvmai_cuda_moe_ep_shutdown(self._h), "ep_shutdown")
 

@@ -92,11 +92,19 @@ def _native_stack(rank, world, out_dir, dist, pl, x_all, st):
         st.synchronize()
         y = torch.empty_like(want)
         outs = []
-        for call in range(3):       # no assertion between the collective calls: a rank that stopped here would hang its peer
+        # calls 0-2: shares through an NCCL all-gather; then the receive areas are mapped into each other and
+        # calls 3-5 send the shares by peer stores from the down stage (plain launches, capture, replay each time).
+        # No assertion between the collective calls: a rank that stopped here would hang its peer.
+        for call in range(6):
+            if call == 3:
+                handles = [None] * world
+                dist.all_gather_object(handles, moe.ep_peer_export())
+                moe.ep_peer_attach(handles)
             y.zero_()
             moe.ep_stack_decode(x_own, B_OWN, y, stream=st)
             moe.synchronize(stream=st)
             outs.append(y.cpu().numpy().copy())
+        dist.barrier()      # nobody unmaps a receive area a peer may still write
     np.save(os.path.join(out_dir, f"want{rank}.npy"), want.cpu().numpy())
     np.save(os.path.join(out_dir, f"calls{rank}.npy"), np.stack(outs))
     np.save(os.path.join(out_dir, f"native{rank}.npy"), y.cpu().numpy())
@@ -139,7 +147,7 @@ def test_two_gpu_expert_parallel_layer_matches_oracle(tmp_path):
         want_s = np.load(tmp_path / f"want{rank}.npy")
         calls = np.load(tmp_path / f"calls{rank}.npy")
         assert np.all(np.isfinite(want_s)) and np.abs(want_s).max() > 0, "torch-driven reference stack"
-        for c in range(3):
+        for c in range(6):
             assert np.all(np.isfinite(calls[c])), f"rank {rank} call {c}: non-finite values ({int((~np.isfinite(calls[c])).sum())})"
             err = np.abs(calls[c] - want_s).max() / np.abs(want_s).max()
             assert err < 1e-5, f"rank {rank} call {c}: {err}"
