@@ -18,7 +18,8 @@
 // D[128 x N] (+)= A[128 x 16] * B[N x 16]^T per instruction, N = the item's row
 // count rounded up to 16: the weights are the M operand, so a short item costs a
 // narrow instruction instead of a padded tile.  Two accumulators of up to 256
-// columns take the SM's 512 tensor-memory columns.
+// columns (four of up to 128 for a narrow item, see the kernel) take the SM's 512
+// tensor-memory columns.
 //
 // Operands in shared memory are fp16, K-major, in the 128-byte swizzle layout the
 // tensor core reads through matrix descriptors: row r of a tile at byte r*128
@@ -31,14 +32,18 @@
 // hands B in work-item order (x rows gathered into sorted pair order by
 // pack_rows_kernel), so an item's rows are one contiguous row range of the map.
 // Sixteen producer warps build the quantised A operand: each thread holds the 32
-// packed codes of one row three K blocks ahead in registers, turns them into fp16
-// w = q*s + b (one rounding: the fp16 fused multiply-add of the exact code, scale and
-// bias; scale and bias are converted from their 16-bit storage type to fp16, exact
-// for magnitudes in fp16's normal range) and stores them swizzled.  A seventeenth
-// warp's elected lane issues the MMAs and commits them to the mbarriers that hand
-// the stage back.  4-bit codes unpack in the order (0,4,1,5,2,6,3,7) within each 8;
-// the B rows are stored in the same K order (the sum over k does not care, as long as
-// both operands agree).
+// packed codes of one row three K blocks ahead in registers, turns them into the
+// fp16 CENTRED weight s * (q - c), c = 8 (4-bit) or 128 (8-bit) (exact in fp16 for
+// 4-bit codes with bf16 scales; the scale is converted from its 16-bit storage type
+// to fp16, exact for magnitudes in fp16's normal range) and stores them swizzled.
+// The rest of w = q*s + b, the per-group constant b + c*s, enters through extra K
+// blocks after the codes: every B row carries the sums of its 64-value groups (fp16
+// hi + lo, written by pack_rows_kernel) and the producers append the constants as
+// [hi | hi | lo] columns against [X_hi | X_lo | X_hi].  One thread of a seventeenth
+// warp issues the MMAs and commits them to the mbarriers that hand stages and ring
+// slots back; one thread of an eighteenth issues the TMA loads.  4-bit codes unpack
+// in the order (0,4,1,5,2,6,3,7) within each 8; the B rows are stored in the same K
+// order (the sum over k does not care, as long as both operands agree).
 //
 // Every wait is bounded; on expiry the status word is set, the CTA still frees its
 // tensor memory and returns, and CTAs that start later return at once.
