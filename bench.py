@@ -525,6 +525,22 @@ def run_batch_layer(args) -> None:
     idx = torch.empty(tokens, K, dtype=torch.int32, device="cuda")
     w = torch.empty(tokens, K, dtype=torch.float16, device="cuda")
     zipf = args.zipf > 0
+    trace_stats = None
+    idx_per_layer = None
+    if args.route_trace:
+        # the routing comes from a trace in the reference's NVMAI_ROUTE_TRACE format (RealForwardRunner.swift:1208-1237):
+        # step i replays `tokens` consecutive recorded tokens of trace layer i % layers; weights 1/K (the trace holds ids only)
+        from nvmai_b200 import route_trace as rt
+        if args.route_trace.startswith("synthetic"):
+            reuse = float(args.route_trace.split(":")[1]) if ":" in args.route_trace else 0.38
+            trace = rt.parse(rt.synthesize(max(tokens, 128), n_layers, num_experts=E, top_k=K, reuse=reuse, seed=9).format(),
+                             num_experts=E, top_k=K)
+        else:
+            trace = rt.parse(args.route_trace, num_experts=E, top_k=K)
+        trace_stats = trace.stats()
+        tl = trace.layer_ids()
+        idx_per_layer = [torch.from_numpy(trace.batch(tl[l % len(tl)], 0, tokens)).cuda() for l in range(n_layers)]
+        w.fill_(1.0 / K)
     if zipf:
         rng = np.random.default_rng(4)
         perm = rng.permutation(E)
@@ -534,8 +550,27 @@ def run_batch_layer(args) -> None:
         idx.copy_(torch.from_numpy(ids))
         w.fill_(1.0 / K)
 
+    prenorm = args.prenorm
+    if prenorm:
+        # the two steps the runner encodes in front of the block (RealForwardRunner.swift:1900-1909), folded into the
+        # block's launches ("fused") or as the separate launches they replace ("unfused": residual add, norm, block)
+        from nvmai_b200 import Elementwise
+        hidden = torch.randn(tokens, D, device="cuda", generator=gen).to(torch.float16)
+        delta = (0.5 * torch.randn(tokens, D, device="cuda", generator=gen)).to(torch.float16)
+        norm_w = (0.5 + torch.rand(D, device="cuda", generator=gen)).to(torch.bfloat16)
+        hid32 = hidden.float()
+
     def step(i: int) -> None:
-        if zipf:
+        if prenorm == "fused":
+            moe.layer_decode_prenorm(i % n_layers, hid32, norm_w, 1e-6, tokens, attn_delta=delta, h2_out=y, out_idx=idx,
+                                     out_w=w, stream=stream)
+        elif prenorm == "unfused":
+            Elementwise.encode_residual_add(hidden, delta, tokens * D, stream=stream)
+            moe.rms_renorm(hid32, tokens, x, stream=stream)
+            moe.layer_decode(i % n_layers, x, tokens, hidden=hid32, h2_out=y, out_idx=idx, out_w=w, stream=stream)
+        elif idx_per_layer is not None:
+            moe.routed_partial(i % n_layers, x, tokens, idx_per_layer[i % n_layers], w, y, stream=stream)
+        elif zipf:
             moe.routed_partial(i % n_layers, x, tokens, idx, w, y, stream=stream)
         else:
             moe.layer_decode(i % n_layers, x, tokens, h2_out=y, out_idx=idx, out_w=w, stream=stream)
@@ -556,7 +591,8 @@ def run_batch_layer(args) -> None:
         ms = start.elapsed_time(end) / args.steps
         clocks = sampler.stop()
     assert torch.isfinite(y).all(), "non-finite output"
-    ids = idx.cpu().numpy()
+    ids = idx.cpu().numpy() if idx_per_layer is None else idx_per_layer[(args.steps - 1) % n_layers].cpu().numpy()
+    zipf = zipf or idx_per_layer is not None          # routed experts only in both replay modes
     distinct = int(np.unique(ids).size)
     blob = expert_bytes(args.bits)
     nbytes = distinct * blob + tokens * (D * 2 + D * 4)
@@ -574,7 +610,12 @@ def run_batch_layer(args) -> None:
            "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "data": "synthetic", "scaling": "weak",
            "dtype": "f16xu%d->f32" % args.bits, "value": tokens / (ms * 1e-3), "ms_per_step": ms, "clocks": clocks,
            "gpu_launches": int(launches),
-           "config": {"workload": ("configs[4]: one layer, %d rows, Zipf(%.1f) routing, routed experts only" % (tokens, args.zipf))
+           "config": {"workload": ("one layer, %d rows, routing replayed from a trace (%s), routed experts only"
+                                   % (tokens, "synthetic" if args.route_trace.startswith("synthetic") else "file"))
+                      if idx_per_layer is not None else
+                      ("one layer, %d rows, attention residual add + post-attention RMS norm + block, %s"
+                       % (tokens, prenorm)) if prenorm else
+                      ("configs[4]: one layer, %d rows, Zipf(%.1f) routing, routed experts only" % (tokens, args.zipf))
                       if zipf else ("configs[1]: one layer, %d independent rows, router + routed + shared" % tokens),
                       "d": D, "f": F, "experts": E, "top_k": K, "bits": args.bits, "layers_rotated": n_layers,
                       "distinct_experts": distinct, "hottest_expert_rows": int(counts.max()),
@@ -582,6 +623,8 @@ def run_batch_layer(args) -> None:
            "roofline": {"bound": "hbm", "kernel": "whole layer call (each distinct expert's bytes counted once)",
                         "achieved": gbs, "peak": peak, "peak_source": which, "unit": "GB/s", "frac": gbs / peak,
                         "traffic": None, "bytes_per_step": nbytes}}
+    if trace_stats is not None:
+        rec["config"]["trace"] = trace_stats
     print(json.dumps(rec), flush=True)
 
 
@@ -719,6 +762,11 @@ def main() -> None:
                     help="measure configs[1] (one layer, --tokens independent rows, batched decode kernels) or, with "
                          "--zipf, configs[4] instead of the decode stack")
     ap.add_argument("--zipf", type=float, default=0.0, help="with --batch-layer: Zipf exponent of the expert popularity")
+    ap.add_argument("--route-trace", default="",
+                    help="with --batch-layer: replay the routing of a trace file in the NVMAI_ROUTE_TRACE line format "
+                         "(`position layer e0..e7`), or `synthetic[:reuse]`")
+    ap.add_argument("--prenorm", default="", choices=["", "fused", "unfused"],
+                    help="with --batch-layer: time the block together with the residual add and RMS norm in front of it")
     ap.add_argument("--prefill", action="store_true",
                     help="measure configs[2] (a prefill chunk through the tensor-core grouped GEMMs) instead of the "
                          "decode stack; --tokens defaults to 4096 and --layers to 2 here")

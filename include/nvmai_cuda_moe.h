@@ -183,6 +183,30 @@ NVMAI_API int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, con
                                 void *hidden_inout, void *h2_out, uint32_t *out_idx, void *out_w_f16,
                                 void *stream);
 
+/* Width-2 verification of a speculated token (`encodeRoutedMoEVerifyPair`,
+ * RealForwardRunner.swift:3016-3235): the decode block, in the decode rounding order,
+ * for exactly two rows x fp16[2][d]; hidden_inout / h2_out / out_idx / out_w as in
+ * _layer_decode with tokens = 2.  The reference encodes phase 1 and phase 2 once per
+ * row and fetches the union of the two rows' experts; here both rows share one launch
+ * of each stage and a blob that both rows selected crosses HBM once. */
+NVMAI_API int nvmai_cuda_moe_layer_verify_pair(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, void *hidden_inout,
+                                               void *h2_out, uint32_t *out_idx, void *out_w_f16, void *stream);
+
+/* The decode block with the two steps the runner encodes in front of it folded in
+ * (RealForwardRunner.swift:1900-1909; residual_add_fp16, utility.metal:94-103;
+ * rmsnorm_bf16w, rmsnorm.metal:69-99):
+ *   hidden' = out(hidden + attn_delta)              (attn_delta fp16[tokens][d], NULL = no add)
+ *   x       = half(hidden' * rsqrt(mean(hidden'^2) + eps) * w)   (w bf16[d])
+ *   hidden  = out(hidden' + h2(x))
+ * hidden_inout is out_dtype[tokens][d] and is written once, by the last stage.
+ * x_out_f16 (optional, fp16[tokens][d]) receives the normalised rows (`routedX`);
+ * h2_out / out_idx / out_w as in _layer_decode.  Saves the two elementwise launches and
+ * their 4 KB round trips per row. */
+NVMAI_API int nvmai_cuda_moe_layer_decode_prenorm(nvmai_cuda_moe *h, uint32_t layer, void *hidden_inout,
+                                                  const void *attn_delta_f16, const void *norm_weight_bf16, float eps,
+                                                  uint32_t tokens, void *h2_out, void *x_out_f16, uint32_t *out_idx,
+                                                  void *out_w_f16, void *stream);
+
 /* `PrefillRouter.makeTokenExpertPairs` + `PrefillMoEGrouping.groupTokenExpertPairs`
  * (PrefillRouter.swift:97-117, PrefillMoEGrouping.swift:90-192) on the device: the
  * tokens*top_k (token, expert, rank, weight) records sorted by (expert, token,

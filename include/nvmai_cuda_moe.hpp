@@ -105,6 +105,21 @@ public:
               "MoE.encodeLayerDecode");
     }
 
+    // encodeRoutedMoEVerifyPair (RealForwardRunner.swift:3016-3235): two rows, decode rounding order
+    void encodeRoutedMoEVerifyPair(Stream commandBuffer, uint32_t layer, const void *routedX, void *hidden,
+                                   void *h2 = nullptr, uint32_t *outIndices = nullptr, void *outWeights = nullptr) {
+        check(nvmai_cuda_moe_layer_verify_pair(h_, layer, routedX, hidden, h2, outIndices, outWeights, commandBuffer),
+              "MoE.encodeRoutedMoEVerifyPair");
+    }
+
+    // encodeResidualAdd + rms.encodeBF16W + the decode block (RealForwardRunner.swift:1900-1909 + 1911-1995)
+    void encodeLayerDecodePreNorm(Stream commandBuffer, uint32_t layer, void *hidden, const void *attnDelta,
+                                  const void *postAttnNormWeight, float eps, uint32_t tokens, void *h2 = nullptr,
+                                  void *routedX = nullptr, uint32_t *outIndices = nullptr, void *outWeights = nullptr) {
+        check(nvmai_cuda_moe_layer_decode_prenorm(h_, layer, hidden, attnDelta, postAttnNormWeight, eps, tokens, h2, routedX,
+                                                  outIndices, outWeights, commandBuffer), "MoE.encodeLayerDecodePreNorm");
+    }
+
     // encodeRoutedMoEPrefill (RealForwardRunner.swift:3244-3591)
     void encodeRoutedMoEPrefill(Stream commandBuffer, uint32_t layer, const void *hiddenRows, uint32_t queryCount,
                                 void *hidden, void *y = nullptr, uint32_t *outIndices = nullptr, void *outWeights = nullptr) {

@@ -542,6 +542,7 @@ struct CombineParams {
     const uint32_t *inv; const __half *routing_w; const float *gate_val;
     const void *residual;
     void *y; void *hidden;
+    const __half *hidden_delta;   // optional fp16 [tokens][D]: decode order only, hidden = out(out(hidden + delta) + y)
     float *partial_y;      // expert parallelism: this rank's share sum_r w[t,r]*partial (local pairs only), fp32, nothing else
     uint32_t D, K;
     // Prefill rounding (prefill.metal:437-458, RealForwardRunner.swift:3560-3569): every
@@ -593,7 +594,11 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
         for (uint32_t r = 0; r < p.K; ++r) acc += wk[r] * p.partial[(size_t)pos[r] * p.D + d];
         const float yv = round_out<OUT>(acc);
         if (p.y != nullptr) store_out<OUT>(p.y, i, yv);
-        if (p.hidden != nullptr) store_out<OUT>(p.hidden, i, load_out<OUT>(p.hidden, i) + yv);
+        if (p.hidden != nullptr) {
+            float hv = load_out<OUT>(p.hidden, i);
+            if (p.hidden_delta != nullptr) hv = round_out<OUT>(hv + __half2float(p.hidden_delta[i]));
+            store_out<OUT>(p.hidden, i, hv + yv);
+        }
     }
 }
 

@@ -396,7 +396,8 @@ int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, 
 // item), then the per-token weighted sum in rank order.
 // partial_y != nullptr: expert-parallel share (local experts only, no shared expert, fp32 rows out).
 int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, uint32_t tokens, const uint32_t *idx,
-                 const __half *w, void *hidden, void *y, cudaStream_t st, float *partial_y = nullptr) {
+                 const __half *w, void *hidden, void *y, cudaStream_t st, float *partial_y = nullptr,
+                 const __half *hidden_delta = nullptr) {
     const auto &c = h->cfg;
     const bool ep = partial_y != nullptr;
     int rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, !ep, st, !ep, ep);
@@ -444,6 +445,7 @@ int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, 
     pc.gate_val = (c.shared_f && c.shared_gate_kind != NVMAI_GATE_NONE) ? h->gate_val : nullptr;
     pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
     pc.partial_y = partial_y;
+    pc.hidden_delta = hidden_delta;
     pc.prefill = 0;
     return dispatch_out(c.out_dtype, [&](auto O) {
         return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
@@ -454,7 +456,7 @@ int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, 
 // same buffer, or the buffer stage 1 writes its normalised rows to).
 int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, const __half *x_rows, uint32_t tokens,
                       void *hidden, void *h2_out, uint32_t *out_idx, __half *out_w, cudaStream_t st,
-                      const LayerViews *next_layer = nullptr) {
+                      const LayerViews *next_layer = nullptr, const __half *hidden_delta = nullptr) {
     const auto &c = h->cfg;
     const LayerViews &lv = h->layers[layer];
     uint32_t *idx = out_idx ? out_idx : h->idx;
@@ -469,7 +471,7 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
                            defer);
     if (rc) return rc;
     h->cur_trace = nullptr;
-    if (grouped) return grouped_tail(h, lv, x_rows, tokens, idx, w, hidden, h2_out ? h2_out : h->y, st);
+    if (grouped) return grouped_tail(h, lv, x_rows, tokens, idx, w, hidden, h2_out ? h2_out : h->y, st, nullptr, hidden_delta);
     h->cur_trace = slot(1);
     RoutedSource src = source_from_layer(h, lv, idx);
     if (defer) {
@@ -498,6 +500,7 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
     p.h1_out = nullptr;
     p.y = h2_out ? h2_out : h->y;
     p.hidden = hidden;
+    p.hidden_delta = hidden_delta;
     p.top_k = c.top_k;
     if (next_layer != nullptr && h->l2_prefetch) {    // stack driver: warm the L2 with what the next layer's first stage reads
         const auto &nw = next_layer->w;
@@ -931,9 +934,41 @@ int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x
                              out_idx, static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
 }
 
-// Layer l > 0 reads the previous layer's block output and renormalises it inside
-// its own stage 1 (every block derives the same rows; block 0 stores them for
-// stage 2), so a layer is exactly three launches.
+// Width-2 verification (RealForwardRunner.swift:3016-3235): the decode block's rounding order for two rows.  Here
+// the two rows share one launch of each stage, and a blob that both rows selected is read from HBM once and served
+// to the second row's blocks by the L2.
+int nvmai_cuda_moe_layer_verify_pair(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, void *hidden_inout,
+                                     void *h2_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    int rc = check_layer(h, layer);
+    if (rc) return rc;
+    if (h->cfg.max_tokens < 2) return NVMAI_CUDA_ERANGE;
+    return nvmai_cuda_moe_layer_decode(h, layer, x_f16, 2, hidden_inout, h2_out, out_idx, out_w_f16, stream);
+}
+
+// The block together with the two steps the runner encodes in front of it (RealForwardRunner.swift:1900-1909):
+// stage 1 derives x = rmsnorm_bf16w(out(hidden + delta)) in every block (block 0 stores the rows for stage 2), the
+// last stage writes hidden = out(out(hidden + delta) + h2); nothing writes the hidden state before that, so no block
+// can read a half-updated row.
+int nvmai_cuda_moe_layer_decode_prenorm(nvmai_cuda_moe *h, uint32_t layer, void *hidden_inout, const void *attn_delta_f16,
+                                        const void *norm_weight_bf16, float eps, uint32_t tokens, void *h2_out,
+                                        void *x_out_f16, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    int rc = check_layer(h, layer);
+    if (rc) return rc;
+    if (!hidden_inout || !norm_weight_bf16 || !(eps >= 0.0f)) return NVMAI_CUDA_EINVAL;
+    if (x_out_f16 && !aligned16(x_out_f16)) return NVMAI_CUDA_EINVAL;
+    if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (h->cfg.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
+    XSource xsrc{};
+    xsrc.y_prev = hidden_inout;
+    xsrc.x_out = x_out_f16 ? static_cast<__half *>(x_out_f16) : h->xnorm;
+    xsrc.delta = static_cast<const __half *>(attn_delta_f16);
+    xsrc.norm_w = static_cast<const uint16_t *>(norm_weight_bf16);
+    xsrc.eps = eps;
+    return layer_decode_impl(h, layer, xsrc, xsrc.x_out, tokens, hidden_inout, h2_out, out_idx,
+                             static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream), nullptr,
+                             xsrc.delta);
+}
+
 int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
                                  void *hidden_inout, void *y_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
     int rc = check_layer(h, layer);
@@ -1025,6 +1060,9 @@ int nvmai_cuda_moe_rms_renorm(nvmai_cuda_moe *h, const void *y, uint32_t tokens,
     return check_launch(h);
 }
 
+// Layer l > 0 reads the previous layer's block output and renormalises it inside
+// its own stage 1 (every block derives the same rows; block 0 stores them for
+// stage 2), so a layer is exactly three launches.
 static int stack_enqueue(nvmai_cuda_moe *h, const __half *x0, uint32_t tokens, void *y_last, cudaStream_t st) {
     const auto &c = h->cfg;
     for (uint32_t l = 0; l < c.num_layers; ++l) {

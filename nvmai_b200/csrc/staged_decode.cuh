@@ -72,12 +72,27 @@ struct DownLayout {       // per warp: barrier, activation row, 16-row down tile
 struct XSource {
     const __half *x;          // fp16 rows [tokens][x_stride] ...
     uint32_t x_stride;
-    const void *y_prev;       // ... or the previous block output [tokens][D] (out dtype), RMS-normalised here
+    const void *y_prev;       // ... or a state [tokens][D] (out dtype) that is RMS-normalised here: the previous
+                              // block output (stack driver) or the hidden state (fused pre-norm entry point)
     __half *x_out;            // normalised rows written back by block 0 for the later stages (or nullptr)
+    // fused pre-norm (RealForwardRunner.swift:1900-1909): the row that is normalised is out(y_prev + delta), the
+    // hidden state after the attention residual add (utility.metal:94-103), and the normalised value is multiplied
+    // by a bf16 weight, x = half(v * inv * w) (rmsnorm.metal:69-99)
+    const __half *delta = nullptr;      // [tokens][D] or nullptr
+    const uint16_t *norm_w = nullptr;   // bf16 [D] or nullptr
+    float eps = 1e-6f;
 };
 
-// Stack driver only: x = half(y * rsqrt(mean(y^2) + 1e-6)), fp32 math, fixed
-// reduction tree, so every block derives bit-identical rows.
+// x = half(v * rsqrt(mean(v^2) + eps) [* w]), fp32 math, fixed reduction tree, so
+// every block derives bit-identical rows.
+template <int OUT>
+__device__ __forceinline__ float norm_input(const XSource &src, size_t i) {
+    const float v = load_out<OUT>(src.y_prev, i);
+    return src.delta != nullptr ? round_out<OUT>(v + __half2float(src.delta[i])) : v;
+}
+__device__ __forceinline__ __half norm_output(const XSource &src, float scaled, int col) {
+    return __float2half_rn(src.norm_w != nullptr ? scaled * meta_to_float<META_BF16>(ldg_u16(src.norm_w + col)) : scaled);
+}
 template <int OUT>
 __device__ __forceinline__ void stage_x(const XSource &src, uint32_t tok, int D, __half *xs, float *wsum,
                                         bool write_back) {
@@ -95,12 +110,12 @@ __device__ __forceinline__ void stage_x(const XSource &src, uint32_t tok, int D,
 #pragma unroll
         for (int j = 0; j < kKeep; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
-            keep[j] = i < D ? load_out<OUT>(src.y_prev, base + i) : 0.0f;
+            keep[j] = i < D ? norm_input<OUT>(src, base + i) : 0.0f;
         }
 #pragma unroll
         for (int j = 0; j < kKeep; ++j) ss = fmaf(keep[j], keep[j], ss);
         for (int i = threadIdx.x + kKeep * blockDim.x; i < D; i += blockDim.x) {
-            const float v = load_out<OUT>(src.y_prev, base + i);
+            const float v = norm_input<OUT>(src, base + i);
             ss = fmaf(v, v, ss);
         }
         ss = warp_sum(ss);
@@ -108,18 +123,18 @@ __device__ __forceinline__ void stage_x(const XSource &src, uint32_t tok, int D,
         __syncthreads();
         float tot = 0.0f;
         for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += wsum[i];
-        const float sc = rsqrtf(tot / (float)D + 1e-6f);
+        const float sc = rsqrtf(tot / (float)D + src.eps);
 #pragma unroll
         for (int j = 0; j < kKeep; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
             if (i < D) {
-                const __half h = __float2half_rn(keep[j] * sc);
+                const __half h = norm_output(src, keep[j] * sc, i);
                 xs[i] = h;
                 if (write_back) src.x_out[base + i] = h;
             }
         }
         for (int i = threadIdx.x + kKeep * blockDim.x; i < D; i += blockDim.x) {
-            const __half h = __float2half_rn(load_out<OUT>(src.y_prev, base + i) * sc);
+            const __half h = norm_output(src, norm_input<OUT>(src, base + i) * sc, i);
             xs[i] = h;
             if (write_back) src.x_out[base + i] = h;
         }
@@ -513,6 +528,8 @@ struct Stage3Params {
                                         // and count the block there
     void *y;                            // out_dtype[tokens][D]  (block output h2)
     void *hidden;                       // optional out_dtype[tokens][D], hidden += y
+    const __half *hidden_delta;         // optional fp16 [tokens][D]: hidden = out(out(hidden + delta) + y), the attention
+                                        // residual add that precedes the block folded into this one
     // ranges the next launch will read (the next layer's router and shared-expert
     // weights): each block asks the L2 for its share
     const void *next_ptr[6]; unsigned long long next_bytes[6];
@@ -754,7 +771,11 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
             acc += wk_s[k] * unit_sum(k);
         const float yv = round_out<OUT>(acc);
         if (p.y != nullptr) store_out<OUT>(p.y, i, yv);
-        if (p.hidden != nullptr) store_out<OUT>(p.hidden, i, load_out<OUT>(p.hidden, i) + yv);   // utility.metal:94-103
+        if (p.hidden != nullptr) {                                                              // utility.metal:94-103
+            float hv = load_out<OUT>(p.hidden, i);
+            if (p.hidden_delta != nullptr) hv = round_out<OUT>(hv + __half2float(p.hidden_delta[i]));
+            store_out<OUT>(p.hidden, i, hv + yv);
+        }
     }
     trace_end(p.trace);
 }

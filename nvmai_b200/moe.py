@@ -216,6 +216,21 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_layer_decode(self._h, layer, _ptr(x), tokens, _ptr(hidden), _ptr(h2_out),
                                                     _ptr(out_idx), _ptr(out_w), _stream(stream)), "layer_decode")
 
+    def layer_verify_pair(self, layer: int, x, *, hidden=None, h2_out=None, out_idx=None, out_w=None,
+                          stream=None) -> None:
+        """`encodeRoutedMoEVerifyPair` (RealForwardRunner.swift:3016-3235): the decode block for two rows."""
+        check(self._lib.nvmai_cuda_moe_layer_verify_pair(self._h, layer, _ptr(x), _ptr(hidden), _ptr(h2_out),
+                                                         _ptr(out_idx), _ptr(out_w), _stream(stream)),
+              "layer_verify_pair")
+
+    def layer_decode_prenorm(self, layer: int, hidden, norm_weight, eps: float, tokens: int, *, attn_delta=None,
+                             h2_out=None, x_out=None, out_idx=None, out_w=None, stream=None) -> None:
+        """Residual add + `rmsnorm_bf16w` + the decode block (RealForwardRunner.swift:1900-1909) in three launches."""
+        check(self._lib.nvmai_cuda_moe_layer_decode_prenorm(self._h, layer, _ptr(hidden), _ptr(attn_delta),
+                                                            _ptr(norm_weight), float(eps), tokens, _ptr(h2_out),
+                                                            _ptr(x_out), _ptr(out_idx), _ptr(out_w), _stream(stream)),
+              "layer_decode_prenorm")
+
     def stack_decode(self, x0, tokens: int, y_last, *, stream=None) -> None:
         check(self._lib.nvmai_cuda_moe_stack_decode(self._h, _ptr(x0), tokens, _ptr(y_last), _stream(stream)),
               "stack_decode")

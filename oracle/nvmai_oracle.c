@@ -626,6 +626,26 @@ void orc_gpu_residual_add(void *hidden, const void *delta, size_t n, int out_dty
     }
 }
 
+/* rmsnorm.metal:33-99 (rms_block_inv + rmsnorm_bf16w): inv = rsqrt(mean(x^2) + eps) with the
+ * squares accumulated in fp32 (here fp64: the order of the shader's tree is not specified),
+ * out[i] = half(x[i] * inv * float(weight[i])).  x in the block's output type (fp16 in the
+ * reference), weight bf16, out fp16. */
+void orc_gpu_rmsnorm_bf16w(const void *x, const uint16_t *w_bf16, uint16_t *out_f16, size_t D, float eps,
+                           int out_dtype) {
+    double acc = 0.0;
+    for (size_t i = 0; i < D; ++i) {
+        const float v = out_dtype == ORC_OUT_FP16 ? orc_f16_to_f32(((const uint16_t *)x)[i]) : ((const float *)x)[i];
+        acc += (double)v * (double)v;
+    }
+    const float mean_sq = (float)acc / (float)D;
+    const float inv = 1.0f / sqrtf(mean_sq + eps);
+    for (size_t i = 0; i < D; ++i) {
+        const float v = out_dtype == ORC_OUT_FP16 ? orc_f16_to_f32(((const uint16_t *)x)[i]) : ((const float *)x)[i];
+        const float wv = w_bf16 ? orc_bf16_to_f32(w_bf16[i]) : 1.0f;
+        out_f16[i] = orc_f32_to_f16(v * inv * wv);
+    }
+}
+
 /* ------------------------------------------------------------------ */
 /* Prefill-side host logic                                             */
 /* ------------------------------------------------------------------ */

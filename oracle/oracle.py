@@ -139,6 +139,7 @@ def _declare(L: C.CDLL) -> None:
                                         sz, sz, C.c_int, vp]
     L.orc_gpu_shared_expert.restype = None
     L.orc_gpu_residual_add.argtypes = [vp, vp, sz, C.c_int]; L.orc_gpu_residual_add.restype = None
+    L.orc_gpu_rmsnorm_bf16w.argtypes = [vp, vp, vp, sz, C.c_float, C.c_int]; L.orc_gpu_rmsnorm_bf16w.restype = None
     L.orc_group_pairs.argtypes = [vp, sz, C.c_long, C.c_long, C.c_long, C.c_long, vp, sz, vp, vp,
                                   vp, vp, C.POINTER(sz), vp, C.POINTER(sz)]
     L.orc_group_pairs.restype = C.c_int

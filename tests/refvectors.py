@@ -259,3 +259,24 @@ def affine_quant_case(bits: int) -> dict:
     return dict(bits=bits, rows=rows, cols=cols, packed=packed, scales=scales, biases=biases,
                 x_f16=orc.f32_to_f16_bits(np.ones(cols, dtype=np.float32)),
                 expected=values.sum(axis=1).astype(np.float32))
+
+
+# ---------------------------------------------------------------------------
+# tests/NVMAI/Core/Kernels/Primitives/RMSNormTests.swift
+# ---------------------------------------------------------------------------
+
+def rmsnorm_bf16w_case(d: int, seed: int) -> dict:
+    """RMSNormTests.swift:22-55: x ~ U(-1, 1) rounded to fp16, weight ~ U(0.5, 1.5) rounded to bf16, eps 1e-6;
+    the comparator is RmsNormRef.apply in its scalar form (RMSNormReferenceTests.swift:16-22), bar 5e-3."""
+    rng = orc.seedtree_key(seed, f"rmsnorm-bf16w-d{d}")
+    x32 = rng.uniform_array(-1.0, 1.0, d)
+    w32 = rng.uniform_array(0.5, 1.5, d)
+    x16 = x32.astype(np.float16)
+    w_bits = orc.f32_to_bf16_bits(w32)
+    x, w = x16.astype(np.float32), orc.bf16_bits_to_f32(w_bits)
+    eps = np.float32(1e-6)
+    sum_sq = np.float32(0.0)
+    for v in x:
+        sum_sq = np.float32(sum_sq + v * v)
+    inv = np.float32(1.0) / np.sqrt(np.float32(sum_sq / np.float32(d) + eps))
+    return {"x16": x16, "w_bits": w_bits, "eps": float(eps), "ref": (x * inv * w).astype(np.float32), "tol": 5e-3}

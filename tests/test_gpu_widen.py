@@ -1,0 +1,215 @@
+"""GPU parity tests of the callers either side of the decode block: the width-2
+verification entry point and the block with the attention residual add and the
+post-attention RMS norm folded in.  Through the C ABI, against the CPU oracle.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import gpu_util as gu
+import refvectors as rv
+from nvmai_b200 import MoE, MoEConfig, synthetic
+from nvmai_b200 import format as fmt
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+FFN_TOL = 1e-3
+
+
+def sync():
+    gu.torch_cuda().cuda.synchronize()
+
+
+def _case(bits, meta, out_dtype, tokens, seed, d=2048, f=512, e=256, router_kind=fmt.ROUTER_DENSE_F16,
+          gate_kind=fmt.ROUTER_DENSE_F16):
+    host = synthetic.layer(seed, d=d, f=f, shared_f=f, num_experts=e, routed_bits=bits, meta=meta,
+                           router_kind=router_kind, gate_kind=gate_kind)
+    cfg = MoEConfig(d=d, f=f, shared_f=f, num_experts=e, top_k=8, routed_bits=bits, shared_bits=bits,
+                    router_kind=router_kind, shared_gate_kind=gate_kind, meta_dtype=meta,
+                    activation=fmt.ACT_SILU, out_dtype=out_dtype, max_tokens=tokens)
+    return host, cfg
+
+
+def _out(t, cfg, rows):
+    if cfg.out_dtype == fmt.OUT_FP16:
+        return orc.f16_bits_to_f32(gu.from_dev(t, np.uint16)).reshape(rows, cfg.d)
+    return t.cpu().numpy().reshape(rows, cfg.d)
+
+
+@pytest.mark.parametrize("bits,out_dtype", [(4, fmt.OUT_FP16), (8, fmt.OUT_FP32)])
+def test_verify_pair_equals_two_decode_rows(bits, out_dtype):
+    """`encodeRoutedMoEVerifyPair`: each of the two rows gets the decode block's result (the reference encodes the
+    decode kernels once per row), indices exact; the second row is the first plus a small perturbation so that the
+    rows share most experts, which is the case the entry point exists for"""
+    kind = fmt.ROUTER_AFFINE8 if out_dtype == fmt.OUT_FP16 else fmt.ROUTER_DENSE_F16
+    host, cfg = _case(bits, fmt.META_BF16, out_dtype, 2, seed=301 + bits, router_kind=kind, gate_kind=kind)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    x = synthetic.hidden_rows(302, 2, cfg.d)
+    x32 = orc.f16_bits_to_f32(x[0])
+    bump = orc.f16_bits_to_f32(synthetic.hidden_rows(303, 1, cfg.d)[0]) * np.float32(0.05)
+    x[1] = orc.f32_to_f16_bits(x32 + bump)
+    esz = "f16" if out_dtype == fmt.OUT_FP16 else "f32"
+    hid0 = synthetic.hidden_rows(304, 2, cfg.d)
+    hid_host = hid0 if out_dtype == fmt.OUT_FP16 else orc.f16_bits_to_f32(hid0).astype(np.float32)
+    hid = gu.to_dev(hid_host.copy())
+    h2 = gu.dev_empty(2 * cfg.d, esz)
+    idx, w = gu.dev_empty(16, "u32"), gu.dev_empty(16, "f16")
+    moe.layer_verify_pair(0, gu.to_dev(x), hidden=hid, h2_out=h2, out_idx=idx, out_w=w)
+    sync()
+    got, got_hid = _out(h2, cfg, 2), _out(hid, cfg, 2)
+    got_idx = gu.from_dev(idx, np.uint32).reshape(2, 8)
+    L, keep = gu.oracle_layer(host, cfg)
+    shared = len(set(got_idx[0].tolist()) & set(got_idx[1].tolist()))
+    assert shared >= 4, f"the two rows share only {shared} experts: not the case under test"
+    tol_gpu = 2e-3 if out_dtype == fmt.OUT_FP16 else 5e-4
+    for t in range(2):
+        o_idx, o_w, o_h2, margin, cpu = gu.oracle_decode(L, cfg, np.ascontiguousarray(x[t]))
+        assert margin > 1e-5
+        assert got_idx[t].tolist() == o_idx.tolist()
+        assert orc.rel_error(got[t], cpu) < FFN_TOL, "vs the reference CPU path"
+        assert orc.rel_error(got[t], o_h2) < tol_gpu, "vs the shader-semantics oracle"
+        # the tail: one residual add per row (RealForwardRunner.swift:3207-3213), in the output type
+        base = orc.f16_bits_to_f32(hid0[t])
+        if out_dtype == fmt.OUT_FP16:
+            want = (base + got[t]).astype(np.float16).astype(np.float32)
+        else:
+            want = base + got[t]
+        assert np.array_equal(got_hid[t], want)
+    # and bitwise the same as the general entry point with two rows
+    h2b = gu.dev_empty(2 * cfg.d, esz)
+    moe.layer_decode(0, gu.to_dev(x), 2, h2_out=h2b)
+    sync()
+    assert np.array_equal(_out(h2b, cfg, 2).view(np.uint32), got.view(np.uint32))
+
+
+@pytest.mark.parametrize("d,seed", [(256, 0xC3), (2048, 0xD4)])
+def test_prenorm_rows_match_reference_rmsnorm_vectors(d, seed):
+    """the normalised rows the fused entry point hands to the block, on the inputs of the reference's own rmsnorm
+    tests (RMSNormTests.swift:22-61), within the reference's bar of its fp32 comparator and within one fp16 ulp of
+    the oracle"""
+    case = rv.rmsnorm_bf16w_case(d, seed)
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP16, 1, seed=311, d=d, f=128, e=32)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    hid = gu.to_dev(case["x16"].view(np.uint16).copy())
+    xo = gu.dev_empty(d, "f16")
+    moe.layer_decode_prenorm(0, hid, gu.to_dev(case["w_bits"]), case["eps"], 1, x_out=xo)
+    sync()
+    got_bits = gu.from_dev(xo, np.uint16).ravel()
+    got = orc.f16_bits_to_f32(got_bits)
+    assert orc.rel_error(got, case["ref"]) < case["tol"]
+    want = np.zeros(d, dtype=np.uint16)
+    orc.lib().orc_gpu_rmsnorm_bf16w(orc.ptr(case["x16"].view(np.uint16)), orc.ptr(case["w_bits"]), orc.ptr(want), d,
+                                    case["eps"], fmt.OUT_FP16)
+    ulp = np.abs(got_bits.astype(np.int32) - want.astype(np.int32))    # same sign bits wherever both are non-zero
+    assert ulp.max() <= 1 and np.count_nonzero(ulp) <= d // 100
+
+
+@pytest.mark.parametrize("tokens,out_dtype,grouped_min", [(1, fmt.OUT_FP16, None), (3, fmt.OUT_FP16, None),
+                                                          (1, fmt.OUT_FP32, None), (6, fmt.OUT_FP16, 4)])
+def test_prenorm_block_matches_unfused_sequence(tokens, out_dtype, grouped_min, monkeypatch):
+    """residual add -> rmsnorm_bf16w -> decode block -> residual add (RealForwardRunner.swift:1900-1909, 1911-1995) in
+    three launches: the hidden state after the first add and the final add are exact given the block output, the
+    normalised rows are within one fp16 ulp of the oracle's, and the block output on those rows meets the decode bars"""
+    if grouped_min is not None:
+        monkeypatch.setenv("NVMAI_CUDA_GROUPED_MIN", str(grouped_min))
+    kind = fmt.ROUTER_AFFINE8 if out_dtype == fmt.OUT_FP16 else fmt.ROUTER_DENSE_F16
+    host, cfg = _case(4, fmt.META_BF16, out_dtype, tokens, seed=321, router_kind=kind, gate_kind=kind)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    f16 = out_dtype == fmt.OUT_FP16
+    esz = "f16" if f16 else "f32"
+    rng = np.random.default_rng(322)
+    hid32 = (rng.standard_normal((tokens, cfg.d)) * 3.0).astype(np.float32)
+    delta16 = (rng.standard_normal((tokens, cfg.d)) * 0.7).astype(np.float16)
+    w_bits = orc.f32_to_bf16_bits(rng.uniform(0.5, 1.5, cfg.d).astype(np.float32))
+    hid_host = hid32.astype(np.float16).view(np.uint16) if f16 else hid32
+    eps = 1e-6
+    hid = gu.to_dev(hid_host.copy())
+    h2 = gu.dev_empty(tokens * cfg.d, esz)
+    xo = gu.dev_empty(tokens * cfg.d, "f16")
+    idx = gu.dev_empty(tokens * 8, "u32")
+    moe.layer_decode_prenorm(0, hid, gu.to_dev(w_bits), eps, tokens, attn_delta=gu.to_dev(delta16.view(np.uint16)),
+                             h2_out=h2, x_out=xo, out_idx=idx)
+    sync()
+    got_h2, got_hid = _out(h2, cfg, tokens), _out(hid, cfg, tokens)
+    got_x = gu.from_dev(xo, np.uint16).reshape(tokens, cfg.d)
+    got_idx = gu.from_dev(idx, np.uint32).reshape(tokens, 8)
+    # hidden' = out(hidden + delta) (utility.metal:94-103)
+    mid = hid_host.copy()
+    orc.lib().orc_gpu_residual_add(orc.ptr(mid), orc.ptr(delta16.view(np.uint16) if f16 else delta16.astype(np.float32)),
+                                   tokens * cfg.d, out_dtype)
+    mid32 = orc.f16_bits_to_f32(mid).reshape(tokens, cfg.d) if f16 else mid
+    L, keep = gu.oracle_layer(host, cfg)
+    tol_gpu = 2e-3 if f16 else 5e-4
+    for t in range(tokens):
+        want_x = np.zeros(cfg.d, dtype=np.uint16)
+        orc.lib().orc_gpu_rmsnorm_bf16w(orc.ptr(np.ascontiguousarray(mid[t])), orc.ptr(w_bits), orc.ptr(want_x), cfg.d,
+                                        eps, out_dtype)
+        ulp = np.abs(got_x[t].astype(np.int32) - want_x.astype(np.int32))
+        assert ulp.max() <= 1 and np.count_nonzero(ulp) <= cfg.d // 100, f"row {t}: normalised rows"
+        o_idx, o_w, o_h2, margin, cpu = gu.oracle_decode(L, cfg, np.ascontiguousarray(got_x[t]))
+        assert margin > 1e-5
+        assert got_idx[t].tolist() == o_idx.tolist()
+        assert orc.rel_error(got_h2[t], cpu) < FFN_TOL, "vs the reference CPU path"
+        assert orc.rel_error(got_h2[t], o_h2) < tol_gpu, "vs the shader-semantics oracle"
+        want_hid = (mid32[t] + got_h2[t]).astype(np.float16).astype(np.float32) if f16 else mid32[t] + got_h2[t]
+        assert np.array_equal(got_hid[t], want_hid), f"row {t}: hidden = out(out(hidden + delta) + h2)"
+
+
+def test_prenorm_rejects_bad_arguments():
+    from nvmai_b200 import NvmaiError, _lib
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP16, 2, seed=331, d=256, f=128, e=32)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    hid = gu.dev_empty(2 * cfg.d, "f16")
+    w = gu.dev_empty(cfg.d, "f16")
+    for args, kw, code in [((0, None, w, 1e-6, 1), {}, _lib.EINVAL),           # no hidden state
+                           ((0, hid, None, 1e-6, 1), {}, _lib.EINVAL),         # no norm weight
+                           ((0, hid, w, -1.0, 1), {}, _lib.EINVAL),            # negative eps
+                           ((0, hid, w, 1e-6, 3), {}, _lib.ERANGE),            # more rows than max_tokens
+                           ((1, hid, w, 1e-6, 1), {}, _lib.ERANGE)]:           # layer out of range
+        with pytest.raises(NvmaiError) as ei:
+            moe.layer_decode_prenorm(*args, **kw)
+        assert ei.value.code == code
+    with pytest.raises(NvmaiError) as ei:
+        moe.layer_verify_pair(5, hid)
+    assert ei.value.code == _lib.ERANGE
+
+
+def test_route_trace_replay_matches_cpu_path():
+    """a recorded routing (`position layer e0..e7`) drives the routed kernels through `routed_partial`; every row's
+    share equals the reference CPU path's accumulation over the recorded experts with the replay's weights"""
+    from nvmai_b200 import route_trace as rt
+    rows, e = 12, 32
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, rows, seed=341, d=256, f=128, e=e)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    trace = rt.parse(rt.synthesize(40, 2, num_experts=e, reuse=0.38, seed=5).format(), num_experts=e, num_layers=2)
+    ids = trace.batch(1, first_row=30, rows=rows)              # wraps past the last recorded token
+    x = synthetic.hidden_rows(342, rows, cfg.d)
+    w16 = np.full((rows, 8), 1.0 / 8, dtype=np.float16)
+    share = gu.dev_empty(rows * cfg.d, "f32")
+    moe.routed_partial(0, gu.to_dev(x), rows, gu.to_dev(ids.astype(np.uint32)), gu.to_dev(w16.view(np.uint16)), share)
+    sync()
+    got = share.cpu().numpy().reshape(rows, cfg.d)
+    off = np.array([host["offsets"][n] for n in fmt.OFFSET_NAMES], dtype=np.uint32)
+    lib, fn = orc.lib(), orc.ref_gemv4_ptr()
+    blobs = host["experts"]
+    scratch = np.zeros(2 * cfg.f + cfg.d, dtype=np.float32)
+    for t in range(rows):
+        want = np.zeros(cfg.d, dtype=np.float32)
+        x32 = orc.f16_bits_to_f32(x[t])
+        for k in range(8):
+            blob = blobs[int(ids[t, k]) * host["stride"]:]
+            lib.orc_cpu_expert_accumulate(orc.ptr(blob), orc.ptr(off), 4, orc.META_BF16, orc.ACT_SILU, orc.ptr(x32),
+                                          cfg.d, cfg.f, float(np.float16(1.0 / 8)), orc.ptr(scratch), orc.ptr(want), fn)
+        assert orc.rel_error(got[t], want) < FFN_TOL, f"row {t}"

@@ -264,3 +264,27 @@ def test_grouping_rejects_invalid_metadata():
     assert _group([(0, 2, 0, 1)], 1, 1, 2, 1)[0] == 8
     assert _group([(0, 0, 0, 1), (0, 1, 0, 2)], 1, 2, 2, 1)[0] == 9
     assert _group([(0, 0, 0, 1)], 1, 1, 2, 1, sort_keys=[0])[0] == 10
+
+
+@pytest.mark.parametrize("d,seed", [(256, 0xC3), (2048, 0xD4)])
+def test_rmsnorm_bf16w_oracle_on_reference_vectors(d, seed):
+    """RMSNormTests.swift:22-61: the oracle's rmsnorm_bf16w against RmsNormRef on the reference's seed-derived inputs,
+    at the reference's bar (Tolerance.fp16Reduction); fp16 rounding of the output is the only difference, so half an
+    ulp is the real distance"""
+    case = rv.rmsnorm_bf16w_case(d, seed)
+    out = np.zeros(d, dtype=np.uint16)
+    orc.lib().orc_gpu_rmsnorm_bf16w(orc.ptr(case["x16"].view(np.uint16)), orc.ptr(case["w_bits"]), orc.ptr(out), d,
+                                    case["eps"], 0)
+    got = orc.f16_bits_to_f32(out)
+    assert orc.rel_error(got, case["ref"]) < case["tol"]
+    assert np.max(np.abs(got - case["ref"]) / np.maximum(np.abs(case["ref"]), 1e-3)) < 1.0 / 1024
+
+
+def test_rmsnorm_closed_form():
+    """x = (3, 4) repeated, w = 1: mean square 12.5, so out = x / sqrt(12.5) up to fp16 rounding"""
+    x = np.tile(np.array([3.0, 4.0], dtype=np.float16), 32)
+    w = orc.f32_to_bf16_bits(np.ones(64, dtype=np.float32))
+    out = np.zeros(64, dtype=np.uint16)
+    orc.lib().orc_gpu_rmsnorm_bf16w(orc.ptr(x.view(np.uint16)), orc.ptr(w), orc.ptr(out), 64, 0.0, 0)
+    want = (x.astype(np.float32) / np.float32(np.sqrt(12.5))).astype(np.float16)
+    assert np.array_equal(out.view(np.float16), want)
