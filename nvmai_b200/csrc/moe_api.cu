@@ -79,6 +79,7 @@ struct nvmai_cuda_moe {
     // B200 (8-bit layer): 4 rows 60 us separate / 102 us grouped, 16 rows 190 / 265, 64 rows 697 / 570.
     // NVMAI_CUDA_GROUPED_MIN overrides it.
     uint32_t grouped_min_tokens = 24;
+    uint32_t tc_min_tokens = 32;     // batched decode calls from this many rows on run the tensor-core (prefill) kernels
     // 8-bit weights on the tensor-core prefill path (fp16 operand tiles: about 3e-3 of one expert's output);
     // off = prefill calls with 8-bit weights run the exact decode kernels.  NVMAI_CUDA_PREFILL_TC8=1 turns it on.
     bool prefill_tc8 = false;
@@ -611,12 +612,25 @@ int launch_pack_rows(nvmai_cuda_moe *h, const void *src, bool src_f32, __half *d
 // The whole block for `tokens` rows: router, grouping, gate/up GEMMs + activation,
 // down GEMMs, rank-ordered weighted sum with the shared expert and the two-step
 // residual of the prefill path (RealForwardRunner.swift:3244-3591).
+// The same launches serve the batched decode entry points from a few dozen rows on, where the tensor-core tiles
+// beat the per-row tiles of the decode kernels:
+//   decode_order  the block's result takes the decode path's rounding (one rounding of h1 + sum, one residual add)
+//   routed_only   routing given by the caller (out_idx / out_w are inputs), no router, no shared expert
+//   partial_y     fp32 rows that receive sum_r w_r * down_r instead of y / hidden (expert-parallel share, replay)
+struct PrefillMode {
+    bool decode_order = false;
+    bool routed_only = false;
+    float *partial_y = nullptr;
+    const __half *hidden_delta = nullptr;
+};
+
 int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint32_t tokens, void *hidden, void *y,
-                       uint32_t *out_idx, __half *out_w, cudaStream_t st) {
-    const auto &c = h->cfg;
+                       uint32_t *out_idx, __half *out_w, cudaStream_t st, const PrefillMode mode = PrefillMode{}) {
     const LayerViews &lv = h->layers[layer];
     int rc = ensure_prefill_scratch(h);
     if (rc) return rc;
+    nvmai_cuda_moe_config c = h->cfg;
+    if (mode.routed_only) c.shared_f = 0;
     uint32_t *idx = out_idx ? out_idx : h->idx;
     __half *w = out_w ? out_w : h->w;
     const bool wide = c.out_dtype == NVMAI_OUT_FP32;
@@ -626,7 +640,9 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     // affine routers keep the exact code-times-activation kernel.
     const bool gemm_router = c.router_kind == NVMAI_ROUTER_DENSE_F16 && lv.w.effective_scale == nullptr &&
                              c.num_experts % (2 * kPfTileM) == 0;
-    if (gemm_router) {
+    if (mode.routed_only) {
+        // nothing to route
+    } else if (gemm_router) {
         PrefillGemmArgs ra{};
         PrefillGemmParams &r = ra.p;
         r.shared_from = 0;
@@ -706,10 +722,22 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     pc.inv = h->inv; pc.routing_w = w;
     pc.gate_val = (c.shared_f && c.shared_gate_kind != NVMAI_GATE_NONE) ? h->gate_val : nullptr;
     pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
-    pc.partial_y = nullptr; pc.prefill = 1;
+    pc.partial_y = mode.partial_y; pc.prefill = mode.decode_order ? 0 : 1;
+    pc.hidden_delta = mode.hidden_delta;
     return dispatch_out(c.out_dtype, [&](auto O) {
         return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
     });
+}
+
+// A batched decode call can take the tensor-core kernels when the fp16 operand holds the centred weight exactly
+// (4-bit codes, bf16 scales), the tile shapes divide the layer and every expert is local.
+bool tc_batch_ok(const nvmai_cuda_moe *h, uint32_t tokens, bool with_shared) {
+    const auto &c = h->cfg;
+    if (tokens < h->tc_min_tokens || h->expert_map != nullptr) return false;
+    if (c.meta_dtype != NVMAI_META_BF16 || c.routed_bits != 4 || c.top_k > (uint32_t)kMaxTopK) return false;
+    if (c.f % kPfTileM != 0 || c.d % (2 * kPfTileM) != 0) return false;
+    if (with_shared && c.shared_f != 0 && (c.shared_bits != 4 || c.shared_f % kPfTileM != 0)) return false;
+    return true;
 }
 
 }  // namespace
@@ -777,6 +805,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
     if (const char *env = std::getenv("NVMAI_CUDA_L2_PREFETCH")) h->l2_prefetch = env[0] == '1';
     if (const char *env = std::getenv("NVMAI_CUDA_PREFILL_TC8")) h->prefill_tc8 = env[0] == '1';
     if (const char *env = std::getenv("NVMAI_CUDA_GROUPED_MIN")) h->grouped_min_tokens = (uint32_t)std::max(1, std::atoi(env));
+    if (const char *env = std::getenv("NVMAI_CUDA_TC_MIN")) h->tc_min_tokens = (uint32_t)std::max(1, std::atoi(env));
     const size_t T = c.max_tokens;
     auto alloc = [&](auto **ptr, size_t bytes) -> bool {
         cudaError_t e = cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16);
@@ -929,6 +958,12 @@ int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x
     if (!x_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
     if (h->cfg.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
+    if (tc_batch_ok(h, tokens, true)) {
+        PrefillMode mode;
+        mode.decode_order = true;
+        return layer_prefill_impl(h, layer, static_cast<const __half *>(x_f16), tokens, hidden_inout, h2_out, out_idx,
+                                  static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream), mode);
+    }
     const XSource xsrc{static_cast<const __half *>(x_f16), h->cfg.d, nullptr, nullptr};
     return layer_decode_impl(h, layer, xsrc, static_cast<const __half *>(x_f16), tokens, hidden_inout, h2_out,
                              out_idx, static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
@@ -1033,6 +1068,13 @@ int nvmai_cuda_moe_routed_partial(nvmai_cuda_moe *h, uint32_t layer, const void 
     if (rc) return rc;
     if (!x_f16 || !idx || !w_f16 || !share_f32 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
+    if (tc_batch_ok(h, tokens, false)) {
+        PrefillMode mode;
+        mode.decode_order = true; mode.routed_only = true; mode.partial_y = share_f32;
+        return layer_prefill_impl(h, layer, static_cast<const __half *>(x_f16), tokens, nullptr, nullptr,
+                                  const_cast<uint32_t *>(idx), static_cast<__half *>(const_cast<void *>(w_f16)),
+                                  static_cast<cudaStream_t>(stream), mode);
+    }
     return grouped_tail(h, h->layers[layer], static_cast<const __half *>(x_f16), tokens, idx,
                         static_cast<const __half *>(w_f16), nullptr, nullptr, static_cast<cudaStream_t>(stream),
                         share_f32);

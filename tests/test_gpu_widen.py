@@ -184,11 +184,13 @@ def test_prenorm_rejects_bad_arguments():
     assert ei.value.code == _lib.ERANGE
 
 
-def test_route_trace_replay_matches_cpu_path():
+@pytest.mark.parametrize("rows", [12, 48])
+def test_route_trace_replay_matches_cpu_path(rows):
     """a recorded routing (`position layer e0..e7`) drives the routed kernels through `routed_partial`; every row's
-    share equals the reference CPU path's accumulation over the recorded experts with the replay's weights"""
+    share equals the reference CPU path's accumulation over the recorded experts with the replay's weights.
+    12 rows run the per-row tiles, 48 rows the tensor-core tiles"""
     from nvmai_b200 import route_trace as rt
-    rows, e = 12, 32
+    e = 32
     host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, rows, seed=341, d=256, f=128, e=e)
     moe = MoE(cfg)
     dl = gu.DeviceLayer(host)
@@ -209,7 +211,50 @@ def test_route_trace_replay_matches_cpu_path():
         want = np.zeros(cfg.d, dtype=np.float32)
         x32 = orc.f16_bits_to_f32(x[t])
         for k in range(8):
-            blob = blobs[int(ids[t, k]) * host["stride"]:]
+            blob = blobs[int(ids[t, k])]
             lib.orc_cpu_expert_accumulate(orc.ptr(blob), orc.ptr(off), 4, orc.META_BF16, orc.ACT_SILU, orc.ptr(x32),
                                           cfg.d, cfg.f, float(np.float16(1.0 / 8)), orc.ptr(scratch), orc.ptr(want), fn)
         assert orc.rel_error(got[t], want) < FFN_TOL, f"row {t}"
+
+
+@pytest.mark.parametrize("out_dtype", [fmt.OUT_FP32, fmt.OUT_FP16])
+def test_large_decode_batch_on_tensor_cores_keeps_decode_semantics(out_dtype, monkeypatch):
+    """from 32 rows on a 4-bit batched decode call runs the grouped GEMMs of the prefill path; indices stay exact,
+    every row stays within the bars of the decode oracle, the residual add keeps the decode order (one add of the
+    rounded block output), and the result agrees with the per-row kernels' result for the same call"""
+    tokens = 40
+    kind = fmt.ROUTER_AFFINE8 if out_dtype == fmt.OUT_FP16 else fmt.ROUTER_DENSE_F16
+    host, cfg = _case(4, fmt.META_BF16, out_dtype, tokens, seed=351, router_kind=kind, gate_kind=kind)
+    f16 = out_dtype == fmt.OUT_FP16
+    esz = "f16" if f16 else "f32"
+    x = synthetic.hidden_rows(352, tokens, cfg.d)
+    hid0 = synthetic.hidden_rows(353, tokens, cfg.d)
+    hid_host = hid0 if f16 else orc.f16_bits_to_f32(hid0).astype(np.float32)
+    dl = gu.DeviceLayer(host)
+
+    def run():
+        moe = MoE(cfg)
+        dl.register(moe, 0)
+        hid = gu.to_dev(hid_host.copy())
+        h2 = gu.dev_empty(tokens * cfg.d, esz)
+        idx = gu.dev_empty(tokens * 8, "u32")
+        moe.layer_decode(0, gu.to_dev(x), tokens, hidden=hid, h2_out=h2, out_idx=idx)
+        sync()
+        return _out(h2, cfg, tokens), _out(hid, cfg, tokens), gu.from_dev(idx, np.uint32).reshape(tokens, 8)
+
+    got, got_hid, got_idx = run()
+    monkeypatch.setenv("NVMAI_CUDA_TC_MIN", "100000")       # the same call on the per-row kernels
+    per_row, _, per_row_idx = run()
+    assert np.array_equal(got_idx, per_row_idx)
+    L, keep = gu.oracle_layer(host, cfg)
+    for t in range(tokens):
+        o_idx, o_w, o_h2, margin, cpu = gu.oracle_decode(L, cfg, np.ascontiguousarray(x[t]))
+        assert margin > 1e-5
+        assert got_idx[t].tolist() == o_idx.tolist()
+        assert orc.rel_error(got[t], cpu) < FFN_TOL, "vs the reference CPU path"
+        own = orc.rel_error(o_h2, cpu)
+        assert orc.rel_error(got[t], o_h2) < max(2e-3 if f16 else 1e-3, own + 2e-4), "vs the shader-semantics oracle"
+        assert orc.rel_error(got[t], per_row[t]) < (2e-3 if f16 else 1e-3), "vs the per-row kernels"
+        base = orc.f16_bits_to_f32(hid0[t])
+        want = (base + got[t]).astype(np.float16).astype(np.float32) if f16 else base + got[t]
+        assert np.array_equal(got_hid[t], want)
