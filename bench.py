@@ -628,6 +628,42 @@ def run_batch_layer(args) -> None:
     print(json.dumps(rec), flush=True)
 
 
+def run_gturbo_load(args) -> None:
+    """One production-size layer file (256 blobs, 453 MB at 4 bits) of a synthetic `.gturbo` artifact read into HBM
+    by `nvmai_cuda_moe_read_file_to_device`; the file sits in the page cache after it is written, so the figure is the
+    reader's pipeline (pread -> pinned buffer -> async copy), not the disk."""
+    import tempfile
+    import time
+    import torch
+    from nvmai_b200 import gturbo
+    from nvmai_b200 import format as fmt
+    torch.cuda.set_device(0)
+    _, blob = fmt.expert_offsets(D, F, args.bits)
+    rng = np.random.default_rng(5)
+    blobs = rng.integers(0, 256, size=(E, blob), dtype=np.uint8)
+    with tempfile.TemporaryDirectory() as root:
+        gturbo.write_packed_experts(root, [blobs], d=D, f=F, bits=args.bits)
+        g = gturbo.GTurboExperts(root)
+        buf = torch.empty(g.layer_bytes, dtype=torch.uint8, device="cuda")
+        t0 = time.perf_counter()
+        g.verify_layer(0)
+        sha_s = time.perf_counter() - t0
+        times = []
+        for i in range(max(args.warmup, 1) + args.steps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            g.load_layer(0, buf)            # returns after the last copy has completed
+            times.append(time.perf_counter() - t0)
+        ok = bool(np.array_equal(buf.cpu().numpy().reshape(E, g.layout.expert_stride)[:, :blob], blobs))
+    ms = float(np.median(times[max(args.warmup, 1):])) * 1e3
+    rec = {"metric": "gturbo_layer_load_gb_per_s", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+           "higher_is_better": True, "vs_baseline": None, "data": "synthetic", "dtype": "u8",
+           "value": g.layer_bytes / (ms * 1e-3) / 1e9, "ms_per_step": ms, "gpu_launches": 0,
+           "config": {"workload": "one packed_experts layer file (%d blobs, %d bytes) from the page cache into HBM"
+                      % (E, g.layer_bytes), "bits": args.bits, "sha256_seconds": round(sha_s, 3), "bytes_match": ok}}
+    print(json.dumps(rec), flush=True)
+
+
 def run_prefill(args) -> None:
     """configs[2]: one layer, `--tokens` rows (4096 by default), 4-bit: router, pair grouping, the grouped
     gate/up and down GEMMs on the tensor cores, ordered combine.  Rotates over `--layers` independently seeded
@@ -762,6 +798,8 @@ def main() -> None:
                     help="measure configs[1] (one layer, --tokens independent rows, batched decode kernels) or, with "
                          "--zipf, configs[4] instead of the decode stack")
     ap.add_argument("--zipf", type=float, default=0.0, help="with --batch-layer: Zipf exponent of the expert popularity")
+    ap.add_argument("--gturbo-load", action="store_true",
+                    help="time the read of one synthetic packed_experts layer file into device memory")
     ap.add_argument("--route-trace", default="",
                     help="with --batch-layer: replay the routing of a trace file in the NVMAI_ROUTE_TRACE line format "
                          "(`position layer e0..e7`), or `synthetic[:reuse]`")
@@ -780,6 +818,9 @@ def main() -> None:
     ap.add_argument("--deadline", type=float, default=600.0,
                     help="multi-GPU runs: give up (exit 2) after this many seconds instead of waiting on a stuck collective")
     args = ap.parse_args()
+    if args.gturbo_load:
+        run_gturbo_load(args)
+        return
     if args.batch_layer:
         run_batch_layer(args)
     elif args.prefill:

@@ -44,6 +44,7 @@ extern "C" {
 #define NVMAI_CUDA_ECUDA 1001   /* CUDA runtime error; see nvmai_cuda_moe_last_cuda_error */
 #define NVMAI_CUDA_ETIMEOUT 1002 /* a bounded device-side wait expired */
 #define NVMAI_CUDA_ENCCL 1003
+#define NVMAI_CUDA_EIO 5        /* a weight file could not be opened or is shorter than the requested range */
 
 /* ---- enums ---- */
 #define NVMAI_META_BF16 0u   /* the reference's format (RepackPlanner.swift:302-305) */
@@ -215,6 +216,17 @@ NVMAI_API int nvmai_cuda_moe_layer_decode_prenorm(nvmai_cuda_moe *h, uint32_t la
  * expert_counts[e] = its number of pairs.  idx / w as written by the router. */
 NVMAI_API int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const void *w_f16, uint32_t tokens,
                                void *sorted_pairs, uint32_t *expert_offsets, uint32_t *expert_counts, void *stream);
+
+/* Reads `bytes` bytes at `file_offset` of a weight file (a `packed_experts/layer_NN.bin`
+ * of a .gturbo artifact, GTurboPackedExpertsLayoutV1.swift:185-196) into device memory:
+ * positioned reads into two pinned staging buffers that alternate with asynchronous
+ * copies on `stream`, so the file read of one piece overlaps the copy of the one before.
+ * Replaces the slot-cache reader of the reference (expert_io.c, ExpertStreamer) for a
+ * host that keeps every expert resident.  Returns after the last copy is enqueued and
+ * the staging buffers are released (the call synchronises the stream once at its end).
+ * NVMAI_CUDA_EIO: cannot open, or the file ends before file_offset + bytes. */
+NVMAI_API int nvmai_cuda_moe_read_file_to_device(const char *path, uint64_t file_offset, uint64_t bytes,
+                                                 void *device_dst, void *stream);
 
 /* ---- expert parallelism (no counterpart in the reference, which runs on one GPU) ----
  * A rank holds n_local of the layer's expert blobs, contiguous at `experts` in

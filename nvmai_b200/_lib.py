@@ -12,7 +12,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libnvmai_cuda_moe.so"
 
-OK, EINVAL, ERANGE, ENOMEM, ECUDA, ETIMEOUT, ENCCL = 0, 22, 34, 12, 1001, 1002, 1003
+OK, EINVAL, ERANGE, ENOMEM, ECUDA, ETIMEOUT, ENCCL, EIO = 0, 22, 34, 12, 1001, 1002, 1003, 5
 
 
 class Config(C.Structure):
@@ -81,6 +81,7 @@ PROTOTYPES = {
     "nvmai_cuda_moe_synchronize": (C.c_int, [vp, vp]),
     "nvmai_cuda_moe_last_cuda_error": (C.c_int, [vp]),
     "nvmai_cuda_moe_error_string": (C.c_char_p, [C.c_int]),
+    "nvmai_cuda_moe_read_file_to_device": (C.c_int, [C.c_char_p, C.c_uint64, C.c_uint64, vp, vp]),
     "nvmai_cuda_moe_launch_count": (u64, []),
 }
 

@@ -5,6 +5,9 @@
 #include "../../include/nvmai_cuda_moe.h"
 
 #include <cuda_runtime.h>
+#include <fcntl.h>
+#include <unistd.h>
+#include <cerrno>
 
 #include <algorithm>
 #include <atomic>
@@ -13,6 +16,7 @@
 #include <cstring>
 #include <map>
 #include <new>
+#include <thread>
 #include <tuple>
 #include <vector>
 
@@ -1540,10 +1544,68 @@ const char *nvmai_cuda_moe_error_string(int code) {
         case NVMAI_CUDA_ECUDA: return "CUDA runtime error";
         case NVMAI_CUDA_ETIMEOUT: return "bounded device-side wait expired";
         case NVMAI_CUDA_ENCCL: return "NCCL error";
+        case NVMAI_CUDA_EIO: return "weight file cannot be opened or is too short";
         default: return "unknown error";
     }
 }
 
 uint64_t nvmai_cuda_moe_launch_count(void) { return g_launches.load(); }
+
+int nvmai_cuda_moe_read_file_to_device(const char *path, uint64_t file_offset, uint64_t bytes, void *device_dst,
+                                       void *stream) {
+    if (!path || (!device_dst && bytes)) return NVMAI_CUDA_EINVAL;
+    if (bytes == 0) return NVMAI_CUDA_OK;
+    const int fd = ::open(path, O_RDONLY);
+    if (fd < 0) return NVMAI_CUDA_EIO;
+    constexpr size_t kPiece = 16u << 20;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned char *stage[2] = {nullptr, nullptr};
+    cudaEvent_t copied[2] = {nullptr, nullptr};
+    int rc = NVMAI_CUDA_OK;
+    for (int i = 0; i < 2 && rc == NVMAI_CUDA_OK; ++i) {
+        if (cudaMallocHost(reinterpret_cast<void **>(&stage[i]), kPiece) != cudaSuccess) rc = NVMAI_CUDA_ENOMEM;
+        else if (cudaEventCreateWithFlags(&copied[i], cudaEventDisableTiming) != cudaSuccess) rc = NVMAI_CUDA_ECUDA;
+    }
+    uint64_t done = 0;
+    for (int piece = 0; rc == NVMAI_CUDA_OK && done < bytes; ++piece) {
+        const int b = piece & 1;
+        const size_t n = (size_t)std::min<uint64_t>(kPiece, bytes - done);
+        if (piece >= 2 && cudaEventSynchronize(copied[b]) != cudaSuccess) { rc = NVMAI_CUDA_ECUDA; break; }
+        // the piece is read by a few threads side by side: one positioned read runs at memcpy speed out of the page
+        // cache, well below what the copy engine takes
+        constexpr int kReaders = 4;
+        const size_t share = ((n + kReaders - 1) / kReaders + 4095) & ~(size_t)4095;
+        std::atomic<int> short_reads{0};
+        auto read_range = [&](size_t lo, size_t hi) {
+            size_t got = lo;
+            while (got < hi) {      // a positioned read may return less than asked
+                const ssize_t r = ::pread(fd, stage[b] + got, hi - got, (off_t)(file_offset + done + got));
+                if (r < 0 && errno == EINTR) continue;
+                if (r <= 0) break;
+                got += (size_t)r;
+            }
+            if (got != hi) short_reads.fetch_add(1);
+        };
+        std::thread readers[kReaders - 1];
+        int started = 0;
+        for (int t = 1; t < kReaders; ++t) {
+            const size_t lo = std::min(n, (size_t)t * share), hi = std::min(n, lo + share);
+            if (lo < hi) readers[started++] = std::thread(read_range, lo, hi);
+        }
+        read_range(0, std::min(n, share));
+        for (int t = 0; t < started; ++t) readers[t].join();
+        if (short_reads.load() != 0) { rc = NVMAI_CUDA_EIO; break; }
+        if (cudaMemcpyAsync(static_cast<unsigned char *>(device_dst) + done, stage[b], n, cudaMemcpyHostToDevice, st) !=
+                cudaSuccess || cudaEventRecord(copied[b], st) != cudaSuccess) { rc = NVMAI_CUDA_ECUDA; break; }
+        done += n;
+    }
+    if (cudaStreamSynchronize(st) != cudaSuccess && rc == NVMAI_CUDA_OK) rc = NVMAI_CUDA_ECUDA;
+    for (int i = 0; i < 2; ++i) {
+        if (copied[i]) cudaEventDestroy(copied[i]);
+        if (stage[i]) cudaFreeHost(stage[i]);
+    }
+    ::close(fd);
+    return rc;
+}
 
 }  // extern "C"
