@@ -4,6 +4,7 @@
 // (oracle/nvmai_oracle.c, linked as the checker).  Exit code 0 = every check passed.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -26,6 +27,7 @@ void orc_gpu_phase1(const uint8_t *const *blobs, const uint32_t off[9], int bits
 void orc_gpu_phase2(const uint8_t *const *blobs, const uint32_t off[9], int bits, int meta, const void *acts,
                     const uint16_t *w_f16, const void *residual, size_t D, size_t F, size_t top_k, int out_dtype, void *y);
 float orc_rel_error(const float *actual, const float *reference, size_t n);
+void orc_gpu_rmsnorm_bf16w(const void *x, const uint16_t *w_bf16, uint16_t *out_f16, size_t D, float eps, int out_dtype);
 }
 
 namespace {
@@ -63,7 +65,7 @@ int main() {
     nvmai_cuda_moe_config cfg{};
     cfg.d = D; cfg.f = F; cfg.shared_f = 0; cfg.num_experts = E; cfg.top_k = K; cfg.routed_bits = BITS; cfg.shared_bits = BITS;
     cfg.router_kind = NVMAI_ROUTER_DENSE_F16; cfg.shared_gate_kind = NVMAI_GATE_NONE; cfg.meta_dtype = NVMAI_META_BF16;
-    cfg.activation = NVMAI_ACT_SILU; cfg.out_dtype = NVMAI_OUT_FP32; cfg.max_tokens = 1; cfg.num_layers = 1;
+    cfg.activation = NVMAI_ACT_SILU; cfg.out_dtype = NVMAI_OUT_FP32; cfg.max_tokens = 2; cfg.num_layers = 1;
 
     // a shape the Swift wrapper would trap on comes back as an error code (MoE.swift:163-165)
     {
@@ -148,6 +150,60 @@ int main() {
     std::vector<float> h2(D);
     CUDA_OK(cudaMemcpy(h2.data(), d_h2, D * 4, cudaMemcpyDeviceToHost));
     expect(orc_rel_error(h2.data(), o_y.data(), D) < 1e-3f, "encodeLayerDecode: same output as the two phases");
+
+    // residual add + rmsnorm_bf16w + block in one call (RealForwardRunner.swift:1900-1909): the rows it hands to the
+    // block against the oracle's norm, and the block output equal to the plain entry point run on those rows
+    {
+        std::vector<float> hidden(D), delta32(D), mid(D);
+        std::vector<uint16_t> delta(D), nw(D), rx(D), o_rx(D);
+        for (uint32_t i = 0; i < D; ++i) {
+            hidden[i] = 2.0f * rng.normal();
+            delta[i] = orc_f32_to_f16(0.5f * rng.normal());
+            nw[i] = orc_f32_to_bf16(rng.uniform(0.5f, 1.5f));
+            mid[i] = hidden[i] + orc_f16_to_f32(delta[i]);
+        }
+        float *d_hidden = upload(hidden);
+        uint16_t *d_delta = upload(delta), *d_nw = upload(nw), *d_rx;
+        CUDA_OK(cudaMalloc(&d_rx, D * 2));
+        moe.encodeLayerDecodePreNorm(st, 0, d_hidden, d_delta, d_nw, 1e-6f, 1, d_h2, d_rx);
+        moe.waitUntilCompleted(st);
+        std::vector<float> h2a(D), h2b(D), hid_out(D);
+        CUDA_OK(cudaMemcpy(rx.data(), d_rx, D * 2, cudaMemcpyDeviceToHost));
+        CUDA_OK(cudaMemcpy(h2a.data(), d_h2, D * 4, cudaMemcpyDeviceToHost));
+        CUDA_OK(cudaMemcpy(hid_out.data(), d_hidden, D * 4, cudaMemcpyDeviceToHost));
+        orc_gpu_rmsnorm_bf16w(mid.data(), nw.data(), o_rx.data(), D, 1e-6f, 1);
+        int worst = 0;
+        for (uint32_t i = 0; i < D; ++i) worst = std::max(worst, std::abs((int)rx[i] - (int)o_rx[i]));
+        expect(worst <= 1, "encodeLayerDecodePreNorm: normalised rows within one fp16 ulp of the oracle");
+        moe.encodeLayerDecode(st, 0, d_rx, 1, nullptr, d_h2);
+        moe.waitUntilCompleted(st);
+        CUDA_OK(cudaMemcpy(h2b.data(), d_h2, D * 4, cudaMemcpyDeviceToHost));
+        expect(std::memcmp(h2a.data(), h2b.data(), D * 4) == 0, "encodeLayerDecodePreNorm: block output equals the plain entry point's");
+        bool tail = true;
+        for (uint32_t i = 0; i < D; ++i) tail = tail && hid_out[i] == mid[i] + h2a[i];
+        expect(tail, "encodeLayerDecodePreNorm: hidden = (hidden + delta) + h2");
+    }
+
+    // width-2 verification: both rows equal the single-row entry point, bit for bit
+    {
+        std::vector<uint16_t> x2(2 * D);
+        for (uint32_t i = 0; i < D; ++i) { x2[i] = x[i]; x2[D + i] = orc_f32_to_f16(orc_f16_to_f32(x[i]) + 0.05f * rng.normal()); }
+        uint16_t *d_x2 = upload(x2);
+        void *d_pair;
+        CUDA_OK(cudaMalloc(&d_pair, 2 * D * 4));
+        moe.encodeRoutedMoEVerifyPair(st, 0, d_x2, nullptr, d_pair);
+        moe.waitUntilCompleted(st);
+        std::vector<float> pair(2 * D), one(D);
+        CUDA_OK(cudaMemcpy(pair.data(), d_pair, 2 * D * 4, cudaMemcpyDeviceToHost));
+        bool same = true;
+        for (int r = 0; r < 2; ++r) {
+            moe.encodeLayerDecode(st, 0, d_x2 + r * D, 1, nullptr, d_h2);
+            moe.waitUntilCompleted(st);
+            CUDA_OK(cudaMemcpy(one.data(), d_h2, D * 4, cudaMemcpyDeviceToHost));
+            same = same && std::memcmp(one.data(), pair.data() + r * D, D * 4) == 0;
+        }
+        expect(same, "encodeRoutedMoEVerifyPair: each row equals the single-row block");
+    }
 
     std::printf("%s\n", failures ? "FAILED" : "PASSED");
     return failures ? 1 : 0;
