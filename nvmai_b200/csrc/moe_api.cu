@@ -735,9 +735,15 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
 
 // A batched decode call can take the tensor-core kernels when the fp16 operand holds the centred weight exactly
 // (4-bit codes, bf16 scales), the tile shapes divide the layer and every expert is local.
-bool tc_batch_ok(const nvmai_cuda_moe *h, uint32_t tokens, bool with_shared) {
+bool tc_batch_ok(const nvmai_cuda_moe *h, uint32_t tokens, bool with_shared, cudaStream_t st) {
     const auto &c = h->cfg;
     if (tokens < h->tc_min_tokens || h->expert_map != nullptr) return false;
+    if (h->pf_acts16 == nullptr && st != nullptr) {
+        // the first such call allocates the packed-row scratch, which a stream under capture does not allow:
+        // a call that is being captured before any eager one stays on the per-row kernels
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return false;
+    }
     if (c.meta_dtype != NVMAI_META_BF16 || c.routed_bits != 4 || c.top_k > (uint32_t)kMaxTopK) return false;
     if (c.f % kPfTileM != 0 || c.d % (2 * kPfTileM) != 0) return false;
     if (with_shared && c.shared_f != 0 && (c.shared_bits != 4 || c.shared_f % kPfTileM != 0)) return false;
@@ -962,7 +968,7 @@ int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x
     if (!x_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
     if (h->cfg.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
-    if (tc_batch_ok(h, tokens, true)) {
+    if (tc_batch_ok(h, tokens, true, static_cast<cudaStream_t>(stream))) {
         PrefillMode mode;
         mode.decode_order = true;
         return layer_prefill_impl(h, layer, static_cast<const __half *>(x_f16), tokens, hidden_inout, h2_out, out_idx,
@@ -1072,7 +1078,7 @@ int nvmai_cuda_moe_routed_partial(nvmai_cuda_moe *h, uint32_t layer, const void 
     if (rc) return rc;
     if (!x_f16 || !idx || !w_f16 || !share_f32 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > h->cfg.max_tokens) return NVMAI_CUDA_ERANGE;
-    if (tc_batch_ok(h, tokens, false)) {
+    if (tc_batch_ok(h, tokens, false, static_cast<cudaStream_t>(stream))) {
         PrefillMode mode;
         mode.decode_order = true; mode.routed_only = true; mode.partial_y = share_f32;
         return layer_prefill_impl(h, layer, static_cast<const __half *>(x_f16), tokens, nullptr, nullptr,
