@@ -296,3 +296,39 @@ def test_gturbo_layers_load_into_hbm_in_logical_order(tmp_path):
     assert lib.nvmai_cuda_moe_read_file_to_device(path + b".missing", 0, 64, buf.data_ptr(), None) == _lib.EIO
     assert lib.nvmai_cuda_moe_read_file_to_device(None, 0, 64, buf.data_ptr(), None) == _lib.EINVAL
     assert lib.nvmai_cuda_moe_read_file_to_device(path, 0, 0, None, None) == _lib.OK
+
+
+def test_large_decode_batch_inside_a_stream_capture():
+    """a 40-row call captured into a CUDA graph: before any eager call the handle has no packed-row scratch and may
+    not allocate under capture, so the captured call uses the per-row kernels; after one eager call the capture takes
+    the tensor-core launches and replays the eager result bit for bit"""
+    torch = gu.torch_cuda()
+    tokens = 40
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, tokens, seed=371, d=256, f=128, e=32)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    x = gu.to_dev(synthetic.hidden_rows(372, tokens, cfg.d))
+    y = gu.dev_empty(tokens * cfg.d, "f32")
+    stream = torch.cuda.Stream()
+
+    def capture_and_replay():
+        y.zero_()
+        graph = torch.cuda.CUDAGraph()
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            moe.layer_decode(0, x, tokens, h2_out=y, stream=torch.cuda.current_stream())
+        graph.replay()
+        sync()
+        return y.cpu().numpy().copy()
+
+    first = capture_and_replay()                 # per-row kernels
+    moe.layer_decode(0, x, tokens, h2_out=y, stream=stream)
+    sync()
+    eager = y.cpu().numpy().copy()               # tensor-core launches, scratch now allocated
+    second = capture_and_replay()
+    assert np.array_equal(second.view(np.uint32), eager.view(np.uint32))
+    assert np.all(np.isfinite(first))
+    for t in range(tokens):
+        a, b = first.reshape(tokens, -1)[t], eager.reshape(tokens, -1)[t]
+        assert orc.rel_error(a, b) < 1e-3
