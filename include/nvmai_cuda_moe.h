@@ -150,6 +150,13 @@ NVMAI_API int nvmai_cuda_moe_router_noalloc(const nvmai_cuda_moe_config *config,
                                   uint32_t x_stride, uint32_t tokens, uint32_t *out_idx, void *out_w_f16,
                                   void *stream);
 
+/* Completion check for nvmai_cuda_moe_router_noalloc (there is no handle whose synchronize
+ * could report it; no counterpart in the reference): waits for `stream`, then returns
+ * NVMAI_CUDA_ETIMEOUT if the last allocation-free router call on the current device gave
+ * up a bounded device-side wait (its out_idx / out_w are then unwritten), else 0.  Copies
+ * four bytes back; allocates nothing. */
+NVMAI_API int nvmai_cuda_moe_router_noalloc_status(void *stream);
+
 /* `SharedExpertRuntime.encode` + scalar gate GEMV + `sigmoid_scalar_mul_fp16`
  * (RealForwardRunner.swift:3866-3905): h1 = sigmoid(g.x) * down(act(gate.x)*up.x).
  * h1 is out_dtype[tokens][d]. */
@@ -307,6 +314,32 @@ NVMAI_API int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_ow
  * y_last out_dtype[tokens][d] = last layer's block output. */
 NVMAI_API int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t tokens, void *y_last,
                                 void *stream);
+
+/* How a single-token nvmai_cuda_moe_stack_decode step runs (no counterpart in the
+ * reference, whose command buffers are its only launch unit):
+ *   0  (default) one resident kernel for the whole step when the shape allows it
+ *      (top_k <= 8, shared_bits == routed_bits, d <= 16 * SM count, f and shared_f <= 1024,
+ *      no expert map, stream not under capture), the staged kernels otherwise;
+ *   1  always the staged kernels (three launches per layer, replayed as a CUDA graph);
+ *   2  the resident kernel, or NVMAI_CUDA_EINVAL when the shape does not allow it.
+ * Both paths give bit-identical results.  NVMAI_CUDA_DECODE_MODE in the environment sets
+ * the initial value. */
+NVMAI_API int nvmai_cuda_moe_set_decode_mode(nvmai_cuda_moe *h, int mode);
+
+/* The experts every layer of the last resident-kernel step selected, u32 [layers][top_k] in
+ * rank order: the data of the reference's NVMAI_ROUTE_TRACE lines
+ * (RealForwardRunner.swift:1208-1237).  Synchronises the device. */
+NVMAI_API int nvmai_cuda_moe_read_route_log(nvmai_cuda_moe *h, uint32_t *out_host, uint32_t layers);
+
+/* Test hook: the longest any device-side wait of this library lasts, in nanoseconds
+ * (0 restores the default of one second).  Process-wide, per device. */
+NVMAI_API int nvmai_cuda_moe_debug_set_wait_limit(uint64_t nanoseconds);
+
+/* Test hook for the failure path of the resident kernel: block `block` keeps its phase-1
+ * results (router logits, shared-expert activations or the gate value) to itself, so that
+ * every other block's bounded wait for them runs out and the step ends with
+ * NVMAI_CUDA_ETIMEOUT at the next synchronize.  Nothing faults; 0xFFFFFFFF switches it off. */
+NVMAI_API int nvmai_cuda_moe_debug_mute_block(nvmai_cuda_moe *h, uint32_t block);
 
 /* Host-buffer convenience of the same call (copies x in, y out on `stream`, and
  * synchronises): the end-to-end path a host runtime without device buffers uses. */

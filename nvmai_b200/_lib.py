@@ -50,6 +50,7 @@ PROTOTYPES = {
     "nvmai_cuda_moe_register_layer": (C.c_int, [vp, u32, C.POINTER(Layer)]),
     "nvmai_cuda_moe_router": (C.c_int, [vp, u32, vp, u32, u32, vp, vp, vp]),
     "nvmai_cuda_moe_router_noalloc": (C.c_int, [C.POINTER(Config), C.POINTER(AffineTensor), vp, vp, vp, u32, u32, vp, vp, vp]),
+    "nvmai_cuda_moe_router_noalloc_status": (C.c_int, [vp]),
     "nvmai_cuda_moe_shared_expert": (C.c_int, [vp, u32, vp, u32, u32, vp, vp]),
     "nvmai_cuda_moe_routed_phase1": (C.c_int, [vp, C.POINTER(vp), C.POINTER(ExpertOffsets), vp, vp,
                                                 C.POINTER(u32), u32, vp]),
@@ -83,6 +84,10 @@ PROTOTYPES = {
     "nvmai_cuda_moe_error_string": (C.c_char_p, [C.c_int]),
     "nvmai_cuda_moe_read_file_to_device": (C.c_int, [C.c_char_p, C.c_uint64, C.c_uint64, vp, vp]),
     "nvmai_cuda_moe_launch_count": (u64, []),
+    "nvmai_cuda_moe_set_decode_mode": (C.c_int, [vp, C.c_int]),
+    "nvmai_cuda_moe_read_route_log": (C.c_int, [vp, vp, u32]),
+    "nvmai_cuda_moe_debug_set_wait_limit": (C.c_int, [u64]),
+    "nvmai_cuda_moe_debug_mute_block": (C.c_int, [vp, u32]),
 }
 
 

@@ -243,8 +243,9 @@ __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, in
 // the others through shared memory; ranks below K are the selection, in order.
 // Order everywhere: score descending, ties to the lower index (moe.metal:252-258).
 // `cand` holds 64 float + 64 u32 of shared memory.  Ends with the block in sync.
-__device__ __forceinline__ void topk_select_block(const float *logits, int E, int K, uint32_t *sel_idx,
-                                                  float *sel_score, float *cand) {
+// `s_in`: the logit of expert threadIdx.x, already in a register (threads >= E pass anything).
+__device__ __forceinline__ void topk_select_block_vals(float s_in, int E, int K, uint32_t *sel_idx,
+                                                       float *sel_score, float *cand) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float *cand_score = cand;
     uint32_t *cand_idx = reinterpret_cast<uint32_t *>(cand + 64);
@@ -252,7 +253,7 @@ __device__ __forceinline__ void topk_select_block(const float *logits, int E, in
     if (tid < K) { sel_idx[tid] = 0; sel_score[tid] = -INFINITY; }
     __syncthreads();
     if (tid < kMaxExperts) {
-        float s = tid < E ? __ldcg(logits + tid) : -INFINITY;
+        float s = tid < E ? s_in : -INFINITY;
         const bool valid = tid < E && s == s && s > -INFINITY;   // NaN and -inf are never selected (moe.metal:246-258)
         if (!valid) s = -INFINITY;
         int rank = 0;
@@ -281,6 +282,13 @@ __device__ __forceinline__ void topk_select_block(const float *logits, int E, in
         }
     }
     __syncthreads();
+}
+
+__device__ __forceinline__ void topk_select_block(const float *logits, int E, int K, uint32_t *sel_idx,
+                                                  float *sel_score, float *cand) {
+    const int tid = threadIdx.x;
+    const float s = (tid < kMaxExperts && tid < E) ? __ldcg(logits + tid) : -INFINITY;
+    topk_select_block_vals(s, E, K, sel_idx, sel_score, cand);
 }
 
 // Routing weights of a selection (moe.metal:271-285): softmax over the K selected

@@ -23,6 +23,7 @@
 #include "ep_comm.cuh"
 #include "grouped_decode.cuh"
 #include "misc_kernels.cuh"
+#include "persistent_decode.cuh"
 #include "prefill_gemm.cuh"
 
 using namespace nvmai;
@@ -114,6 +115,19 @@ struct nvmai_cuda_moe {
     size_t ep_buf_elems = 0;
     struct EpGraph { cudaGraphExec_t exec = nullptr; uint32_t calls = 0; };
     std::map<StackGraphKey, EpGraph> ep_graphs;
+    // one-launch decode step (persistent_decode.cuh): per-layer views on the device, the tagged exchange words,
+    // the epoch word and the experts each layer selected
+    PdLayer *pd_layers = nullptr;
+    bool pd_layers_stale = true;
+    unsigned long long *pd_xchg = nullptr;
+    unsigned int *pd_epoch = nullptr;
+    uint32_t *pd_route_log = nullptr;     // [num_layers][top_k]
+    int sm_count = 0;
+    // 0: a single-token stack step takes the one-launch kernel when the shape allows it; 1: always the staged
+    // kernels; 2: the one-launch kernel or NVMAI_CUDA_EINVAL
+    int decode_mode = 0;
+    uint32_t pd_trace_block = 0;
+    uint32_t pd_mute_block = 0xFFFFFFFFu;     // test hook, see nvmai_cuda_moe_debug_mute_block
 };
 
 namespace {
@@ -276,6 +290,7 @@ int launch_stage1(nvmai_cuda_moe *h, const LayerViews &lv, const XSource &xsrc, 
     if (grid == 0) return NVMAI_CUDA_OK;
     size_t smem = 0;
     if (with_router) smem = std::max(smem, RowsLayout(c.d, c.router_kind).total);
+    if (with_router && !defer_topk) smem = std::max(smem, kTopkSmemBytes);      // the last router block selects in place
     if (gated) smem = std::max(smem, RowsLayout(c.d, c.shared_gate_kind).total);
     if (with_shared) smem = std::max(smem, GateUpLayout(c.d, c.shared_bits).total);
     return dispatch_bits_meta(c.shared_f ? c.shared_bits : 4, c.meta_dtype, [&](auto B, auto M) {
@@ -750,6 +765,117 @@ bool tc_batch_ok(const nvmai_cuda_moe *h, uint32_t tokens, bool with_shared, cud
     return true;
 }
 
+
+// ---- one-launch decode step ----------------------------------------------------------
+struct PdPlan { uint32_t router_rows = 0, slots = 0, max_tiles = 0; size_t smem = 0; };
+
+// exchange words: logits [E] | shared activations [Fs] | gate [2] | routed activations [K][F] | block output [D]
+struct PdXchg {
+    size_t logits, sact, gate, acts, y, words;
+    explicit PdXchg(const nvmai_cuda_moe_config &c) {
+        auto up = [](size_t v) { return (v + 15) & ~(size_t)15; };      // keep every area 128-byte aligned
+        size_t o = 0;
+        logits = o; o += up(c.num_experts);
+        sact = o; o += up(c.shared_f ? c.shared_f : 1);
+        gate = o; o += 16;
+        acts = o; o += up((size_t)c.top_k * c.f);
+        y = o; o += up(c.d);
+        words = o;
+    }
+};
+
+// Can a single-token step of this handle run as one resident kernel?  (Shapes outside these limits take the
+// staged kernels.)
+bool pd_plan(const nvmai_cuda_moe *h, PdPlan &plan) {
+    const auto &c = h->cfg;
+    const uint32_t G = (uint32_t)h->sm_count;
+    if (G == 0 || h->pd_xchg == nullptr || h->expert_map != nullptr) return false;
+    if (c.top_k > (uint32_t)kMaxTopK || c.num_experts > (uint32_t)kPdThreads) return false;
+    if (c.shared_f != 0 && c.shared_bits != c.routed_bits) return false;
+    if (c.d > (uint32_t)(kPdKeep * kPdThreads) || c.d / kTileRows > G) return false;
+    if (c.f > 1024 || c.shared_f > 1024) return false;
+    const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
+    uint32_t rows = 0;
+    for (uint32_t r = 1; r <= (uint32_t)kPdWarps; ++r) {
+        const uint32_t units = c.shared_f / kTileFeatures + (c.num_experts + r - 1) / r + (gated ? 1 : 0);
+        if (units <= G) { rows = r; break; }
+    }
+    if (rows == 0) return false;
+    const uint32_t tiles_total = c.top_k * (c.f / kTileFeatures);
+    const uint32_t max_tiles = (tiles_total + G - 1) / G;
+    if (max_tiles == 0 || max_tiles > (uint32_t)kPdMaxTiles) return false;
+    uint32_t slots = std::min<uint32_t>(max_tiles, kPdMaxSlots);
+    for (; slots >= 1; --slots) {
+        const size_t smem = PdLayout(c.d, c.f, c.shared_f, c.routed_bits, c.top_k, c.router_kind,
+                                     gated ? c.shared_gate_kind : NVMAI_GATE_NONE, rows, slots, max_tiles).total;
+        if (smem <= kMaxSmem) { plan.smem = smem; break; }
+    }
+    if (slots == 0) return false;
+    plan.router_rows = rows; plan.slots = slots; plan.max_tiles = max_tiles;
+    return true;
+}
+
+int pd_launch(nvmai_cuda_moe *h, const PdPlan &plan, const __half *x0, void *y_last, cudaStream_t st) {
+    const auto &c = h->cfg;
+    if (h->pd_layers_stale) {
+        std::vector<PdLayer> host(c.num_layers);
+        for (uint32_t l = 0; l < c.num_layers; ++l) {
+            const auto &w = h->layers[l].w;
+            PdLayer &d = host[l];
+            d.experts = static_cast<const uint8_t *>(w.experts);
+            d.stride = w.expert_stride;
+            d.off = to_offsets(w.offsets);
+            d.rW = static_cast<const uint8_t *>(w.router.w);
+            d.rS = static_cast<const uint16_t *>(w.router.scales);
+            d.rB = static_cast<const uint16_t *>(w.router.biases);
+            d.eff = static_cast<const uint16_t *>(w.effective_scale);
+            d.pes = static_cast<const uint16_t *>(w.per_expert_scale);
+            d.sgate = to_mat(w.shared_gate_proj); d.sup = to_mat(w.shared_up_proj); d.sdown = to_mat(w.shared_down_proj);
+            d.gW = static_cast<const uint8_t *>(w.shared_gate.w);
+            d.gS = static_cast<const uint16_t *>(w.shared_gate.scales);
+            d.gB = static_cast<const uint16_t *>(w.shared_gate.biases);
+        }
+        int rc = record(h, cudaMemcpyAsync(h->pd_layers, host.data(), host.size() * sizeof(PdLayer), cudaMemcpyHostToDevice, st));
+        if (rc) return rc;
+        if ((rc = record(h, cudaStreamSynchronize(st)))) return rc;     // `host` goes out of scope
+        h->pd_layers_stale = false;
+    }
+    const PdXchg X(c);
+    const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
+    PdParams p{};
+    p.layers = h->pd_layers; p.num_layers = c.num_layers;
+    p.x0 = x0; p.y_last = y_last;
+    p.xlogits = h->pd_xchg + X.logits; p.xsact = h->pd_xchg + X.sact; p.xgate = h->pd_xchg + X.gate;
+    p.xacts = h->pd_xchg + X.acts; p.xy = h->pd_xchg + X.y;
+    p.epoch = h->pd_epoch; p.status = h->status; p.route_log = h->pd_route_log;
+    p.D = c.d; p.F = c.f; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation; p.shared_f = c.shared_f;
+    p.router_kind = c.router_kind; p.gate_kind = gated ? c.shared_gate_kind : NVMAI_GATE_NONE;
+    p.router_rows = plan.router_rows; p.slots = plan.slots; p.max_tiles = plan.max_tiles;
+    p.debug_mute_block = h->pd_mute_block;
+    p.trace = h->trace_on ? h->trace : nullptr;      // [layer][3 x 8 words]: the resident kernel uses them as 24 marks
+    p.trace_block = h->pd_trace_block;
+    return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            auto kern = persistent_decode_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>;
+            cudaError_t e = ensure_smem(kern, plan.smem);
+            if (e != cudaSuccess) return record(h, e);
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3((unsigned)h->sm_count);
+            cfg.blockDim = dim3(kPdThreads);
+            cfg.dynamicSmemBytes = plan.smem;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeCooperative;      // every block resident: they wait on one another
+            attr[0].val.cooperative = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            e = cudaLaunchKernelEx(&cfg, kern, p);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return record(h, e);
+        });
+    });
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------
@@ -796,7 +922,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
     // every block stages its weight tile in shared memory: the tile must fit
     {
         size_t need = GateUpLayout(c.d, c.routed_bits).total;
-        need = std::max(need, RowsLayout(c.d, c.router_kind).total);
+        need = std::max(need, std::max(RowsLayout(c.d, c.router_kind).total, kTopkSmemBytes));
         if (c.shared_f) need = std::max(need, GateUpLayout(c.d, c.shared_bits).total);
         const uint32_t warps = (c.top_k < (uint32_t)kMaxTopK ? c.top_k : (uint32_t)kMaxTopK) + (c.shared_f ? 1 : 0);
         need = std::max(need, DownLayout(c.f, c.shared_f, c.routed_bits, c.shared_bits, warps).total);
@@ -840,6 +966,20 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
         if (ok)
             ok = alloc(&h->partial, P * c.d * sizeof(float)) && alloc(&h->shared_partial, T * c.d * sizeof(float));
     }
+    if (ok) {     // the one-launch decode step: exchange words (zeroed: tag 0 is never used), epoch word, layer table
+        int dev = 0;
+        const size_t xbytes = PdXchg(c).words * sizeof(unsigned long long);
+        const unsigned int first_epoch = 1;
+        ok = cudaGetDevice(&dev) == cudaSuccess &&
+             cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+             alloc(&h->pd_xchg, xbytes) && alloc(&h->pd_epoch, 16) && alloc(&h->pd_layers, (size_t)c.num_layers * sizeof(PdLayer)) &&
+             alloc(&h->pd_route_log, (size_t)c.num_layers * c.top_k * 4) &&
+             cudaMemset(h->pd_xchg, 0, xbytes) == cudaSuccess && cudaMemset(h->pd_epoch, 0, 16) == cudaSuccess &&
+             cudaMemset(h->pd_route_log, 0, (size_t)c.num_layers * c.top_k * 4) == cudaSuccess &&
+             cudaMemcpy(h->pd_epoch, &first_epoch, sizeof(first_epoch), cudaMemcpyHostToDevice) == cudaSuccess;
+    }
+    if (const char *env = std::getenv("NVMAI_CUDA_DECODE_MODE")) h->decode_mode = std::atoi(env);
+    if (const char *env = std::getenv("NVMAI_CUDA_TRACE_BLOCK")) h->pd_trace_block = (uint32_t)std::atoi(env);
     if (!ok) {
         const bool oom = h->last_cuda_error == (int)cudaErrorMemoryAllocation;
         nvmai_cuda_moe_destroy(h);
@@ -854,7 +994,8 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     if (!h) return;
     for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
     ep_release(h);
-    cudaFree(h->pf_x); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
+    cudaFree(h->pd_layers); cudaFree(h->pd_xchg); cudaFree(h->pd_epoch); cudaFree(h->pd_route_log);
+    cudaFree(h->pf_x); cudaFree(h->pf_xn); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y);
@@ -886,6 +1027,7 @@ int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, const nvmai
     h->layers[layer].w = *wts;
     h->layers[layer].registered = true;
     h->graphs_stale = h->ep_graphs_stale = true;
+    h->pd_layers_stale = true;
     return NVMAI_CUDA_OK;
 }
 
@@ -1144,6 +1286,13 @@ int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t 
     // itself being captured, or the legacy default stream, gets plain launches.
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     if (st != nullptr) cudaStreamIsCapturing(st, &cs);
+    // One token and a shape the resident kernel covers: the whole step is one launch (no graph needed).  A stream
+    // under capture keeps the staged launches (the layer table may have to be uploaded, which a capture forbids).
+    if (h->decode_mode != 1 && tokens == 1 && cs == cudaStreamCaptureStatusNone) {
+        PdPlan plan;
+        if (pd_plan(h, plan)) return pd_launch(h, plan, static_cast<const __half *>(x0_f16), y_last, st);
+    }
+    if (h->decode_mode == 2) return NVMAI_CUDA_EINVAL;
     if (st == nullptr || cs != cudaStreamCaptureStatusNone)
         return stack_enqueue(h, static_cast<const __half *>(x0_f16), tokens, y_last, st);
     if (h->graphs_stale) {
@@ -1534,6 +1683,13 @@ int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream) {
     if (rc) return rc;
     if (st != 0) {      // a kernel gave up a bounded wait; its outputs are undefined
         cudaMemset(h->status, 0, sizeof(st));
+        // the one-launch step may have stopped half way: move its epoch past every tag it can have written
+        unsigned int epoch = 0;
+        if (h->pd_epoch && cudaMemcpy(&epoch, h->pd_epoch, sizeof(epoch), cudaMemcpyDeviceToHost) == cudaSuccess) {
+            epoch += h->cfg.num_layers + 1;
+            if (epoch == 0) epoch = 1;
+            cudaMemcpy(h->pd_epoch, &epoch, sizeof(epoch), cudaMemcpyHostToDevice);
+        }
         return NVMAI_CUDA_ETIMEOUT;
     }
     return NVMAI_CUDA_OK;
@@ -1556,6 +1712,28 @@ const char *nvmai_cuda_moe_error_string(int code) {
 }
 
 uint64_t nvmai_cuda_moe_launch_count(void) { return g_launches.load(); }
+
+int nvmai_cuda_moe_set_decode_mode(nvmai_cuda_moe *h, int mode) {
+    if (!h || mode < 0 || mode > 2) return NVMAI_CUDA_EINVAL;
+    h->decode_mode = mode;
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_read_route_log(nvmai_cuda_moe *h, uint32_t *out_host, uint32_t layers) {
+    if (!h || !out_host || layers > h->cfg.num_layers) return NVMAI_CUDA_EINVAL;
+    return record(h, cudaMemcpy(out_host, h->pd_route_log, (size_t)layers * h->cfg.top_k * 4, cudaMemcpyDeviceToHost));
+}
+
+int nvmai_cuda_moe_debug_mute_block(nvmai_cuda_moe *h, uint32_t block) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    h->pd_mute_block = block;
+    return NVMAI_CUDA_OK;
+}
+
+int nvmai_cuda_moe_debug_set_wait_limit(uint64_t nanoseconds) {
+    const unsigned long long v = nanoseconds ? nanoseconds : 1000000000ull;
+    return cudaMemcpyToSymbol(g_wait_limit_ns, &v, sizeof(v)) == cudaSuccess ? NVMAI_CUDA_OK : NVMAI_CUDA_ECUDA;
+}
 
 int nvmai_cuda_moe_read_file_to_device(const char *path, uint64_t file_offset, uint64_t bytes, void *device_dst,
                                        void *stream) {

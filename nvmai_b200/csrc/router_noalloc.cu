@@ -11,6 +11,7 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "staged_decode.cuh"
@@ -81,7 +82,8 @@ extern "C" int nvmai_cuda_moe_router_noalloc(const nvmai_cuda_moe_config *config
     if (x_stride < c.d || x_stride % 8 != 0) return NVMAI_CUDA_EINVAL;
     // the fixed scratch holds kMaxTokens rows of logits: larger batches do not fit, by construction
     if (tokens == 0 || tokens > kMaxTokens) return NVMAI_CUDA_ERANGE;
-    const size_t smem = RowsLayout(c.d, c.router_kind).total;
+    // the rows a block stages, or the top-k scratch the last block lays over them, whichever is larger
+    const size_t smem = std::max(RowsLayout(c.d, c.router_kind).total, kTopkSmemBytes);
     if (smem > 227 * 1024) return NVMAI_CUDA_ERANGE;
 
     unsigned char *scratch = nullptr;
@@ -117,4 +119,22 @@ extern "C" int nvmai_cuda_moe_router_noalloc(const nvmai_cuda_moe_config *config
     p.n_router_blocks = p.router_row_blocks * chunks;
     return c.meta_dtype == NVMAI_META_BF16 ? launch<META_BF16>(p, p.n_router_blocks, smem, st)
                                            : launch<META_FP16>(p, p.n_router_blocks, smem, st);
+}
+
+// Did a bounded wait of the allocation-free router expire?  Waits for `stream`, reads the
+// status word of the fixed array back (a 4-byte copy into a local variable: still no
+// allocation) and returns NVMAI_CUDA_ETIMEOUT when the last call on this device gave up a
+// wait, in which case that call left out_idx / out_w unwritten.
+extern "C" int nvmai_cuda_moe_router_noalloc_status(void *stream) {
+    unsigned char *scratch = nullptr;
+    int rc = scratch_for_current_device(&scratch);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int status = 0;
+    if (cudaMemcpyAsync(&status, scratch + kLogitsBytes + kCounterBytes, sizeof(status), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess) {
+        cudaGetLastError();
+        return NVMAI_CUDA_ECUDA;
+    }
+    return status != 0 ? NVMAI_CUDA_ETIMEOUT : NVMAI_CUDA_OK;
 }

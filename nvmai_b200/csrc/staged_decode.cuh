@@ -6,6 +6,9 @@
 namespace nvmai {
 
 constexpr int kRowsPerRouterBlock = 8;
+// A router block that ends with the block-wide top-k (topk_softmax_block) reuses its dynamic shared memory from
+// byte 16 on as the selection scratch: kMaxExperts logits + 32 scores + 32 indices, whatever D and E are.
+constexpr size_t kTopkSmemBytes = 16 + (kMaxExperts + 64) * sizeof(float);
 
 // ---------------------------------------------------------------------------
 // shared-memory layouts (one definition for the host's size computation and the

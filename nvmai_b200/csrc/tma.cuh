@@ -78,13 +78,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return done != 0;
 }
 
-// Bounded wait: at most kWaitTryLimit suspended waits (of the order of a second
-// in total), then the failure is recorded in *status (global) so that the host
-// reports a timeout instead of the GPU hanging.  Returns false on expiry.
-constexpr uint32_t kWaitTryLimit = 1u << 20;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Longest time any device-side wait of this library lasts (nanoseconds of the GPU's
+// global timer).  One second unless a test shortens it through
+// nvmai_cuda_moe_debug_set_wait_limit.
+static __device__ unsigned long long g_wait_limit_ns = 1000000000ull;
+
+// Bounded wait: suspended waits until the phase completes or the time limit passes;
+// then the failure is recorded in *status (global) so that the host reports a
+// timeout instead of the GPU hanging.  Returns false on expiry.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsigned int *status) {
-    for (uint32_t it = 0; it < kWaitTryLimit; ++it)
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns(), limit = g_wait_limit_ns;
+    for (;;) {
+#pragma unroll 1
+        for (int it = 0; it < 8; ++it)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > limit) break;
+    }
     if (status != nullptr) atomicExch(status, 1u);
     return false;
 }
@@ -96,11 +112,6 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 // Kernel-level timeline for the optional trace: slot[0] = time block 0 started,
 // slot[1] = latest time any block finished (GPU global timer, ns).
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ void trace_begin(unsigned long long *slot) {
     if (slot != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
         slot[0] = global_timer_ns();

@@ -240,6 +240,24 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_stack_decode_host(self._h, _ptr(x0_host), tokens, _ptr(y_last_host),
                                                          _stream(stream)), "stack_decode_host")
 
+    DECODE_AUTO, DECODE_STAGED, DECODE_RESIDENT = 0, 1, 2
+
+    def set_decode_mode(self, mode: int) -> None:
+        """How a single-token stack step runs: one resident kernel (auto / forced) or the staged launches."""
+        check(self._lib.nvmai_cuda_moe_set_decode_mode(self._h, int(mode)), "set_decode_mode")
+
+    def debug_mute_block(self, block: int = 0xFFFFFFFF) -> None:
+        """Test hook: one block of the resident kernel withholds its phase-1 results (bounded waits then expire)."""
+        check(self._lib.nvmai_cuda_moe_debug_mute_block(self._h, block & 0xFFFFFFFF), "debug_mute_block")
+
+    def read_route_log(self, layers: int | None = None):
+        """-> uint32 [layers, top_k]: the experts each layer of the last resident-kernel step selected."""
+        import numpy as np
+        n = self.config.num_layers if layers is None else layers
+        out = np.zeros((n, self.config.top_k), dtype=np.uint32)
+        check(self._lib.nvmai_cuda_moe_read_route_log(self._h, out.ctypes.data, n), "read_route_log")
+        return out
+
     def set_trace(self, enable: bool) -> None:
         check(self._lib.nvmai_cuda_moe_set_trace(self._h, int(enable)), "set_trace")
 
@@ -283,6 +301,11 @@ def router_noalloc(config: MoEConfig, router, x, out_idx, out_w, *, tokens: int 
                                                    _ptr(out_idx), _ptr(out_w), _stream(stream)), "router_noalloc")
 
 
+def router_noalloc_status(stream=None) -> None:
+    """Waits for `stream`; raises NvmaiError(ETIMEOUT) if the last allocation-free router call gave up a wait."""
+    check(_lib.lib().nvmai_cuda_moe_router_noalloc_status(_stream(stream)), "router_noalloc_status")
+
+
 class Elementwise:
     """`Elementwise` (sources/NVMAI/Kernels/Primitives/Elementwise.swift), the three MoE-side kernels."""
 
@@ -300,6 +323,11 @@ class Elementwise:
     def encode_residual_add(hidden, delta, count: int, stream=None) -> None:
         check(_lib.lib().nvmai_cuda_moe_residual_add_f16(_ptr(hidden), _ptr(delta), count, _stream(stream)),
               "residual_add")
+
+
+def debug_set_wait_limit(nanoseconds: int) -> None:
+    """Test hook: the longest any device-side wait lasts (0 = the default of one second)."""
+    check(_lib.lib().nvmai_cuda_moe_debug_set_wait_limit(int(nanoseconds)), "debug_set_wait_limit")
 
 
 def launch_count() -> int:
