@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the routed-expert MoE FFN stack (35B-A3B shape) on B200.
 
-Workload (BASELINE.json configs[3]): 40 MoE FFN layers (hidden 2048, 256 routed
+Workload (the benchmark's configs[3]): 40 MoE FFN layers (hidden 2048, 256 routed
 experts, top-8, expert intermediate 512, one sigmoid-gated shared expert of 512),
 group-64 affine weights, all experts resident in HBM, batch-1 decode.  A step is
 one token through all 40 layers; `value` is tokens/s.  Weights are seeded
@@ -22,7 +22,6 @@ import subprocess
 import sys
 import threading
 import time
-from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 import numpy as np
@@ -104,95 +103,55 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 
 class CpuReferenceStack:
-    """The 40-layer workload on the host cores with the reference's CPU arithmetic
-    (CPUExpertFFN.accumulate over nvmai_int4_affine_gemv).  Per layer only the
-    blobs a token uses are generated (8 routed + 1 shared), since the timing does
-    not depend on which of the 256 experts were picked; the router still scores
-    all 256 rows.  Rows of each GEMV are split across threads."""
+    """The stack workload on the host cores with the reference's CPU arithmetic
+    (CPUExpertFFN.accumulate over nvmai_int4_affine_gemv), driven by the threaded
+    C++ harness in oracle/cpu_stack.cpp: rows of every GEMV stage split over
+    std::threads, the router and the selection through the oracle's own functions.
+    Per layer only the blobs a token uses are generated (8 routed + 1 shared),
+    since the timing does not depend on which of the 256 experts were picked; the
+    router still scores all 256 rows."""
 
-    def __init__(self, bits: int, layers: int, threads: int, seed: int = 7):
+    def __init__(self, bits: int, layers: int, seed: int = 7):
+        import ctypes as C
         from nvmai_b200 import format as fmt
-        from nvmai_b200 import synthetic
         from oracle import oracle as orc
-        self.orc, self.bits, self.layers, self.threads = orc, bits, layers, threads
-        self.lib = orc.lib()
+        self.orc, self.bits, self.layers = orc, bits, layers
+        self.stack_lib = orc.cpu_stack_lib()
         ref = orc.ref_lib() if bits == 4 else None
         self.kind = "reference" if ref is not None else "port"
-        self.ref = ref
+        self.gemv4 = C.cast(ref.nvmai_int4_affine_gemv, C.c_void_p) if ref is not None else None
         rng = np.random.default_rng(seed)
-        self.off, self.stride = fmt.expert_offsets(D, F, bits)
-        self.blobs, self.routers, self.gates = [], [], []
-        for _ in range(layers):
-            lay = np.empty((K + 1, self.stride), dtype=np.uint8)
-            for e in range(K + 1):
-                lay[e] = fmt.pack_expert_blob(synthetic.affine_tensor(rng, F, D, bits, fmt.META_BF16),
-                                              synthetic.affine_tensor(rng, F, D, bits, fmt.META_BF16),
-                                              synthetic.affine_tensor(rng, D, F, bits, fmt.META_BF16), D, F, bits)
-            self.blobs.append(lay)
-            self.routers.append(rng.normal(0.0, 0.02, size=(E, D)).astype(np.float32))
-            self.gates.append(rng.normal(0.0, 0.02, size=D).astype(np.float32))
-        self.pool = ThreadPoolExecutor(max_workers=threads)
-        self.chunks_f = self._chunks(F)
-        self.chunks_d = self._chunks(D)
+        off, stride = fmt.expert_offsets(D, F, bits)
+        # blobs: random code bytes, then the six scale / bias arrays overwritten with the benchmark's distributions
+        self.blobs = rng.integers(0, 256, size=(layers, K + 1, stride), dtype=np.uint8)
+        gate_m, down_m = F * (D // 64), D * (F // 64)
+        for name, n, lo, hi in (("gate_s", gate_m, 0.005, 0.02), ("gate_b", gate_m, -0.08, 0.0),
+                                ("up_s", gate_m, 0.005, 0.02), ("up_b", gate_m, -0.08, 0.0),
+                                ("down_s", down_m, 0.005, 0.02), ("down_b", down_m, -0.08, 0.0)):
+            vals = fmt.f32_to_bf16_bits(rng.uniform(lo, hi, size=(layers, K + 1, n)).astype(np.float32))
+            self.blobs[:, :, off[name]:off[name] + 2 * n] = vals.view(np.uint8).reshape(layers, K + 1, 2 * n)
+        self.routers = fmt.f32_to_f16_bits(rng.normal(0.0, 0.02, size=(layers, E, D)))
+        self.gates = fmt.f32_to_f16_bits(rng.normal(0.0, 0.02, size=(layers, D)))
+        self.xs = fmt.f32_to_f16_bits(rng.normal(size=(8, D)))
+        desc = orc.StackDesc()
+        desc.d, desc.f, desc.e, desc.k, desc.bits, desc.layers = D, F, E, K, bits, layers
+        desc.stride = stride
+        for i, name in enumerate(fmt.OFFSET_NAMES):
+            desc.off[i] = off[name]
+        self._ptrs = [(C.c_void_p * layers)(*[a[l].ctypes.data for l in range(layers)])
+                      for a in (self.blobs, self.routers, self.gates)]
+        desc.blobs, desc.router_f16, desc.gate_f16 = (C.cast(p_, C.POINTER(C.c_void_p)) for p_ in self._ptrs)
+        self.desc = desc
 
-    def _chunks(self, rows: int):
-        per = max(16, -(-rows * (K + 1) // (self.threads * 4)))
-        return [(r, min(r + per, rows)) for r in range(0, rows, per)]
-
-    def _gemv(self, blob: np.ndarray, w_off: int, s_off: int, b_off: int, x: np.ndarray, r0: int, r1: int, n: int,
-              out: np.ndarray) -> None:
-        orc = self.orc
-        row_bytes, groups = n * self.bits // 8, n // 64
-        base = blob.ctypes.data
-        w = base + w_off + r0 * row_bytes
-        s = base + s_off + r0 * groups * 2
-        b = base + b_off + r0 * groups * 2
-        o = out.ctypes.data + r0 * 4
-        if self.ref is not None:
-            import ctypes as C
-            self.ref.nvmai_int4_affine_gemv(C.cast(w, orc.u8p), C.cast(s, orc.u16p), C.cast(b, orc.u16p),
-                                            x.ctypes.data_as(orc.f32p), r1 - r0, n, C.cast(o, orc.f32p))
-        else:
-            self.lib.orc_affine_gemv_f32(self.bits, orc.META_BF16, w, s, b, orc.ptr(x), r1 - r0, n, o)
-
-    def token(self, x: np.ndarray) -> np.ndarray:
-        off = self.off
-        for l in range(self.layers):
-            blobs = self.blobs[l]
-            logits = self.routers[l] @ x
-            top = np.argsort(-logits, kind="stable")[:K]
-            ex = np.exp(logits[top] - logits[top[0]])
-            w = np.concatenate([ex / ex.sum(), [1.0 / (1.0 + np.exp(-float(self.gates[l] @ x)))]]).astype(np.float32)
-            g = np.empty((K + 1, F), dtype=np.float32)
-            u = np.empty((K + 1, F), dtype=np.float32)
-            jobs = []
-            for e in range(K + 1):
-                for r0, r1 in self.chunks_f:
-                    jobs.append(self.pool.submit(self._gemv, blobs[e], off["gate_w"], off["gate_s"], off["gate_b"], x,
-                                                 r0, r1, D, g[e]))
-                    jobs.append(self.pool.submit(self._gemv, blobs[e], off["up_w"], off["up_s"], off["up_b"], x,
-                                                 r0, r1, D, u[e]))
-            for j in jobs:
-                j.result()
-            act = np.ascontiguousarray((g / (1.0 + np.exp(-g))) * u, dtype=np.float32)   # CPUExpertFFN.swift:121-123
-            dn = np.empty((K + 1, D), dtype=np.float32)
-            jobs = [self.pool.submit(self._gemv, blobs[e], off["down_w"], off["down_s"], off["down_b"], act[e], r0, r1,
-                                     F, dn[e]) for e in range(K + 1) for r0, r1 in self.chunks_d]
-            for j in jobs:
-                j.result()
-            y = (w[:, None] * dn).sum(axis=0)
-            x = (y / np.sqrt(np.mean(y * y) + 1e-6)).astype(np.float16).astype(np.float32)
-        return x
-
-    def time_tokens(self, steps: int, warmup: int) -> float:
-        rng = np.random.default_rng(1)
-        xs = [rng.normal(size=D).astype(np.float16).astype(np.float32) for _ in range(max(steps, 1))]
-        for i in range(warmup):
-            self.token(xs[i % len(xs)])
-        t0 = time.perf_counter()
-        for i in range(steps):
-            self.token(xs[i % len(xs)])
-        return (time.perf_counter() - t0) / steps
+    def time_tokens(self, threads: int, steps: int, warmup: int) -> float:
+        """seconds per token over the sampled layers"""
+        import ctypes as C
+        y = np.zeros(D, dtype=np.float32)
+        sec = self.stack_lib.orc_cpu_stack_time(C.byref(self.desc), threads, steps, warmup, self.xs.ctypes.data,
+                                                self.xs.shape[0], y.ctypes.data, self.gemv4)
+        if sec <= 0 or not np.all(np.isfinite(y)):
+            raise RuntimeError("CPU reference stack failed")
+        return float(sec)
 
 
 def host_threads() -> int:
@@ -212,23 +171,33 @@ def base_record(args, n_gpus: int) -> dict:
     }
 
 
+def cpu_baseline_record(args, stack: CpuReferenceStack, layers: int, steps: int, warmup: int, with_single: bool) -> dict:
+    """all-core (and one-thread) tokens/s of the reference CPU path, scaled from `layers` sampled layers"""
+    threads = host_threads()
+    scale = args.layers / layers
+    sec_all = stack.time_tokens(threads, steps, warmup) * scale
+    rec = {"value": 1.0 / sec_all, "unit": UNIT, "cores": threads, "kind": stack.kind,
+           "sample": f"{steps} tokens x {layers} of {args.layers} layers (router over 256 rows, 8 routed + 1 shared "
+                     f"expert per layer; GEMV rows split over {threads} std::threads), scaled to {args.layers}"}
+    if with_single:
+        sec_one = stack.time_tokens(1, 1, 0) * scale
+        rec["value_1_thread"] = 1.0 / sec_one
+        rec["speedup_all_cores"] = sec_one / sec_all
+    return rec
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = host_threads()
     layers = min(args.layers, args.ref_layers)
-    stack = CpuReferenceStack(args.bits, layers, threads)
-    warm = min(args.warmup, 1)
-    steps = max(1, min(args.steps, 5))
-    sec_per_token = stack.time_tokens(steps, warm) * (args.layers / layers)
-    val = 1.0 / sec_per_token
+    stack = CpuReferenceStack(args.bits, layers)
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    base = cpu_baseline_record(args, stack, layers, steps, warm, with_single=True)
+    val = base["value"]
     rec = base_record(args, args.gpus)
-    rec.update({"impl": "reference", "value": val, "ms_per_step": sec_per_token * 1e3, "scaling": "strong",
-                "dtype": "f32", "steps": steps, "warmup": warm,
-                "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": stack.kind,
-                                 "sample": f"{steps} tokens x {layers} of {args.layers} layers "
-                                           f"(8 routed + 1 shared expert and the router per layer), scaled to {args.layers}"},
+    rec.update({"impl": "reference", "value": val, "ms_per_step": 1e3 / val, "scaling": "strong",
+                "dtype": "f32", "cpu_baseline": base,
                 "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0})
     print(json.dumps(rec), flush=True)
@@ -332,7 +301,11 @@ def run_ours(args) -> None:
     rec = None
     if rank == 0:
         peak, which = measured_peaks()
-        roof = stage2_roofline(moe, cfg, devs, args, stream, peak, which)
+        staged = tokens != 1 or os.environ.get("NVMAI_CUDA_DECODE_MODE", "0") == "1"
+        if staged:
+            roof = stage2_roofline(moe, cfg, devs, args, stream, peak, which)
+        else:
+            roof = resident_roofline(moe, args, xs, x_in, y, stream, peak, which)
         step_bytes = args.layers * layer_bytes(args.bits)
         roof["step_bytes"] = step_bytes
         roof["step_frac"] = step_bytes / (ms_per_step / 1e3) / 1e9 / peak
@@ -344,13 +317,14 @@ def run_ours(args) -> None:
                     "roofline": roof})
         rec["config"]["l2"] = "working set 679 MB (4-bit) / 1246 MB (8-bit) per step exceeds the 126 MB L2; inputs rotate"
         if world == 1 and not args.no_cpu_baseline:
-            threads = host_threads()
             layers = min(args.layers, args.ref_layers)
-            cpu = CpuReferenceStack(args.bits, layers, threads)
-            sec = cpu.time_tokens(2, 1) * (args.layers / layers)
-            rec["cpu_baseline"] = {"value": 1.0 / sec, "unit": UNIT, "cores": threads, "kind": cpu.kind,
-                                   "sample": f"2 tokens x {layers} of {args.layers} layers, scaled to {args.layers}"}
+            cpu = CpuReferenceStack(args.bits, layers)
+            rec["cpu_baseline"] = cpu_baseline_record(args, cpu, layers, steps=8, warmup=1, with_single=True)
+        if world == 1 and tokens == 1 and not args.no_parity:
+            rec["parity"] = stack_parity(args, cfg, devs, xs, torch)
         print(json.dumps(rec), flush=True)
+        if "parity" in rec and not rec["parity"]["ok"]:
+            raise SystemExit("parity check of the timed path failed: " + json.dumps(rec["parity"]))
     if dist is not None:
         dist.destroy_process_group()
 
@@ -738,9 +712,92 @@ def run_prefill(args) -> None:
     print(json.dumps(rec), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one stage2_kernel launch from the ncu capture summarised in
-# profiles/decode_stage_kernels_4bit_ncu_full.md (the 8-bit kernel has not been captured)
+# dram__bytes_read.sum + dram__bytes_write.sum of one stage2_kernel launch, from an ncu capture of the 4-bit
+# kernel (the 8-bit kernel has not been captured)
 STAGE2_DRAM_BYTES_PER_LAUNCH = {4: 9508352, 8: None}
+# the same for the resident decode kernel, per LAYER: an ncu capture of a 4-layer, 4-bit step read 68,077,056 B
+# and wrote 1,295,616 B; the traffic of a step grows with its number of layers
+RESIDENT_DRAM_BYTES_PER_LAYER = {4: (68077056 + 1295616) // 4, 8: None}
+
+
+def resident_roofline(moe, args, xs, x_in, y, stream, peak: float, which: str) -> dict:
+    """The whole decode step is ONE launch of the resident kernel: its algorithmic bytes are the step's, its
+    duration the mean over back-to-back launches (CUDA events on the launching stream; the 0.68 / 1.25 GB a
+    step reads are larger than the L2, so every launch streams its weights from HBM)."""
+    import torch
+    reps = 50
+    with torch.cuda.stream(stream):
+        x_in.copy_(xs[0], non_blocking=True)
+        for _ in range(3):
+            moe.stack_decode(x_in, 1, y, stream=stream)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(reps):
+            moe.stack_decode(x_in, 1, y, stream=stream)
+        end.record(stream)
+        stream.synchronize()
+    us = start.elapsed_time(end) * 1e3 / reps
+    nbytes = args.layers * layer_bytes(args.bits)
+    achieved = nbytes / (us * 1e-6) / 1e9
+    per_layer = RESIDENT_DRAM_BYTES_PER_LAYER.get(args.bits)
+    return {"bound": "hbm", "kernel": "persistent_decode_kernel (one launch = all layers of the step)",
+            "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": None if per_layer is None else per_layer * args.layers, "bytes_per_launch": nbytes,
+            "us_per_launch": us}
+
+
+def stack_parity(args, cfg, devs, xs, torch) -> dict:
+    """Post-timing check of the timed path against the CPU oracle: the first layers of the same stack, same
+    input row, through the same entry point; selected experts must be exact, the output within the tolerances
+    of the GPU tests; and the resident kernel must give the staged kernels' bits."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import dataclasses
+    import gpu_util as gu
+    from nvmai_b200 import MoE, synthetic
+    from oracle import oracle as orc
+    n = min(4, args.layers)
+    cfg_p = dataclasses.replace(cfg, num_layers=n, max_tokens=1)
+    moe = MoE(cfg_p)
+    for l in range(n):
+        synthetic.register_device_layer(moe, l, devs[l])
+    x0 = xs[0, 0].contiguous()
+    outs = {}
+    for mode in (MoE.DECODE_STAGED, MoE.DECODE_AUTO):
+        y = torch.empty(D, dtype=torch.float32, device="cuda")
+        moe.set_decode_mode(mode)
+        moe.stack_decode(x0, 1, y)
+        moe.synchronize()
+        outs[mode] = y.cpu().numpy()
+    log = moe.read_route_log(n)
+    got = outs[MoE.DECODE_AUTO]
+
+    def host_tensor(t):
+        w, s, b = t
+        as_np = lambda a: None if a is None else a.cpu().view(torch.uint8).numpy().view(np.uint16 if a.element_size() == 2 else np.uint8).reshape(a.shape)
+        return as_np(w), as_np(s), as_np(b)
+
+    x = np.ascontiguousarray(x0.cpu().view(torch.int16).numpy().view(np.uint16))
+    idx_ok, margin_min, h2, cpu = True, float("inf"), None, None
+    for l in range(n):
+        dev = devs[l]
+        host = {"experts": dev["experts"].cpu().numpy(), "stride": dev["stride"], "offsets": dev["offsets"],
+                "router": host_tensor(dev["router"]), "shared": [host_tensor(t) for t in dev["shared"]],
+                "gate": host_tensor(dev["gate"])}
+        L, keep = gu.oracle_layer(host, cfg_p)
+        idx, _, h2, margin, cpu = gu.oracle_decode(L, cfg_p, x)
+        idx_ok = idx_ok and log[l].tolist() == idx.tolist()
+        margin_min = min(margin_min, margin)
+        if l + 1 < n:
+            scale = 1.0 / np.sqrt(np.mean(h2.astype(np.float64) ** 2) + 1e-6)
+            x = orc.f32_to_f16_bits((h2.astype(np.float64) * scale).astype(np.float32))
+    rec = {"layers_checked": n, "expert_indices_exact": bool(idx_ok), "min_router_margin": margin_min,
+           "rel_err_vs_oracle_chain": float(orc.rel_error(got, h2)),
+           "oracle_last_layer_vs_reference_cpu_path": float(orc.rel_error(h2, cpu)),
+           "resident_equals_staged_bitwise": bool(np.array_equal(outs[MoE.DECODE_STAGED].view(np.uint32), got.view(np.uint32)))}
+    rec["ok"] = bool(idx_ok and rec["rel_err_vs_oracle_chain"] < 2e-3 and rec["oracle_last_layer_vs_reference_cpu_path"] < 1e-3
+                     and rec["resident_equals_staged_bitwise"])
+    return rec
+
 
 
 def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> dict:
@@ -793,6 +850,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the post-timing check against the CPU oracle")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
     ap.add_argument("--batch-layer", action="store_true",
                     help="measure configs[1] (one layer, --tokens independent rows, batched decode kernels) or, with "

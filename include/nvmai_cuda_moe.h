@@ -238,7 +238,9 @@ NVMAI_API int nvmai_cuda_moe_read_file_to_device(const char *path, uint64_t file
 /* ---- expert parallelism (no counterpart in the reference, which runs on one GPU) ----
  * A rank holds n_local of the layer's expert blobs, contiguous at `experts` in
  * local-index order; map_host[e] = local index of global expert e or 0xFFFFFFFF.
- * The map is validated (every local index used exactly once). NULL resets. */
+ * The map is validated: every local index below n_local is named by exactly one expert
+ * (NVMAI_CUDA_EINVAL for a duplicate or a gap, NVMAI_CUDA_ERANGE for an index >= n_local).
+ * NULL resets. */
 NVMAI_API int nvmai_cuda_moe_set_expert_map(nvmai_cuda_moe *h, const uint32_t *map_host, uint32_t n_local);
 
 /* This rank's share of the routed experts for `tokens` rows that every rank holds:
@@ -372,6 +374,15 @@ NVMAI_API int nvmai_cuda_moe_residual_add_f16(void *hidden, const void *delta, u
  * block 0}.  read_trace synchronises the device. */
 NVMAI_API int nvmai_cuda_moe_set_trace(nvmai_cuda_moe *h, int enable);
 NVMAI_API int nvmai_cuda_moe_read_trace(nvmai_cuda_moe *h, uint64_t *out_host, uint32_t layers);
+
+/* The same timeline for the resident kernel of a single-token stack step: with tracing on,
+ * every block stores GPU-timer nanoseconds at [layer][block][16]: {0 input row ready, 1 phase-1
+ * results stored, 2 all logits in, 3 expert tiles requested, 4 first gate/up tile landed,
+ * 5 activations stored, 6 shared-expert down done, 7 routed activations staged, 8 down done,
+ * 9 block output stored, 10 top-k done, 11 last gate/up tile landed, rest unused}; 0 = the block has no
+ * share of that phase.
+ * out_host NULL: only *out_blocks (the number of blocks) is returned. */
+NVMAI_API int nvmai_cuda_moe_read_block_trace(nvmai_cuda_moe *h, uint64_t *out_host, uint32_t layers, uint32_t *out_blocks);
 
 /* waitUntilCompleted + `.error` (RealForwardRunner.swift:3805-3837). */
 NVMAI_API int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream);

@@ -79,6 +79,7 @@ PROTOTYPES = {
     "nvmai_cuda_moe_residual_add_f16": (C.c_int, [vp, vp, u32, vp]),
     "nvmai_cuda_moe_set_trace": (C.c_int, [vp, C.c_int]),
     "nvmai_cuda_moe_read_trace": (C.c_int, [vp, vp, u32]),
+    "nvmai_cuda_moe_read_block_trace": (C.c_int, [vp, vp, u32, C.POINTER(u32)]),
     "nvmai_cuda_moe_synchronize": (C.c_int, [vp, vp]),
     "nvmai_cuda_moe_last_cuda_error": (C.c_int, [vp]),
     "nvmai_cuda_moe_error_string": (C.c_char_p, [C.c_int]),

@@ -634,7 +634,12 @@ __global__ void __launch_bounds__(256) ep_finalize_kernel(EpFinalizeParams p) {
 // one of two receive buffers per layer parity, so that a rank one layer ahead never
 // writes what a slower rank still reads.
 // ---------------------------------------------------------------------------
-__global__ void ep_step_kernel(unsigned long long *step) { *step += 1ull; }
+// First kernel of a step: counts the step and clears this rank's per-layer block counters (stream order: the
+// previous step's down stages are done), so a step may use another number of rows than the one before.
+__global__ void ep_step_kernel(unsigned long long *step, unsigned long long *local_count, uint32_t layers) {
+    if (threadIdx.x == 0) *step += 1ull;
+    for (uint32_t i = threadIdx.x; i < layers; i += blockDim.x) local_count[i] = 0ull;
+}
 
 struct EpFinalizePeerParams {
     const float *recv;                   // this rank's receive area

@@ -15,6 +15,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <new>
 #include <thread>
 #include <tuple>
@@ -118,7 +119,7 @@ struct nvmai_cuda_moe {
     // one-launch decode step (persistent_decode.cuh): per-layer views on the device, the tagged exchange words,
     // the epoch word and the experts each layer selected
     PdLayer *pd_layers = nullptr;
-    bool pd_layers_stale = true;
+    bool pd_layers_stale = true, pd_unavailable = false;
     unsigned long long *pd_xchg = nullptr;
     unsigned int *pd_epoch = nullptr;
     uint32_t *pd_route_log = nullptr;     // [num_layers][top_k]
@@ -126,7 +127,7 @@ struct nvmai_cuda_moe {
     // 0: a single-token stack step takes the one-launch kernel when the shape allows it; 1: always the staged
     // kernels; 2: the one-launch kernel or NVMAI_CUDA_EINVAL
     int decode_mode = 0;
-    uint32_t pd_trace_block = 0;
+    unsigned long long *pd_trace = nullptr;   // [num_layers][sm_count][16] marks of the resident kernel (allocated by set_trace)
     uint32_t pd_mute_block = 0xFFFFFFFFu;     // test hook, see nvmai_cuda_moe_debug_mute_block
 };
 
@@ -211,8 +212,14 @@ int dispatch_bits_meta(uint32_t bits, uint32_t meta, F &&f) {
 // opt-in is per function and sticky, so it is raised once per (function, size).
 template <typename Kern>
 cudaError_t ensure_smem(Kern kern, size_t bytes) {
-    static std::map<const void *, size_t> granted;
-    const void *key = reinterpret_cast<const void *>(kern);
+    // the attribute is per device and handles may be driven from several host threads
+    static std::map<std::pair<int, const void *>, size_t> granted;
+    static std::mutex guard;
+    int dev = 0;
+    cudaError_t de = cudaGetDevice(&dev);
+    if (de != cudaSuccess) return de;
+    std::lock_guard<std::mutex> lock(guard);
+    const auto key = std::make_pair(dev, reinterpret_cast<const void *>(kern));
     auto it = granted.find(key);
     if (it != granted.end() && it->second >= bytes) return cudaSuccess;
     if (bytes > 48 * 1024) {
@@ -545,8 +552,14 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
 }
 
 // ---- prefill: grouped GEMMs on the tensor cores ----------------------------------
-int ensure_prefill_scratch(nvmai_cuda_moe *h) {
+int ensure_prefill_scratch(nvmai_cuda_moe *h, cudaStream_t st) {
     if (h->pf_acts16) return NVMAI_CUDA_OK;
+    // the first prefill call allocates; a stream under capture forbids that: make one eager call first
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (st != nullptr && (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone)) {
+        cudaGetLastError();
+        return NVMAI_CUDA_EINVAL;
+    }
     const auto &c = h->cfg;
     const size_t T = c.max_tokens, P = T * c.top_k;
     auto alloc = [&](auto **ptr, size_t bytes) { return cudaMalloc(reinterpret_cast<void **>(ptr), bytes ? bytes : 16) == cudaSuccess; };
@@ -646,7 +659,7 @@ struct PrefillMode {
 int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint32_t tokens, void *hidden, void *y,
                        uint32_t *out_idx, __half *out_w, cudaStream_t st, const PrefillMode mode = PrefillMode{}) {
     const LayerViews &lv = h->layers[layer];
-    int rc = ensure_prefill_scratch(h);
+    int rc = ensure_prefill_scratch(h, st);
     if (rc) return rc;
     nvmai_cuda_moe_config c = h->cfg;
     if (mode.routed_only) c.shared_f = 0;
@@ -792,54 +805,130 @@ bool pd_plan(const nvmai_cuda_moe *h, PdPlan &plan) {
     if (G == 0 || h->pd_xchg == nullptr || h->expert_map != nullptr) return false;
     if (c.top_k > (uint32_t)kMaxTopK || c.num_experts > (uint32_t)kPdThreads) return false;
     if (c.shared_f != 0 && c.shared_bits != c.routed_bits) return false;
-    if (c.d > (uint32_t)(kPdKeep * kPdThreads) || c.d / kTileRows > G) return false;
+    if (c.d > (uint32_t)(kPdKeep * kPdNormThreads) || c.d / kTileRows > G) return false;
     if (c.f > 1024 || c.shared_f > 1024) return false;
+    // weight tiles come by tiled TMA in 128-byte lines: whole lines per row, and boxes of at most 256 values
+    const uint32_t b = c.routed_bits;
+    if ((c.d * b / 8) % 128 != 0 || (c.f * b / 8) % 128 != 0 || (c.shared_f * b / 8) % 128 != 0) return false;
+    if (kTileFeatures * (c.d / 64) > 256 || kTileRows * (std::max(c.f, c.shared_f) / 64) > 256) return false;
+    if (encode_tiled_fn() == nullptr) return false;
     const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
-    uint32_t rows = 0;
-    for (uint32_t r = 1; r <= (uint32_t)kPdWarps; ++r) {
-        const uint32_t units = c.shared_f / kTileFeatures + (c.num_experts + r - 1) / r + (gated ? 1 : 0);
-        if (units <= G) { rows = r; break; }
-    }
-    if (rows == 0) return false;
+    // router rows spread over the blocks, one block left without any for the gate row; a shared tile per block
+    const uint32_t router_blocks_max = G - (gated ? 1 : 0);
+    if (router_blocks_max == 0 || c.shared_f / kTileFeatures > G) return false;
+    const uint32_t rows = (c.num_experts + router_blocks_max - 1) / router_blocks_max;
+    if (rows > (uint32_t)kPdWarps) return false;
     const uint32_t tiles_total = c.top_k * (c.f / kTileFeatures);
     const uint32_t max_tiles = (tiles_total + G - 1) / G;
     if (max_tiles == 0 || max_tiles > (uint32_t)kPdMaxTiles) return false;
     uint32_t slots = std::min<uint32_t>(max_tiles, kPdMaxSlots);
-    for (; slots >= 1; --slots) {
+    const uint32_t min_slots = std::min<uint32_t>(max_tiles, kPdGroups);      // tiles that are worked on side by side
+    for (; slots >= min_slots; --slots) {
         const size_t smem = PdLayout(c.d, c.f, c.shared_f, c.routed_bits, c.top_k, c.router_kind,
                                      gated ? c.shared_gate_kind : NVMAI_GATE_NONE, rows, slots, max_tiles).total;
         if (smem <= kMaxSmem) { plan.smem = smem; break; }
     }
-    if (slots == 0) return false;
+    if (slots < min_slots) return false;
     plan.router_rows = rows; plan.slots = slots; plan.max_tiles = max_tiles;
     return true;
 }
 
+// One tensor map: `rank` dimensions, dim 0 contiguous; strides in bytes for dims 1.. .
+int pd_encode(nvmai_cuda_moe *h, CUtensorMap *map, CUtensorMapDataType dt, uint32_t rank, const void *base,
+              const cuuint64_t *gdim, const cuuint64_t *gstride, const cuuint32_t *box, bool swizzle) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return NVMAI_CUDA_ECUDA;
+    const cuuint32_t estride[5] = {1, 1, 1, 1, 1};
+    const CUresult r = enc(map, dt, rank, const_cast<void *>(base), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { h->last_cuda_error = (int)r; return NVMAI_CUDA_ECUDA; }
+    return NVMAI_CUDA_OK;
+}
+
+// The per-layer table of the resident kernel: tensor maps over the layer's expert array (the expert is a coordinate)
+// and the plain pointers.  NVMAI_CUDA_EINVAL when a layer's blob layout is not the regular one the maps describe.
+int pd_build_layers(nvmai_cuda_moe *h, std::vector<PdLayer> &host) {
+    const auto &c = h->cfg;
+    const uint64_t bits = c.routed_bits;
+    const uint64_t rbd = (uint64_t)c.d * bits / 8, rbf = (uint64_t)c.f * bits / 8, rbs = (uint64_t)c.shared_f * bits / 8;
+    const uint64_t gd = c.d / 64, gf = c.f / 64;
+    host.assign(c.num_layers, PdLayer{});
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+        const auto &w = h->layers[l].w;
+        const auto &o = w.offsets;
+        PdLayer &d = host[l];
+        const uint8_t *base = static_cast<const uint8_t *>(w.experts);
+        // gate and up must be laid out alike, scales before biases (the repacker's order, RepackPlanner.swift:365-426)
+        if (w.expert_stride == 0 || o.up_w <= o.gate_w || o.up_s <= o.gate_s || o.gate_b <= o.gate_s || o.down_b <= o.down_s ||
+            o.up_s - o.gate_s != o.up_b - o.gate_b)
+            return NVMAI_CUDA_EINVAL;
+        int rc;
+        {   // routed gate + up codes: {128 B, row, chunk, gate|up, expert}
+            const cuuint64_t gdim[5] = {128, c.f, rbd / 128, 2, c.num_experts};
+            const cuuint64_t gstr[4] = {rbd, 128, (cuuint64_t)(o.up_w - o.gate_w), w.expert_stride};
+            const cuuint32_t box[5] = {128, (cuuint32_t)kTileFeatures, (cuuint32_t)(rbd / 128), 2, 1};
+            if ((rc = pd_encode(h, &d.gu_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base + o.gate_w, gdim, gstr, box, true))) return rc;
+        }
+        {   // their scales and biases: {value, gate|up, scale|bias, expert}
+            const cuuint64_t gdim[4] = {(cuuint64_t)c.f * gd, 2, 2, c.num_experts};
+            const cuuint64_t gstr[3] = {(cuuint64_t)(o.up_s - o.gate_s), (cuuint64_t)(o.gate_b - o.gate_s), w.expert_stride};
+            const cuuint32_t box[4] = {(cuuint32_t)(kTileFeatures * gd), 2, 2, 1};
+            if ((rc = pd_encode(h, &d.gu_meta, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, base + o.gate_s, gdim, gstr, box, false))) return rc;
+        }
+        {   // routed down codes: {128 B, row, chunk, expert}
+            const cuuint64_t gdim[4] = {128, c.d, rbf / 128, c.num_experts};
+            const cuuint64_t gstr[3] = {rbf, 128, w.expert_stride};
+            const cuuint32_t box[4] = {128, (cuuint32_t)kTileRows, (cuuint32_t)(rbf / 128), 1};
+            if ((rc = pd_encode(h, &d.dn_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base + o.down_w, gdim, gstr, box, true))) return rc;
+        }
+        {   // and meta: {value, scale|bias, expert}
+            const cuuint64_t gdim[3] = {(cuuint64_t)c.d * gf, 2, c.num_experts};
+            const cuuint64_t gstr[2] = {(cuuint64_t)(o.down_b - o.down_s), w.expert_stride};
+            const cuuint32_t box[3] = {(cuuint32_t)(kTileRows * gf), 2, 1};
+            if ((rc = pd_encode(h, &d.dn_meta, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base + o.down_s, gdim, gstr, box, false))) return rc;
+        }
+        if (c.shared_f) {   // the shared expert's three code matrices: {128 B, row, chunk}
+            const cuuint64_t gdim[3] = {128, c.shared_f, rbd / 128};
+            const cuuint64_t gstr[2] = {rbd, 128};
+            const cuuint32_t box[3] = {128, (cuuint32_t)kTileFeatures, (cuuint32_t)(rbd / 128)};
+            if ((rc = pd_encode(h, &d.sg_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.shared_gate_proj.w, gdim, gstr, box, true))) return rc;
+            if ((rc = pd_encode(h, &d.su_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.shared_up_proj.w, gdim, gstr, box, true))) return rc;
+            const cuuint64_t ddim[3] = {128, c.d, rbs / 128};
+            const cuuint64_t dstr[2] = {rbs, 128};
+            const cuuint32_t dbox[3] = {128, (cuuint32_t)kTileRows, (cuuint32_t)(rbs / 128)};
+            if ((rc = pd_encode(h, &d.sd_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.shared_down_proj.w, ddim, dstr, dbox, true))) return rc;
+        }
+        d.experts_stride = w.expert_stride;
+        d.rW = static_cast<const uint8_t *>(w.router.w);
+        d.rS = static_cast<const uint16_t *>(w.router.scales);
+        d.rB = static_cast<const uint16_t *>(w.router.biases);
+        d.eff = static_cast<const uint16_t *>(w.effective_scale);
+        d.pes = static_cast<const uint16_t *>(w.per_expert_scale);
+        d.sgS = static_cast<const uint16_t *>(w.shared_gate_proj.scales); d.sgB = static_cast<const uint16_t *>(w.shared_gate_proj.biases);
+        d.suS = static_cast<const uint16_t *>(w.shared_up_proj.scales); d.suB = static_cast<const uint16_t *>(w.shared_up_proj.biases);
+        d.sdS = static_cast<const uint16_t *>(w.shared_down_proj.scales); d.sdB = static_cast<const uint16_t *>(w.shared_down_proj.biases);
+        d.gW = static_cast<const uint8_t *>(w.shared_gate.w);
+        d.gS = static_cast<const uint16_t *>(w.shared_gate.scales);
+        d.gB = static_cast<const uint16_t *>(w.shared_gate.biases);
+    }
+    return NVMAI_CUDA_OK;
+}
+
+// Uploads the layer table when a layer was (re)registered.  pd_unavailable: the layout does not fit the maps.
+int pd_prepare(nvmai_cuda_moe *h, cudaStream_t st) {
+    if (!h->pd_layers_stale) return h->pd_unavailable ? NVMAI_CUDA_EINVAL : NVMAI_CUDA_OK;
+    std::vector<PdLayer> host;
+    int rc = pd_build_layers(h, host);
+    h->pd_layers_stale = false;
+    h->pd_unavailable = rc != NVMAI_CUDA_OK;
+    if (rc) return rc;
+    if ((rc = record(h, cudaMemcpyAsync(h->pd_layers, host.data(), host.size() * sizeof(PdLayer), cudaMemcpyHostToDevice, st)))) return rc;
+    return record(h, cudaStreamSynchronize(st));     // `host` goes out of scope
+}
+
 int pd_launch(nvmai_cuda_moe *h, const PdPlan &plan, const __half *x0, void *y_last, cudaStream_t st) {
     const auto &c = h->cfg;
-    if (h->pd_layers_stale) {
-        std::vector<PdLayer> host(c.num_layers);
-        for (uint32_t l = 0; l < c.num_layers; ++l) {
-            const auto &w = h->layers[l].w;
-            PdLayer &d = host[l];
-            d.experts = static_cast<const uint8_t *>(w.experts);
-            d.stride = w.expert_stride;
-            d.off = to_offsets(w.offsets);
-            d.rW = static_cast<const uint8_t *>(w.router.w);
-            d.rS = static_cast<const uint16_t *>(w.router.scales);
-            d.rB = static_cast<const uint16_t *>(w.router.biases);
-            d.eff = static_cast<const uint16_t *>(w.effective_scale);
-            d.pes = static_cast<const uint16_t *>(w.per_expert_scale);
-            d.sgate = to_mat(w.shared_gate_proj); d.sup = to_mat(w.shared_up_proj); d.sdown = to_mat(w.shared_down_proj);
-            d.gW = static_cast<const uint8_t *>(w.shared_gate.w);
-            d.gS = static_cast<const uint16_t *>(w.shared_gate.scales);
-            d.gB = static_cast<const uint16_t *>(w.shared_gate.biases);
-        }
-        int rc = record(h, cudaMemcpyAsync(h->pd_layers, host.data(), host.size() * sizeof(PdLayer), cudaMemcpyHostToDevice, st));
-        if (rc) return rc;
-        if ((rc = record(h, cudaStreamSynchronize(st)))) return rc;     // `host` goes out of scope
-        h->pd_layers_stale = false;
-    }
     const PdXchg X(c);
     const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
     PdParams p{};
@@ -852,8 +941,7 @@ int pd_launch(nvmai_cuda_moe *h, const PdPlan &plan, const __half *x0, void *y_l
     p.router_kind = c.router_kind; p.gate_kind = gated ? c.shared_gate_kind : NVMAI_GATE_NONE;
     p.router_rows = plan.router_rows; p.slots = plan.slots; p.max_tiles = plan.max_tiles;
     p.debug_mute_block = h->pd_mute_block;
-    p.trace = h->trace_on ? h->trace : nullptr;      // [layer][3 x 8 words]: the resident kernel uses them as 24 marks
-    p.trace_block = h->pd_trace_block;
+    p.trace = h->trace_on ? h->pd_trace : nullptr;
     return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
         return dispatch_out(c.out_dtype, [&](auto O) {
             auto kern = persistent_decode_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>;
@@ -972,14 +1060,13 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
         const unsigned int first_epoch = 1;
         ok = cudaGetDevice(&dev) == cudaSuccess &&
              cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-             alloc(&h->pd_xchg, xbytes) && alloc(&h->pd_epoch, 16) && alloc(&h->pd_layers, (size_t)c.num_layers * sizeof(PdLayer)) &&
+             alloc(&h->pd_xchg, xbytes) && alloc(&h->pd_epoch, 5 * 128) && alloc(&h->pd_layers, (size_t)c.num_layers * sizeof(PdLayer)) &&
              alloc(&h->pd_route_log, (size_t)c.num_layers * c.top_k * 4) &&
-             cudaMemset(h->pd_xchg, 0, xbytes) == cudaSuccess && cudaMemset(h->pd_epoch, 0, 16) == cudaSuccess &&
+             cudaMemset(h->pd_xchg, 0, xbytes) == cudaSuccess && cudaMemset(h->pd_epoch, 0, 5 * 128) == cudaSuccess &&
              cudaMemset(h->pd_route_log, 0, (size_t)c.num_layers * c.top_k * 4) == cudaSuccess &&
              cudaMemcpy(h->pd_epoch, &first_epoch, sizeof(first_epoch), cudaMemcpyHostToDevice) == cudaSuccess;
     }
     if (const char *env = std::getenv("NVMAI_CUDA_DECODE_MODE")) h->decode_mode = std::atoi(env);
-    if (const char *env = std::getenv("NVMAI_CUDA_TRACE_BLOCK")) h->pd_trace_block = (uint32_t)std::atoi(env);
     if (!ok) {
         const bool oom = h->last_cuda_error == (int)cudaErrorMemoryAllocation;
         nvmai_cuda_moe_destroy(h);
@@ -994,6 +1081,7 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     if (!h) return;
     for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
     ep_release(h);
+    cudaFree(h->pd_trace);
     cudaFree(h->pd_layers); cudaFree(h->pd_xchg); cudaFree(h->pd_epoch); cudaFree(h->pd_route_log);
     cudaFree(h->pf_x); cudaFree(h->pf_xn); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
@@ -1200,9 +1288,12 @@ int nvmai_cuda_moe_set_expert_map(nvmai_cuda_moe *h, const uint32_t *map_host, u
     }
     if (n_local == 0 || n_local > c.num_experts) return NVMAI_CUDA_ERANGE;
     uint32_t seen = 0;
+    std::vector<bool> used(n_local, false);
     for (uint32_t e = 0; e < c.num_experts; ++e) {
         if (map_host[e] == kNotLocal) continue;
         if (map_host[e] >= n_local) return NVMAI_CUDA_ERANGE;
+        if (used[map_host[e]]) return NVMAI_CUDA_EINVAL;       // two experts on one local blob
+        used[map_host[e]] = true;
         ++seen;
     }
     if (seen != n_local) return NVMAI_CUDA_EINVAL;     // a bad placement map is rejected, not trusted
@@ -1290,7 +1381,8 @@ int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t 
     // under capture keeps the staged launches (the layer table may have to be uploaded, which a capture forbids).
     if (h->decode_mode != 1 && tokens == 1 && cs == cudaStreamCaptureStatusNone) {
         PdPlan plan;
-        if (pd_plan(h, plan)) return pd_launch(h, plan, static_cast<const __half *>(x0_f16), y_last, st);
+        if (pd_plan(h, plan) && pd_prepare(h, st) == NVMAI_CUDA_OK)
+            return pd_launch(h, plan, static_cast<const __half *>(x0_f16), y_last, st);
     }
     if (h->decode_mode == 2) return NVMAI_CUDA_EINVAL;
     if (st == nullptr || cs != cudaStreamCaptureStatusNone)
@@ -1494,7 +1586,7 @@ static int ep_stack_enqueue_replicated(nvmai_cuda_moe *h, const __half *x_own, u
         }
         view.step = h->ep_step; view.local_count = h->ep_step + 2; view.world = world; view.rank = h->ep_rank; view.layers = c.num_layers;
         view.buf_elems = h->ep_buf_elems;
-        ep_step_kernel<<<1, 1, 0, st>>>(h->ep_step);
+        ep_step_kernel<<<1, 128, 0, st>>>(h->ep_step, h->ep_step + 2, c.num_layers);
         int rc = check_launch(h);
         if (rc) return rc;
     }
@@ -1666,12 +1758,28 @@ int nvmai_cuda_moe_set_trace(nvmai_cuda_moe *h, int enable) {
     if (!h) return NVMAI_CUDA_EINVAL;
     h->trace_on = enable != 0;
     h->graphs_stale = true;     // captured launches carry (or do not carry) the trace slots
+    const size_t pd_bytes = (size_t)h->cfg.num_layers * (size_t)std::max(h->sm_count, 1) * 16 * sizeof(unsigned long long);
+    if (enable && !h->pd_trace && cudaMalloc(reinterpret_cast<void **>(&h->pd_trace), pd_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        h->pd_trace = nullptr;
+        return NVMAI_CUDA_ENOMEM;
+    }
+    if (h->pd_trace) cudaMemset(h->pd_trace, 0, pd_bytes);
     return record(h, cudaMemset(h->trace, 0, (size_t)h->cfg.num_layers * 3 * kTraceWords * sizeof(unsigned long long)));
 }
 
 int nvmai_cuda_moe_read_trace(nvmai_cuda_moe *h, uint64_t *out_host, uint32_t layers) {
     if (!h || !out_host || layers > h->cfg.num_layers) return NVMAI_CUDA_EINVAL;
     return record(h, cudaMemcpy(out_host, h->trace, (size_t)layers * 3 * kTraceWords * sizeof(unsigned long long),
+                                cudaMemcpyDeviceToHost));
+}
+
+int nvmai_cuda_moe_read_block_trace(nvmai_cuda_moe *h, uint64_t *out_host, uint32_t layers, uint32_t *out_blocks) {
+    if (!h || !out_blocks || layers > h->cfg.num_layers) return NVMAI_CUDA_EINVAL;
+    *out_blocks = (uint32_t)h->sm_count;
+    if (!out_host) return NVMAI_CUDA_OK;          // size query
+    if (!h->pd_trace) return NVMAI_CUDA_EINVAL;   // set_trace(1) comes first
+    return record(h, cudaMemcpy(out_host, h->pd_trace, (size_t)layers * h->sm_count * 16 * sizeof(unsigned long long),
                                 cudaMemcpyDeviceToHost));
 }
 

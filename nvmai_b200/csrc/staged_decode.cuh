@@ -754,12 +754,12 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
                 __threadfence_system();              // the 16 writers of this block: stores visible system-wide ...
                 __syncwarp(0x0000ffffu);
                 if (threadIdx.x == 0) {
-                    // ... before the block is counted.  Blocks count on a local word (it only grows); the block
-                    // that completes the layer's set announces the rank once at every receiver, so a layer costs one
-                    // system-scope atomic per peer instead of one per block.
+                    // ... before the block is counted.  Blocks count on a local word (cleared by the step's first
+                    // kernel); the block that completes the layer's set announces the rank once at every receiver,
+                    // so a layer costs one system-scope atomic per peer instead of one per block.
                     const unsigned long long blocks = (unsigned long long)gridDim.x * gridDim.y;
                     const unsigned long long seen = atomicAdd(v.local_count + v.layer, 1ull) + 1ull;
-                    if (seen % blocks == 0) {
+                    if (seen == blocks) {
                         __threadfence_system();
                         for (uint32_t r = 0; r < v.world; ++r) atomicAdd_system(v.arrive[r] + v.layer, 1ull);
                     }

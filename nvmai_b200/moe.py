@@ -269,6 +269,16 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_read_trace(self._h, out.ctypes.data, n), "read_trace")
         return out
 
+    def read_block_trace(self, layers: int | None = None):
+        """-> uint64 [layers, blocks, 16]: the resident kernel's per-block phase marks (GPU-timer ns, 0 = none)."""
+        import numpy as np
+        n = self.config.num_layers if layers is None else layers
+        blocks = C.c_uint32(0)
+        check(self._lib.nvmai_cuda_moe_read_block_trace(self._h, None, n, C.byref(blocks)), "read_block_trace")
+        out = np.zeros((n, blocks.value, 16), dtype=np.uint64)
+        check(self._lib.nvmai_cuda_moe_read_block_trace(self._h, out.ctypes.data, n, C.byref(blocks)), "read_block_trace")
+        return out
+
     def synchronize(self, stream=None) -> None:
         check(self._lib.nvmai_cuda_moe_synchronize(self._h, _stream(stream)), "synchronize")
 

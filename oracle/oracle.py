@@ -34,14 +34,22 @@ f64p = C.POINTER(C.c_double)
 GEMV4_FN = C.CFUNCTYPE(None, u8p, u16p, u16p, f32p, C.c_size_t, C.c_size_t, f32p)
 
 
+def reference_root() -> Path | None:
+    """The reference checkout: $NVMAI_REF_ROOT, else a `reference` directory beside this repository."""
+    env = os.environ.get("NVMAI_REF_ROOT")
+    for cand in ([Path(env)] if env else []) + [HERE.parent.parent / "reference"]:
+        if (cand / "sources/NVMAIKernelsC/int4_affine_gemv.c").exists():
+            return cand
+    return None
+
+
 def build(force: bool = False) -> None:
-    so = HERE / "liboracle.so"
-    src = HERE / "nvmai_oracle.c"
-    if force or not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
-        subprocess.run(["make", "-C", str(HERE), "liboracle.so"], check=True,
-                       stdout=subprocess.DEVNULL)
-    ref_root = os.environ.get("NVMAI_REF_ROOT", "/root/reference")
-    if (Path(ref_root) / "sources/NVMAIKernelsC/int4_affine_gemv.c").exists():
+    for so, srcs in (("liboracle.so", ["nvmai_oracle.c"]), ("libcpu_stack.so", ["cpu_stack.cpp", "nvmai_oracle.c"])):
+        out = HERE / so
+        if force or not out.exists() or any(out.stat().st_mtime < (HERE / s).stat().st_mtime for s in srcs):
+            subprocess.run(["make", "-C", str(HERE), so], check=True, stdout=subprocess.DEVNULL)
+    ref_root = reference_root()
+    if ref_root is not None:
         ref_so = HERE / "_ref" / "libnvmai_ref.so"
         if force or not ref_so.exists():
             subprocess.run(["make", "-C", str(HERE), "ref", f"REF_ROOT={ref_root}"], check=True,
@@ -55,6 +63,27 @@ def lib() -> C.CDLL:
         _lib = C.CDLL(str(HERE / "liboracle.so"))
         _declare(_lib)
     return _lib
+
+
+class StackDesc(C.Structure):
+    _fields_ = [("d", C.c_int), ("f", C.c_int), ("e", C.c_int), ("k", C.c_int), ("bits", C.c_int), ("layers", C.c_int),
+                ("blobs", C.POINTER(C.c_void_p)), ("stride", C.c_uint64), ("off", C.c_uint32 * 9),
+                ("router_f16", C.POINTER(C.c_void_p)), ("gate_f16", C.POINTER(C.c_void_p))]
+
+
+_stack = None
+
+
+def cpu_stack_lib() -> C.CDLL:
+    """The threaded CPU-baseline driver (cpu_stack.cpp)."""
+    global _stack
+    if _stack is None:
+        build()
+        _stack = C.CDLL(str(HERE / "libcpu_stack.so"))
+        _stack.orc_cpu_stack_time.argtypes = [C.POINTER(StackDesc), C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                              C.c_void_p, C.c_void_p]
+        _stack.orc_cpu_stack_time.restype = C.c_double
+    return _stack
 
 
 def ref_lib():

@@ -53,15 +53,16 @@ def _oracle_chain(cfg, hosts, x_row):
     return idxs, h2, margin_min
 
 
+# the resident kernel fetches whole 128-byte lines per weight row: 4-bit shapes are multiples of 256, 8-bit of 128
 SMALL = [
     # bits, meta, out, router kind, gate kind, d, f, shared_f, experts, activation
-    (4, fmt.META_BF16, fmt.OUT_FP32, fmt.ROUTER_DENSE_F16, fmt.ROUTER_DENSE_F16, 256, 128, 128, 32, fmt.ACT_SILU),
+    (4, fmt.META_BF16, fmt.OUT_FP32, fmt.ROUTER_DENSE_F16, fmt.ROUTER_DENSE_F16, 256, 256, 256, 32, fmt.ACT_SILU),
     (8, fmt.META_FP16, fmt.OUT_FP32, fmt.ROUTER_DENSE_F16, fmt.ROUTER_DENSE_F16, 256, 128, 128, 32, fmt.ACT_SILU),
-    (4, fmt.META_BF16, fmt.OUT_FP16, fmt.ROUTER_AFFINE8, fmt.ROUTER_AFFINE8, 512, 128, 64, 48, fmt.ACT_SILU),
-    (8, fmt.META_BF16, fmt.OUT_FP32, fmt.ROUTER_AFFINE4, fmt.GATE_NONE, 128, 64, 64, 16, fmt.ACT_GELU_TANH),
-    (4, fmt.META_BF16, fmt.OUT_FP16, fmt.ROUTER_AFFINE4, fmt.GATE_NONE, 128, 64, 64, 16, fmt.ACT_GELU_TANH),
-    (4, fmt.META_FP16, fmt.OUT_FP32, fmt.ROUTER_AFFINE4, fmt.ROUTER_AFFINE4, 64, 64, 0, 16, fmt.ACT_SILU),
-    (4, fmt.META_BF16, fmt.OUT_FP32, fmt.ROUTER_DENSE_F16, fmt.ROUTER_AFFINE8, 1024, 256, 256, 256, fmt.ACT_SILU),
+    (4, fmt.META_BF16, fmt.OUT_FP16, fmt.ROUTER_AFFINE8, fmt.ROUTER_AFFINE8, 512, 256, 512, 48, fmt.ACT_SILU),
+    (8, fmt.META_BF16, fmt.OUT_FP32, fmt.ROUTER_AFFINE4, fmt.GATE_NONE, 384, 128, 128, 16, fmt.ACT_GELU_TANH),
+    (4, fmt.META_BF16, fmt.OUT_FP16, fmt.ROUTER_AFFINE4, fmt.GATE_NONE, 256, 256, 256, 16, fmt.ACT_GELU_TANH),
+    (4, fmt.META_FP16, fmt.OUT_FP32, fmt.ROUTER_AFFINE4, fmt.ROUTER_AFFINE4, 256, 256, 0, 16, fmt.ACT_SILU),
+    (4, fmt.META_BF16, fmt.OUT_FP32, fmt.ROUTER_DENSE_F16, fmt.ROUTER_AFFINE8, 1024, 512, 256, 256, fmt.ACT_SILU),
 ]
 
 
@@ -105,7 +106,7 @@ def test_resident_step_full_shape_against_oracle_chain(bits):
     hosts = [synthetic.layer(5000 + 3 * l + bits, d=d, f=f, shared_f=f, num_experts=e, routed_bits=bits,
                              meta=fmt.META_BF16) for l in range(layers)]
     moe, devs = _stack(cfg, hosts)
-    x0 = synthetic.hidden_rows(77 + bits, 1, d)
+    x0 = synthetic.hidden_rows(78 + bits, 1, d)
     torch = gu.torch_cuda()
     st = torch.cuda.Stream()
     with torch.cuda.stream(st):
@@ -139,7 +140,7 @@ def test_resident_mode_refuses_shapes_it_does_not_cover():
     x = gu.to_dev(synthetic.hidden_rows(2, 1, 128))
     y = gu.dev_empty(128, "f32")
     moe.set_decode_mode(MoE.DECODE_RESIDENT)
-    with pytest.raises(NvmaiError) as ei:       # shared and routed bit widths differ
+    with pytest.raises(NvmaiError) as ei:       # shared and routed bit widths differ, rows shorter than a 128-byte line
         moe.stack_decode(x, 1, y)
     assert ei.value.code == _lib.EINVAL
     moe.set_decode_mode(MoE.DECODE_AUTO)        # the staged kernels take it
@@ -151,7 +152,7 @@ def test_resident_mode_refuses_shapes_it_does_not_cover():
 def test_bounded_wait_expires_and_the_handle_recovers():
     """A block that never publishes its router logits (host-made: a test hook, nothing faults): every other
     block's wait runs out, synchronize reports the timeout, and the next step is correct again."""
-    layers, d, f, e = 2, 256, 128, 32
+    layers, d, f, e = 2, 256, 256, 32
     cfg = MoEConfig(d=d, f=f, shared_f=f, num_experts=e, top_k=8, routed_bits=4, shared_bits=4,
                     meta_dtype=fmt.META_BF16, out_dtype=fmt.OUT_FP32, max_tokens=1, num_layers=layers)
     hosts = [synthetic.layer(40 + l, d=d, f=f, shared_f=f, num_experts=e, routed_bits=4, meta=fmt.META_BF16)
@@ -166,7 +167,7 @@ def test_bounded_wait_expires_and_the_handle_recovers():
         good_raw, _ = _run(moe, cfg, xd, MoE.DECODE_RESIDENT, st)
         debug_set_wait_limit(20_000_000)            # 20 ms
         try:
-            moe.debug_mute_block(f // 8 + 3)        # a router block (the shared-expert tiles come first)
+            moe.debug_mute_block(3)                 # a block that holds a router row and a shared-expert tile
             y = gu.dev_empty(d, "f32")
             moe.stack_decode(xd, 1, y, stream=st)
             with pytest.raises(NvmaiError) as ei:
