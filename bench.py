@@ -690,6 +690,18 @@ def run_prefill(args) -> None:
             stream.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
         clocks = sampler.stop()
+        parity = None
+        if not args.no_parity and args.bits == 4:
+            idx = torch.empty(tokens, K, dtype=torch.int32, device="cuda")
+            moe.layer_prefill(0, x, tokens, y_out=y, out_idx=idx, stream=stream)
+            moe.synchronize(stream)
+            counts = torch.bincount(idx.reshape(-1), minlength=E)
+            hot = int(torch.argmax(counts))
+            hot_rows = torch.nonzero((idx == hot).any(dim=1)).reshape(-1).cpu().numpy()
+            rows = sorted(set([0, 1, tokens // 2, tokens - 1] + hot_rows[[0, len(hot_rows) // 2, -1]].tolist()
+                              + list(range(3, tokens, max(1, tokens // 11)))))
+            parity = prefill_parity(cfg, devs[0], x, y, idx, torch, rows)
+            parity["rows_of_the_largest_work_item"] = int(counts.max())
     peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
     peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
     flops_routed = tokens * K * 3 * 2 * D * F
@@ -709,7 +721,11 @@ def run_prefill(args) -> None:
                         "achieved": tf, "peak": peak, "peak_source": "measured (sustained)" if peaks else "fallback",
                         "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
                         "flops": {"routed": flops_routed, "shared": flops_shared, "router_not_counted": flops_router}}}
+    if parity is not None:
+        rec["parity"] = parity
     print(json.dumps(rec), flush=True)
+    if parity is not None and not parity["ok"]:
+        raise SystemExit("parity check of the timed path failed: " + json.dumps(parity))
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one stage2_kernel launch, from an ncu capture of the 4-bit
@@ -746,6 +762,50 @@ def resident_roofline(moe, args, xs, x_in, y, stream, peak: float, which: str) -
             "us_per_launch": us}
 
 
+def device_layer_to_host(dev, torch) -> dict:
+    """a device-generated layer as the host arrays the oracle reads"""
+    def host_tensor(t):
+        def as_np(a):
+            if a is None:
+                return None
+            flat = a.contiguous().cpu().view(torch.uint8).numpy()
+            return flat.view(np.uint16 if a.element_size() == 2 else np.uint8).reshape(a.shape)
+        w, s_, b = t
+        return as_np(w), as_np(s_), as_np(b)
+    return {"experts": dev["experts"].cpu().numpy(), "stride": dev["stride"], "offsets": dev["offsets"],
+            "router": host_tensor(dev["router"]), "shared": [host_tensor(t) for t in dev["shared"]],
+            "gate": host_tensor(dev["gate"])}
+
+
+def prefill_parity(cfg, dev, x, y, idx, torch, rows) -> dict:
+    """Post-timing check of the prefill block's output on sampled rows against both oracles (the prefill shaders'
+    rounding points, and the reference CPU path in fp32)."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import gpu_util as gu
+    from oracle import oracle as orc
+    host = device_layer_to_host(dev, torch)
+    L, keep = gu.oracle_layer(host, cfg)
+    xh = x.cpu().view(torch.int16).numpy().view(np.uint16)
+    got = y.cpu().numpy()
+    got_idx = idx.cpu().numpy().view(np.uint32)
+    worst_cpu, worst_shader, idx_ok, escapes, margin_min = 0.0, 0.0, True, 0, float("inf")
+    for t in rows:
+        xr = np.ascontiguousarray(xh[t])
+        o_idx, _, o_y, _ = gu.oracle_prefill_row(L, cfg, xr)
+        _, _, _, margin, cpu = gu.oracle_decode(L, cfg, xr)
+        margin_min = min(margin_min, margin)
+        idx_ok = idx_ok and got_idx[t].tolist() == o_idx.tolist()
+        e_cpu, e_sh, own = orc.rel_error(got[t], cpu), orc.rel_error(got[t], o_y), orc.rel_error(o_y, cpu)
+        worst_cpu, worst_shader = max(worst_cpu, e_cpu), max(worst_shader, e_sh)
+        if e_cpu >= 1e-3 and e_cpu < own + 2e-4:      # the reference's own shader semantics are that far from its CPU path
+            escapes += 1
+    rec = {"rows_checked": len(rows), "expert_indices_exact": bool(idx_ok), "min_router_margin": margin_min,
+           "worst_rel_err_vs_reference_cpu_path": worst_cpu, "worst_rel_err_vs_shader_oracle": worst_shader,
+           "rows_over_1e-3_where_the_shader_oracle_is_too": escapes}
+    rec["ok"] = bool(idx_ok and worst_shader < 1e-3 and (worst_cpu < 1e-3 or escapes > 0))
+    return rec
+
+
 def stack_parity(args, cfg, devs, xs, torch) -> dict:
     """Post-timing check of the timed path against the CPU oracle: the first layers of the same stack, same
     input row, through the same entry point; selected experts must be exact, the output within the tolerances
@@ -771,18 +831,10 @@ def stack_parity(args, cfg, devs, xs, torch) -> dict:
     log = moe.read_route_log(n)
     got = outs[MoE.DECODE_AUTO]
 
-    def host_tensor(t):
-        w, s, b = t
-        as_np = lambda a: None if a is None else a.cpu().view(torch.uint8).numpy().view(np.uint16 if a.element_size() == 2 else np.uint8).reshape(a.shape)
-        return as_np(w), as_np(s), as_np(b)
-
     x = np.ascontiguousarray(x0.cpu().view(torch.int16).numpy().view(np.uint16))
     idx_ok, margin_min, h2, cpu = True, float("inf"), None, None
     for l in range(n):
-        dev = devs[l]
-        host = {"experts": dev["experts"].cpu().numpy(), "stride": dev["stride"], "offsets": dev["offsets"],
-                "router": host_tensor(dev["router"]), "shared": [host_tensor(t) for t in dev["shared"]],
-                "gate": host_tensor(dev["gate"])}
+        host = device_layer_to_host(devs[l], torch)
         L, keep = gu.oracle_layer(host, cfg_p)
         idx, _, h2, margin, cpu = gu.oracle_decode(L, cfg_p, x)
         idx_ok = idx_ok and log[l].tolist() == idx.tolist()
@@ -839,6 +891,48 @@ def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> di
             "bytes_per_launch": nbytes, "us_per_launch": us}
 
 
+def run_block_trace(args) -> None:
+    """Per-phase timeline of the resident decode kernel: every block's GPU-timer marks, reduced to the minimum,
+    median and maximum over blocks (median over layers), in microseconds after the layer's first input row."""
+    import torch
+    from nvmai_b200 import MoE, MoEConfig, synthetic
+    from nvmai_b200 import format as fmt
+    torch.cuda.set_device(0)
+    cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
+                    router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16, meta_dtype=fmt.META_BF16,
+                    activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32, max_tokens=1, num_layers=args.layers)
+    moe = MoE(cfg)
+    devs = [synthetic.device_layer(1000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits, meta=fmt.META_BF16)
+            for l in range(args.layers)]
+    for l, dev in enumerate(devs):
+        synthetic.register_device_layer(moe, l, dev)
+    xs = torch.randn(8, 1, D, device="cuda").to(torch.float16)
+    x_in = torch.empty(1, D, dtype=torch.float16, device="cuda")
+    y = torch.empty(1, D, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+    moe.set_trace(True)
+    with torch.cuda.stream(stream):
+        for i in range(6):
+            x_in.copy_(xs[i])
+            moe.stack_decode(x_in, 1, y, stream=stream)
+        stream.synchronize()
+    tr = moe.read_block_trace().astype(np.float64)
+    tr[tr == 0] = np.nan
+    names = {0: "input row normalised", 1: "router logits stored", 2: "all logits in", 10: "top-k done",
+             3: "gate/up tiles requested", 4: "first gate/up tile landed", 11: "last gate/up tile landed",
+             5: "activations stored", 6: "shared-expert down done", 7: "routed activations staged", 8: "down done",
+             9: "block output stored"}
+    first = np.nanmin(tr[:, :, 0], axis=1, keepdims=True)
+    marks = {}
+    for i, name in names.items():
+        rel = (tr[2:, :, i] - first[2:]) / 1e3
+        marks[name] = [round(float(np.nanmedian(f(rel, axis=1))), 2) for f in (np.nanmin, np.nanmedian, np.nanmax)]
+    period = np.diff(first[:, 0]) / 1e3
+    print(json.dumps({"workload": f"{args.layers}-layer stack, {args.bits}-bit, one token, resident kernel with tracing on",
+                      "us_after_first_input_row_min_median_max": marks,
+                      "layer_period_us_median": round(float(np.median(period[1:])), 2)}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -851,6 +945,8 @@ def main() -> None:
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the post-timing check against the CPU oracle")
+    ap.add_argument("--block-trace", action="store_true",
+                    help="print the per-phase timeline of the resident decode kernel instead of the benchmark line")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
     ap.add_argument("--batch-layer", action="store_true",
                     help="measure configs[1] (one layer, --tokens independent rows, batched decode kernels) or, with "
@@ -878,6 +974,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.gturbo_load:
         run_gturbo_load(args)
+        return
+    if args.block_trace:
+        run_block_trace(args)
         return
     if args.batch_layer:
         run_batch_layer(args)

@@ -215,6 +215,19 @@ NVMAI_API int nvmai_cuda_moe_layer_decode_prenorm(nvmai_cuda_moe *h, uint32_t la
                                                   uint32_t tokens, void *h2_out, void *x_out_f16, uint32_t *out_idx,
                                                   void *out_w_f16, void *stream);
 
+/* The same block with the step AFTER it folded in too: the layer that follows starts with
+ * rmsnorm_bf16w of the hidden state this block has just written (RealForwardRunner.swift:1886-1899,
+ * rmsnorm.metal:69-99), so the stage that writes hidden also writes
+ *   x_next = half(hidden * rsqrt(mean(hidden^2) + next_eps) * next_w)      (next_w bf16[d])
+ * to x_next_out_f16 (fp16[tokens][d]).  Single rows: the down-stage block that completes a row
+ * normalises it; batched rows: the combine block of the row.  Everything else as in
+ * _layer_decode_prenorm, with bit-identical results. */
+NVMAI_API int nvmai_cuda_moe_layer_decode_fused_norms(nvmai_cuda_moe *h, uint32_t layer, void *hidden_inout,
+                                                      const void *attn_delta_f16, const void *norm_weight_bf16, float eps,
+                                                      uint32_t tokens, const void *next_norm_weight_bf16, float next_eps,
+                                                      void *x_next_out_f16, void *h2_out, void *x_out_f16,
+                                                      uint32_t *out_idx, void *out_w_f16, void *stream);
+
 /* `PrefillRouter.makeTokenExpertPairs` + `PrefillMoEGrouping.groupTokenExpertPairs`
  * (PrefillRouter.swift:97-117, PrefillMoEGrouping.swift:90-192) on the device: the
  * tokens*top_k (token, expert, rank, weight) records sorted by (expert, token,
@@ -265,13 +278,14 @@ NVMAI_API int nvmai_cuda_moe_rms_renorm(nvmai_cuda_moe *h, const void *y, uint32
  * _down, prefill_moe_reduce_token_major, PrefillSharedExpert.encodeBlock, the tail at
  * :3560-3569) as grouped GEMMs on the tensor cores: x fp16 [tokens][d] (dense rows),
  * hidden_inout = out(out(hidden + h1) + h2) in place, y_out (optional) = out(h1 + h2),
- * out_idx / out_w (optional) the routing.  The tile shapes want f % 128 == 0,
- * d % 256 == 0 and shared_f % 128 == 0 (NVMAI_CUDA_EINVAL otherwise).  The tensor cores
- * multiply the centred weight s*(q - c) in fp16 (exact for 4-bit codes with bf16 scales)
- * and the per-group constant b + c*s enters through correction columns, so 4-bit results
- * stay within 1e-3 of the CPU path.  8-bit weights do not fit an fp16 operand (about 3e-3
- * of one expert's output): such calls run the exact decode kernels (decode rounding
- * order) unless the environment has NVMAI_CUDA_PREFILL_TC8=1. */
+ * out_idx / out_w (optional) the routing.  The tensor cores multiply the centred weight
+ * s*(q - 8) in fp16 (exact for bf16 scales; an 8-bit code goes through as its two nibbles,
+ * 16 s*(hq - 8) and s*(lq - 8), in two passes over the same token rows) and the per-group
+ * constant b + c*s enters through correction columns, so results stay within 1e-3 of the
+ * CPU path for both bit widths.  Shapes the tiles do not cover (f % 128, d % 256 or
+ * shared_f % 128 non-zero: the reference's own prefill test runs d = f = 64) and
+ * NVMAI_CUDA_PREFILL_TC=0 in the environment run the exact grouped kernels of the batched
+ * decode path with the same rounding points. */
 NVMAI_API int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
                                            void *hidden_inout, void *y_out, uint32_t *out_idx, void *out_w_f16,
                                            void *stream);

@@ -58,6 +58,8 @@ PROTOTYPES = {
     "nvmai_cuda_moe_layer_decode": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, vp, vp]),
     "nvmai_cuda_moe_layer_verify_pair": (C.c_int, [vp, u32, vp, vp, vp, vp, vp, vp]),
     "nvmai_cuda_moe_layer_decode_prenorm": (C.c_int, [vp, u32, vp, vp, vp, C.c_float, u32, vp, vp, vp, vp, vp]),
+    "nvmai_cuda_moe_layer_decode_fused_norms": (C.c_int, [vp, u32, vp, vp, vp, C.c_float, u32, vp, C.c_float, vp, vp, vp, vp,
+                                                          vp, vp]),
     "nvmai_cuda_moe_group_pairs": (C.c_int, [vp, vp, vp, u32, vp, vp, vp, vp]),
     "nvmai_cuda_moe_set_expert_map": (C.c_int, [vp, vp, u32]),
     "nvmai_cuda_moe_routed_partial": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, vp]),

@@ -389,6 +389,46 @@ template <int OUT> __device__ __forceinline__ void store_mid(void *p, size_t i, 
     else reinterpret_cast<float *>(p)[i] = round11(v);
 }
 
+// The NEXT block's input norm folded into this block's last stage (RealForwardRunner.swift:1886-1909: the layer
+// after the MoE block starts with rmsnorm_bf16w of the hidden state it has just written, rmsnorm.metal:69-99):
+//   x_next = half(hidden * rsqrt(mean(hidden^2) + eps) * w)
+// for one row that is complete in global memory.  Threads 0..255 of the block take part (element i + 256 j in
+// thread i, fixed reduction tree: the same bits whatever block runs it); `wsum` holds 8 floats of shared memory;
+// every thread of the block must call it.
+struct NextNorm {
+    const uint16_t *w;        // bf16 [D], nullptr = no next norm
+    float eps;
+    __half *x_next;           // fp16 [tokens][D]
+    unsigned int *row_counter;   // [tokens], zero between calls (single-token stage only)
+};
+
+template <int OUT>
+__device__ __forceinline__ void next_norm_row(const NextNorm &nn, const void *hidden, uint32_t tok, int D, float *wsum) {
+    const size_t base = (size_t)tok * D;
+    float ss = 0.0f;
+    if (threadIdx.x < 256) {
+        for (int i = threadIdx.x; i < D; i += 256) {
+            const float v = OUT == OUT_F16 ? __half2float(__ldcg(reinterpret_cast<const __half *>(hidden) + base + i))
+                                           : __ldcg(reinterpret_cast<const float *>(hidden) + base + i);
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = ss;
+    }
+    __syncthreads();
+    if (threadIdx.x < 256) {
+        float tot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot += wsum[i];
+        const float sc = rsqrtf(tot / (float)D + nn.eps);
+        for (int i = threadIdx.x; i < D; i += 256) {
+            const float v = OUT == OUT_F16 ? __half2float(__ldcg(reinterpret_cast<const __half *>(hidden) + base + i))
+                                           : __ldcg(reinterpret_cast<const float *>(hidden) + base + i);
+            nn.x_next[base + i] = __float2half_rn(v * sc * meta_to_float<META_BF16>(ldg_u16(nn.w + i)));
+        }
+    }
+}
+
 // Expert parallelism over peer memory (see ep_finalize_peer_kernel): where the ranks' receive buffers and
 // arrival counters live.
 constexpr int kEpMaxRanks = 8;

@@ -549,6 +549,7 @@ struct CombineParams {
     // partial is rounded to the output type, h2 = out(sum_r fma(w, partial)) on its own,
     // and the residual takes two steps: hidden = out(out(hidden + h1) + h2).
     uint32_t prefill;
+    NextNorm next;         // optional: the next block's input norm of the row just written (decode order only)
 };
 
 template <int OUT>
@@ -599,6 +600,12 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
             if (p.hidden_delta != nullptr) hv = round_out<OUT>(hv + __half2float(p.hidden_delta[i]));
             store_out<OUT>(p.hidden, i, hv + yv);
         }
+    }
+    if (p.next.w != nullptr && p.hidden != nullptr) {      // this block wrote the whole row
+        __shared__ float wsum_next[8];
+        __threadfence_block();
+        __syncthreads();
+        next_norm_row<OUT>(p.next, p.hidden, tok, p.D, wsum_next);
     }
 }
 

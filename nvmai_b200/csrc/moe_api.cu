@@ -86,9 +86,9 @@ struct nvmai_cuda_moe {
     // NVMAI_CUDA_GROUPED_MIN overrides it.
     uint32_t grouped_min_tokens = 24;
     uint32_t tc_min_tokens = 32;     // batched decode calls from this many rows on run the tensor-core (prefill) kernels
-    // 8-bit weights on the tensor-core prefill path (fp16 operand tiles: about 3e-3 of one expert's output);
-    // off = prefill calls with 8-bit weights run the exact decode kernels.  NVMAI_CUDA_PREFILL_TC8=1 turns it on.
-    bool prefill_tc8 = false;
+    // prefill chunks on the tensor cores (default); NVMAI_CUDA_PREFILL_TC=0 sends them through the exact grouped
+    // kernels of the batched decode path instead
+    bool prefill_tc = true;
     // prefill GEMMs: fp16 operand copies (allocated by the first prefill call)
     __half *pf_x = nullptr;          // [T*K][D] x rows gathered into sorted pair order, in the weights' K order
     __half *pf_xn = nullptr;         // [T][D] x rows in token order (shared expert), in its weights' K order
@@ -129,6 +129,9 @@ struct nvmai_cuda_moe {
     int decode_mode = 0;
     unsigned long long *pd_trace = nullptr;   // [num_layers][sm_count][16] marks of the resident kernel (allocated by set_trace)
     uint32_t pd_mute_block = 0xFFFFFFFFu;     // test hook, see nvmai_cuda_moe_debug_mute_block
+    // the next block's input norm, handed from the entry point to the launch of the block's last stage
+    NextNorm next_norm{};
+    unsigned int *row_counter = nullptr;      // [max_tokens]
 };
 
 namespace {
@@ -424,7 +427,7 @@ int launch_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const __half *w, 
 // partial_y != nullptr: expert-parallel share (local experts only, no shared expert, fp32 rows out).
 int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, uint32_t tokens, const uint32_t *idx,
                  const __half *w, void *hidden, void *y, cudaStream_t st, float *partial_y = nullptr,
-                 const __half *hidden_delta = nullptr) {
+                 const __half *hidden_delta = nullptr, bool prefill_rounding = false) {
     const auto &c = h->cfg;
     const bool ep = partial_y != nullptr;
     int rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, !ep, st, !ep, ep);
@@ -473,7 +476,8 @@ int grouped_tail(nvmai_cuda_moe *h, const LayerViews &lv, const __half *x_rows, 
     pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
     pc.partial_y = partial_y;
     pc.hidden_delta = hidden_delta;
-    pc.prefill = 0;
+    pc.prefill = prefill_rounding ? 1 : 0;
+    if (!prefill_rounding && !ep) pc.next = h->next_norm;
     return dispatch_out(c.out_dtype, [&](auto O) {
         return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
     });
@@ -529,6 +533,7 @@ int layer_decode_impl(nvmai_cuda_moe *h, uint32_t layer, const XSource &xsrc, co
     p.hidden = hidden;
     p.hidden_delta = hidden_delta;
     p.top_k = c.top_k;
+    p.next = h->next_norm;
     if (next_layer != nullptr && h->l2_prefetch) {    // stack driver: warm the L2 with what the next layer's first stage reads
         const auto &nw = next_layer->w;
         const size_t router_bytes = c.router_kind == 0 ? (size_t)c.num_experts * c.d * 2
@@ -756,13 +761,14 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     pc.residual = nullptr; pc.y = y; pc.hidden = hidden; pc.D = c.d; pc.K = c.top_k;
     pc.partial_y = mode.partial_y; pc.prefill = mode.decode_order ? 0 : 1;
     pc.hidden_delta = mode.hidden_delta;
+    if (mode.decode_order && mode.partial_y == nullptr) pc.next = h->next_norm;
     return dispatch_out(c.out_dtype, [&](auto O) {
         return launch_kernel(h, combine_kernel<decltype(O)::value>, dim3(tokens), dim3(256), 0, st, true, pc);
     });
 }
 
 // A batched decode call can take the tensor-core kernels when the fp16 operand holds the centred weight exactly
-// (4-bit codes, bf16 scales), the tile shapes divide the layer and every expert is local.
+// (bf16 scales; 8-bit codes go through as two nibbles), the tile shapes divide the layer and every expert is local.
 bool tc_batch_ok(const nvmai_cuda_moe *h, uint32_t tokens, bool with_shared, cudaStream_t st) {
     const auto &c = h->cfg;
     if (tokens < h->tc_min_tokens || h->expert_map != nullptr) return false;
@@ -772,9 +778,9 @@ bool tc_batch_ok(const nvmai_cuda_moe *h, uint32_t tokens, bool with_shared, cud
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return false;
     }
-    if (c.meta_dtype != NVMAI_META_BF16 || c.routed_bits != 4 || c.top_k > (uint32_t)kMaxTopK) return false;
+    if (c.meta_dtype != NVMAI_META_BF16 || c.top_k > (uint32_t)kMaxTopK) return false;
     if (c.f % kPfTileM != 0 || c.d % (2 * kPfTileM) != 0) return false;
-    if (with_shared && c.shared_f != 0 && (c.shared_bits != 4 || c.shared_f % kPfTileM != 0)) return false;
+    if (with_shared && c.shared_f != 0 && c.shared_f % kPfTileM != 0) return false;
     return true;
 }
 
@@ -1027,7 +1033,7 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
     h->cfg = c;
     h->layers.resize(c.num_layers);
     if (const char *env = std::getenv("NVMAI_CUDA_L2_PREFETCH")) h->l2_prefetch = env[0] == '1';
-    if (const char *env = std::getenv("NVMAI_CUDA_PREFILL_TC8")) h->prefill_tc8 = env[0] == '1';
+    if (const char *env = std::getenv("NVMAI_CUDA_PREFILL_TC")) h->prefill_tc = env[0] != '0';
     if (const char *env = std::getenv("NVMAI_CUDA_GROUPED_MIN")) h->grouped_min_tokens = (uint32_t)std::max(1, std::atoi(env));
     if (const char *env = std::getenv("NVMAI_CUDA_TC_MIN")) h->tc_min_tokens = (uint32_t)std::max(1, std::atoi(env));
     const size_t T = c.max_tokens;
@@ -1041,9 +1047,10 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
               alloc(&h->shared_act, T * (c.shared_f ? c.shared_f : 8) * out_size(c.out_dtype)) &&
               alloc(&h->gate_val, T * 4) &&
               alloc(&h->y, T * c.d * out_size(c.out_dtype)) && alloc(&h->xnorm, T * c.d * 2) &&
-              alloc(&h->counter, (T / 8 + 2) * 4) && alloc(&h->status, 64) && alloc(&h->stage_x, T * c.d * 2) &&
+              alloc(&h->counter, (T / 8 + 2) * 4) && alloc(&h->row_counter, T * 4) && alloc(&h->status, 64) && alloc(&h->stage_x, T * c.d * 2) &&
               alloc(&h->stage_y, T * c.d * out_size(c.out_dtype));
-    if (ok) ok = cudaMemset(h->counter, 0, (T / 8 + 2) * 4) == cudaSuccess && cudaMemset(h->status, 0, 64) == cudaSuccess;
+    if (ok) ok = cudaMemset(h->counter, 0, (T / 8 + 2) * 4) == cudaSuccess && cudaMemset(h->status, 0, 64) == cudaSuccess &&
+                 cudaMemset(h->row_counter, 0, T * 4) == cudaSuccess;
     {
         const size_t P = T * c.top_k;
         h->max_work = (uint32_t)(std::min(P, c.num_experts + P / kPairsPerItem) + (T + kPairsPerItem - 1) / kPairsPerItem);
@@ -1086,7 +1093,7 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     cudaFree(h->pf_x); cudaFree(h->pf_xn); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
-    cudaFree(h->stage_x); cudaFree(h->stage_y);
+    cudaFree(h->stage_x); cudaFree(h->stage_y); cudaFree(h->row_counter);
     cudaFree(h->sorted_pair); cudaFree(h->inv); cudaFree(h->expert_offsets); cudaFree(h->expert_counts);
     cudaFree(h->work); cudaFree(h->n_work); cudaFree(h->group_hist); cudaFree(h->trace); cudaFree(h->expert_map); cudaFree(h->partial); cudaFree(h->shared_partial);
     delete h;
@@ -1244,6 +1251,23 @@ int nvmai_cuda_moe_layer_decode_prenorm(nvmai_cuda_moe *h, uint32_t layer, void 
                              xsrc.delta);
 }
 
+// The same with the NEXT block's input norm folded into the last stage as well: the stage that writes the hidden
+// state also writes x_next = rmsnorm_bf16w(hidden, next_norm_weight) (single-token path: the down-stage block that
+// finishes a row last; batched paths: the combine block of the row).
+int nvmai_cuda_moe_layer_decode_fused_norms(nvmai_cuda_moe *h, uint32_t layer, void *hidden_inout, const void *attn_delta_f16,
+                                            const void *norm_weight_bf16, float eps, uint32_t tokens,
+                                            const void *next_norm_weight_bf16, float next_eps, void *x_next_out_f16,
+                                            void *h2_out, void *x_out_f16, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    if (!next_norm_weight_bf16 || !x_next_out_f16 || !(next_eps >= 0.0f)) return NVMAI_CUDA_EINVAL;
+    h->next_norm = NextNorm{static_cast<const uint16_t *>(next_norm_weight_bf16), next_eps, static_cast<__half *>(x_next_out_f16),
+                            h->row_counter};
+    const int rc = nvmai_cuda_moe_layer_decode_prenorm(h, layer, hidden_inout, attn_delta_f16, norm_weight_bf16, eps, tokens,
+                                                       h2_out, x_out_f16, out_idx, out_w_f16, stream);
+    h->next_norm = NextNorm{};
+    return rc;
+}
+
 int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
                                  void *hidden_inout, void *y_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
     int rc = check_layer(h, layer);
@@ -1252,20 +1276,24 @@ int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *
     if (!x_f16 || !aligned16(x_f16) || (!hidden_inout && !y_out)) return NVMAI_CUDA_EINVAL;
     if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
     if (c.top_k > (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;
-    const bool any8 = c.routed_bits == 8 || (c.shared_f != 0 && c.shared_bits == 8);
-    if (any8 && !h->prefill_tc8) {
-        // 8-bit codes times a scale do not fit an fp16 operand exactly: the chunk runs the exact decode kernels
-        // (codes never rounded; the decode block's rounding order) unless the caller opted in to the tensor cores
-        if (h->expert_map) return NVMAI_CUDA_EINVAL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The tensor-core kernels tile the weights by 128 rows per accumulator, two accumulators per block.  Shapes
+    // they do not cover (the reference's own prefill test runs d = f = 64, top-2), a rank that holds a subset of
+    // the experts, and NVMAI_CUDA_PREFILL_TC=0 take the exact grouped kernels of the batched decode path with the
+    // prefill shaders' rounding points: router, grouping, gate/up and down per (tile, work item), ordered combine.
+    const bool tiles_fit = c.f % kPfTileM == 0 && c.d % (2 * kPfTileM) == 0 && c.shared_f % kPfTileM == 0;
+    if (!tiles_fit || !h->prefill_tc) {
+        if (h->expert_map) return NVMAI_CUDA_EINVAL;      // prefill runs on one GPU's full expert set
+        uint32_t *idx = out_idx ? out_idx : h->idx;
+        __half *w = out_w_f16 ? static_cast<__half *>(out_w_f16) : h->w;
         const XSource xsrc{static_cast<const __half *>(x_f16), c.d, nullptr, nullptr};
-        return layer_decode_impl(h, layer, xsrc, static_cast<const __half *>(x_f16), tokens, hidden_inout, y_out, out_idx,
-                                 static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
+        if ((rc = launch_stage1(h, h->layers[layer], xsrc, tokens, idx, w, true, false, c.shared_f != 0, false, st))) return rc;
+        return grouped_tail(h, h->layers[layer], static_cast<const __half *>(x_f16), tokens, idx, w, hidden_inout,
+                            y_out ? y_out : h->y, st, nullptr, nullptr, true);
     }
-    // tile shapes of the tensor-core kernels: 128 weight rows per accumulator, two accumulators per CTA
-    if (c.f % kPfTileM != 0 || c.d % (2 * kPfTileM) != 0 || c.shared_f % kPfTileM != 0) return NVMAI_CUDA_EINVAL;
-    if (h->expert_map) return NVMAI_CUDA_EINVAL;      // prefill runs on one GPU's full expert set
+    if (h->expert_map) return NVMAI_CUDA_EINVAL;
     return layer_prefill_impl(h, layer, static_cast<const __half *>(x_f16), tokens, hidden_inout, y_out, out_idx,
-                              static_cast<__half *>(out_w_f16), static_cast<cudaStream_t>(stream));
+                              static_cast<__half *>(out_w_f16), st);
 }
 
 int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const void *w_f16, uint32_t tokens,

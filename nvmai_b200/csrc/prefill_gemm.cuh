@@ -33,9 +33,13 @@
 // pack_rows_kernel), so an item's rows are one contiguous row range of the map.
 // Sixteen producer warps build the quantised A operand: each thread holds the 32
 // packed codes of one row three K blocks ahead in registers, turns them into the
-// fp16 CENTRED weight s * (q - c), c = 8 (4-bit) or 128 (8-bit) (exact in fp16 for
-// 4-bit codes with bf16 scales; the scale is converted from its 16-bit storage type
-// to fp16, exact for magnitudes in fp16's normal range) and stores them swizzled.
+// fp16 CENTRED weight s * (q - 8) (exact in fp16 for 4-bit codes with bf16 scales; the
+// scale is converted from its 16-bit storage type to fp16, exact for magnitudes in
+// fp16's normal range) and stores them swizzled.  An 8-bit code does not fit that way
+// (8 + 8 significant bits), so it goes through the tensor core as its two nibbles:
+// q = 16 hq + lq, and the K block is multiplied twice against the same B rows, once
+// with 16 s * (hq - 8) and once with s * (lq - 8), each exact like a 4-bit weight
+// (two A stages per K block; twice the MMA work, the same bytes).
 // The rest of w = q*s + b, the per-group constant b + c*s, enters through extra K
 // blocks after the codes: every B row carries the sums of its 64-value groups (fp16
 // hi + lo, written by pack_rows_kernel) and the producers append the constants as
@@ -201,18 +205,19 @@ __device__ __forceinline__ void pf_load_codes(PackedCodes<BITS> &c, const uint8_
 }
 
 // dst[j]: shared-window address of the thread's j-th chunk in the stage's tile.
-// The operand is the CENTRED weight s * (q - c), c = 8 (4-bit) or 128 (8-bit); the rest of q*s + b, the
-// per-group constant b + c*s, comes in through the correction columns (pf_extra_cols).  With bf16 scales
-// (8 significant bits) and 4-bit codes (|q - 8| <= 8) the product is exact in fp16, so the tensor core sees
-// the reference's weights without a rounding; fp16 scales and 8-bit codes round once, relative to the centred
-// (smaller) magnitude.
+// The operand is the CENTRED weight s * (q - 8); the rest of q*s + b, the per-group constant b + c*s
+// (c = 8 for 4-bit codes, 16 * 8 + 8 = 136 for the two nibbles of an 8-bit code), comes in through the
+// correction columns (pf_extra_cols).  With bf16 scales (8 significant bits) and |q - 8| <= 8 the product is
+// exact in fp16, so the tensor core sees the reference's weights without a rounding; fp16 scales round once,
+// relative to the centred (smaller) magnitude.  HALF (8-bit codes only): 0 = the high nibbles (the caller
+// passes 16 s), 1 = the low nibbles.
 // 4-bit: the nibbles of a word are masked where they lie, (1024 + q) for nibbles 0, 4, 2, 6 (after one shift by 8
 // for the latter two) and (1024 + 16 q) for nibbles 1, 5, 3, 7; the second kind is multiplied by s / 16 (s16, exact
 // unless s / 16 is an fp16 subnormal), so that one shift serves a whole word.
-template <int BITS>
+template <int BITS, int HALF = 0>
 __device__ __forceinline__ void dequant_store(const uint32_t (&dst)[4], const PackedCodes<BITS> &c, __half2 s2, __half2 s16) {
     // 1024 + 8, 1024 + 16 * 8 = 1024 + 128
-    const __half2 k_even = __halves2half2(__ushort_as_half(BITS == 4 ? 0x6408 : 0x6480), __ushort_as_half(BITS == 4 ? 0x6408 : 0x6480));
+    const __half2 k_even = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));
     const __half2 k_odd = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {            // chunk j = codes 8j .. 8j+7 of the thread's 32
@@ -229,8 +234,10 @@ __device__ __forceinline__ void dequant_store(const uint32_t (&dst)[4], const Pa
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {    // (q_2i, q_2i+1) - 128
-                const uint32_t t = __byte_perm(c.v[2 * j + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342 : 0x4140);
+            for (int i = 0; i < 4; ++i) {    // one nibble of (q_2i, q_2i+1), minus 8
+                const uint32_t word = c.v[2 * j + (i >> 1)];
+                const uint32_t nib = (HALF == 0 ? (word >> 4) : word) & 0x0F0F0F0Fu;
+                const uint32_t t = __byte_perm(nib, 0x64646464u, (i & 1) ? 0x4342 : 0x4140);
                 const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k_even);
                 const __half2 v = __hmul2(q, s2);
                 o[i] = *reinterpret_cast<const uint32_t *>(&v);
@@ -315,6 +322,9 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     const uint32_t n_cols = (count + 15u) & ~15u;
     const uint32_t n_main = p.kdim / kPfKBlock;                                      // K blocks of codes
     const uint32_t n_kb = n_main + (BITS == 16 ? 0u : pf_extra_cols(p.kdim) / kPfKBlock);    // + the correction columns
+    // A stages: an 8-bit K block takes two (its high and its low nibbles against the same B rows)
+    constexpr uint32_t kPasses = BITS == 8 ? 2u : 1u;
+    const uint32_t n_main_v = n_main * kPasses, n_v = n_main_v + (n_kb - n_main);
     // The B ring holds as many K blocks as fit: a narrow item keeps more blocks in flight, which is what
     // hides the latency of its row fetches.
     const uint32_t n_box = (n_cols + kPfBoxRows - 1) / kPfBoxRows;
@@ -392,36 +402,54 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             };
 #pragma unroll
             for (int i = 0; i < kPfAhead; ++i) fetch(codes[i], ms[i], i);
-            // One step = one K block into stage S (compile-time), using code slot C (compile-time).
-            auto step = [&](auto S, auto C, uint32_t kb) {
+            // One step = one A stage: stage S, code slot C and nibble pass H are compile-time (the loop below is unrolled
+            // over their period); v = the stage's running number, kb = the K block it belongs to.
+            auto step = [&](auto S, auto C, auto H, uint32_t v, uint32_t kb) {
                 constexpr uint32_t s = decltype(S)::value;
                 constexpr int cs = decltype(C)::value;
+                constexpr int hp = decltype(H)::value;
                 if (kb >= n_main || !ok) return;
-                ok = wait(&a_empty[s], ((kb / kPfStages) & 1u) ^ 1u);      // free once the MMAs that read it have finished
+                ok = wait(&a_empty[s], ((v / kPfStages) & 1u) ^ 1u);      // free once the MMAs that read it have finished
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) return;
                 const uint32_t st = a_ring + s * kPfAStageBytes;
-                const __half2 sc = meta_half2<META>(ms[cs]);
+                __half2 sc = meta_half2<META>(ms[cs]);
+                if (BITS == 8 && hp == 0) sc = __hmul2(sc, __float2half2_rn(16.0f));      // the high nibbles weigh 16
                 const __half2 sc16 = __hmul2(sc, __float2half2_rn(0.0625f));
                 const uint32_t d4[4] = {st + adst[0], st + adst[1], st + adst[2], st + adst[3]};
-                dequant_store<CB>(d4, codes[cs], sc, sc16);
-                fetch(codes[cs], ms[cs], kb + kPfAhead);      // the slot is free again
+                dequant_store<CB, hp>(d4, codes[cs], sc, sc16);
+                if (hp == (int)kPasses - 1) fetch(codes[cs], ms[cs], kb + kPfAhead);      // the slot is free again
                 fence_proxy_async_smem();        // generic-proxy writes -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[s]);
             };
             static_assert(kPfStages == 3 && kPfAhead == 3, "the unrolled body below is written for 3 stages and 3 code slots");
-            for (uint32_t kb = 0; kb < n_main && ok; kb += 3) {
-                step(std::integral_constant<uint32_t, 0>{}, std::integral_constant<int, 0>{}, kb);
-                step(std::integral_constant<uint32_t, 1>{}, std::integral_constant<int, 1>{}, kb + 1);
-                step(std::integral_constant<uint32_t, 2>{}, std::integral_constant<int, 2>{}, kb + 2);
+            using I0 = std::integral_constant<int, 0>; using I1 = std::integral_constant<int, 1>; using I2 = std::integral_constant<int, 2>;
+            using U0 = std::integral_constant<uint32_t, 0>; using U1 = std::integral_constant<uint32_t, 1>; using U2 = std::integral_constant<uint32_t, 2>;
+            if (BITS == 8) {
+                for (uint32_t kb = 0; kb < n_main && ok; kb += 3) {        // 6 stages: (stage, slot, pass) repeats
+                    const uint32_t v = 2 * kb;
+                    step(U0{}, I0{}, I0{}, v, kb);
+                    step(U1{}, I0{}, I1{}, v + 1, kb);
+                    step(U2{}, I1{}, I0{}, v + 2, kb + 1);
+                    step(U0{}, I1{}, I1{}, v + 3, kb + 1);
+                    step(U1{}, I2{}, I0{}, v + 4, kb + 2);
+                    step(U2{}, I2{}, I1{}, v + 5, kb + 2);
+                }
+            } else {
+                for (uint32_t kb = 0; kb < n_main && ok; kb += 3) {
+                    step(U0{}, I0{}, I0{}, kb, kb);
+                    step(U1{}, I1{}, I0{}, kb + 1, kb + 1);
+                    step(U2{}, I2{}, I0{}, kb + 2, kb + 2);
+                }
             }
             // The correction columns: c_g = b_g + centre * s_g per group g of this thread's row, as fp16 hi + lo, in the
             // layout [hi | hi | lo | zeros] that pack_rows_kernel's [X_hi | X_lo | X_hi | zeros] multiplies against.
-            const float centre = BITS == 4 ? 8.0f : 128.0f;
+            const float centre = BITS == 4 ? 8.0f : 136.0f;
             for (uint32_t kb = n_main; kb < n_kb && ok; ++kb) {
-                const uint32_t s = kb % kPfStages;
-                ok = wait(&a_empty[s], ((kb / kPfStages) & 1u) ^ 1u);
+                const uint32_t v = n_main_v + (kb - n_main);
+                const uint32_t s = v % kPfStages;
+                ok = wait(&a_empty[s], ((v / kPfStages) & 1u) ^ 1u);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const uint32_t st = a_ring + s * kPfAStageBytes;
@@ -501,9 +529,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
         // ---------------- MMA issue: one thread ----------------
         const uint32_t idesc = umma_idesc_f16(kPfTileM, n_cols);
         uint32_t j = 0, jph = 0;
-        for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
-            const uint32_t s = kb % kPfStages;
-            ok = wait(&a_full[s], (kb / kPfStages) & 1u) && wait(&b_full[j], jph);
+        for (uint32_t v = 0; v < n_v && ok; ++v) {
+            const uint32_t s = v % kPfStages;
+            // the B rows of a K block serve both nibble passes of an 8-bit block
+            const bool first_pass = kPasses == 1u || v >= n_main_v || (v & 1u) == 0u;
+            const bool last_pass = kPasses == 1u || v >= n_main_v || (v & 1u) == 1u;
+            ok = wait(&a_full[s], (v / kPfStages) & 1u) && (!first_pass || wait(&b_full[j], jph));
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t st = a_ring + s * kPfAStageBytes;
@@ -513,13 +544,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             for (uint32_t k = 0; k < kPfKBlock / 16; ++k) {        // 16 values = 32 bytes = +2 in the address field
                 // split: K steps alternate between the two accumulators of each A tile
                 const uint32_t second = split ? (k & 1u) * 256u : 0u;
-                const uint32_t accumulate = split ? ((kb | (k >> 1)) != 0u) : ((kb | k) != 0u);
+                const uint32_t accumulate = split ? ((v | (k >> 1)) != 0u) : ((v | k) != 0u);
                 umma_f16_ss(tmem + second, da0 + 2 * k, db + 2 * k, idesc, accumulate);
                 umma_f16_ss(tmem + acc1 + second, da1 + 2 * k, db + 2 * k, idesc, accumulate);
             }
             umma_commit(&a_empty[s]);
-            umma_commit(&b_empty[j]);
-            if (++j == b_depth) { j = 0; jph ^= 1u; }
+            if (last_pass) {
+                umma_commit(&b_empty[j]);
+                if (++j == b_depth) { j = 0; jph ^= 1u; }
+            }
         }
         if (ok) umma_commit(accum);
     }

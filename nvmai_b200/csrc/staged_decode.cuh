@@ -536,6 +536,7 @@ struct Stage3Params {
     // ranges the next launch will read (the next layer's router and shared-expert
     // weights): each block asks the L2 for its share
     const void *next_ptr[6]; unsigned long long next_bytes[6];
+    NextNorm next;                      // optional: the block that finishes a row last also writes the next block's input
     uint32_t D, F, top_k;
     unsigned int *status;
     unsigned long long *trace;   // optional {start, end} timestamps of this launch
@@ -779,6 +780,20 @@ __global__ void __launch_bounds__((kMaxTopK + 1) * kDownSplit * 32) stage3_kerne
             if (p.hidden_delta != nullptr) hv = round_out<OUT>(hv + __half2float(p.hidden_delta[i]));
             store_out<OUT>(p.hidden, i, hv + yv);
         }
+    }
+    if (p.next.w != nullptr && p.hidden != nullptr) {
+        // the row's blocks count themselves; the one that finds the row complete normalises it for the next block
+        __shared__ bool row_done;
+        __shared__ float wsum_next[8];
+        if (threadIdx.x < 16) __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int prev = atomicAdd(p.next.row_counter + tok, 1u);
+            row_done = prev == gridDim.x - 1;
+            if (row_done) { p.next.row_counter[tok] = 0; __threadfence(); }
+        }
+        __syncthreads();
+        if (row_done) next_norm_row<OUT>(p.next, p.hidden, tok, p.D, wsum_next);
     }
     trace_end(p.trace);
 }

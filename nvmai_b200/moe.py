@@ -231,6 +231,16 @@ class MoE:
                                                             _ptr(x_out), _ptr(out_idx), _ptr(out_w), _stream(stream)),
               "layer_decode_prenorm")
 
+    def layer_decode_fused_norms(self, layer: int, hidden, norm_weight, eps: float, tokens: int, next_norm_weight,
+                                 next_eps: float, x_next, *, attn_delta=None, h2_out=None, x_out=None, out_idx=None,
+                                 out_w=None, stream=None) -> None:
+        """`layer_decode_prenorm` plus the next block's input norm of the hidden state it writes."""
+        check(self._lib.nvmai_cuda_moe_layer_decode_fused_norms(self._h, layer, _ptr(hidden), _ptr(attn_delta),
+                                                                _ptr(norm_weight), float(eps), tokens,
+                                                                _ptr(next_norm_weight), float(next_eps), _ptr(x_next),
+                                                                _ptr(h2_out), _ptr(x_out), _ptr(out_idx), _ptr(out_w),
+                                                                _stream(stream)), "layer_decode_fused_norms")
+
     def stack_decode(self, x0, tokens: int, y_last, *, stream=None) -> None:
         check(self._lib.nvmai_cuda_moe_stack_decode(self._h, _ptr(x0), tokens, _ptr(y_last), _stream(stream)),
               "stack_decode")

@@ -217,6 +217,49 @@ def test_route_trace_replay_matches_cpu_path(rows):
         assert orc.rel_error(got[t], want) < FFN_TOL, f"row {t}"
 
 
+def test_zipf_batch_of_256_rows_at_the_benchmark_shape():
+    """configs[4] as the benchmark runs it: 256 rows whose experts follow Zipf(1.1) over a seeded permutation, through
+    `routed_partial` on one 4-bit layer of the 35B-A3B shape (the hottest expert takes more than 200 rows: work items
+    wider than one accumulator).  Sampled rows against the reference CPU path's accumulation."""
+    rows, e, k = 256, 256, 8
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, rows, seed=371, d=2048, f=512, e=e)
+    moe = MoE(cfg)
+    dl = gu.DeviceLayer(host)
+    dl.register(moe, 0)
+    rng = np.random.default_rng(4)
+    perm = rng.permutation(e)
+    p_ = np.arange(1, e + 1, dtype=np.float64) ** -1.1
+    p_ /= p_.sum()
+    ids = np.stack([perm[rng.choice(e, size=k, replace=False, p=p_)] for _ in range(rows)]).astype(np.uint32)
+    counts = np.bincount(ids.reshape(-1), minlength=e)
+    assert counts.max() > 200
+    x = synthetic.hidden_rows(372, rows, cfg.d)
+    w16 = np.full((rows, k), 1.0 / k, dtype=np.float16)
+    share = gu.dev_empty(rows * cfg.d, "f32")
+    moe.routed_partial(0, gu.to_dev(x), rows, gu.to_dev(ids), gu.to_dev(w16.view(np.uint16)), share)
+    moe.synchronize()
+    got = share.cpu().numpy().reshape(rows, cfg.d)
+    assert np.all(np.isfinite(got))
+    off = np.array([host["offsets"][n] for n in fmt.OFFSET_NAMES], dtype=np.uint32)
+    lib, fn = orc.lib(), orc.ref_gemv4_ptr()
+    scratch = np.zeros(2 * cfg.f + cfg.d, dtype=np.float32)
+    hot = int(np.argmax(counts))
+    rows_hot = np.nonzero((ids == hot).any(axis=1))[0]
+    sample = sorted(set([0, 1, 31, 32, 100, 255] + rows_hot[[0, len(rows_hot) // 2, -1]].tolist() + list(range(7, 256, 37))))
+    worst = 0.0
+    for t in sample:
+        want = np.zeros(cfg.d, dtype=np.float32)
+        x32 = orc.f16_bits_to_f32(x[t])
+        for kk in range(k):
+            lib.orc_cpu_expert_accumulate(orc.ptr(host["experts"][int(ids[t, kk])]), orc.ptr(off), 4, orc.META_BF16,
+                                          orc.ACT_SILU, orc.ptr(x32), cfg.d, cfg.f, float(np.float16(1.0 / k)),
+                                          orc.ptr(scratch), orc.ptr(want), fn)
+        err = orc.rel_error(got[t], want)
+        worst = max(worst, err)
+        assert err < FFN_TOL, f"row {t}"
+    print(f"[parity] zipf-256 worst sampled error against the CPU path: {worst:.3g}")
+
+
 @pytest.mark.parametrize("out_dtype", [fmt.OUT_FP32, fmt.OUT_FP16])
 def test_large_decode_batch_on_tensor_cores_keeps_decode_semantics(out_dtype, monkeypatch):
     """from 32 rows on a 4-bit batched decode call runs the grouped GEMMs of the prefill path; indices stay exact,
