@@ -163,6 +163,53 @@ def test_prenorm_block_matches_unfused_sequence(tokens, out_dtype, grouped_min, 
         assert np.array_equal(got_hid[t], want_hid), f"row {t}: hidden = out(out(hidden + delta) + h2)"
 
 
+@pytest.mark.parametrize("tokens,out_dtype,grouped_min", [(1, fmt.OUT_FP16, None), (3, fmt.OUT_FP32, None),
+                                                          (6, fmt.OUT_FP16, 4), (40, fmt.OUT_FP32, None)])
+def test_next_block_input_norm_is_written_by_the_last_stage(tokens, out_dtype, grouped_min, monkeypatch):
+    """RealForwardRunner.swift:1886-1909: the layer after the MoE block starts with rmsnorm_bf16w of the hidden state the
+    block wrote; with the fused entry point the block's last stage writes that row too.  Everything else must be the
+    bits of the call without it; the normalised rows within one fp16 ulp of the oracle's rmsnorm of the same hidden
+    state.  1 / 3 rows: the down stage's last block per row; 6 rows: the grouped combine; 40 rows: the tensor-core path."""
+    if grouped_min is not None:
+        monkeypatch.setenv("NVMAI_CUDA_GROUPED_MIN", str(grouped_min))
+    kind = fmt.ROUTER_AFFINE8 if out_dtype == fmt.OUT_FP16 else fmt.ROUTER_DENSE_F16
+    host, cfg = _case(4, fmt.META_BF16, out_dtype, tokens, seed=325, d=512, f=256, e=32, router_kind=kind, gate_kind=kind)
+    f16 = out_dtype == fmt.OUT_FP16
+    esz = "f16" if f16 else "f32"
+    rng = np.random.default_rng(326)
+    hid32 = (rng.standard_normal((tokens, cfg.d)) * 3.0).astype(np.float32)
+    delta16 = (rng.standard_normal((tokens, cfg.d)) * 0.7).astype(np.float16)
+    w_bits = orc.f32_to_bf16_bits(rng.uniform(0.5, 1.5, cfg.d).astype(np.float32))
+    wn_bits = orc.f32_to_bf16_bits(rng.uniform(0.5, 1.5, cfg.d).astype(np.float32))
+    hid_host = hid32.astype(np.float16).view(np.uint16) if f16 else hid32
+    dl = gu.DeviceLayer(host)
+    outs = []
+    for fused in (False, True):
+        moe = MoE(cfg)
+        dl.register(moe, 0)
+        hid = gu.to_dev(hid_host.copy())
+        h2 = gu.dev_empty(tokens * cfg.d, esz)
+        xn = gu.to_dev(np.full(tokens * cfg.d, 0x7E00, dtype=np.uint16))
+        delta = gu.to_dev(delta16.view(np.uint16))
+        if fused:
+            moe.layer_decode_fused_norms(0, hid, gu.to_dev(w_bits), 1e-6, tokens, gu.to_dev(wn_bits), 1e-5, xn,
+                                         attn_delta=delta, h2_out=h2)
+        else:
+            moe.layer_decode_prenorm(0, hid, gu.to_dev(w_bits), 1e-6, tokens, attn_delta=delta, h2_out=h2)
+        moe.synchronize()
+        raw = np.uint16 if f16 else np.uint32
+        outs.append((gu.from_dev(hid, raw).copy(), gu.from_dev(h2, raw).copy(), gu.from_dev(xn, np.uint16).copy()))
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    hid_out = outs[1][0].reshape(tokens, cfg.d)
+    got = outs[1][2].reshape(tokens, cfg.d)
+    for t in range(tokens):
+        want = np.zeros(cfg.d, dtype=np.uint16)
+        row = np.ascontiguousarray(hid_out[t] if f16 else hid_out[t].view(np.float32))
+        orc.lib().orc_gpu_rmsnorm_bf16w(orc.ptr(row), orc.ptr(wn_bits), orc.ptr(want), cfg.d, 1e-5, out_dtype)
+        ulp = np.abs(got[t].astype(np.int32) - want.astype(np.int32))
+        assert ulp.max() <= 1 and np.count_nonzero(ulp) <= max(1, cfg.d // 100), f"row {t}"
+
+
 def test_prenorm_rejects_bad_arguments():
     from nvmai_b200 import NvmaiError, _lib
     host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP16, 2, seed=331, d=256, f=128, e=32)
