@@ -186,6 +186,10 @@ __device__ __forceinline__ float router_row_logit(uint32_t kind, const uint8_t *
 
 // One warp per token, K sequential arg-max passes.  Used where only a warp is
 // at hand; the block-wide version below replaces it on the decode path.
+// v[i] = the logit of expert lane + 32 i (anything for experts >= E)
+__device__ __forceinline__ void topk_softmax_warp_vals(float (&v)[kMaxExperts / 32], int E, int K, const uint16_t *pes,
+                                                       uint32_t *out_idx, __half *out_w);
+
 __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, int K, const uint16_t *pes,
                                                   uint32_t *out_idx, __half *out_w) {
     const int lane = threadIdx.x & 31;
@@ -195,6 +199,15 @@ __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, in
         const int e = lane + 32 * i;
         v[i] = (e < E) ? __ldcg(logits + e) : -INFINITY;
     }
+    topk_softmax_warp_vals(v, E, K, pes, out_idx, out_w);
+}
+
+__device__ __forceinline__ void topk_softmax_warp_vals(float (&v)[kMaxExperts / 32], int E, int K, const uint16_t *pes,
+                                                       uint32_t *out_idx, __half *out_w) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i)
+        if (lane + 32 * i >= E) v[i] = -INFINITY;
     float sel_score = 0.0f;      // lane k keeps the k-th selected score (K <= 32)
     uint32_t sel_idx = 0;
     uint32_t taken = 0;          // bit i: v[i] already selected

@@ -24,6 +24,7 @@
 #include "ep_comm.cuh"
 #include "grouped_decode.cuh"
 #include "misc_kernels.cuh"
+#include "persistent_batch.cuh"
 #include "persistent_decode.cuh"
 #include "prefill_gemm.cuh"
 
@@ -121,6 +122,7 @@ struct nvmai_cuda_moe {
     PdLayer *pd_layers = nullptr;
     bool pd_layers_stale = true, pd_unavailable = false;
     unsigned long long *pd_xchg = nullptr;
+    unsigned long long *pb_xchg = nullptr;    // the batch kernel's exchange words (up to kPbMaxRows rows)
     unsigned int *pd_epoch = nullptr;
     uint32_t *pd_route_log = nullptr;     // [num_layers][top_k]
     int sm_count = 0;
@@ -860,6 +862,7 @@ int pd_build_layers(nvmai_cuda_moe *h, std::vector<PdLayer> &host) {
     const uint64_t rbd = (uint64_t)c.d * bits / 8, rbf = (uint64_t)c.f * bits / 8, rbs = (uint64_t)c.shared_f * bits / 8;
     const uint64_t gd = c.d / 64, gf = c.f / 64;
     host.assign(c.num_layers, PdLayer{});
+    const uint64_t n_blobs = h->expert_map ? h->n_local : c.num_experts;      // blobs this rank holds, in local-index order
     for (uint32_t l = 0; l < c.num_layers; ++l) {
         const auto &w = h->layers[l].w;
         const auto &o = w.offsets;
@@ -871,25 +874,25 @@ int pd_build_layers(nvmai_cuda_moe *h, std::vector<PdLayer> &host) {
             return NVMAI_CUDA_EINVAL;
         int rc;
         {   // routed gate + up codes: {128 B, row, chunk, gate|up, expert}
-            const cuuint64_t gdim[5] = {128, c.f, rbd / 128, 2, c.num_experts};
+            const cuuint64_t gdim[5] = {128, c.f, rbd / 128, 2, n_blobs};
             const cuuint64_t gstr[4] = {rbd, 128, (cuuint64_t)(o.up_w - o.gate_w), w.expert_stride};
             const cuuint32_t box[5] = {128, (cuuint32_t)kTileFeatures, (cuuint32_t)(rbd / 128), 2, 1};
             if ((rc = pd_encode(h, &d.gu_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, base + o.gate_w, gdim, gstr, box, true))) return rc;
         }
         {   // their scales and biases: {value, gate|up, scale|bias, expert}
-            const cuuint64_t gdim[4] = {(cuuint64_t)c.f * gd, 2, 2, c.num_experts};
+            const cuuint64_t gdim[4] = {(cuuint64_t)c.f * gd, 2, 2, n_blobs};
             const cuuint64_t gstr[3] = {(cuuint64_t)(o.up_s - o.gate_s), (cuuint64_t)(o.gate_b - o.gate_s), w.expert_stride};
             const cuuint32_t box[4] = {(cuuint32_t)(kTileFeatures * gd), 2, 2, 1};
             if ((rc = pd_encode(h, &d.gu_meta, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, base + o.gate_s, gdim, gstr, box, false))) return rc;
         }
         {   // routed down codes: {128 B, row, chunk, expert}
-            const cuuint64_t gdim[4] = {128, c.d, rbf / 128, c.num_experts};
+            const cuuint64_t gdim[4] = {128, c.d, rbf / 128, n_blobs};
             const cuuint64_t gstr[3] = {rbf, 128, w.expert_stride};
             const cuuint32_t box[4] = {128, (cuuint32_t)kTileRows, (cuuint32_t)(rbf / 128), 1};
             if ((rc = pd_encode(h, &d.dn_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base + o.down_w, gdim, gstr, box, true))) return rc;
         }
         {   // and meta: {value, scale|bias, expert}
-            const cuuint64_t gdim[3] = {(cuuint64_t)c.d * gf, 2, c.num_experts};
+            const cuuint64_t gdim[3] = {(cuuint64_t)c.d * gf, 2, n_blobs};
             const cuuint64_t gstr[2] = {(cuuint64_t)(o.down_b - o.down_s), w.expert_stride};
             const cuuint32_t box[3] = {(cuuint32_t)(kTileRows * gf), 2, 1};
             if ((rc = pd_encode(h, &d.dn_meta, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base + o.down_s, gdim, gstr, box, false))) return rc;
@@ -960,6 +963,93 @@ int pd_launch(nvmai_cuda_moe *h, const PdPlan &plan, const __half *x0, void *y_l
             cfg.stream = st;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeCooperative;      // every block resident: they wait on one another
+            attr[0].val.cooperative = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            e = cudaLaunchKernelEx(&cfg, kern, p);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return record(h, e);
+        });
+    });
+}
+
+
+// ---- the resident kernel for 2..8 rows and for experts spread over ranks -----------------
+// exchange words: logits [T][E] | shared activations [T][Fs] | gate [16] | routed activations [64][F] | block
+// output [T][D] | one word per block
+struct PbXchg {
+    size_t logits, sact, gate, acts, y, beat, words;
+    PbXchg(const nvmai_cuda_moe_config &c, uint32_t T, uint32_t blocks) {
+        auto up = [](size_t v) { return (v + 15) & ~(size_t)15; };
+        size_t o = 0;
+        logits = o; o += up((size_t)T * c.num_experts);
+        sact = o; o += up((size_t)T * (c.shared_f ? c.shared_f : 1));
+        gate = o; o += 16;
+        acts = o; o += up((size_t)kPbMaxPairs * c.f);
+        y = o; o += up((size_t)T * c.d);
+        beat = o; o += up(blocks);
+        words = o;
+    }
+};
+
+struct PbPlan { uint32_t router_rows = 0, slots = 0; size_t smem = 0; };
+
+bool pb_plan(const nvmai_cuda_moe *h, uint32_t T, PbPlan &plan) {
+    const auto &c = h->cfg;
+    const uint32_t G = (uint32_t)h->sm_count;
+    if (G == 0 || h->pb_xchg == nullptr || T == 0 || T > (uint32_t)kPbMaxRows || T > c.max_tokens) return false;
+    if (c.top_k > (uint32_t)kMaxTopK || c.num_experts > (uint32_t)kMaxExperts) return false;
+    if (c.shared_f != 0 && c.shared_bits != c.routed_bits) return false;
+    if (c.d / kTileRows > G) return false;
+    if (c.f > 1024 || c.shared_f > 1024) return false;
+    const uint32_t b = c.routed_bits;
+    if ((c.d * b / 8) % 128 != 0 || (c.f * b / 8) % 128 != 0 || (c.shared_f * b / 8) % 128 != 0) return false;
+    if (kTileFeatures * (c.d / 64) > 256 || kTileRows * (std::max(c.f, c.shared_f) / 64) > 256) return false;
+    if (T * kTileRows > (uint32_t)kPdThreads / 2 || encode_tiled_fn() == nullptr) return false;
+    const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
+    const uint32_t router_blocks_max = G - (gated ? 1 : 0);
+    if (router_blocks_max == 0 || c.shared_f / kTileFeatures > G) return false;
+    const uint32_t rows = (c.num_experts + router_blocks_max - 1) / router_blocks_max;
+    if (rows > (uint32_t)kPdWarps) return false;
+    for (uint32_t slots = kPdMaxSlots; slots >= 1; --slots) {
+        const size_t smem = PbLayout(c.d, c.f, c.shared_f, c.routed_bits, T, c.router_kind,
+                                     gated ? c.shared_gate_kind : NVMAI_GATE_NONE, rows, slots).total;
+        if (smem <= kMaxSmem) { plan.router_rows = rows; plan.slots = slots; plan.smem = smem; return true; }
+    }
+    return false;
+}
+
+// world == 1: every expert is local (or the handle's map says which are, for tests); world > 1: recv[r] = rank r's
+// receive area as mapped in this process.
+int pb_launch(nvmai_cuda_moe *h, const PbPlan &plan, const __half *x_all, uint32_t T, void *y_all, uint32_t rank, uint32_t world,
+              unsigned long long *const *recv, cudaStream_t st) {
+    const auto &c = h->cfg;
+    const PbXchg X(c, kPbMaxRows, (uint32_t)h->sm_count);
+    const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
+    PbParams p{};
+    p.layers = h->pd_layers; p.num_layers = c.num_layers; p.T = T;
+    p.x0 = x_all; p.y_last = y_all;
+    p.xlogits = h->pb_xchg + X.logits; p.xsact = h->pb_xchg + X.sact; p.xgate = h->pb_xchg + X.gate;
+    p.xacts = h->pb_xchg + X.acts; p.xy = h->pb_xchg + X.y; p.xbeat = h->pb_xchg + X.beat;
+    p.expert_map = h->expert_map;
+    p.rank = rank; p.world = world;
+    for (uint32_t r = 0; r < world && r < (uint32_t)kEpMaxRanks; ++r) p.recv[r] = recv ? recv[r] : nullptr;
+    p.epoch = h->pd_epoch; p.status = h->status; p.route_log = nullptr;
+    p.D = c.d; p.F = c.f; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation; p.shared_f = c.shared_f;
+    p.router_kind = c.router_kind; p.gate_kind = gated ? c.shared_gate_kind : NVMAI_GATE_NONE;
+    p.router_rows = plan.router_rows; p.slots = plan.slots;
+    return dispatch_bits_meta(c.routed_bits, c.meta_dtype, [&](auto B, auto M) {
+        return dispatch_out(c.out_dtype, [&](auto O) {
+            auto kern = persistent_batch_kernel<decltype(B)::value, decltype(M)::value, decltype(O)::value>;
+            cudaError_t e = ensure_smem(kern, plan.smem);
+            if (e != cudaSuccess) return record(h, e);
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3((unsigned)h->sm_count);
+            cfg.blockDim = dim3(kPdThreads);
+            cfg.dynamicSmemBytes = plan.smem;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeCooperative;
             attr[0].val.cooperative = 1;
             cfg.attrs = attr;
             cfg.numAttrs = 1;
@@ -1067,7 +1157,9 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
         const unsigned int first_epoch = 1;
         ok = cudaGetDevice(&dev) == cudaSuccess &&
              cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-             alloc(&h->pd_xchg, xbytes) && alloc(&h->pd_epoch, 5 * 128) && alloc(&h->pd_layers, (size_t)c.num_layers * sizeof(PdLayer)) &&
+             alloc(&h->pd_xchg, xbytes) && alloc(&h->pd_epoch, 5 * 128) &&
+             alloc(&h->pb_xchg, PbXchg(c, kPbMaxRows, (uint32_t)std::max(h->sm_count, 1)).words * sizeof(unsigned long long)) &&
+             cudaMemset(h->pb_xchg, 0, PbXchg(c, kPbMaxRows, (uint32_t)std::max(h->sm_count, 1)).words * sizeof(unsigned long long)) == cudaSuccess && alloc(&h->pd_layers, (size_t)c.num_layers * sizeof(PdLayer)) &&
              alloc(&h->pd_route_log, (size_t)c.num_layers * c.top_k * 4) &&
              cudaMemset(h->pd_xchg, 0, xbytes) == cudaSuccess && cudaMemset(h->pd_epoch, 0, 5 * 128) == cudaSuccess &&
              cudaMemset(h->pd_route_log, 0, (size_t)c.num_layers * c.top_k * 4) == cudaSuccess &&
@@ -1089,6 +1181,7 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     for (auto &kv : h->stack_graphs) cudaGraphExecDestroy(kv.second);
     ep_release(h);
     cudaFree(h->pd_trace);
+    cudaFree(h->pb_xchg);
     cudaFree(h->pd_layers); cudaFree(h->pd_xchg); cudaFree(h->pd_epoch); cudaFree(h->pd_route_log);
     cudaFree(h->pf_x); cudaFree(h->pf_xn); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
@@ -1308,6 +1401,7 @@ int nvmai_cuda_moe_group_pairs(nvmai_cuda_moe *h, const uint32_t *idx, const voi
 int nvmai_cuda_moe_set_expert_map(nvmai_cuda_moe *h, const uint32_t *map_host, uint32_t n_local) {
     if (!h) return NVMAI_CUDA_EINVAL;
     const auto &c = h->cfg;
+    h->pd_layers_stale = true;              // the tensor maps span the blobs this rank holds
     if (map_host == nullptr) {              // back to "every expert is local"
         cudaFree(h->expert_map);
         h->expert_map = nullptr;
@@ -1412,6 +1506,11 @@ int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t 
         if (pd_plan(h, plan) && pd_prepare(h, st) == NVMAI_CUDA_OK)
             return pd_launch(h, plan, static_cast<const __half *>(x0_f16), y_last, st);
     }
+    if (h->decode_mode != 1 && tokens >= 2 && tokens <= (uint32_t)kPbMaxRows && cs == cudaStreamCaptureStatusNone) {
+        PbPlan bplan;      // a few rows: the resident kernel with the rows as the tensor-core step's columns
+        if (pb_plan(h, tokens, bplan) && pd_prepare(h, st) == NVMAI_CUDA_OK)
+            return pb_launch(h, bplan, static_cast<const __half *>(x0_f16), tokens, y_last, 0, 1, nullptr, st);
+    }
     if (h->decode_mode == 2) return NVMAI_CUDA_EINVAL;
     if (st == nullptr || cs != cudaStreamCaptureStatusNone)
         return stack_enqueue(h, static_cast<const __half *>(x0_f16), tokens, y_last, st);
@@ -1493,7 +1592,9 @@ int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank
     }
     h->ep_buf_elems = (size_t)world * rows * c.d;
     {
-        const size_t xbytes = 4096 + 2 * rows * c.d * sizeof(float) * world;
+        // counters (4 KB), then the receive area: [2][world][rows][D] 64-bit words (the resident kernel's tagged shares;
+        // the staged peer exchange uses the first half of it as fp32 rows)
+        const size_t xbytes = 4096 + 2 * rows * c.d * sizeof(unsigned long long) * world;
         if (world > (uint32_t)kEpMaxRanks || c.num_layers > (uint32_t)kEpMaxLayers ||
             cudaMalloc(reinterpret_cast<void **>(&h->ep_xchg), xbytes) != cudaSuccess ||
             cudaMemset(h->ep_xchg, 0, xbytes) != cudaSuccess ||
@@ -1519,6 +1620,20 @@ int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank
         return NVMAI_CUDA_ENCCL;
     }
     h->ep_rank = rank; h->ep_world = world; h->ep_rows_own = rows_own;
+    // Every rank's resident kernels must tag a layer alike: the epoch restarts at 1 and the exchange words are
+    // cleared on all ranks here (ep_init is collective).  From here to ep_shutdown every rank makes the same
+    // sequence of calls on its handle.
+    {
+        const unsigned int first_epoch = 1;
+        const size_t pd_bytes = PdXchg(c).words * sizeof(unsigned long long);
+        const size_t pb_bytes = PbXchg(c, kPbMaxRows, (uint32_t)std::max(h->sm_count, 1)).words * sizeof(unsigned long long);
+        if (cudaMemset(h->pd_xchg, 0, pd_bytes) != cudaSuccess || cudaMemset(h->pb_xchg, 0, pb_bytes) != cudaSuccess ||
+            cudaMemcpy(h->pd_epoch, &first_epoch, sizeof(first_epoch), cudaMemcpyHostToDevice) != cudaSuccess) {
+            cudaGetLastError();
+            ep_release(h);
+            return NVMAI_CUDA_ECUDA;
+        }
+    }
     return NVMAI_CUDA_OK;
 }
 
@@ -1689,6 +1804,23 @@ int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uin
     const __half *x = static_cast<const __half *>(x_own_f16);
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     if (st != nullptr) cudaStreamIsCapturing(st, &cs);
+    // Up to eight rows in total with the peers' receive areas mapped: one all-gather of the rows, then ONE resident
+    // kernel per rank for the whole step; the ranks' shares cross NVLink by peer stores from inside the down phase.
+    if (h->ep_peers_attached && h->decode_mode != 1 && cs == cudaStreamCaptureStatusNone) {
+        const uint32_t T = h->ep_world * rows_own;
+        PbPlan plan;
+        if (T <= (uint32_t)kPbMaxRows && pb_plan(h, T, plan) && pd_prepare(h, st) == NVMAI_CUDA_OK) {
+            const NcclApi &nccl = nccl_api();
+            const size_t own_elems = (size_t)rows_own * c.d;
+            if (nccl.AllGather(x, h->ep_x_all, own_elems, kNcclFloat16, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
+            unsigned long long *recv[kEpMaxRanks] = {};
+            for (uint32_t r = 0; r < h->ep_world; ++r) recv[r] = reinterpret_cast<unsigned long long *>(h->ep_peer_base[r] + 4096);
+            int rc = pb_launch(h, plan, h->ep_x_all, T, h->y, h->ep_rank, h->ep_world, recv, st);
+            if (rc) return rc;
+            return record(h, cudaMemcpyAsync(y_own, static_cast<const char *>(h->y) + (size_t)h->ep_rank * own_elems * out_size(c.out_dtype),
+                                             own_elems * out_size(c.out_dtype), cudaMemcpyDeviceToDevice, st));
+        }
+    }
     if (st == nullptr || cs != cudaStreamCaptureStatusNone) return (ep_replicated_mode(h, rows_own) ? ep_stack_enqueue_replicated(h, x, rows_own, y_own, st) : ep_stack_enqueue(h, x, rows_own, y_own, st));
     if (h->ep_graphs_stale) {
         for (auto &kv : h->ep_graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);

@@ -178,3 +178,64 @@ def test_bounded_wait_expires_and_the_handle_recovers():
             debug_set_wait_limit(0)
         again_raw, _ = _run(moe, cfg, xd, MoE.DECODE_RESIDENT, st)
     assert np.array_equal(again_raw, good_raw)
+
+
+# ---------------------------------------------------------------------------------------------------
+# a few rows per step: the rows are the columns of the tensor-core step
+# ---------------------------------------------------------------------------------------------------
+
+def _run_rows(moe, cfg, x_dev, rows, mode, stream):
+    y = gu.dev_empty(rows * cfg.d, "f32")
+    moe.set_decode_mode(mode)
+    moe.stack_decode(x_dev, rows, y, stream=stream)
+    moe.synchronize(stream)
+    return y.cpu().numpy().reshape(rows, cfg.d).copy()
+
+
+@pytest.mark.parametrize("rows,bits,d,f,fs,e,rkind", [(2, 4, 512, 256, 256, 64, fmt.ROUTER_DENSE_F16),
+                                                     (5, 8, 256, 128, 256, 32, fmt.ROUTER_AFFINE8),
+                                                     (8, 4, 2048, 512, 512, 256, fmt.ROUTER_DENSE_F16)])
+def test_resident_rows_one_layer_equals_staged_kernels_bitwise(rows, bits, d, f, fs, e, rkind):
+    """one layer (no input norm in play): every row of the batch kernel carries the bits of the staged per-row kernels"""
+    cfg = MoEConfig(d=d, f=f, shared_f=fs, num_experts=e, top_k=8, routed_bits=bits, shared_bits=bits, router_kind=rkind,
+                    shared_gate_kind=rkind, meta_dtype=fmt.META_BF16, out_dtype=fmt.OUT_FP32, max_tokens=rows, num_layers=1)
+    hosts = [synthetic.layer(1200 + bits, d=d, f=f, shared_f=fs, num_experts=e, routed_bits=bits, meta=fmt.META_BF16,
+                             router_kind=rkind, gate_kind=rkind)]
+    moe, devs = _stack(cfg, hosts)
+    x0 = synthetic.hidden_rows(1201 + rows, rows, d)
+    torch = gu.torch_cuda()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        xd = gu.to_dev(x0)
+        st.synchronize()
+        staged = _run_rows(moe, cfg, xd, rows, MoE.DECODE_STAGED, st)
+        res = _run_rows(moe, cfg, xd, rows, MoE.DECODE_RESIDENT, st)
+        res2 = _run_rows(moe, cfg, xd, rows, MoE.DECODE_RESIDENT, st)
+    assert np.all(np.isfinite(res))
+    assert np.array_equal(res.view(np.uint32), staged.view(np.uint32))
+    assert np.array_equal(res.view(np.uint32), res2.view(np.uint32))
+
+
+@pytest.mark.parametrize("rows,bits", [(3, 4), (8, 4), (4, 8)])
+def test_resident_rows_stack_against_oracle_chain(rows, bits):
+    """three layers: the per-row input norm is the batch kernel's own reduction, so the bar is the oracle chain's"""
+    layers, d, f, e = 3, 512, 256, 64
+    cfg = MoEConfig(d=d, f=f, shared_f=f, num_experts=e, top_k=8, routed_bits=bits, shared_bits=bits,
+                    meta_dtype=fmt.META_BF16, out_dtype=fmt.OUT_FP32, max_tokens=rows, num_layers=layers)
+    hosts = [synthetic.layer(1300 + 5 * l + bits, d=d, f=f, shared_f=f, num_experts=e, routed_bits=bits, meta=fmt.META_BF16)
+             for l in range(layers)]
+    moe, devs = _stack(cfg, hosts)
+    x0 = synthetic.hidden_rows(1301 + rows, rows, d)
+    torch = gu.torch_cuda()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        xd = gu.to_dev(x0)
+        st.synchronize()
+        res = _run_rows(moe, cfg, xd, rows, MoE.DECODE_RESIDENT, st)
+        staged = _run_rows(moe, cfg, xd, rows, MoE.DECODE_STAGED, st)
+    for t in range(rows):
+        idxs, h2, margin = _oracle_chain(cfg, hosts, x0[t])
+        if margin <= 1e-5 or np.abs(h2).max() < 1e-20:
+            continue        # a degenerate chain (tie, or a layer that came out all zero) tests nothing
+        assert orc.rel_error(res[t], h2) < 2e-3, f"row {t} vs the oracle chain"
+        assert orc.rel_error(res[t], staged[t]) < 1e-4, f"row {t} vs the staged kernels"
