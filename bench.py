@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import warnings
 import os
 import subprocess
 import sys
@@ -405,7 +406,7 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
             x_in.copy_(xs[i % n_inputs], non_blocking=True)
             run_step()
 
-        for i in range(max(args.warmup, 3)):
+        for i in range(max(args.warmup, 10)):
             step(i)
         dist.barrier()
         torch.cuda.synchronize()
@@ -435,6 +436,50 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
     times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_per_step = float(times[0]) / args.steps
+    resident = native and args.ep_exchange == "p2p" and world * tokens <= 8
+    if resident and args.block_trace:
+        # every rank's timeline of a few traced steps, on stderr (the marks slow the kernel a little: after the timing)
+        moe.set_trace(True)
+        with torch.cuda.stream(stream):
+            for i in range(4):
+                step(i)
+            stream.synchronize()
+        dist.barrier()
+        print(json.dumps(block_trace_summary(moe.read_block_trace(), world * tokens,
+                                             f"rank {rank} of {world}, {world * tokens} rows per step", False)),
+              file=sys.stderr, flush=True)
+        moe.set_trace(False)
+        dist.barrier()
+    single = None
+    if rank == 0 and resident and not args.no_single_gpu:
+        # the same total batch on ONE GPU that holds every expert (the figure an expert-parallel run has to beat)
+        one_cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
+                            router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16,
+                            meta_dtype=fmt.META_BF16, activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32,
+                            max_tokens=world * tokens, num_layers=args.layers)
+        one = MoE(one_cfg)
+        full = []
+        for l in range(args.layers):
+            dev = synthetic.device_layer(1000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits, meta=fmt.META_BF16)
+            synthetic.register_device_layer(one, l, dev)
+            full.append(dev)
+        rows = world * tokens
+        xa = torch.randn(n_inputs, rows, D, device="cuda", generator=gen).to(torch.float16)
+        xin = torch.empty(rows, D, dtype=torch.float16, device="cuda")
+        ya = torch.empty(rows, D, dtype=torch.float32, device="cuda")
+        with torch.cuda.stream(stream):
+            for i in range(5):
+                xin.copy_(xa[i], non_blocking=True)
+                one.stack_decode(xin, rows, ya, stream=stream)
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(stream)
+            for i in range(args.steps):
+                xin.copy_(xa[i % n_inputs], non_blocking=True)
+                one.stack_decode(xin, rows, ya, stream=stream)
+            s1.record(stream)
+            stream.synchronize()
+        single = rows / (s0.elapsed_time(s1) / args.steps / 1e3)
+        del one, full
     if rank == 0:
         peak, which = measured_peaks()
         rec = base_record(args, world)
@@ -450,13 +495,22 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
                                  "peak": peak, "peak_source": which, "unit": "GB/s",
                                  "frac": args.layers * layer_bytes(args.bits) * tokens / (ms_per_step / 1e3) / 1e9 / peak,
                                  "traffic": None}})
+        if resident:
+            exchange = ("one resident kernel per rank and step: every rank keeps all rows, the share rows of a rank's experts "
+                        "cross NVLink as tagged 64-bit peer stores from inside the down phase (no collective per layer); one "
+                        "NCCL all-gather of the step's rows before the kernel")
+            rec["roofline"]["kernel"] = "persistent_batch_kernel (one launch per rank = all layers of the step)"
+        elif native and world * tokens < 24:
+            exchange = ("all_gather(fp32 share rows) per layer, NCCL" if args.ep_exchange != "p2p" else
+                        "shares by peer stores from the staged down kernel + counted arrival") + "; every rank keeps all rows"
+        else:
+            exchange = "all_gather(x) + all_to_all(share rows) per layer, NCCL"
         rec["config"].update({"parallelism": f"ep{world}", "experts_per_gpu": E // world, "placement": args.placement,
-                              "tokens_per_step": world * tokens, "graph": native,
-                              "ep_driver": args.ep_driver,
-                              "collectives_per_layer": (("shares by peer stores from the down stage + counted arrival; " if args.ep_exchange == "p2p"
-                                                         else "all_gather(fp32 share rows), NCCL; ") + "every rank keeps all rows (replicated mode)"
-                                                        if native and world * tokens < 24 else
-                                                        "all_gather(x) + all_to_all(share rows), NCCL")})
+                              "tokens_per_step": world * tokens, "ep_driver": args.ep_driver, "exchange": exchange})
+        if single is not None:
+            rec["single_gpu_same_batch"] = {"value": single, "unit": UNIT, "rows_per_step": world * tokens,
+                                            "note": "one GPU holding all 256 experts of every layer, the same rows through "
+                                                    "the same resident kernel"}
         print(json.dumps(rec), flush=True)
     note("end-to-end region done")
     dist.barrier()
@@ -892,45 +946,61 @@ def stage2_roofline(moe, cfg, devs, args, stream, peak: float, which: str) -> di
 
 
 def run_block_trace(args) -> None:
-    """Per-phase timeline of the resident decode kernel: every block's GPU-timer marks, reduced to the minimum,
+    """Per-phase timeline of the resident decode kernels: every block's GPU-timer marks, reduced to the minimum,
     median and maximum over blocks (median over layers), in microseconds after the layer's first input row."""
     import torch
     from nvmai_b200 import MoE, MoEConfig, synthetic
     from nvmai_b200 import format as fmt
     torch.cuda.set_device(0)
+    rows = args.tokens
     cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
                     router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16, meta_dtype=fmt.META_BF16,
-                    activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32, max_tokens=1, num_layers=args.layers)
+                    activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32, max_tokens=rows, num_layers=args.layers)
     moe = MoE(cfg)
     devs = [synthetic.device_layer(1000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits, meta=fmt.META_BF16)
             for l in range(args.layers)]
     for l, dev in enumerate(devs):
         synthetic.register_device_layer(moe, l, dev)
-    xs = torch.randn(8, 1, D, device="cuda").to(torch.float16)
-    x_in = torch.empty(1, D, dtype=torch.float16, device="cuda")
-    y = torch.empty(1, D, dtype=torch.float32, device="cuda")
+    xs = torch.randn(8, rows, D, device="cuda").to(torch.float16)
+    x_in = torch.empty(rows, D, dtype=torch.float16, device="cuda")
+    y = torch.empty(rows, D, dtype=torch.float32, device="cuda")
     stream = torch.cuda.Stream()
     moe.set_trace(True)
     with torch.cuda.stream(stream):
         for i in range(6):
             x_in.copy_(xs[i])
-            moe.stack_decode(x_in, 1, y, stream=stream)
+            moe.stack_decode(x_in, rows, y, stream=stream)
         stream.synchronize()
-    tr = moe.read_block_trace().astype(np.float64)
+    print(json.dumps(block_trace_summary(moe.read_block_trace(), rows,
+                                         f"{args.layers}-layer stack, {args.bits}-bit, {rows} row(s) per step, resident kernel "
+                                         "with tracing on")), flush=True)
+
+
+def block_trace_summary(trace, rows: int, workload: str, single_row_kernel: bool | None = None) -> dict:
+    tr = trace.astype(np.float64)
     tr[tr == 0] = np.nan
-    names = {0: "input row normalised", 1: "router logits stored", 2: "all logits in", 10: "top-k done",
-             3: "gate/up tiles requested", 4: "first gate/up tile landed", 11: "last gate/up tile landed",
-             5: "activations stored", 6: "shared-expert down done", 7: "routed activations staged", 8: "down done",
-             9: "block output stored"}
+    if single_row_kernel if single_row_kernel is not None else rows == 1:
+        names = {0: "input row normalised", 1: "router logits stored", 2: "all logits in", 10: "top-k done",
+                 3: "gate/up tiles requested", 4: "first gate/up tile landed", 11: "last gate/up tile landed",
+                 5: "activations stored", 6: "shared-expert down done", 7: "routed activations staged", 8: "down done",
+                 9: "block output stored"}
+    else:
+        names = {0: "input rows normalised", 1: "phase 1 stored (logits, shared gate/up)", 2: "selection of every row done",
+                 3: "gate/up tiles requested", 4: "first gate/up tile landed", 11: "last gate/up tile landed",
+                 5: "activations stored", 6: "shared-expert down done", 7: "first eight pairs' down done",
+                 8: "down done", 12: "this rank's shares stored to every rank", 9: "block output stored"}
     first = np.nanmin(tr[:, :, 0], axis=1, keepdims=True)
     marks = {}
-    for i, name in names.items():
-        rel = (tr[2:, :, i] - first[2:]) / 1e3
-        marks[name] = [round(float(np.nanmedian(f(rel, axis=1))), 2) for f in (np.nanmin, np.nanmedian, np.nanmax)]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", category=RuntimeWarning)
+        for i, name in names.items():
+            rel = (tr[2:, :, i] - first[2:]) / 1e3
+            if np.all(np.isnan(rel)):
+                continue
+            marks[name] = [round(float(np.nanmedian(f(rel, axis=1))), 2) for f in (np.nanmin, np.nanmedian, np.nanmax)]
     period = np.diff(first[:, 0]) / 1e3
-    print(json.dumps({"workload": f"{args.layers}-layer stack, {args.bits}-bit, one token, resident kernel with tracing on",
-                      "us_after_first_input_row_min_median_max": marks,
-                      "layer_period_us_median": round(float(np.median(period[1:])), 2)}), flush=True)
+    return {"workload": workload, "us_after_first_input_row_min_median_max": marks,
+            "layer_period_us_median": round(float(np.median(period[1:])), 2)}
 
 
 def main() -> None:
@@ -945,6 +1015,8 @@ def main() -> None:
     ap.add_argument("--ref-layers", type=int, default=8, help="layers the CPU sample runs before scaling to --layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the post-timing check against the CPU oracle")
+    ap.add_argument("--no-single-gpu", action="store_true",
+                    help="expert-parallel runs: skip the one-GPU run of the same total batch on rank 0")
     ap.add_argument("--block-trace", action="store_true",
                     help="print the per-phase timeline of the resident decode kernel instead of the benchmark line")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "strided"])
@@ -962,9 +1034,10 @@ def main() -> None:
     ap.add_argument("--prefill", action="store_true",
                     help="measure configs[2] (a prefill chunk through the tensor-core grouped GEMMs) instead of the "
                          "decode stack; --tokens defaults to 4096 and --layers to 2 here")
-    ap.add_argument("--ep-exchange", default="nccl", choices=["p2p", "nccl"],
-                    help="expert-parallel runs, small batches: shares by an NCCL all-gather between the kernels (nccl, "
-                         "1.82 ms per step at N = 2) or by peer stores from the down stage (p2p, 1.93 ms)")
+    ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="expert-parallel runs, up to 8 rows in total: p2p = one resident kernel per rank and step, the "
+                         "ranks' shares cross NVLink by peer stores from inside its down phase; nccl = the staged kernels "
+                         "with an NCCL all-gather of the shares per layer")
     ap.add_argument("--ep-driver", default="native", choices=["native", "torch"],
                     help="expert-parallel runs: the library's own communicator and CUDA graph (native), or "
                          "torch.distributed collectives around per-stage calls with plain launches (torch)")
@@ -975,7 +1048,7 @@ def main() -> None:
     if args.gturbo_load:
         run_gturbo_load(args)
         return
-    if args.block_trace:
+    if args.block_trace and args.gpus == 1:
         run_block_trace(args)
         return
     if args.batch_layer:

@@ -202,46 +202,56 @@ __device__ __forceinline__ void topk_softmax_warp(const float *logits, int E, in
     topk_softmax_warp_vals(v, E, K, pes, out_idx, out_w);
 }
 
+// Order-preserving map of a float onto an unsigned key (larger float = larger key; -0 counts as +0, as in a float
+// compare).  NaN maps to 0, below every number: a NaN logit is never selected.
+__device__ __forceinline__ uint32_t topk_key(float v) {
+    const uint32_t b = __float_as_uint(v + 0.0f);
+    const uint32_t key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return v != v ? 0u : key;
+}
+__device__ __forceinline__ float topk_key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
+}
+
 __device__ __forceinline__ void topk_softmax_warp_vals(float (&v)[kMaxExperts / 32], int E, int K, const uint16_t *pes,
                                                        uint32_t *out_idx, __half *out_w) {
     const int lane = threadIdx.x & 31;
+    // K rounds; a round is two warp-wide integer reductions (the largest key, then the lowest expert index among
+    // the lanes that hold it) instead of a shuffle tree over (score, index) pairs.  Key 0 = not selectable.
+    uint32_t key[kMaxExperts / 32];
 #pragma unroll
-    for (int i = 0; i < kMaxExperts / 32; ++i)
-        if (lane + 32 * i >= E) v[i] = -INFINITY;
+    for (int i = 0; i < kMaxExperts / 32; ++i) key[i] = lane + 32 * i < E ? topk_key(v[i]) : 0u;
     float sel_score = 0.0f;      // lane k keeps the k-th selected score (K <= 32)
     uint32_t sel_idx = 0;
-    uint32_t taken = 0;          // bit i: v[i] already selected
     float top0 = 0.0f;
     for (int k = 0; k < K; ++k) {
-        float best = -INFINITY;
-        int best_e = 0x7fffffff;
+        uint32_t head = 0u;
+        int head_i = 0;
 #pragma unroll
-        for (int i = 0; i < kMaxExperts / 32; ++i) {
-            const int e = lane + 32 * i;
-            // bitwise, not short-circuit, logic: short-circuit operators become divergent branches here
-            const bool free_slot = (!((taken >> i) & 1u)) & (e < E);
-            const bool better = free_slot & ((v[i] > best) | ((v[i] == best) & (e < best_e)));
-            best = better ? v[i] : best;
-            best_e = better ? e : best_e;
+        for (int i = kMaxExperts / 32 - 1; i >= 0; --i) {       // ties inside a lane go to the lower index
+            const bool better = key[i] >= head;
+            head = better ? key[i] : head;
+            head_i = better ? i : head_i;
         }
+        const uint32_t m = __reduce_max_sync(0xffffffffu, head);
+        const uint32_t cand = (head == m) ? (uint32_t)(lane + 32 * head_i) : 0x7fffffffu;
+        uint32_t best_e = __reduce_min_sync(0xffffffffu, cand);
+        float best = topk_key_value(m);
+        if (m == 0u) { best_e = 0u; best = -INFINITY; }         // nothing selectable (every logit NaN)
+        else if ((best_e & 31u) == (uint32_t)lane) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            const bool better = (ob > best) | ((ob == best) & (oe < best_e));
-            best = better ? ob : best;
-            best_e = better ? oe : best_e;
+            for (int i = 0; i < kMaxExperts / 32; ++i)
+                if ((int)(best_e >> 5) == i) key[i] = 0u;
         }
-        best_e = best_e == 0x7fffffff ? 0 : best_e;         // nothing selectable (every logit NaN)
-        taken |= ((best_e & 31) == lane) ? (1u << (best_e >> 5)) : 0u;
         top0 = k == 0 ? best : top0;
-        if (k == lane) { sel_score = best; sel_idx = (uint32_t)best_e; }
+        if (k == lane) { sel_score = best; sel_idx = best_e; }
     }
     // softmax over the K selected scores only, summed in rank order (moe.metal:271-277)
+    const float ek = lane < K ? expf(sel_score - top0) : 0.0f;
     float sum_exp = 0.0f;
-    for (int k = 0; k < K; ++k) sum_exp += expf(__shfl_sync(0xffffffffu, sel_score, k) - top0);
+    for (int k = 0; k < K; ++k) sum_exp += __shfl_sync(0xffffffffu, ek, k);
     if (lane < K) {
-        const float w = expf(sel_score - top0) / sum_exp;
+        const float w = ek / sum_exp;
         const float gain = pes ? __uint_as_float(((uint32_t)ldg_u16(pes + sel_idx)) << 16) : 1.0f;
         out_idx[lane] = sel_idx;
         out_w[lane] = __float2half_rn(w * gain);

@@ -1035,6 +1035,7 @@ int pb_launch(nvmai_cuda_moe *h, const PbPlan &plan, const __half *x_all, uint32
     p.rank = rank; p.world = world;
     for (uint32_t r = 0; r < world && r < (uint32_t)kEpMaxRanks; ++r) p.recv[r] = recv ? recv[r] : nullptr;
     p.epoch = h->pd_epoch; p.status = h->status; p.route_log = nullptr;
+    p.trace = h->trace_on ? h->pd_trace : nullptr;
     p.D = c.d; p.F = c.f; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation; p.shared_f = c.shared_f;
     p.router_kind = c.router_kind; p.gate_kind = gated ? c.shared_gate_kind : NVMAI_GATE_NONE;
     p.router_rows = plan.router_rows; p.slots = plan.slots;

@@ -36,6 +36,8 @@ constexpr int kPbMaxRows = 8;           // rows per step = columns of the tensor
 constexpr int kPbMaxPairs = kPbMaxRows * kMaxTopK;
 constexpr int kPbBatchTiles = 8;        // gate/up tiles a block reduces together
 constexpr uint32_t kPbNotLocal = 0xFFFFFFFFu;
+constexpr int kPbNormRows = 4;          // rows whose previous block output a block polls at once
+static_assert(kPbNormRows * kPdKeep <= 32, "one pending bit per (row, element)");
 
 __device__ __forceinline__ void st_tagged_sys(unsigned long long *p, uint32_t tag, float v) {
     const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
@@ -48,7 +50,7 @@ __device__ __forceinline__ unsigned long long ld_tagged_sys(const unsigned long 
 }
 
 struct PbLayout {
-    size_t bar_p1, bar_p1s, bar_p2, bar_p3, xs, xsum, red, pairs, wk, part, sh_part, p1, p1_meta0, p1_meta1, p1s, p2, p2_step,
+    size_t bar_p1, bar_p1s, bar_p2, bar_p3, xs, xsum, red, pairs, emap, sscale, wk, part, sh_part, p1, p1_meta0, p1_meta1, p1s, p2, p2_step,
         tile_meta_s, tile_meta_b, p3, p3_step, dn_meta_s, dn_act, dn_xsum, sd, sd_act, sd_xsum, total;
     __host__ __device__ static size_t a16(size_t v) { return (v + 15) & ~(size_t)15; }
     __host__ __device__ static size_t a1k(size_t v) { return (v + 1023) & ~(size_t)1023; }
@@ -64,6 +66,8 @@ struct PbLayout {
         // partial sums: [warp][16 rows][8 cols] of a shared-expert tile, or [tile][warp][16] of a batch of routed tiles
         red = o; o += (size_t)kPdGroupWarps * 16 * (kPbMaxRows > kPbBatchTiles ? kPbMaxRows : kPbBatchTiles) * sizeof(float);
         pairs = o; o += 1024;                     // n_pairs, then per pair: row, slot, local expert
+        emap = o; o += (size_t)kMaxExperts * sizeof(uint32_t);      // global expert -> local blob of this rank
+        sscale = o; o += a16(kPbMaxRows * sizeof(float));           // the shared activations' power-of-two row scales
         wk = o; o += (size_t)kPbMaxRows * kMaxTopK * (sizeof(float) + sizeof(uint32_t));           // routing weights, expert ids
         part = o; o += (size_t)kPbMaxPairs * kDownSplit * 16 * sizeof(float);                     // [pair][half][16]
         sh_part = o; o += (size_t)kDownSplit * 16 * kPbMaxRows * sizeof(float);                   // shared down: [half][16][8 cols]
@@ -117,6 +121,7 @@ struct PbParams {
     unsigned int *epoch;
     unsigned int *status;
     uint32_t *route_log;              // optional [num_layers][T][K]
+    unsigned long long *trace;        // optional [num_layers][blocks][16] GPU-timer marks of every block
     uint32_t D, F, E, K, act, shared_f, router_kind, gate_kind;
     uint32_t router_rows, slots;
 };
@@ -209,6 +214,8 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
     uint32_t *idx_s = reinterpret_cast<uint32_t *>(wk_s + kPbMaxRows * kMaxTopK);  // [T][K]
     float *part = reinterpret_cast<float *>(smem + L.part);
     float *sh_part = reinterpret_cast<float *>(smem + L.sh_part);
+    uint32_t *emap_s = reinterpret_cast<uint32_t *>(smem + L.emap);
+    float *scale_s = reinterpret_cast<float *>(smem + L.sscale);
 
     if (tid == 0) {
         mbar_init(bar_p1, 1);
@@ -217,6 +224,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
         for (int u = 0; u <= kMaxTopK; ++u) mbar_init(bar_p3(u), 1);
         mbar_fence_init();
     }
+    for (uint32_t e = tid; e < p.E; e += kPdThreads) emap_s[e] = p.expert_map != nullptr ? p.expert_map[e] : e;
     __syncthreads();
     const uint32_t epoch0 = *p.epoch;
     uint32_t ph_p1 = 0, ph_p1s = 0, ph_p2 = 0, ph_p3 = 0;
@@ -276,46 +284,88 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
     if (has_down && Fs) { if (warp == 3) issue_shared_down(0); fly_p3 |= 1u << kMaxTopK; }
 
     bool alive = true;
-    for (uint32_t l = 0; l < p.num_layers && alive; ++l) {
+    uint32_t l = 0;
+    // marks of one layer: 0 input rows ready, 1 phase 1 stored, 2 selection done, 3 tiles requested, 4 first gate/up
+    // tile landed, 11 last one landed, 5 activations stored, 6 shared down done, 7 first chunk of pairs done, 8 down
+    // done, 12 this rank's shares sent, 9 output stored
+    auto mark = [&](int i) {
+        if (p.trace != nullptr && tid == 0) p.trace[((size_t)l * G + c) * 16 + i] = global_timer_ns();
+    };
+    for (; l < p.num_layers && alive; ++l) {
         const uint32_t tag = epoch0 + l;
         const PdLayer &ly = p.layers[l];
         const bool last = l + 1 == p.num_layers;
 
-        // ---- the rows' inputs: warp t normalises row t ----
+        // ---- the rows' inputs: x = half(y * rsqrt(mean(y^2) + eps)), four rows at a time; per row the reduction
+        // tree of the single-row kernel (256 threads, element i + 256 j in thread i), so a row's bits do not depend
+        // on how many rows travel with it ----
         bool ok = true;
         if (l == 0) {
             for (int i = tid * 8; i < T * D; i += kPdThreads * 8)
                 *reinterpret_cast<uint4 *>(xs + i) = *reinterpret_cast<const uint4 *>(p.x0 + i);
         } else {
-            for (int row = warp; row < T; row += kPdWarps) {
-                const unsigned long long *src = p.xy + (size_t)row * D;
-                float ss = 0.0f;
-                // two passes over the row's words (they stay in L2): sum of squares, then the scaled values
-                for (int i = lane * 2; i < D; i += 64) {
-                    unsigned long long a, b;
-                    PollClock clk;
-                    for (;;) {
-                        ld_tagged2(src + i, a, b);
-                        if (tag_is(a, tag - 1) & tag_is(b, tag - 1)) break;
-                        if (clk.expired(p.status)) { atomicExch(p.status, 1u); ok = false; break; }
+            float *wsum = red;                      // [4 rows][8 warps]; red is idle here
+            for (int r0 = 0; r0 < T; r0 += kPbNormRows) {
+                const int nr = min(kPbNormRows, T - r0);
+                float keep[kPbNormRows][kPdKeep];
+                uint32_t pending = 0;
+#pragma unroll
+                for (int r = 0; r < kPbNormRows; ++r)
+#pragma unroll
+                    for (int j = 0; j < kPdKeep; ++j) {
+                        keep[r][j] = 0.0f;
+                        if (r < nr && tid + j * kPdThreads < D) pending |= 1u << (r * kPdKeep + j);
                     }
-                    if (!ok) break;
-                    ss = fmaf(tag_val(a), tag_val(a), ss);
-                    ss = fmaf(tag_val(b), tag_val(b), ss);
+                PollClock clk;
+                while (pending) {
+                    // a round requests every word still missing before it looks at any: one L2 round trip for all
+                    const uint32_t round = pending;
+                    unsigned long long w[kPbNormRows][kPdKeep];
+#pragma unroll
+                    for (int r = 0; r < kPbNormRows; ++r)
+#pragma unroll
+                        for (int j = 0; j < kPdKeep; ++j)
+                            w[r][j] = (round >> (r * kPdKeep + j)) & 1u ? ld_tagged(p.xy + (size_t)(r0 + r) * D + tid + j * kPdThreads) : 0ull;
+#pragma unroll
+                    for (int r = 0; r < kPbNormRows; ++r)
+#pragma unroll
+                        for (int j = 0; j < kPdKeep; ++j)
+                            if (((round >> (r * kPdKeep + j)) & 1u) && tag_is(w[r][j], tag - 1)) {
+                                keep[r][j] = tag_val(w[r][j]);
+                                pending &= ~(1u << (r * kPdKeep + j));
+                            }
+                    if (pending && clk.expired(p.status)) { atomicExch(p.status, 1u); break; }
                 }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                ss = warp_sum(ss);
-                const float sc = rsqrtf(ss / (float)D + 1e-6f);
-                for (int i = lane * 2; i < D; i += 64) {
-                    unsigned long long a, b;
-                    ld_tagged2(src + i, a, b);
-                    *reinterpret_cast<__half2 *>(xs + (size_t)row * D + i) = __floats2half2_rn(tag_val(a) * sc, tag_val(b) * sc);
+                const bool got = pending == 0;
+#pragma unroll
+                for (int r = 0; r < kPbNormRows; ++r) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < kPdKeep; ++j) ss = fmaf(keep[r][j], keep[r][j], ss);
+                    ss = warp_sum(ss);
+                    if (lane == 0) wsum[r * kPdWarps + warp] = ss;
                 }
+                if (!__syncthreads_and(got)) { ok = false; break; }
+#pragma unroll
+                for (int r = 0; r < kPbNormRows; ++r) {
+                    if (r < nr) {
+                        float tot = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < kPdWarps; ++i) tot += wsum[r * kPdWarps + i];
+                        const float sc = rsqrtf(tot / (float)D + 1e-6f);
+#pragma unroll
+                        for (int j = 0; j < kPdKeep; ++j) {
+                            const int i = tid + j * kPdThreads;
+                            if (i < D) xs[(size_t)(r0 + r) * D + i] = __float2half_rn(keep[r][j] * sc);
+                        }
+                    }
+                }
+                __syncthreads();
             }
         }
         if (!__syncthreads_and(ok)) { alive = false; break; }
         pb_group_sums(xs, D, T, xsum_s);
+        mark(0);
 
         // ---- phase 1a: router rows (or the gate row) against every token ----
         if (has_rows) {
@@ -367,6 +417,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
             }
         }
         __syncthreads();              // phase-1 buffers are read out
+        mark(1);
         if (!last) {
             if (has_rows) { if (warp == 0) issue_rows(l + 1); fly_p1 = 1; }
             if (has_stile) { if (warp == 1) issue_stile(l + 1); fly_p1s = 1; }
@@ -376,12 +427,10 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
         ok = true;
         for (int row = warp; row < T; row += kPdWarps) {
             float v[kMaxExperts / 32];
+            ok = poll_strided<kMaxExperts / 32, 32>(p.xlogits + (size_t)row * p.E, lane, (int)p.E, tag, v, p.status);
 #pragma unroll
-            for (int i = 0; i < kMaxExperts / 32; ++i) {
-                v[i] = -INFINITY;
-                const int e = lane + 32 * i;
-                if (e < (int)p.E && ok) ok = poll_tagged(p.xlogits + (size_t)row * p.E + e, tag, v[i], p.status);
-            }
+            for (int i = 0; i < kMaxExperts / 32; ++i)
+                if (lane + 32 * i >= (int)p.E) v[i] = -INFINITY;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             __half w16[1];
@@ -397,15 +446,13 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
             }
         }
         if (!__syncthreads_and(ok)) { alive = false; break; }
+        mark(2);
         if (warp == 0) {              // pairs in (row, slot) order whose expert this rank holds
             uint32_t base = 0;
             for (int i0 = 0; i0 < T * K; i0 += 32) {
                 const int i = i0 + lane;
                 uint32_t blob = kPbNotLocal;
-                if (i < T * K) {
-                    const uint32_t e = min(idx_s[(i / K) * kMaxTopK + (i % K)], p.E - 1u);
-                    blob = p.expert_map != nullptr ? p.expert_map[e] : e;
-                }
+                if (i < T * K) blob = emap_s[min(idx_s[(i / K) * kMaxTopK + (i % K)], p.E - 1u)];
                 const uint32_t m = __ballot_sync(0xffffffffu, blob != kPbNotLocal);
                 if (blob != kPbNotLocal) {
                     const uint32_t at = base + __popc(m & ((1u << lane) - 1u));
@@ -414,16 +461,58 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                 base += __popc(m);
             }
             if (lane == 0) n_pairs_s[0] = base;
+            __syncwarp();
+            // the warp that made the list requests this block's first gate/up tiles at once
+            const uint32_t tiles = base * tiles_per_expert;
+            const int mine = tiles > c ? (int)((tiles - c + G - 1) / G) : 0;
+            if (lane < mine && lane < (int)p.slots) issue_tile(lane, ly, c + (uint32_t)lane * G);
         }
         __syncthreads();
         if (!has_down && tid == 0) st_tagged(p.xbeat + c, tag, 0.0f);      // this block has read the layer's logits
         const int n_pairs = (int)n_pairs_s[0];
         const uint32_t tiles_total = (uint32_t)n_pairs * tiles_per_expert;
         const int n_my = tiles_total > c ? (int)((tiles_total - c + G - 1) / G) : 0;
-
-        // ---- phase 2: gate/up tiles of the pairs, in batches of tiles that are reduced together ----
-        if (warp == 0 && lane < n_my && lane < (int)p.slots) issue_tile(lane, ly, c + (uint32_t)lane * G);
         for (int j = 0; j < n_my && j < (int)p.slots; ++j) fly_p2 |= 1u << j;
+        mark(3);
+        // ---- the shared expert's down tile against all rows, while the first gate/up tiles travel: the rows' shared
+        // activations went out in phase 1 and the tile was requested a layer ago.  Warps 6, 7 take a half of the
+        // groups each ----
+        bool ok_sd = true;
+        if (has_down && Fs != 0) {
+            __half *sact = reinterpret_cast<__half *>(sdbuf + L.sd_act);
+            float *sxsum = reinterpret_cast<float *>(sdbuf + L.sd_xsum);
+            ok = true;
+            for (int row = warp; row < T; row += kPdWarps) {
+                float scale_up;
+                ok = pd_stage_row<OUT>(p.xsact + (size_t)row * Fs, tag, Fs, 0, Fs, sact + (size_t)row * Fs, scale_up, p.status) && ok;
+                if (lane == 0) scale_s[row] = scale_up;
+            }
+            if (!__syncthreads_and(ok)) { alive = false; break; }
+            pb_group_sums(sact, Fs, T, sxsum);
+            __syncthreads();
+            if (warp >= kPdWarps - kDownSplit) {
+                const int half = warp - (kPdWarps - kDownSplit);
+                const int groups = Fs / kGroup, gpw = (groups + kDownSplit - 1) / kDownSplit;
+                const int g_begin = min(half * gpw, groups), g_end = min(g_begin + gpw, groups);
+                ok_sd = pd_mbar_wait(bar_p3(kMaxTopK), (ph_p3 >> kMaxTopK) & 1u, p.status);
+                if (ok_sd) {
+                    const uint32_t w_bytes = (uint32_t)(kTileRows * Fs * BITS / 8);
+                    const uint16_t *ms = reinterpret_cast<const uint16_t *>(sdbuf + w_bytes);
+                    float acc[1][4] = {};
+                    swz_accumulate_cols<BITS, META>(sdbuf, sdbuf, kTileRows, g, g + 8, ms, ms + kTileRows * groups, g, g + 8, groups,
+                                                    g_begin, g_end, sact, Fs, T, sxsum, acc);
+                    float *sp = sh_part + (size_t)half * 16 * kPbMaxRows;
+                    const int c0 = 2 * t4, c1 = 2 * t4 + 1;
+                    sp[g * kPbMaxRows + c0] = acc[0][0] * (c0 < T ? scale_s[c0] : 0.0f);
+                    sp[g * kPbMaxRows + c1] = acc[0][1] * (c1 < T ? scale_s[c1] : 0.0f);
+                    sp[(g + 8) * kPbMaxRows + c0] = acc[0][2] * (c0 < T ? scale_s[c0] : 0.0f);
+                    sp[(g + 8) * kPbMaxRows + c1] = acc[0][3] * (c1 < T ? scale_s[c1] : 0.0f);
+                }
+            }
+            ph_p3 ^= 1u << kMaxTopK; fly_p3 &= ~(1u << kMaxTopK);
+            // (a wait that gave up is seen by the whole block at the barrier after the gate/up tiles)
+            mark(6);
+        }
         bool down_issued = false;
         ok = true;
         for (int b0 = 0; b0 < n_my && ok; b0 += kPbBatchTiles) {
@@ -432,6 +521,8 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                 const int slot = j % (int)p.slots;
                 ok = pd_mbar_wait(bar_p2(slot), (ph_p2 >> slot) & 1u, p.status) && ok;
                 ph_p2 ^= 1u << slot; fly_p2 &= ~(1u << slot);
+                if (j == 0) mark(4);
+                if (j == n_my - 1) mark(11);
                 if (!down_issued && has_down) {
                     if (warp == 1 && lane < min(n_pairs, kMaxTopK)) issue_pair_down(lane, ly, lane);
                     fly_p3 |= (1u << min(n_pairs, kMaxTopK)) - 1u;
@@ -458,7 +549,8 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
             }
             __syncthreads();          // red is reused by the next batch
         }
-        if (!__syncthreads_and(ok)) { alive = false; break; }
+        if (!__syncthreads_and(ok && ok_sd)) { alive = false; break; }
+        mark(5);
         if (!down_issued && has_down) {
             if (warp == 1 && lane < min(n_pairs, kMaxTopK)) issue_pair_down(lane, ly, lane);
             fly_p3 |= (1u << min(n_pairs, kMaxTopK)) - 1u;
@@ -467,46 +559,11 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
         // ---- phase 3 (blocks that own 16 output features) ----
         if (has_down) {
             ok = true;
-            // the shared expert's down tile against all rows: warps 6, 7 take a half of the groups each
-            if (Fs != 0) {
-                __half *sact = reinterpret_cast<__half *>(sdbuf + L.sd_act);
-                float *sxsum = reinterpret_cast<float *>(sdbuf + L.sd_xsum);
-                float *scale_s = reinterpret_cast<float *>(red);              // [T] power-of-two row scales (red is idle)
-                for (int row = warp; row < T; row += kPdWarps) {
-                    float scale_up;
-                    ok = pd_stage_row<OUT>(p.xsact + (size_t)row * Fs, tag, Fs, 0, Fs, sact + (size_t)row * Fs, scale_up, p.status) && ok;
-                    if (lane == 0) scale_s[row] = scale_up;
-                }
-                if (!__syncthreads_and(ok)) { alive = false; break; }
-                pb_group_sums(sact, Fs, T, sxsum);
-                __syncthreads();
-                if (warp >= kPdWarps - kDownSplit) {
-                    const int half = warp - (kPdWarps - kDownSplit);
-                    const int groups = Fs / kGroup, gpw = (groups + kDownSplit - 1) / kDownSplit;
-                    const int g_begin = min(half * gpw, groups), g_end = min(g_begin + gpw, groups);
-                    ok = pd_mbar_wait(bar_p3(kMaxTopK), (ph_p3 >> kMaxTopK) & 1u, p.status);
-                    if (ok) {
-                        const uint32_t w_bytes = (uint32_t)(kTileRows * Fs * BITS / 8);
-                        const uint16_t *ms = reinterpret_cast<const uint16_t *>(sdbuf + w_bytes);
-                        float acc[1][4] = {};
-                        swz_accumulate_cols<BITS, META>(sdbuf, sdbuf, kTileRows, g, g + 8, ms, ms + kTileRows * groups, g, g + 8, groups,
-                                                        g_begin, g_end, sact, Fs, T, sxsum, acc);
-                        float *sp = sh_part + (size_t)half * 16 * kPbMaxRows;
-                        const int c0 = 2 * t4, c1 = 2 * t4 + 1;
-                        sp[g * kPbMaxRows + c0] = acc[0][0] * (c0 < T ? scale_s[c0] : 0.0f);
-                        sp[g * kPbMaxRows + c1] = acc[0][1] * (c1 < T ? scale_s[c1] : 0.0f);
-                        sp[(g + 8) * kPbMaxRows + c0] = acc[0][2] * (c0 < T ? scale_s[c0] : 0.0f);
-                        sp[(g + 8) * kPbMaxRows + c1] = acc[0][3] * (c1 < T ? scale_s[c1] : 0.0f);
-                    }
-                }
-                ph_p3 ^= 1u << kMaxTopK; fly_p3 &= ~(1u << kMaxTopK);
-                if (!__syncthreads_and(ok)) { alive = false; break; }
-                ok = true;
-            }
             // the pairs' down tiles, eight at a time: warp w takes pair chunk + w (both halves of its row)
             for (int chunk = 0; chunk < n_pairs; chunk += kMaxTopK) {
                 if (chunk != 0) {       // regions are read out: request the next eight
                     if (!__syncthreads_and(ok)) { ok = false; break; }
+                    if (chunk == kMaxTopK) mark(7);
                     if (warp == 1 && lane < min(n_pairs - chunk, kMaxTopK)) issue_pair_down(lane, ly, chunk + lane);
                     fly_p3 |= (1u << min(n_pairs - chunk, kMaxTopK)) - 1u;
                 }
@@ -544,6 +601,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                     ok = poll_tagged(p.xbeat + b, tag, ignored, p.status);
             }
             if (!__syncthreads_and(ok)) { alive = false; break; }
+            mark(8);
             if (fin) {
                 float h1 = 0.0f;
                 if (Fs != 0) {
@@ -565,16 +623,27 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                     const size_t buf = (size_t)(tag & 1u) * p.world;
                     const size_t at = ((buf + p.rank) * T + frow) * D + row0 + fr;
                     for (uint32_t q = 0; q < p.world; ++q) st_tagged_sys(p.recv[q] + at, tag, acc);
-                    float total = h1;
-                    for (uint32_t s = 0; s < p.world && ok; ++s) {
-                        const unsigned long long *src = p.recv[p.rank] + ((buf + s) * T + frow) * D + row0 + fr;
-                        PollClock clk;
-                        for (;;) {
-                            const unsigned long long w = ld_tagged_sys(src);
-                            if (tag_is(w, tag)) { total += tag_val(w); break; }
-                            if (clk.expired(p.status)) { atomicExch(p.status, 1u); ok = false; break; }
-                        }
+                    mark(12);
+                    // the ranks' shares of this (row, feature), requested together round by round, summed in rank order
+                    const unsigned long long *mine = p.recv[p.rank] + (buf * T + frow) * D + row0 + fr;
+                    const size_t rank_step = (size_t)T * D;
+                    float share[kEpMaxRanks];
+                    uint32_t pending = (1u << p.world) - 1u;
+                    PollClock clk;
+                    while (pending) {
+                        const uint32_t round = pending;
+                        unsigned long long w[kEpMaxRanks];
+#pragma unroll
+                        for (int s = 0; s < kEpMaxRanks; ++s) w[s] = (round >> s) & 1u ? ld_tagged_sys(mine + s * rank_step) : 0ull;
+#pragma unroll
+                        for (int s = 0; s < kEpMaxRanks; ++s)
+                            if (((round >> s) & 1u) && tag_is(w[s], tag)) { share[s] = tag_val(w[s]); pending &= ~(1u << s); }
+                        if (pending && clk.expired(p.status)) { atomicExch(p.status, 1u); ok = false; break; }
                     }
+                    float total = h1;
+#pragma unroll
+                    for (int s = 0; s < kEpMaxRanks; ++s)
+                        if (s < (int)p.world && ok) total += share[s];
                     acc = total;
                 }
                 const float yv = round_out<OUT>(acc);
@@ -582,6 +651,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                 if (last) store_out<OUT>(p.y_last, (size_t)frow * D + row0 + fr, yv);
             }
             if (!__syncthreads_and(ok)) { alive = false; break; }
+            mark(9);
             if (Fs != 0 && !last) { if (warp == 3) issue_shared_down(l + 1); fly_p3 |= 1u << kMaxTopK; }
         }
     }

@@ -103,6 +103,33 @@ __device__ __forceinline__ bool poll_tagged(const unsigned long long *p, uint32_
     }
 }
 
+// out[j] = the value of word first + j * STRIDE of src (j < N, index below limit; 0 for the others), each waited for
+// until it carries `tag`.  A round requests every word still missing before it looks at any, so the requests overlap
+// (one L2 round trip per round instead of one per word).
+template <int N, int STRIDE>
+__device__ __forceinline__ bool poll_strided(const unsigned long long *src, int first, int limit, uint32_t tag, float (&out)[N],
+                                             unsigned int *status) {
+    static_assert(N <= 32, "one pending bit per word");
+    uint32_t pending = 0;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+        out[j] = 0.0f;
+        if (first + j * STRIDE < limit) pending |= 1u << j;
+    }
+    PollClock clk;
+    while (pending) {
+        const uint32_t round = pending;
+        unsigned long long w[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) w[j] = (round >> j) & 1u ? ld_tagged(src + first + j * STRIDE) : 0ull;
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+            if (((round >> j) & 1u) && tag_is(w[j], tag)) { out[j] = tag_val(w[j]); pending &= ~(1u << j); }
+        if (pending && clk.expired(status)) { atomicExch(status, 1u); return false; }
+    }
+    return true;
+}
+
 // ---- per-layer weight views (device array) -----------------------------------
 struct PdLayer {
     // tensor maps (64-byte aligned): routed gate+up codes {128 B, row, 128-B chunk of the row, gate|up, expert},
@@ -444,19 +471,23 @@ __device__ __noinline__ bool pd_stage_row(const unsigned long long *src, uint32_
     }
     PollClock clk;
     while (pending) {
+        // a round requests every word still missing before it looks at any (the requests overlap)
+        const uint32_t round = pending;
+        unsigned long long a[kKeep], b[kKeep], c[kKeep], d[kKeep];
 #pragma unroll
         for (int j = 0; j < kKeep; ++j) {
-            if (pending & (1u << j)) {
-                const int i = lane * 4 + j * 128;
-                unsigned long long a, b, c, d;
-                ld_tagged2(src + i, a, b);
-                ld_tagged2(src + i + 2, c, d);
-                if (tag_is(a, tag) & tag_is(b, tag) & tag_is(c, tag) & tag_is(d, tag)) {
-                    keep[j] = make_float4(tag_val(a), tag_val(b), tag_val(c), tag_val(d));
-                    pending &= ~(1u << j);
-                }
+            a[j] = b[j] = c[j] = d[j] = 0ull;
+            if ((round >> j) & 1u) {
+                ld_tagged2(src + lane * 4 + j * 128, a[j], b[j]);
+                ld_tagged2(src + lane * 4 + j * 128 + 2, c[j], d[j]);
             }
         }
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j)
+            if (((round >> j) & 1u) && (tag_is(a[j], tag) & tag_is(b[j], tag) & tag_is(c[j], tag) & tag_is(d[j], tag))) {
+                keep[j] = make_float4(tag_val(a[j]), tag_val(b[j]), tag_val(c[j]), tag_val(d[j]));
+                pending &= ~(1u << j);
+            }
         if (pending && clk.expired(status)) { atomicExch(status, 1u); break; }
     }
     if (!__all_sync(0xffffffffu, pending == 0)) return false;
@@ -687,31 +718,16 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_decode_kernel(PdPara
                 // x = half(y * rsqrt(mean(y^2) + eps)): the previous block output arrives tagged; the reduction tree of
                 // the staged kernels (256 threads, element i + 256 j in thread i)
                 float keep[kPdKeep];
-                uint32_t pending = 0;
+                bool ok_x = true;
                 if (tid < kPdNormThreads) {
-#pragma unroll
-                    for (int j = 0; j < kPdKeep; ++j) {
-                        keep[j] = 0.0f;
-                        if (tid + j * kPdNormThreads < D) pending |= 1u << j;
-                    }
-                    PollClock clk;
-                    while (pending) {
-#pragma unroll
-                        for (int j = 0; j < kPdKeep; ++j) {
-                            if (pending & (1u << j)) {
-                                const unsigned long long w = ld_tagged(p.xy + tid + j * kPdNormThreads);
-                                if (tag_is(w, tag - 1)) { keep[j] = tag_val(w); pending &= ~(1u << j); }
-                            }
-                        }
-                        if (pending && clk.expired(p.status)) { atomicExch(p.status, 1u); break; }
-                    }
+                    ok_x = poll_strided<kPdKeep, kPdNormThreads>(p.xy, tid, D, tag - 1, keep, p.status);
                     float ss = 0.0f;
 #pragma unroll
                     for (int j = 0; j < kPdKeep; ++j) ss = fmaf(keep[j], keep[j], ss);
                     ss = warp_sum(ss);
                     if (lane == 0) wsum[warp] = ss;
                 }
-                if (!__syncthreads_and(pending == 0)) { alive = false; break; }
+                if (!__syncthreads_and(ok_x)) { alive = false; break; }
                 if (tid < kPdNormThreads) {
                     float tot = 0.0f;
 #pragma unroll

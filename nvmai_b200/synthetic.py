@@ -1,11 +1,12 @@
 """Seeded synthetic MoE layers with the benchmark's value distributions.
 
-Codes uniform over the code range; scale ~ U(0.005, 0.02) and bias ~ U(-0.08, 0)
-per (row, group), drawn in fp32 and rounded once to the 16-bit meta type; router
-gate dense fp16 ~ N(0, 0.02); hidden rows fp16 ~ N(0, 1).  numpy builds a layer on
-the host (tests, single-layer runs); `device_stack` builds many layers directly
-in device memory with torch's CUDA generator (tens of GB would be too slow to
-make on the host and upload).
+Codes uniform over the code range; router and gate dense fp16 ~ N(0, 0.02); hidden
+rows fp16 ~ N(0, 1).  numpy builds a layer on the host (tests, single-layer runs:
+scale ~ U(0.005, 0.02) and bias ~ U(-0.08, 0) per (row, group), drawn in fp32 and
+rounded once to the 16-bit meta type); `device_layer` builds the benchmark's layers
+directly in device memory with torch's CUDA generator (tens of GB would be too slow
+to make on the host and upload), with the scales and biases of a min/max quantizer
+over zero-mean weights so that a deep stack keeps its routing diverse.
 """
 from __future__ import annotations
 
@@ -60,11 +61,21 @@ def hidden_rows(seed: int, tokens: int, d: int = 2048) -> np.ndarray:
 # device-side generation (torch is plumbing here: allocation + RNG only)
 # ---------------------------------------------------------------------------
 
+def _device_meta(torch, gen, shape, bits: int, mdt, device):
+    """Scales and biases of a min/max group quantizer over zero-mean weights: the scale spans U(0.005, 0.02) at 4 bits
+    (the same weight range at 8), the bias sits half the code range below zero, within 10 %.  The weights of a row
+    then have no common sign, so a stack of such layers keeps routing different rows to different experts (with a
+    one-sided bias every block output is nearly a constant vector and every row of a layer picks the same experts)."""
+    top = float((1 << bits) - 1)
+    s = (torch.rand(shape, device=device, generator=gen) * 0.015 + 0.005) * (15.0 / top)
+    b = -s * (top / 2.0) * (torch.rand(shape, device=device, generator=gen) * 0.2 + 0.9)
+    return s.to(mdt), b.to(mdt)
+
+
 def _device_affine(torch, gen, rows: int, n: int, bits: int, meta: int, device):
     mdt = torch.bfloat16 if meta == fmt.META_BF16 else torch.float16
     w = torch.randint(0, 256, (rows, n * bits // 8), dtype=torch.uint8, device=device, generator=gen)
-    s = (torch.rand(rows, n // fmt.GROUP, device=device, generator=gen) * 0.015 + 0.005).to(mdt)
-    b = (torch.rand(rows, n // fmt.GROUP, device=device, generator=gen) * 0.08 - 0.08).to(mdt)
+    s, b = _device_meta(torch, gen, (rows, n // fmt.GROUP), bits, mdt, device)
     return w, s, b
 
 
@@ -85,11 +96,10 @@ def device_layer(seed: int, *, d: int = 2048, f: int = 512, shared_f: int = 512,
     experts = torch.randint(0, 256, (n_local, stride), dtype=torch.uint8, device=device, generator=gen)
     gate_m = f * (d // fmt.GROUP) * 2
     down_m = d * (f // fmt.GROUP) * 2
-    for name, nbytes, lo, width in (("gate_s", gate_m, 0.005, 0.015), ("gate_b", gate_m, -0.08, 0.08),
-                                    ("up_s", gate_m, 0.005, 0.015), ("up_b", gate_m, -0.08, 0.08),
-                                    ("down_s", down_m, 0.005, 0.015), ("down_b", down_m, -0.08, 0.08)):
-        vals = (torch.rand(n_local, nbytes // 2, device=device, generator=gen) * width + lo).to(mdt)
-        experts[:, off[name]:off[name] + nbytes] = vals.view(torch.uint8)
+    for name, nbytes in (("gate", gate_m), ("up", gate_m), ("down", down_m)):
+        sc, bi = _device_meta(torch, gen, (n_local, nbytes // 2), routed_bits, mdt, device)
+        experts[:, off[name + "_s"]:off[name + "_s"] + nbytes] = sc.view(torch.uint8)
+        experts[:, off[name + "_b"]:off[name + "_b"] + nbytes] = bi.view(torch.uint8)
     out = {"experts": experts, "stride": stride, "offsets": off}
     out["router"] = ((torch.randn(num_experts, d, device=device, generator=gen) * 0.02).to(torch.float16), None, None)
     if shared_f:
