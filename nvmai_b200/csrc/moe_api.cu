@@ -1005,12 +1005,12 @@ bool pb_plan(const nvmai_cuda_moe *h, uint32_t T, PbPlan &plan) {
     const uint32_t b = c.routed_bits;
     if ((c.d * b / 8) % 128 != 0 || (c.f * b / 8) % 128 != 0 || (c.shared_f * b / 8) % 128 != 0) return false;
     if (kTileFeatures * (c.d / 64) > 256 || kTileRows * (std::max(c.f, c.shared_f) / 64) > 256) return false;
-    if (T * kTileRows > (uint32_t)kPdThreads / 2 || encode_tiled_fn() == nullptr) return false;
+    if (T * kTileRows > (uint32_t)kPbThreads / 2 || encode_tiled_fn() == nullptr) return false;
     const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
     const uint32_t router_blocks_max = G - (gated ? 1 : 0);
     if (router_blocks_max == 0 || c.shared_f / kTileFeatures > G) return false;
     const uint32_t rows = (c.num_experts + router_blocks_max - 1) / router_blocks_max;
-    if (rows > (uint32_t)kPdWarps) return false;
+    if (rows > (uint32_t)kPbWarps) return false;
     for (uint32_t slots = kPdMaxSlots; slots >= 1; --slots) {
         const size_t smem = PbLayout(c.d, c.f, c.shared_f, c.routed_bits, T, c.router_kind,
                                      gated ? c.shared_gate_kind : NVMAI_GATE_NONE, rows, slots).total;
@@ -1046,7 +1046,7 @@ int pb_launch(nvmai_cuda_moe *h, const PbPlan &plan, const __half *x_all, uint32
             if (e != cudaSuccess) return record(h, e);
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3((unsigned)h->sm_count);
-            cfg.blockDim = dim3(kPdThreads);
+            cfg.blockDim = dim3(kPbThreads);
             cfg.dynamicSmemBytes = plan.smem;
             cfg.stream = st;
             cudaLaunchAttribute attr[1];

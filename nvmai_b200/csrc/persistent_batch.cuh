@@ -31,7 +31,8 @@
 
 namespace nvmai {
 
-static_assert(kPdThreads == 256, "the batch kernel is written for one group of 8 warps");
+constexpr int kPbThreads = 256;          // one group of 8 warps, whatever the single-row kernel is built with
+constexpr int kPbWarps = kPbThreads / 32;
 constexpr int kPbMaxRows = 8;           // rows per step = columns of the tensor-core step
 constexpr int kPbMaxPairs = kPbMaxRows * kMaxTopK;
 constexpr int kPbBatchTiles = 8;        // gate/up tiles a block reduces together
@@ -161,7 +162,7 @@ __device__ __forceinline__ void swz_accumulate_cols(const unsigned char *box_a, 
 // group sums of fp16 rows [cols][n] -> xsum [cols][n / 64]; the whole block
 __device__ __forceinline__ void pb_group_sums(const __half *x, int n, int cols, float *xsum) {
     const int groups = n / kGroup, total = cols * groups;
-    for (int base = 0; base < total; base += kPdThreads >> 3) {       // 8 threads per group; every lane runs every pass
+    for (int base = 0; base < total; base += kPbThreads >> 3) {       // 8 threads per group; every lane runs every pass
         const int i = base + (threadIdx.x >> 3);
         float v = 0.0f;
         if (i < total) {
@@ -176,7 +177,7 @@ __device__ __forceinline__ void pb_group_sums(const __half *x, int n, int cols, 
 }
 
 template <int BITS, int META, int OUT>
-__global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParams p) {
+__global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -224,7 +225,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
         for (int u = 0; u <= kMaxTopK; ++u) mbar_init(bar_p3(u), 1);
         mbar_fence_init();
     }
-    for (uint32_t e = tid; e < p.E; e += kPdThreads) emap_s[e] = p.expert_map != nullptr ? p.expert_map[e] : e;
+    for (uint32_t e = tid; e < p.E; e += kPbThreads) emap_s[e] = p.expert_map != nullptr ? p.expert_map[e] : e;
     __syncthreads();
     const uint32_t epoch0 = *p.epoch;
     uint32_t ph_p1 = 0, ph_p1s = 0, ph_p2 = 0, ph_p3 = 0;
@@ -301,7 +302,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
         // on how many rows travel with it ----
         bool ok = true;
         if (l == 0) {
-            for (int i = tid * 8; i < T * D; i += kPdThreads * 8)
+            for (int i = tid * 8; i < T * D; i += kPbThreads * 8)
                 *reinterpret_cast<uint4 *>(xs + i) = *reinterpret_cast<const uint4 *>(p.x0 + i);
         } else {
             float *wsum = red;                      // [4 rows][8 warps]; red is idle here
@@ -314,7 +315,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
 #pragma unroll
                     for (int j = 0; j < kPdKeep; ++j) {
                         keep[r][j] = 0.0f;
-                        if (r < nr && tid + j * kPdThreads < D) pending |= 1u << (r * kPdKeep + j);
+                        if (r < nr && tid + j * kPbThreads < D) pending |= 1u << (r * kPdKeep + j);
                     }
                 PollClock clk;
                 while (pending) {
@@ -325,7 +326,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                     for (int r = 0; r < kPbNormRows; ++r)
 #pragma unroll
                         for (int j = 0; j < kPdKeep; ++j)
-                            w[r][j] = (round >> (r * kPdKeep + j)) & 1u ? ld_tagged(p.xy + (size_t)(r0 + r) * D + tid + j * kPdThreads) : 0ull;
+                            w[r][j] = (round >> (r * kPdKeep + j)) & 1u ? ld_tagged(p.xy + (size_t)(r0 + r) * D + tid + j * kPbThreads) : 0ull;
 #pragma unroll
                     for (int r = 0; r < kPbNormRows; ++r)
 #pragma unroll
@@ -343,7 +344,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
 #pragma unroll
                     for (int j = 0; j < kPdKeep; ++j) ss = fmaf(keep[r][j], keep[r][j], ss);
                     ss = warp_sum(ss);
-                    if (lane == 0) wsum[r * kPdWarps + warp] = ss;
+                    if (lane == 0) wsum[r * kPbWarps + warp] = ss;
                 }
                 if (!__syncthreads_and(got)) { ok = false; break; }
 #pragma unroll
@@ -351,11 +352,11 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                     if (r < nr) {
                         float tot = 0.0f;
 #pragma unroll
-                        for (int i = 0; i < kPdWarps; ++i) tot += wsum[r * kPdWarps + i];
+                        for (int i = 0; i < kPbWarps; ++i) tot += wsum[r * kPbWarps + i];
                         const float sc = rsqrtf(tot / (float)D + 1e-6f);
 #pragma unroll
                         for (int j = 0; j < kPdKeep; ++j) {
-                            const int i = tid + j * kPdThreads;
+                            const int i = tid + j * kPbThreads;
                             if (i < D) xs[(size_t)(r0 + r) * D + i] = __float2half_rn(keep[r][j] * sc);
                         }
                     }
@@ -373,7 +374,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
             ph_p1 ^= 1u; fly_p1 = 0;
             if (!__syncthreads_and(ok)) { alive = false; break; }
             const int nr = router_nrows != 0 ? router_nrows : 1;
-            for (int i = warp; i < nr * T; i += kPdWarps) {
+            for (int i = warp; i < nr * T; i += kPbWarps) {
                 const int r = i / T, tok = i % T;
                 const float v = pd_row_logit<META>(router_nrows != 0 ? p.router_kind : p.gate_kind, p1buf,
                                                    reinterpret_cast<const uint16_t *>(p1buf + L.p1_meta0),
@@ -425,7 +426,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
 
         // ---- every row's logits -> top-k by one warp per row; then the list of this rank's pairs ----
         ok = true;
-        for (int row = warp; row < T; row += kPdWarps) {
+        for (int row = warp; row < T; row += kPbWarps) {
             float v[kMaxExperts / 32];
             ok = poll_strided<kMaxExperts / 32, 32>(p.xlogits + (size_t)row * p.E, lane, (int)p.E, tag, v, p.status);
 #pragma unroll
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
             __half *sact = reinterpret_cast<__half *>(sdbuf + L.sd_act);
             float *sxsum = reinterpret_cast<float *>(sdbuf + L.sd_xsum);
             ok = true;
-            for (int row = warp; row < T; row += kPdWarps) {
+            for (int row = warp; row < T; row += kPbWarps) {
                 float scale_up;
                 ok = pd_stage_row<OUT>(p.xsact + (size_t)row * Fs, tag, Fs, 0, Fs, sact + (size_t)row * Fs, scale_up, p.status) && ok;
                 if (lane == 0) scale_s[row] = scale_up;
@@ -490,8 +491,8 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
             if (!__syncthreads_and(ok)) { alive = false; break; }
             pb_group_sums(sact, Fs, T, sxsum);
             __syncthreads();
-            if (warp >= kPdWarps - kDownSplit) {
-                const int half = warp - (kPdWarps - kDownSplit);
+            if (warp >= kPbWarps - kDownSplit) {
+                const int half = warp - (kPbWarps - kDownSplit);
                 const int groups = Fs / kGroup, gpw = (groups + kDownSplit - 1) / kDownSplit;
                 const int g_begin = min(half * gpw, groups), g_end = min(g_begin + gpw, groups);
                 ok_sd = pd_mbar_wait(bar_p3(kMaxTopK), (ph_p3 >> kMaxTopK) & 1u, p.status);
@@ -570,17 +571,19 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
                 const int pr = chunk + warp;
                 if (warp < kMaxTopK && pr < n_pairs) {
                     unsigned char *rg = region(warp);
-                    float scale_up, v[2];
+                    float scale_up;
                     ok = pd_stage_row<OUT>(p.xacts + (size_t)pr * F, tag, F, 0, F, reinterpret_cast<__half *>(rg + L.dn_act), scale_up,
                                            p.status);
                     ok = ok && pd_mbar_wait(bar_p3(warp), (ph_p3 >> warp) & 1u, p.status);
                     if (ok) {
-                        for (int half = 0; half < kDownSplit; ++half) {
-                            pd_down_half<BITS, META>(rg, (uint32_t)L.dn_xsum, (uint32_t)L.dn_meta_s, F, half,
-                                                     reinterpret_cast<const __half *>(rg + L.dn_act), scale_up, v);
-                            if (t4 == 0) {
-                                part[((size_t)pr * kDownSplit + half) * 16 + g] = v[0];
-                                part[((size_t)pr * kDownSplit + half) * 16 + g + 8] = v[1];
+                        float vv[kDownSplit][2];
+                        pd_down_both<BITS, META>(rg, (uint32_t)L.dn_xsum, (uint32_t)L.dn_meta_s, F,
+                                                 reinterpret_cast<const __half *>(rg + L.dn_act), scale_up, vv);
+                        if (t4 == 0) {
+#pragma unroll
+                            for (int half = 0; half < kDownSplit; ++half) {
+                                part[((size_t)pr * kDownSplit + half) * 16 + g] = vv[half][0];
+                                part[((size_t)pr * kDownSplit + half) * 16 + g + 8] = vv[half][1];
                             }
                         }
                     }
@@ -595,9 +598,9 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_batch_kernel(PbParam
             if (gated && fin && ok) ok = poll_tagged(p.xgate + frow, tag, gate_v, p.status);
             // the blocks that own no output features must have read this layer's logits before the output that lets
             // the next layer start is stored: otherwise one of them could fall a layer behind and miss its words
-            if (tid >= kPdThreads / 2) {
+            if (tid >= kPbThreads / 2) {
                 float ignored;
-                for (uint32_t b = (uint32_t)(D / kTileRows) + (uint32_t)(tid - kPdThreads / 2); b < G && ok; b += kPdThreads / 2)
+                for (uint32_t b = (uint32_t)(D / kTileRows) + (uint32_t)(tid - kPbThreads / 2); b < G && ok; b += kPbThreads / 2)
                     ok = poll_tagged(p.xbeat + b, tag, ignored, p.status);
             }
             if (!__syncthreads_and(ok)) { alive = false; break; }

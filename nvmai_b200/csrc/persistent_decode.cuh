@@ -556,6 +556,41 @@ __device__ __noinline__ void pd_down_half(unsigned char *region, uint32_t dn_xsu
     out[1] = acc[0][2] * scale_up;
 }
 
+// Both halves of a staged down tile by one warp.  When the row has eight groups (two halves of four) the two halves
+// run as one straight block of code with separate accumulators, so that their loads and tensor-core steps overlap;
+// each half's own arithmetic (group sums, order of accumulation) is that of pd_down_half.
+template <int BITS, int META>
+__device__ __noinline__ void pd_down_both(unsigned char *region, uint32_t dn_xsum, uint32_t dn_meta_s, int n, const __half *arow,
+                                          float scale_up, float (&out)[kDownSplit][2]) {
+    const int groups = n / kGroup;
+    if (kDownSplit == 2 && groups == 8) {
+        const int lane = threadIdx.x & 31, g = lane >> 2;
+        float va = sum8_halves(*reinterpret_cast<const uint4 *>(arow + (size_t)(lane >> 3) * kGroup + (lane & 7) * 8));
+        float vb = sum8_halves(*reinterpret_cast<const uint4 *>(arow + (size_t)(4 + (lane >> 3)) * kGroup + (lane & 7) * 8));
+        va += __shfl_xor_sync(0xffffffffu, va, 1); vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+        va += __shfl_xor_sync(0xffffffffu, va, 2); vb += __shfl_xor_sync(0xffffffffu, vb, 2);
+        va += __shfl_xor_sync(0xffffffffu, va, 4); vb += __shfl_xor_sync(0xffffffffu, vb, 4);
+        float xsa[4], xsb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            xsa[j] = __shfl_sync(0xffffffffu, va, j * 8);
+            xsb[j] = __shfl_sync(0xffffffffu, vb, j * 8);
+        }
+        const uint16_t *ms = reinterpret_cast<const uint16_t *>(region + dn_meta_s);
+        const uint16_t *mb = ms + kTileRows * groups;
+        uint32_t xa[4][8], xb[4][8];
+        load_x_fragments<BITS, 4>(arow, 0, xa);
+        load_x_fragments<BITS, 4>(arow, 4, xb);
+        float acc_a[1][4] = {}, acc_b[1][4] = {};
+        swz_accumulate_prepared<BITS, META, 4>(region, region, kTileRows, g, g + 8, ms, mb, g, g + 8, groups, 0, xa, xsa, acc_a);
+        swz_accumulate_prepared<BITS, META, 4>(region, region, kTileRows, g, g + 8, ms, mb, g, g + 8, groups, 4, xb, xsb, acc_b);
+        out[0][0] = acc_a[0][0] * scale_up; out[0][1] = acc_a[0][2] * scale_up;
+        out[1][0] = acc_b[0][0] * scale_up; out[1][1] = acc_b[0][2] * scale_up;
+    } else {
+        for (int half = 0; half < kDownSplit; ++half) pd_down_half<BITS, META>(region, dn_xsum, dn_meta_s, n, half, arow, scale_up, out[half]);
+    }
+}
+
 // ---- top-k over 256 logits with 512 threads ------------------------------------------
 // The selection of topk_select_block_vals (same order: score descending, ties to the lower index; NaN and -inf
 // never selected), with the second level spread over the whole block: a few threads per candidate rank it against a
@@ -914,7 +949,18 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_decode_kernel(PdPara
                                        reinterpret_cast<__half *>(rg + L.dn_act), scale_up, p.status);
                 mark(7);
                 ok = ok && pd_mbar_wait(bar_p3(slot), (ph_p3 >> slot) & 1u, p.status);
-                if (ok) {
+                if (ok && kPdWarpsPerSlot == 1) {
+                    float vv[kDownSplit][2];
+                    pd_down_both<BITS, META>(rg, (uint32_t)L.dn_xsum, (uint32_t)L.dn_meta_s, F,
+                                             reinterpret_cast<const __half *>(rg + L.dn_act), scale_up, vv);
+                    if (t == 0) {
+#pragma unroll
+                        for (int half = 0; half < kDownSplit; ++half) {
+                            part[(slot * kDownSplit + half) * 16 + g] = vv[half][0];
+                            part[(slot * kDownSplit + half) * 16 + g + 8] = vv[half][1];
+                        }
+                    }
+                } else if (ok) {
                     for (int half = h_begin; half < h_end; ++half) {
                         pd_down_half<BITS, META>(rg, (uint32_t)L.dn_xsum, (uint32_t)L.dn_meta_s, F, half,
                                                  reinterpret_cast<const __half *>(rg + L.dn_act), scale_up, v);
