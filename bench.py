@@ -999,8 +999,19 @@ def block_trace_summary(trace, rows: int, workload: str, single_row_kernel: bool
                 continue
             marks[name] = [round(float(np.nanmedian(f(rel, axis=1))), 2) for f in (np.nanmin, np.nanmedian, np.nanmax)]
     period = np.diff(first[:, 0]) / 1e3
+    # the blocks that reach a mark last, most often over the layers (where a straggler sits)
+    late = {}
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", category=RuntimeWarning)
+        for i, name in names.items():
+            col = tr[2:, :, i]
+            if np.all(np.isnan(col)):
+                continue
+            worst = np.argsort(np.nan_to_num(col, nan=-1.0), axis=1)[:, -3:].ravel()
+            ids, counts = np.unique(worst, return_counts=True)
+            late[name] = [int(b) for b in ids[np.argsort(-counts)][:4]]
     return {"workload": workload, "us_after_first_input_row_min_median_max": marks,
-            "layer_period_us_median": round(float(np.median(period[1:])), 2)}
+            "layer_period_us_median": round(float(np.median(period[1:])), 2), "blocks_most_often_last": late}
 
 
 def main() -> None:
