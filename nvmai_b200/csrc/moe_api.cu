@@ -1000,7 +1000,7 @@ bool pb_plan(const nvmai_cuda_moe *h, uint32_t T, PbPlan &plan) {
     if (G == 0 || h->pb_xchg == nullptr || T == 0 || T > (uint32_t)kPbMaxRows || T > c.max_tokens) return false;
     if (c.top_k > (uint32_t)kMaxTopK || c.num_experts > (uint32_t)kMaxExperts) return false;
     if (c.shared_f != 0 && c.shared_bits != c.routed_bits) return false;
-    if (c.d / kTileRows > G) return false;
+    if (c.d / kTileRows > G || c.d > (uint32_t)(kPdKeep * kPbThreads)) return false;
     if (c.f > 1024 || c.shared_f > 1024) return false;
     const uint32_t b = c.routed_bits;
     if ((c.d * b / 8) % 128 != 0 || (c.f * b / 8) % 128 != 0 || (c.shared_f * b / 8) % 128 != 0) return false;

@@ -297,43 +297,47 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
         const PdLayer &ly = p.layers[l];
         const bool last = l + 1 == p.num_layers;
 
-        // ---- the rows' inputs: x = half(y * rsqrt(mean(y^2) + eps)), four rows at a time; per row the reduction
-        // tree of the single-row kernel (256 threads, element i + 256 j in thread i), so a row's bits do not depend
-        // on how many rows travel with it ----
+        // ---- the rows' inputs: x = half(y * rsqrt(mean(y^2) + eps)), four rows at a time.  Thread i holds the element
+        // pairs 2 (i + 256 j) of a row (one 16-byte load for two tagged words); a row's sum of squares is reduced
+        // thread, warp, block in that fixed order, so a row's bits do not depend on how many rows travel with it ----
         bool ok = true;
         if (l == 0) {
             for (int i = tid * 8; i < T * D; i += kPbThreads * 8)
                 *reinterpret_cast<uint4 *>(xs + i) = *reinterpret_cast<const uint4 *>(p.x0 + i);
         } else {
+            constexpr int kPairs = kPdKeep / 2;
             float *wsum = red;                      // [4 rows][8 warps]; red is idle here
             for (int r0 = 0; r0 < T; r0 += kPbNormRows) {
                 const int nr = min(kPbNormRows, T - r0);
-                float keep[kPbNormRows][kPdKeep];
+                float2 keep[kPbNormRows][kPairs];
                 uint32_t pending = 0;
 #pragma unroll
                 for (int r = 0; r < kPbNormRows; ++r)
 #pragma unroll
-                    for (int j = 0; j < kPdKeep; ++j) {
-                        keep[r][j] = 0.0f;
-                        if (r < nr && tid + j * kPbThreads < D) pending |= 1u << (r * kPdKeep + j);
+                    for (int j = 0; j < kPairs; ++j) {
+                        keep[r][j] = make_float2(0.0f, 0.0f);
+                        if (r < nr && 2 * (tid + j * kPbThreads) < D) pending |= 1u << (r * kPairs + j);
                     }
                 PollClock clk;
                 while (pending) {
                     // a round requests every word still missing before it looks at any: one L2 round trip for all
                     const uint32_t round = pending;
-                    unsigned long long w[kPbNormRows][kPdKeep];
+                    unsigned long long wa[kPbNormRows][kPairs], wb[kPbNormRows][kPairs];
 #pragma unroll
                     for (int r = 0; r < kPbNormRows; ++r)
 #pragma unroll
-                        for (int j = 0; j < kPdKeep; ++j)
-                            w[r][j] = (round >> (r * kPdKeep + j)) & 1u ? ld_tagged(p.xy + (size_t)(r0 + r) * D + tid + j * kPbThreads) : 0ull;
+                        for (int j = 0; j < kPairs; ++j) {
+                            wa[r][j] = wb[r][j] = 0ull;
+                            if ((round >> (r * kPairs + j)) & 1u)
+                                ld_tagged2(p.xy + (size_t)(r0 + r) * D + 2 * (tid + j * kPbThreads), wa[r][j], wb[r][j]);
+                        }
 #pragma unroll
                     for (int r = 0; r < kPbNormRows; ++r)
 #pragma unroll
-                        for (int j = 0; j < kPdKeep; ++j)
-                            if (((round >> (r * kPdKeep + j)) & 1u) && tag_is(w[r][j], tag - 1)) {
-                                keep[r][j] = tag_val(w[r][j]);
-                                pending &= ~(1u << (r * kPdKeep + j));
+                        for (int j = 0; j < kPairs; ++j)
+                            if (((round >> (r * kPairs + j)) & 1u) && (tag_is(wa[r][j], tag - 1) & tag_is(wb[r][j], tag - 1))) {
+                                keep[r][j] = make_float2(tag_val(wa[r][j]), tag_val(wb[r][j]));
+                                pending &= ~(1u << (r * kPairs + j));
                             }
                     if (pending && clk.expired(p.status)) { atomicExch(p.status, 1u); break; }
                 }
@@ -342,7 +346,10 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
                 for (int r = 0; r < kPbNormRows; ++r) {
                     float ss = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < kPdKeep; ++j) ss = fmaf(keep[r][j], keep[r][j], ss);
+                    for (int j = 0; j < kPairs; ++j) {
+                        ss = fmaf(keep[r][j].x, keep[r][j].x, ss);
+                        ss = fmaf(keep[r][j].y, keep[r][j].y, ss);
+                    }
                     ss = warp_sum(ss);
                     if (lane == 0) wsum[r * kPbWarps + warp] = ss;
                 }
@@ -355,9 +362,11 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
                         for (int i = 0; i < kPbWarps; ++i) tot += wsum[r * kPbWarps + i];
                         const float sc = rsqrtf(tot / (float)D + 1e-6f);
 #pragma unroll
-                        for (int j = 0; j < kPdKeep; ++j) {
-                            const int i = tid + j * kPbThreads;
-                            if (i < D) xs[(size_t)(r0 + r) * D + i] = __float2half_rn(keep[r][j] * sc);
+                        for (int j = 0; j < kPairs; ++j) {
+                            const int i = 2 * (tid + j * kPbThreads);
+                            if (i < D)
+                                *reinterpret_cast<__half2 *>(xs + (size_t)(r0 + r) * D + i) =
+                                    __floats2half2_rn(keep[r][j].x * sc, keep[r][j].y * sc);
                         }
                     }
                 }
