@@ -396,9 +396,17 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
 
     with torch.cuda.stream(stream):
         x_in.copy_(xs[0])
+        def wait_step():
+            # the library's own host-polled wait: a step whose peer is gone ends as an error (the communicator is
+            # aborted) after --deadline seconds instead of blocking in the driver for good
+            if native:
+                moe.ep_synchronize(stream, int(args.deadline * 1000))
+            else:
+                stream.synchronize()
+
         for call in range(3):       # plain launches, graph capture, first replay
             run_step()
-            stream.synchronize()
+            wait_step()
             note(f"step call {call} done")
         dist.barrier()
 
@@ -428,7 +436,7 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
             x_in.copy_(xs_host[i % n_inputs], non_blocking=True)
             run_step()
             y_host.copy_(y_out, non_blocking=True)
-            stream.synchronize()
+            wait_step()
         dist.barrier()
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0

@@ -302,6 +302,17 @@ NVMAI_API int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uin
                                      uint32_t rows_own);
 NVMAI_API int nvmai_cuda_moe_ep_shutdown(nvmai_cuda_moe *h);
 
+/* Waits for `stream` as a rank of an expert-parallel job has to: a collective whose peer is
+ * gone never ends, so this polls the stream and the communicator's asynchronous error state
+ * (ncclCommGetAsyncError) from the host instead of blocking in the driver.  When NCCL
+ * reports an error (NVMAI_CUDA_ENCCL), or `timeout_ms` (0 = no limit) passes without the
+ * stream finishing (NVMAI_CUDA_ETIMEOUT), the communicator is aborted (ncclCommAbort ends
+ * its kernels in flight), the handle's expert-parallel state is dropped as by ep_shutdown,
+ * and the step's outputs are undefined; ep_init opens a new communicator.  Otherwise the
+ * result is that of nvmai_cuda_moe_synchronize.  NVMAI_CUDA_NCCL_LIB in the environment
+ * names the NCCL library to load instead of libnccl.so.2. */
+NVMAI_API int nvmai_cuda_moe_ep_synchronize(nvmai_cuda_moe *h, void *stream, uint32_t timeout_ms);
+
 /* Optional, after ep_init: exchange the ranks' shares through peer memory instead of NCCL
  * (small batches, where every rank keeps all rows).  Every rank exports the handle of its
  * receive area (a CUDA IPC handle, 64 bytes), the launcher collects the handles of all
@@ -350,6 +361,10 @@ NVMAI_API int nvmai_cuda_moe_read_route_log(nvmai_cuda_moe *h, uint32_t *out_hos
 /* Test hook: the longest any device-side wait of this library lasts, in nanoseconds
  * (0 restores the default of one second).  Process-wide, per device. */
 NVMAI_API int nvmai_cuda_moe_debug_set_wait_limit(uint64_t nanoseconds);
+
+/* Test hook: holds `stream` for `ms` milliseconds with a host function (no kernel runs, the
+ * device stays idle), so that a test can watch a host-side wait run out. */
+NVMAI_API int nvmai_cuda_moe_debug_host_delay(nvmai_cuda_moe *h, void *stream, uint32_t ms);
 
 /* Test hook for the failure path of the resident kernel: block `block` keeps its phase-1
  * results (router logits, shared-expert activations or the gate value) to itself, so that

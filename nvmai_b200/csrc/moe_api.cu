@@ -8,6 +8,7 @@
 #include <fcntl.h>
 #include <unistd.h>
 #include <cerrno>
+#include <chrono>
 
 #include <algorithm>
 #include <atomic>
@@ -1962,6 +1963,53 @@ int nvmai_cuda_moe_synchronize(nvmai_cuda_moe *h, void *stream) {
         return NVMAI_CUDA_ETIMEOUT;
     }
     return NVMAI_CUDA_OK;
+}
+
+// Waits for `stream` the way a rank of an expert-parallel job has to: a collective whose peer died never ends, so the
+// wait polls the stream and the communicator's asynchronous error state from the host instead of blocking in the
+// driver.  An error reported by NCCL, or `timeout_ms` without the stream finishing, aborts the communicator (which
+// ends its kernels in flight), drops the expert-parallel state of the handle (ep_init makes a new one) and returns
+// NVMAI_CUDA_ENCCL / NVMAI_CUDA_ETIMEOUT.  Otherwise the result is that of nvmai_cuda_moe_synchronize.
+int nvmai_cuda_moe_ep_synchronize(nvmai_cuda_moe *h, void *stream, uint32_t timeout_ms) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    if (!h->ep_comm) return nvmai_cuda_moe_synchronize(h, stream);
+    const NcclApi &nccl = nccl_api();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const auto t0 = std::chrono::steady_clock::now();
+    int verdict = NVMAI_CUDA_OK;
+    for (uint32_t spins = 0;; ++spins) {
+        const cudaError_t q = cudaStreamQuery(st);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady) return record(h, q);
+        int async = kNcclSuccess;
+        if (nccl.CommGetAsyncError(h->ep_comm, &async) != kNcclSuccess || (async != kNcclSuccess && async != kNcclInProgress)) {
+            verdict = NVMAI_CUDA_ENCCL;
+            break;
+        }
+        const auto waited = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (timeout_ms != 0 && waited >= (long long)timeout_ms) { verdict = NVMAI_CUDA_ETIMEOUT; break; }
+        if (spins > 1000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (verdict != NVMAI_CUDA_OK) {
+        nccl.CommAbort(h->ep_comm);      // frees the communicator and ends what it still has on the device
+        h->ep_comm = nullptr;
+        cudaStreamSynchronize(st);       // the rest of the stream (kernels of this library wait bounded times only)
+        cudaGetLastError();
+        ep_release(h);
+        unsigned int zero = 0;
+        cudaMemcpy(h->status, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+        return verdict;
+    }
+    return nvmai_cuda_moe_synchronize(h, stream);
+}
+
+// Test hook: holds `stream` for `ms` milliseconds with a host function (no kernel runs, the device is idle), so that
+// a test can watch a wait run out without anything being wrong on the GPU.
+int nvmai_cuda_moe_debug_host_delay(nvmai_cuda_moe *h, void *stream, uint32_t ms) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    return record(h, cudaLaunchHostFunc(static_cast<cudaStream_t>(stream),
+                                        [](void *arg) { std::this_thread::sleep_for(std::chrono::milliseconds((uintptr_t)arg)); },
+                                        reinterpret_cast<void *>((uintptr_t)ms)));
 }
 
 int nvmai_cuda_moe_last_cuda_error(const nvmai_cuda_moe *h) { return h ? h->last_cuda_error : 0; }

@@ -203,6 +203,14 @@ class MoE:
     def ep_shutdown(self) -> None:
         check(self._lib.nvmai_cuda_moe_ep_shutdown(self._h), "ep_shutdown")
 
+    def ep_synchronize(self, stream=None, timeout_ms: int = 0) -> None:
+        """Host-polled wait of an expert-parallel rank: raises (and aborts the communicator) when NCCL reports an
+        asynchronous error or the stream has not finished after `timeout_ms`."""
+        check(self._lib.nvmai_cuda_moe_ep_synchronize(self._h, _stream(stream), int(timeout_ms)), "ep_synchronize")
+
+    def debug_host_delay(self, ms: int, stream=None) -> None:
+        check(self._lib.nvmai_cuda_moe_debug_host_delay(self._h, _stream(stream), int(ms)), "debug_host_delay")
+
     def ep_stack_decode(self, x_own, rows_own: int, y_own, *, stream=None) -> None:
         check(self._lib.nvmai_cuda_moe_ep_stack_decode(self._h, _ptr(x_own), rows_own, _ptr(y_own), _stream(stream)),
               "ep_stack_decode")
