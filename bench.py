@@ -664,6 +664,98 @@ def run_batch_layer(args) -> None:
     print(json.dumps(rec), flush=True)
 
 
+def run_batch_layer_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
+    """configs[4] on several GPUs: the 256-row Zipf batch on one layer whose experts are spread over the ranks.  Every
+    rank owns tokens / world rows.  A step is: all-gather of the rows (a row is needed by nearly every rank, its eight
+    experts being spread over them), every rank's tensor-core items over ITS experts' pairs
+    (`nvmai_cuda_moe_routed_partial` under the rank's expert map), all-to-all of the fp32 share rows to the rows'
+    owners, rank-ordered sum there.  Collectives by torch.distributed (NCCL); no shared expert (as at one GPU)."""
+    from nvmai_b200 import MoE, MoEConfig, launch_count, synthetic
+    from nvmai_b200 import format as fmt
+    from nvmai_b200.ep import ExpertPlacement
+    tokens, n_layers = args.tokens, 16
+    assert tokens % world == 0, "--tokens must divide by the number of GPUs"
+    own = tokens // world
+    pl = ExpertPlacement(E, world, args.placement)
+    cfg = MoEConfig(d=D, f=F, shared_f=FS, num_experts=E, top_k=K, routed_bits=args.bits, shared_bits=args.bits,
+                    router_kind=fmt.ROUTER_DENSE_F16, shared_gate_kind=fmt.ROUTER_DENSE_F16, meta_dtype=fmt.META_BF16,
+                    activation=fmt.ACT_SILU, out_dtype=fmt.OUT_FP32, max_tokens=tokens, num_layers=n_layers)
+    moe = MoE(cfg)
+    devs = []
+    for l in range(n_layers):
+        dev = synthetic.device_layer(3000 + l, d=D, f=F, shared_f=FS, num_experts=E, routed_bits=args.bits,
+                                     meta=fmt.META_BF16, expert_ids=pl.local_experts(rank))
+        synthetic.register_device_layer(moe, l, dev)
+        devs.append(dev)
+    moe.set_expert_map(pl.expert_map(rank))
+    stream = torch.cuda.Stream()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11 + rank)
+    x_own = torch.randn(own, D, device="cuda", generator=gen).to(torch.float16)
+    x_all = torch.empty(tokens, D, dtype=torch.float16, device="cuda")
+    share = torch.empty(tokens, D, dtype=torch.float32, device="cuda")
+    recv = torch.empty(world, own, D, dtype=torch.float32, device="cuda")
+    y_own = torch.empty(own, D, dtype=torch.float32, device="cuda")
+    rng = np.random.default_rng(4)              # the same routing on every rank
+    perm = rng.permutation(E)
+    p = (np.arange(1, E + 1, dtype=np.float64) ** -args.zipf)
+    p /= p.sum()
+    ids = np.stack([perm[rng.choice(E, size=K, replace=False, p=p)] for _ in range(tokens)]).astype(np.int32)
+    idx = torch.from_numpy(ids).cuda()
+    w = torch.full((tokens, K), 1.0 / K, dtype=torch.float16, device="cuda")
+
+    def step(i: int) -> None:
+        dist.all_gather_into_tensor(x_all, x_own)
+        moe.routed_partial(i % n_layers, x_all, tokens, idx, w, share, stream=stream)
+        dist.all_to_all_single(recv.view(tokens, D), share)
+        moe.ep_finalize(recv, world, None, own, y=y_own, stream=stream)
+
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 5)):
+            step(i)
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local) if rank == 0 else None
+        l0 = launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for i in range(args.steps):
+            step(i)
+        end.record(stream)
+        dist.barrier()
+        torch.cuda.synchronize()
+        launches = launch_count() - l0
+        ms = start.elapsed_time(end)
+        # the routed kernels alone, no collective: what the exchange adds to a step
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record(stream)
+        for i in range(args.steps):
+            moe.routed_partial(i % n_layers, x_all, tokens, idx, w, share, stream=stream)
+        c1.record(stream)
+        stream.synchronize()
+        compute_ms = c0.elapsed_time(c1) / args.steps
+        clocks = sampler.stop() if sampler else None
+    assert torch.isfinite(y_own).all(), "non-finite output"
+    times = torch.tensor([ms, compute_ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms = float(times[0]) / args.steps
+    if rank == 0:
+        per = pl.pairs_per_rank(ids.ravel())
+        rec = {"metric": "moe_ffn_layer_batch_tokens_per_s", "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+               "scaling": "strong", "dtype": "f16xu%d->f32" % args.bits, "value": tokens / (ms * 1e-3), "ms_per_step": ms,
+               "clocks": clocks, "gpu_launches": int(launches),
+               "config": {"workload": "configs[4]: one layer, %d rows, Zipf(%.1f) routing, routed experts only, experts on "
+                                      "%d GPUs" % (tokens, args.zipf, world),
+                          "d": D, "f": F, "experts": E, "top_k": K, "bits": args.bits, "layers_rotated": n_layers,
+                          "placement": args.placement, "rows_per_gpu": own, "pairs_per_gpu": [int(v) for v in per],
+                          "max_over_mean_pairs_per_gpu": round(max(per) / (sum(per) / world), 3),
+                          "all_gather_bytes_in_per_gpu": (world - 1) * own * D * 2,
+                          "all_to_all_bytes_out_per_gpu": (world - 1) * own * D * 4,
+                          "routed_kernels_alone_ms_max_over_gpus": float(times[1])}}
+        print(json.dumps(rec), flush=True)
+
+
 def run_gturbo_load(args) -> None:
     """One production-size layer file (256 blobs, 453 MB at 4 bits) of a synthetic `.gturbo` artifact read into HBM
     by `nvmai_cuda_moe_read_file_to_device`; the file sits in the page cache after it is written, so the figure is the
@@ -1070,7 +1162,20 @@ def main() -> None:
     if args.block_trace and args.gpus == 1:
         run_block_trace(args)
         return
-    if args.batch_layer:
+    if args.batch_layer and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch
+        import torch.distributed as dist
+        assert args.zipf > 0, "the multi-GPU batch-layer run is the Zipf batch (--zipf S)"
+        rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        killer = threading.Timer(args.deadline, lambda: os._exit(2))
+        killer.daemon = True
+        killer.start()
+        run_batch_layer_ep(args, torch, dist, rank, world, local)
+        killer.cancel()
+        dist.destroy_process_group()
+    elif args.batch_layer:
         run_batch_layer(args)
     elif args.prefill:
         if args.tokens == 1:

@@ -642,8 +642,9 @@ int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParam
 // rows of src (out_dtype for intermediates, fp16 for x) -> fp16 rows in the K order the weights of `bits` unpack
 // in; gather != nullptr: output row r comes from source row gather[r] / gather_div
 int launch_pack_rows(nvmai_cuda_moe *h, const void *src, bool src_f32, __half *dst, float *row_scale, uint32_t rows,
-                     uint32_t n, uint32_t bits, cudaStream_t st, const uint32_t *gather = nullptr, uint32_t gather_div = 1) {
-    PackRowsParams p{src, dst, src_f32 ? row_scale : nullptr, rows, n, bits == 4 ? 1u : 0u, gather, gather_div, pf_extra_cols(n)};
+                     uint32_t n, uint32_t bits, cudaStream_t st, const uint32_t *gather = nullptr, uint32_t gather_div = 1,
+                     uint32_t src_rows = 1) {
+    PackRowsParams p{src, dst, src_f32 ? row_scale : nullptr, rows, n, bits == 4 ? 1u : 0u, gather, gather_div, src_rows, pf_extra_cols(n)};
     const dim3 grid((rows + 7) / 8), block(256);
     if (src_f32) return launch_kernel(h, pack_rows_kernel<1>, grid, block, 0, st, true, p);
     return launch_kernel(h, pack_rows_kernel<0>, grid, block, 0, st, true, p);
@@ -699,18 +700,22 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
     } else if ((rc = launch_stage1(h, lv, xsrc, tokens, idx, w, true, false, c.shared_f != 0, false, st))) {
         return rc;
     }
-    if ((rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st, false, false, kPfTileN, true)))
+    // with an expert map (this rank holds a part of the experts) the pairs of the other ranks' experts are left out
+    // of the grouping: the items, the packed rows and the partial rows then cover this rank's pairs only
+    const bool use_map = h->expert_map != nullptr;
+    if ((rc = launch_group_pairs(h, idx, w, tokens, nullptr, nullptr, nullptr, true, true, st, false, use_map, kPfTileN, true)))
         return rc;
     const uint32_t P = tokens * c.top_k;
     const uint32_t max_items = std::min(P, c.num_experts + P / kPfTileN);
     const uint32_t shared_items = (tokens + kPfTileN - 1) / kPfTileN;
     // x rows as the GEMMs read them: gathered into sorted pair order for the routed items (an item's rows are then
     // one row range of the tensor map), token order for the shared expert; each in its weights' K order
-    if ((rc = launch_pack_rows(h, x, false, h->pf_x, nullptr, P, c.d, c.routed_bits, st, h->sorted_pair, c.top_k))) return rc;
+    if ((rc = launch_pack_rows(h, x, false, h->pf_x, nullptr, P, c.d, c.routed_bits, st, h->sorted_pair, c.top_k, tokens))) return rc;
     if (c.shared_f && (rc = launch_pack_rows(h, x, false, h->pf_xn, nullptr, tokens, c.d, c.shared_bits, st))) return rc;
 
     PrefillGemmParams g{};
-    g.experts = static_cast<const uint8_t *>(lv.w.experts); g.stride = lv.w.expert_stride; g.num_experts = c.num_experts;
+    g.experts = static_cast<const uint8_t *>(lv.w.experts); g.stride = lv.w.expert_stride;
+    g.num_experts = use_map ? h->n_local : c.num_experts;
     g.off = to_offsets(lv.w.offsets);
     g.work = h->work; g.n_work = h->n_work; g.sorted_pair = h->sorted_pair;
     g.tokens = tokens; g.top_k = c.top_k; g.act = c.activation; g.status = h->status;
@@ -771,10 +776,13 @@ int layer_prefill_impl(nvmai_cuda_moe *h, uint32_t layer, const __half *x, uint3
 }
 
 // A batched decode call can take the tensor-core kernels when the fp16 operand holds the centred weight exactly
-// (bf16 scales; 8-bit codes go through as two nibbles), the tile shapes divide the layer and every expert is local.
+// (bf16 scales; 8-bit codes go through as two nibbles) and the tile shapes divide the layer.
 bool tc_batch_ok(const nvmai_cuda_moe *h, uint32_t tokens, bool with_shared, cudaStream_t st) {
     const auto &c = h->cfg;
-    if (tokens < h->tc_min_tokens || h->expert_map != nullptr) return false;
+    if (tokens < h->tc_min_tokens) return false;
+    // with an expert map only the routed-only form is taken (a rank's share of the routed sum); the whole block on
+    // a part of the experts is the per-row kernels' business
+    if (h->expert_map != nullptr && with_shared) return false;
     if (h->pf_acts16 == nullptr && st != nullptr) {
         // the first such call allocates the packed-row scratch, which a stream under capture does not allow:
         // a call that is being captured before any eager one stays on the per-row kernels
@@ -1692,7 +1700,13 @@ static int ep_stack_enqueue(nvmai_cuda_moe *h, const __half *x_own, uint32_t row
         if (nccl.AllGather(x, h->ep_x_all, own_elems, kNcclFloat16, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
         const XSource all{h->ep_x_all, c.d, nullptr, nullptr};
         if ((rc = launch_stage1(h, lv, all, rows, h->idx, h->w, true, false, false, false, st))) return rc;
-        if ((rc = grouped_tail(h, lv, h->ep_x_all, rows, h->idx, h->w, nullptr, nullptr, st, h->ep_share))) return rc;
+        if (tc_batch_ok(h, rows, false, st)) {      // enough rows for the tensor-core items over this rank's experts
+            PrefillMode mode;
+            mode.decode_order = true; mode.routed_only = true; mode.partial_y = h->ep_share;
+            if ((rc = layer_prefill_impl(h, l, h->ep_x_all, rows, nullptr, nullptr, h->idx, h->w, st, mode))) return rc;
+        } else if ((rc = grouped_tail(h, lv, h->ep_x_all, rows, h->idx, h->w, nullptr, nullptr, st, h->ep_share))) {
+            return rc;
+        }
         bool ok = nccl.GroupStart() == kNcclSuccess;      // all-to-all: block r of my shares -> rank r
         for (uint32_t r = 0; r < world && ok; ++r) {
             ok = nccl.Send(h->ep_share + r * own_elems, own_elems, kNcclFloat32, (int)r, h->ep_comm, st) == kNcclSuccess &&

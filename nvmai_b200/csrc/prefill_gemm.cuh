@@ -643,6 +643,7 @@ struct PackRowsParams {
     float *row_scale;       // fp32 sources: per row, the power of two taken out (nullptr for fp16 sources)
     uint32_t rows, n, permute;
     const uint32_t *gather; uint32_t gather_div;   // optional: source row = gather[row] / gather_div (pair id -> token)
+    uint32_t src_rows;      // with gather: rows of the source; entries past the live pairs may hold anything and are clamped
     // After the n values every row carries extra_cols more (a multiple of 64): the sums X_g of its n / 64 groups of
     // fp16 values, split into fp16 hi + lo, laid out [hi_0..hi_G-1 | lo_0..lo_G-1 | hi_0..hi_G-1 | zeros].  Against
     // the weights' [c_hi | c_hi | c_lo | 0] columns they add sum_g c_g * X_g to a GEMM row (pf_extra_cols).
@@ -661,7 +662,7 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(PackRowsParams p) {
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= p.rows) return;
     const size_t stride = (size_t)p.n + p.extra_cols;
-    const size_t srow = p.gather != nullptr ? p.gather[row] / p.gather_div : row;
+    const size_t srow = p.gather != nullptr ? min(p.gather[row] / p.gather_div, p.src_rows - 1u) : row;
     float mul = 1.0f;
     if (SRC_F32) {
         const float *src = static_cast<const float *>(p.src) + srow * p.n;

@@ -307,6 +307,56 @@ def test_zipf_batch_of_256_rows_at_the_benchmark_shape():
     print(f"[parity] zipf-256 worst sampled error against the CPU path: {worst:.3g}")
 
 
+@pytest.mark.parametrize("placement", ["contiguous", "strided"])
+def test_zipf_batch_on_a_rank_that_holds_a_part_of_the_experts(placement):
+    """the 256-row Zipf batch on one of two expert-parallel ranks: the handle holds only its rank's blobs (expert
+    map), the tensor-core items cover that rank's pairs, and the share equals what a handle with all experts
+    computes when the other rank's pairs get weight zero (their products vanish exactly); the two ranks' shares
+    add up to the full result within rounding"""
+    from nvmai_b200.ep import ExpertPlacement
+    rows, e, k = 256, 256, 8
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, rows, seed=381, d=2048, f=512, e=e)
+    rng = np.random.default_rng(5)
+    perm = rng.permutation(e)
+    p_ = np.arange(1, e + 1, dtype=np.float64) ** -1.1
+    p_ /= p_.sum()
+    ids = np.stack([perm[rng.choice(e, size=k, replace=False, p=p_)] for _ in range(rows)]).astype(np.uint32)
+    x = synthetic.hidden_rows(382, rows, cfg.d)
+    w16 = np.full((rows, k), 1.0 / k, dtype=np.float16)
+    pl = ExpertPlacement(e, 2, placement)
+
+    full = MoE(cfg)
+    dl_full = gu.DeviceLayer(host)
+    dl_full.register(full, 0)
+
+    def full_share(weights):
+        out = gu.dev_empty(rows * cfg.d, "f32")
+        full.routed_partial(0, gu.to_dev(x), rows, gu.to_dev(ids), gu.to_dev(weights.view(np.uint16)), out)
+        full.synchronize()
+        return out.cpu().numpy().reshape(rows, cfg.d)
+
+    whole = full_share(w16)
+    total = np.zeros_like(whole)
+    for rank in range(2):
+        local = dict(host)
+        local["experts"] = np.ascontiguousarray(host["experts"][pl.local_experts(rank)])
+        moe = MoE(cfg)
+        dl = gu.DeviceLayer(local)
+        dl.register(moe, 0)
+        moe.set_expert_map(pl.expert_map(rank))
+        share = gu.dev_empty(rows * cfg.d, "f32")
+        moe.routed_partial(0, gu.to_dev(x), rows, gu.to_dev(ids), gu.to_dev(w16.view(np.uint16)), share)
+        moe.synchronize()
+        got = share.cpu().numpy().reshape(rows, cfg.d)
+        owners = np.vectorize(pl.owner)(ids)
+        masked = np.where(owners == rank, w16, np.float16(0.0)).astype(np.float16)
+        want = full_share(masked)
+        assert np.all(np.isfinite(got))
+        np.testing.assert_allclose(got, want, rtol=0, atol=1e-6 * float(np.abs(want).max()))
+        total += got
+    assert orc.rel_error(total.reshape(-1), whole.reshape(-1)) < 1e-5
+
+
 @pytest.mark.parametrize("out_dtype", [fmt.OUT_FP32, fmt.OUT_FP16])
 def test_large_decode_batch_on_tensor_cores_keeps_decode_semantics(out_dtype, monkeypatch):
     """from 32 rows on a 4-bit batched decode call runs the grouped GEMMs of the prefill path; indices stay exact,
