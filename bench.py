@@ -381,10 +381,24 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
         dist.broadcast_object_list(ids, src=0)
         moe.ep_init(ids[0], rank, world, tokens)
         if args.ep_exchange == "p2p":
-            # the ranks' receive areas mapped into each other (CUDA IPC): the down stage stores its shares there itself
+            # the ranks' receive areas mapped into each other (CUDA IPC): the down phase stores its shares there itself
             handles = [None] * world
             dist.all_gather_object(handles, moe.ep_peer_export())
-            moe.ep_peer_attach(handles)
+            try:
+                moe.ep_peer_attach(handles)
+                attached = 1
+            except Exception as err:       # no peer access between some pair of GPUs
+                note(f"peer attach failed: {err}")
+                attached = 0
+            flag = torch.tensor([attached], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                # every rank falls back together: a fresh communicator, shares by NCCL between the staged kernels
+                args.ep_exchange = "nccl"
+                moe.ep_shutdown()
+                ids = [moe.ep_unique_id() if rank == 0 else None]
+                dist.broadcast_object_list(ids, src=0)
+                moe.ep_init(ids[0], rank, world, tokens)
 
         def run_step():
             moe.ep_stack_decode(x_in, tokens, y_out, stream=stream)
@@ -1156,6 +1170,8 @@ def main() -> None:
     ap.add_argument("--deadline", type=float, default=600.0,
                     help="multi-GPU runs: give up (exit 2) after this many seconds instead of waiting on a stuck collective")
     args = ap.parse_args()
+    # the collectives of this benchmark are a few KB per step: NVLink SHARP (multicast objects) has nothing to speed up
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if args.gturbo_load:
         run_gturbo_load(args)
         return
