@@ -93,7 +93,12 @@ typedef struct {
 } nvmai_affine_tensor;
 
 /* Per-layer weight views: `Model.routedExpertOffsets` + the runner's per-layer
- * shared-expert projections (ModelExpertIO.swift:67-82, RealForwardRunner.swift:587-610). */
+ * shared-expert projections (ModelExpertIO.swift:67-82, RealForwardRunner.swift:587-610).
+ * `experts` and `expert_stride` must be 16-byte aligned (the blobs are never copied).  The
+ * other tensors may start at any even address, as they do in the reference's weight file
+ * (RepackPlanner.swift:310-316; DequantInt4GEMVTests.swift:114-121 tests a base off by two
+ * bytes): register_layer copies a tensor whose base is not 16-byte aligned into an aligned
+ * buffer of its own, once, and uses that. */
 typedef struct {
     const void *experts;         /* num_experts blobs, expert_stride bytes apart */
     uint64_t expert_stride;

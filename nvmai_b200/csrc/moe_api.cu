@@ -36,6 +36,7 @@ static std::atomic<uint64_t> g_launches{0};
 struct LayerViews {
     bool registered = false;
     nvmai_cuda_moe_layer w{};
+    std::vector<void *> owned;      // aligned copies of resident tensors whose base was not 16-byte aligned
 };
 
 struct StackGraphKey {
@@ -1194,6 +1195,8 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     cudaFree(h->pb_xchg);
     cudaFree(h->pd_layers); cudaFree(h->pd_xchg); cudaFree(h->pd_epoch); cudaFree(h->pd_route_log);
     cudaFree(h->pf_x); cudaFree(h->pf_xn); cudaFree(h->pf_acts16); cudaFree(h->pf_sacts16); cudaFree(h->pf_rowscale); cudaFree(h->pf_srowscale);
+    for (auto &lv : h->layers)
+        for (void *p : lv.owned) cudaFree(p);
     cudaFree(h->logits); cudaFree(h->idx); cudaFree(h->w); cudaFree(h->acts); cudaFree(h->shared_act);
     cudaFree(h->gate_val); cudaFree(h->y); cudaFree(h->xnorm); cudaFree(h->counter); cudaFree(h->status);
     cudaFree(h->stage_x); cudaFree(h->stage_y); cudaFree(h->row_counter);
@@ -1202,26 +1205,55 @@ void nvmai_cuda_moe_destroy(nvmai_cuda_moe *h) {
     delete h;
 }
 
-int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, const nvmai_cuda_moe_layer *wts) {
-    if (!h || !wts) return NVMAI_CUDA_EINVAL;
+int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, const nvmai_cuda_moe_layer *wts_in) {
+    if (!h || !wts_in) return NVMAI_CUDA_EINVAL;
     if (layer >= h->layers.size()) return NVMAI_CUDA_ERANGE;
     const auto &c = h->cfg;
+    nvmai_cuda_moe_layer copy = *wts_in;
+    nvmai_cuda_moe_layer *wts = &copy;
     if (!wts->experts || !aligned16(wts->experts) || (wts->expert_stride & 15u)) return NVMAI_CUDA_EINVAL;
     int rc = check_offsets(c, wts->offsets, wts->expert_stride);
     if (rc) return rc;
-    auto tensor_ok = [&](const nvmai_affine_tensor &t, uint32_t kind_or_bits) {
-        if (!t.w || !aligned16(t.w)) return false;
-        if (kind_or_bits == 0) return true;   // dense: no meta
-        return t.scales && t.biases && aligned16(t.scales) && aligned16(t.biases);
+    // The resident tensors (router, shared expert, gate row, input scale) sit back to back in the reference's weight
+    // file with no alignment (RepackPlanner.swift:310-316; its kernels are tested on a base that is off by two bytes,
+    // DequantInt4GEMVTests.swift:114-121), while the bulk copies here want 16-byte aligned sources: a tensor whose base
+    // is not aligned is copied once, at registration, into an aligned buffer the handle owns (a few MB per layer).
+    // The expert blobs are never copied: their base and stride must be aligned.
+    std::vector<void *> owned;
+    auto fail = [&](int code) {
+        for (void *p : owned) cudaFree(p);
+        return code;
     };
-    if (!tensor_ok(wts->router, c.router_kind)) return NVMAI_CUDA_EINVAL;
+    auto realign = [&](const void *&ptr, size_t bytes) -> int {
+        if (ptr == nullptr || aligned16(ptr)) return NVMAI_CUDA_OK;
+        if (reinterpret_cast<uintptr_t>(ptr) & 1u) return NVMAI_CUDA_EINVAL;       // 16-bit elements at an odd address
+        void *buf = nullptr;
+        if (cudaMalloc(&buf, (bytes + 15) & ~(size_t)15) != cudaSuccess) { cudaGetLastError(); return NVMAI_CUDA_ENOMEM; }
+        owned.push_back(buf);
+        int r = record(h, cudaMemcpy(buf, ptr, bytes, cudaMemcpyDeviceToDevice));
+        ptr = buf;
+        return r;
+    };
+    // kind_or_bits: 0 = dense fp16 rows, else the code width of an affine tensor [rows][n]
+    auto tensor = [&](nvmai_affine_tensor &t, uint32_t kind_or_bits, size_t rows, size_t n) -> int {
+        if (!t.w) return NVMAI_CUDA_EINVAL;
+        int r = realign(t.w, kind_or_bits == 0 ? rows * n * 2 : rows * n * kind_or_bits / 8);
+        if (r || kind_or_bits == 0) return r;
+        if (!t.scales || !t.biases) return NVMAI_CUDA_EINVAL;
+        if ((r = realign(t.scales, rows * (n / kGroup) * 2))) return r;
+        return realign(t.biases, rows * (n / kGroup) * 2);
+    };
+    if ((rc = tensor(wts->router, c.router_kind, c.num_experts, c.d))) return fail(rc);
     if (c.shared_f) {
-        if (!tensor_ok(wts->shared_gate_proj, c.shared_bits) || !tensor_ok(wts->shared_up_proj, c.shared_bits) ||
-            !tensor_ok(wts->shared_down_proj, c.shared_bits)) return NVMAI_CUDA_EINVAL;
-        if (c.shared_gate_kind != NVMAI_GATE_NONE && !tensor_ok(wts->shared_gate, c.shared_gate_kind))
-            return NVMAI_CUDA_EINVAL;
+        if ((rc = tensor(wts->shared_gate_proj, c.shared_bits, c.shared_f, c.d)) ||
+            (rc = tensor(wts->shared_up_proj, c.shared_bits, c.shared_f, c.d)) ||
+            (rc = tensor(wts->shared_down_proj, c.shared_bits, c.d, c.shared_f)))
+            return fail(rc);
+        if (c.shared_gate_kind != NVMAI_GATE_NONE && (rc = tensor(wts->shared_gate, c.shared_gate_kind, 1, c.d))) return fail(rc);
     }
-    if (wts->effective_scale && !aligned16(wts->effective_scale)) return NVMAI_CUDA_EINVAL;
+    if ((rc = realign(wts->effective_scale, (size_t)c.d * 2))) return fail(rc);
+    for (void *p : h->layers[layer].owned) cudaFree(p);       // copies made for an earlier registration of this layer
+    h->layers[layer].owned = std::move(owned);
     h->layers[layer].w = *wts;
     h->layers[layer].registered = true;
     h->graphs_stale = h->ep_graphs_stale = true;

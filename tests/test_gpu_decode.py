@@ -491,3 +491,43 @@ def test_errors_are_codes_not_traps():
         moe.register_layer(0, experts=dl.experts, expert_stride=host["stride"], offsets=bad, router=dl.router,
                            shared=dl.shared, shared_gate=dl.gate)
     assert ei.value.code == _lib.ERANGE
+
+
+def test_resident_tensors_at_bases_that_are_off_by_two_bytes():
+    """the reference packs router / shared-expert tensors back to back without alignment and tests its kernels on a
+    base that is off by two bytes (DequantInt4GEMVTests.swift:114-121): such tensors are realigned at registration
+    and the layer gives the same bits as with aligned tensors"""
+    import torch
+    tokens = 3
+    host = synthetic.layer(611, d=256, f=128, shared_f=128, num_experts=16, routed_bits=4, shared_bits=4,
+                           meta=fmt.META_BF16, router_kind=fmt.ROUTER_AFFINE8, gate_kind=fmt.ROUTER_AFFINE8)
+    cfg = MoEConfig(d=256, f=128, shared_f=128, num_experts=16, top_k=8, routed_bits=4, shared_bits=4,
+                    router_kind=fmt.ROUTER_AFFINE8, shared_gate_kind=fmt.ROUTER_AFFINE8, meta_dtype=fmt.META_BF16,
+                    out_dtype=fmt.OUT_FP32, max_tokens=tokens)
+    x = gu.to_dev(synthetic.hidden_rows(612, tokens, 256))
+    dl = gu.DeviceLayer(host)
+
+    def off_by_two(t):
+        if t is None:
+            return None
+        flat = t.contiguous().view(torch.uint8).reshape(-1)
+        buf = torch.zeros(flat.numel() + 32, dtype=torch.uint8, device=flat.device)
+        view = buf[2:2 + flat.numel()]
+        view.copy_(flat)
+        assert view.data_ptr() % 16 == 2
+        return view
+
+    def run(shift):
+        moe = MoE(cfg)
+        if shift:
+            fix = lambda t3: tuple(off_by_two(t) for t in t3)
+            moe.register_layer(0, experts=dl.experts, expert_stride=host["stride"], offsets=host["offsets"],
+                               router=fix(dl.router), shared=[fix(t) for t in dl.shared], shared_gate=fix(dl.gate))
+        else:
+            dl.register(moe, 0)
+        y = gu.dev_empty(tokens * 256, "f32")
+        moe.layer_decode(0, x, tokens, h2_out=y)
+        moe.synchronize()
+        return y.cpu().numpy()
+
+    np.testing.assert_array_equal(run(True), run(False))
