@@ -363,6 +363,11 @@ NVMAI_API int nvmai_cuda_moe_set_decode_mode(nvmai_cuda_moe *h, int mode);
  * (RealForwardRunner.swift:1208-1237).  Synchronises the device. */
 NVMAI_API int nvmai_cuda_moe_read_route_log(nvmai_cuda_moe *h, uint32_t *out_host, uint32_t layers);
 
+/* The same after a step of several rows (2..8 rows through the resident kernel, or an
+ * expert-parallel step, where the rows are those of all ranks): u32 [layers][rows][top_k].
+ * `rows` must be the row count of that step. */
+NVMAI_API int nvmai_cuda_moe_read_route_log_rows(nvmai_cuda_moe *h, uint32_t *out_host, uint32_t layers, uint32_t rows);
+
 /* Test hook: the longest any device-side wait of this library lasts, in nanoseconds
  * (0 restores the default of one second).  Process-wide, per device. */
 NVMAI_API int nvmai_cuda_moe_debug_set_wait_limit(uint64_t nanoseconds);

@@ -91,6 +91,7 @@ PROTOTYPES = {
     "nvmai_cuda_moe_launch_count": (u64, []),
     "nvmai_cuda_moe_set_decode_mode": (C.c_int, [vp, C.c_int]),
     "nvmai_cuda_moe_read_route_log": (C.c_int, [vp, vp, u32]),
+    "nvmai_cuda_moe_read_route_log_rows": (C.c_int, [vp, vp, u32, u32]),
     "nvmai_cuda_moe_debug_set_wait_limit": (C.c_int, [u64]),
     "nvmai_cuda_moe_debug_mute_block": (C.c_int, [vp, u32]),
 }

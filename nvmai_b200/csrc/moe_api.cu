@@ -126,7 +126,8 @@ struct nvmai_cuda_moe {
     unsigned long long *pd_xchg = nullptr;
     unsigned long long *pb_xchg = nullptr;    // the batch kernel's exchange words (up to kPbMaxRows rows)
     unsigned int *pd_epoch = nullptr;
-    uint32_t *pd_route_log = nullptr;     // [num_layers][top_k]
+    uint32_t *pd_route_log = nullptr;     // [num_layers][rows of the step <= 8][top_k]
+    uint32_t pd_route_rows = 1;           // rows of the last resident-kernel step
     int sm_count = 0;
     // 0: a single-token stack step takes the one-launch kernel when the shape allows it; 1: always the staged
     // kernels; 2: the one-launch kernel or NVMAI_CUDA_EINVAL
@@ -956,6 +957,7 @@ int pd_launch(nvmai_cuda_moe *h, const PdPlan &plan, const __half *x0, void *y_l
     p.xlogits = h->pd_xchg + X.logits; p.xsact = h->pd_xchg + X.sact; p.xgate = h->pd_xchg + X.gate;
     p.xacts = h->pd_xchg + X.acts; p.xy = h->pd_xchg + X.y;
     p.epoch = h->pd_epoch; p.status = h->status; p.route_log = h->pd_route_log;
+    h->pd_route_rows = 1;
     p.D = c.d; p.F = c.f; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation; p.shared_f = c.shared_f;
     p.router_kind = c.router_kind; p.gate_kind = gated ? c.shared_gate_kind : NVMAI_GATE_NONE;
     p.router_rows = plan.router_rows; p.slots = plan.slots; p.max_tiles = plan.max_tiles;
@@ -1044,7 +1046,8 @@ int pb_launch(nvmai_cuda_moe *h, const PbPlan &plan, const __half *x_all, uint32
     p.expert_map = h->expert_map;
     p.rank = rank; p.world = world;
     for (uint32_t r = 0; r < world && r < (uint32_t)kEpMaxRanks; ++r) p.recv[r] = recv ? recv[r] : nullptr;
-    p.epoch = h->pd_epoch; p.status = h->status; p.route_log = nullptr;
+    p.epoch = h->pd_epoch; p.status = h->status; p.route_log = h->pd_route_log;
+    h->pd_route_rows = T;
     p.trace = h->trace_on ? h->pd_trace : nullptr;
     p.D = c.d; p.F = c.f; p.E = c.num_experts; p.K = c.top_k; p.act = c.activation; p.shared_f = c.shared_f;
     p.router_kind = c.router_kind; p.gate_kind = gated ? c.shared_gate_kind : NVMAI_GATE_NONE;
@@ -1171,9 +1174,9 @@ nvmai_cuda_moe *nvmai_cuda_moe_create(const nvmai_cuda_moe_config *config, int *
              alloc(&h->pd_xchg, xbytes) && alloc(&h->pd_epoch, 5 * 128) &&
              alloc(&h->pb_xchg, PbXchg(c, kPbMaxRows, (uint32_t)std::max(h->sm_count, 1)).words * sizeof(unsigned long long)) &&
              cudaMemset(h->pb_xchg, 0, PbXchg(c, kPbMaxRows, (uint32_t)std::max(h->sm_count, 1)).words * sizeof(unsigned long long)) == cudaSuccess && alloc(&h->pd_layers, (size_t)c.num_layers * sizeof(PdLayer)) &&
-             alloc(&h->pd_route_log, (size_t)c.num_layers * c.top_k * 4) &&
+             alloc(&h->pd_route_log, (size_t)c.num_layers * kPbMaxRows * c.top_k * 4) &&
              cudaMemset(h->pd_xchg, 0, xbytes) == cudaSuccess && cudaMemset(h->pd_epoch, 0, 5 * 128) == cudaSuccess &&
-             cudaMemset(h->pd_route_log, 0, (size_t)c.num_layers * c.top_k * 4) == cudaSuccess &&
+             cudaMemset(h->pd_route_log, 0, (size_t)c.num_layers * kPbMaxRows * c.top_k * 4) == cudaSuccess &&
              cudaMemcpy(h->pd_epoch, &first_epoch, sizeof(first_epoch), cudaMemcpyHostToDevice) == cudaSuccess;
     }
     if (const char *env = std::getenv("NVMAI_CUDA_DECODE_MODE")) h->decode_mode = std::atoi(env);
@@ -2083,8 +2086,13 @@ int nvmai_cuda_moe_set_decode_mode(nvmai_cuda_moe *h, int mode) {
 }
 
 int nvmai_cuda_moe_read_route_log(nvmai_cuda_moe *h, uint32_t *out_host, uint32_t layers) {
-    if (!h || !out_host || layers > h->cfg.num_layers) return NVMAI_CUDA_EINVAL;
+    if (!h || !out_host || layers > h->cfg.num_layers || h->pd_route_rows != 1) return NVMAI_CUDA_EINVAL;
     return record(h, cudaMemcpy(out_host, h->pd_route_log, (size_t)layers * h->cfg.top_k * 4, cudaMemcpyDeviceToHost));
+}
+
+int nvmai_cuda_moe_read_route_log_rows(nvmai_cuda_moe *h, uint32_t *out_host, uint32_t layers, uint32_t rows) {
+    if (!h || !out_host || layers > h->cfg.num_layers || rows != h->pd_route_rows) return NVMAI_CUDA_EINVAL;
+    return record(h, cudaMemcpy(out_host, h->pd_route_log, (size_t)layers * rows * h->cfg.top_k * 4, cudaMemcpyDeviceToHost));
 }
 
 int nvmai_cuda_moe_debug_mute_block(nvmai_cuda_moe *h, uint32_t block) {

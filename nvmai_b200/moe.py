@@ -276,6 +276,14 @@ class MoE:
         check(self._lib.nvmai_cuda_moe_read_route_log(self._h, out.ctypes.data, n), "read_route_log")
         return out
 
+    def read_route_log_rows(self, rows: int, layers: int | None = None):
+        """-> uint32 [layers, rows, top_k] after a resident-kernel step of `rows` rows (2..8, or all ranks' rows)."""
+        import numpy as np
+        n = self.config.num_layers if layers is None else layers
+        out = np.zeros((n, rows, self.config.top_k), dtype=np.uint32)
+        check(self._lib.nvmai_cuda_moe_read_route_log_rows(self._h, out.ctypes.data, n, rows), "read_route_log_rows")
+        return out
+
     def set_trace(self, enable: bool) -> None:
         check(self._lib.nvmai_cuda_moe_set_trace(self._h, int(enable)), "set_trace")
 

@@ -82,6 +82,21 @@ class RouteTrace:
         return out.getvalue()
 
 
+def from_route_log(log, first_position: int = 0, *, num_experts: int = 256) -> RouteTrace:
+    """The routing a decode step recorded on the device (`MoE.read_route_log`: [layers][top_k], or
+    `read_route_log_rows`: [layers][rows][top_k]) as trace records: row r of the step is position
+    first_position + r, layers in order.  `.format()` then gives the reference's NVMAI_ROUTE_TRACE lines
+    (`position layer e0..e7`, RealForwardRunner.swift:1208-1237)."""
+    log = np.asarray(log)
+    if log.ndim == 2:
+        log = log[:, None, :]
+    layers, rows, k = log.shape
+    pos = np.repeat(np.arange(rows, dtype=np.int64) + first_position, layers)
+    lay = np.tile(np.arange(layers, dtype=np.int32), rows)
+    exp = log.transpose(1, 0, 2).reshape(rows * layers, k).astype(np.int32)
+    return RouteTrace(positions=pos, layers=lay, experts=exp, num_experts=num_experts)
+
+
 def parse(source, *, num_experts: int = 256, top_k: int = 8, num_layers: int | None = None) -> RouteTrace:
     """`source`: a path, or the text itself.  Every line must read `position layer e0 .. e{top_k-1}` with
     0 <= e < num_experts, no expert twice in a line and (when given) layer < num_layers; blank lines are skipped.

@@ -233,9 +233,24 @@ def test_resident_rows_stack_against_oracle_chain(rows, bits):
         st.synchronize()
         res = _run_rows(moe, cfg, xd, rows, MoE.DECODE_RESIDENT, st)
         staged = _run_rows(moe, cfg, xd, rows, MoE.DECODE_STAGED, st)
+    checked = []
     for t in range(rows):
         idxs, h2, margin = _oracle_chain(cfg, hosts, x0[t])
         if margin <= 1e-5 or np.abs(h2).max() < 1e-20:
             continue        # a degenerate chain (tie, or a layer that came out all zero) tests nothing
         assert orc.rel_error(res[t], h2) < 2e-3, f"row {t} vs the oracle chain"
         assert orc.rel_error(res[t], staged[t]) < 1e-4, f"row {t} vs the staged kernels"
+        checked.append((t, idxs))
+    # the step's own routing record, and its dump in the reference's NVMAI_ROUTE_TRACE line format
+    from nvmai_b200 import route_trace as rt
+    log = moe.read_route_log_rows(rows)
+    assert log.shape == (layers, rows, 8)
+    for t, idxs in checked:
+        for l in range(layers):
+            np.testing.assert_array_equal(log[l, t], idxs[l])
+    text = rt.from_route_log(log, 100, num_experts=e).format()
+    back = rt.parse(text, num_experts=e, top_k=8)
+    assert len(back) == layers * rows
+    for t in range(rows):
+        for l in range(layers):
+            np.testing.assert_array_equal(back.batch(l, t, 1)[0], log[l, t])
