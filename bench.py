@@ -859,7 +859,7 @@ def run_prefill(args) -> None:
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
         clocks = sampler.stop()
         parity = None
-        if not args.no_parity and args.bits == 4:
+        if not args.no_parity:
             idx = torch.empty(tokens, K, dtype=torch.int32, device="cuda")
             moe.layer_prefill(0, x, tokens, y_out=y, out_idx=idx, stream=stream)
             moe.synchronize(stream)
@@ -988,7 +988,32 @@ def stack_parity(args, cfg, devs, xs, torch) -> dict:
     moe = MoE(cfg_p)
     for l in range(n):
         synthetic.register_device_layer(moe, l, devs[l])
-    x0 = xs[0, 0].contiguous()
+    hosts = [device_layer_to_host(devs[l], torch) for l in range(n)]        # kept alive: the oracle reads them in place
+    oracle_layers = [gu.oracle_layer(hosts[l], cfg_p) for l in range(n)]
+
+    def chain(x_bits):
+        idxs, margin_min, h2, cpu = [], float("inf"), None, None
+        x = x_bits
+        for l in range(n):
+            idx, _, h2, margin, cpu = gu.oracle_decode(oracle_layers[l][0], cfg_p, x)
+            idxs.append(idx.tolist())
+            margin_min = min(margin_min, margin)
+            if l + 1 < n:
+                scale = 1.0 / np.sqrt(np.mean(h2.astype(np.float64) ** 2) + 1e-6)
+                x = orc.f32_to_f16_bits((h2.astype(np.float64) * scale).astype(np.float32))
+        return idxs, margin_min, h2, cpu
+
+    # Each layer's input is the previous layer's output, which differs between the two sides by their rounding: a
+    # selection decided by less than that difference proves nothing either way, so of the first eight input rows the
+    # one whose chain keeps the widest gap between its eighth and ninth logit is checked
+    best = None
+    for cand in range(min(8, xs.shape[0])):
+        x_bits = np.ascontiguousarray(xs[cand, 0].contiguous().cpu().view(torch.int16).numpy().view(np.uint16))
+        res = chain(x_bits)
+        if best is None or res[1] > best[1][1]:
+            best = (cand, res)
+    row, (idxs, margin_min, h2, cpu) = best
+    x0 = xs[row, 0].contiguous()
     outs = {}
     for mode in (MoE.DECODE_STAGED, MoE.DECODE_AUTO):
         y = torch.empty(D, dtype=torch.float32, device="cuda")
@@ -998,19 +1023,8 @@ def stack_parity(args, cfg, devs, xs, torch) -> dict:
         outs[mode] = y.cpu().numpy()
     log = moe.read_route_log(n)
     got = outs[MoE.DECODE_AUTO]
-
-    x = np.ascontiguousarray(x0.cpu().view(torch.int16).numpy().view(np.uint16))
-    idx_ok, margin_min, h2, cpu = True, float("inf"), None, None
-    for l in range(n):
-        host = device_layer_to_host(devs[l], torch)
-        L, keep = gu.oracle_layer(host, cfg_p)
-        idx, _, h2, margin, cpu = gu.oracle_decode(L, cfg_p, x)
-        idx_ok = idx_ok and log[l].tolist() == idx.tolist()
-        margin_min = min(margin_min, margin)
-        if l + 1 < n:
-            scale = 1.0 / np.sqrt(np.mean(h2.astype(np.float64) ** 2) + 1e-6)
-            x = orc.f32_to_f16_bits((h2.astype(np.float64) * scale).astype(np.float32))
-    rec = {"layers_checked": n, "expert_indices_exact": bool(idx_ok), "min_router_margin": margin_min,
+    idx_ok = all(log[l].tolist() == idxs[l] for l in range(n))
+    rec = {"layers_checked": n, "input_row": row, "expert_indices_exact": bool(idx_ok), "min_router_margin": margin_min,
            "rel_err_vs_oracle_chain": float(orc.rel_error(got, h2)),
            "oracle_last_layer_vs_reference_cpu_path": float(orc.rel_error(h2, cpu)),
            "resident_equals_staged_bitwise": bool(np.array_equal(outs[MoE.DECODE_STAGED].view(np.uint32), got.view(np.uint32)))}
