@@ -372,6 +372,13 @@ NVMAI_API int nvmai_cuda_moe_read_route_log_rows(nvmai_cuda_moe *h, uint32_t *ou
  * (0 restores the default of one second).  Process-wide, per device. */
 NVMAI_API int nvmai_cuda_moe_debug_set_wait_limit(uint64_t nanoseconds);
 
+/* Test hook for the failure path of the prefill GEMM: in the next gate/up launch one block
+ * leaves out the copy of one K block of its activation rows, so its bounded waits run out:
+ * the block sets the status word, frees its tensor memory and returns, blocks that start
+ * later return at once, nvmai_cuda_moe_synchronize reports NVMAI_CUDA_ETIMEOUT, and the next
+ * call runs normally.  Nothing faults or hangs. */
+NVMAI_API int nvmai_cuda_moe_debug_drop_prefill_copy(nvmai_cuda_moe *h);
+
 /* Test hook: holds `stream` for `ms` milliseconds with a host function (no kernel runs, the
  * device stays idle), so that a test can watch a host-side wait run out. */
 NVMAI_API int nvmai_cuda_moe_debug_host_delay(nvmai_cuda_moe *h, void *stream, uint32_t ms);

@@ -71,6 +71,7 @@ PROTOTYPES = {
     "nvmai_cuda_moe_ep_shutdown": (C.c_int, [vp]),
     "nvmai_cuda_moe_ep_synchronize": (C.c_int, [vp, vp, u32]),
     "nvmai_cuda_moe_debug_host_delay": (C.c_int, [vp, vp, u32]),
+    "nvmai_cuda_moe_debug_drop_prefill_copy": (C.c_int, [vp]),
     "nvmai_cuda_moe_ep_peer_export": (C.c_int, [vp, vp]),
     "nvmai_cuda_moe_ep_peer_attach": (C.c_int, [vp, vp]),
     "nvmai_cuda_moe_ep_stack_decode": (C.c_int, [vp, vp, u32, vp, vp]),

@@ -128,6 +128,7 @@ struct nvmai_cuda_moe {
     unsigned int *pd_epoch = nullptr;
     uint32_t *pd_route_log = nullptr;     // [num_layers][rows of the step <= 8][top_k]
     uint32_t pd_route_rows = 1;           // rows of the last resident-kernel step
+    bool pf_debug_drop = false;           // test hook: the next gate/up GEMM launch leaves out one copy (its waits run out)
     int sm_count = 0;
     // 0: a single-token stack step takes the one-launch kernel when the shape allows it; 1: always the staged
     // kernels; 2: the one-launch kernel or NVMAI_CUDA_EINVAL
@@ -625,6 +626,7 @@ int launch_prefill_gemm(nvmai_cuda_moe *h, uint32_t bits, const PrefillGemmParam
     const auto &c = h->cfg;
     PrefillGemmArgs args{};
     args.p = p;
+    if (PHASE == 0 && h->pf_debug_drop) { args.p.debug_drop_b = 1; h->pf_debug_drop = false; }     // one launch only
     const uint64_t cols = p.kdim + pf_extra_cols(p.kdim);        // the rows carry their correction columns
     int rc = make_rows_tmap(h, &args.tmap_b, b_rows, b_count, cols, cols, kPfBoxRows);
     if (rc) return rc;
@@ -2093,6 +2095,12 @@ int nvmai_cuda_moe_read_route_log(nvmai_cuda_moe *h, uint32_t *out_host, uint32_
 int nvmai_cuda_moe_read_route_log_rows(nvmai_cuda_moe *h, uint32_t *out_host, uint32_t layers, uint32_t rows) {
     if (!h || !out_host || layers > h->cfg.num_layers || rows != h->pd_route_rows) return NVMAI_CUDA_EINVAL;
     return record(h, cudaMemcpy(out_host, h->pd_route_log, (size_t)layers * rows * h->cfg.top_k * 4, cudaMemcpyDeviceToHost));
+}
+
+int nvmai_cuda_moe_debug_drop_prefill_copy(nvmai_cuda_moe *h) {
+    if (!h) return NVMAI_CUDA_EINVAL;
+    h->pf_debug_drop = true;
+    return NVMAI_CUDA_OK;
 }
 
 int nvmai_cuda_moe_debug_mute_block(nvmai_cuda_moe *h, uint32_t block) {

@@ -85,7 +85,6 @@ __host__ __device__ constexpr uint32_t pf_extra_cols(uint32_t kdim) { return ((3
 // The group sums in the correction columns are stored times this factor (and the constants they multiply divided
 // by it): 64 fp16 values can add up to 2^22.
 constexpr float kPfSumScale = 1.0f / 128.0f;
-constexpr uint32_t kPfWaitTries = 1u << 22;    // bounded: a few seconds at the hardware's default try_wait limit
 
 // ---- tcgen05 / async-proxy primitives ---------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t cols) {
@@ -121,7 +120,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 // Pipeline waits here are short (a stage turns over in well under a microsecond), so the wait must wake
-// promptly: try_wait without a suspend-time hint (the hardware's own short limit), retried up to kPfWaitTries.
+// promptly: try_wait without a suspend-time hint (the hardware's own short limit), retried until the clock limit of the caller.
 __device__ __forceinline__ bool pf_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -267,6 +266,7 @@ struct PrefillGemmParams {
     uint32_t act;                  // activation kind (phase 0)
     uint32_t round_gate_up;        // phase 0: round gate and up before the activation (the shared expert does)
     unsigned int *status;
+    uint32_t debug_drop_b;         // test hook: block (0, 0) leaves out the B rows of its second K block, so its waits run out
     unsigned long long *trace;     // optional timeline of block (0, 0): start, end, marks (setup, loop, MMAs done, epilogue)
 };
 
@@ -351,11 +351,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     bool ok = true;
     trace_mark(p.trace, 0);
+    // bounded by the GPU's nanosecond timer (one second unless a test shortens it), looked at every 16 tries
     auto wait = [&](uint64_t *bar, uint32_t parity) {
-        bool done = false;
-        for (uint32_t t = 0; t < kPfWaitTries && !done; ++t) done = pf_try_wait(bar, parity);
-        if (!done) atomicExch(p.status, 1u);
-        return done;
+        if (pf_try_wait(bar, parity)) return true;
+        const unsigned long long t0 = global_timer_ns(), limit = g_wait_limit_ns;
+        for (;;) {
+#pragma unroll 1
+            for (int it = 0; it < 16; ++it)
+                if (pf_try_wait(bar, parity)) return true;
+            if (global_timer_ns() - t0 > limit) break;
+        }
+        atomicExch(p.status, 1u);
+        return false;
     };
 
     if (warp < kPfProducerWarps) {
@@ -509,10 +516,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_gemm_kernel(const __gri
             for (uint32_t kb = 0; kb < n_kb && ok; ++kb) {
                 ok = wait(&b_empty[j], jph ^ 1u);
                 if (!ok) break;
-                mbar_expect_tx(&b_full[j], b_slot);
-                for (uint32_t x = 0; x < n_box; ++x)
-                    tma_load_2d(b_ring + j * b_slot + x * (kPfBoxRows * 128u), b_map, kb * kPfKBlock,
-                                item.start + x * kPfBoxRows, &b_full[j]);
+                if (!(p.debug_drop_b != 0u && kb == 1u && blockIdx.x == 0u && blockIdx.y == 0u)) {
+                    mbar_expect_tx(&b_full[j], b_slot);
+                    for (uint32_t x = 0; x < n_box; ++x)
+                        tma_load_2d(b_ring + j * b_slot + x * (kPfBoxRows * 128u), b_map, kb * kPfKBlock,
+                                    item.start + x * kPfBoxRows, &b_full[j]);
+                }
                 if (BITS == 16) {                 // a dense A matrix comes the same way
                     const uint32_t s = kb % kPfStages;
                     ok = wait(&a_empty[s], ((kb / kPfStages) & 1u) ^ 1u);

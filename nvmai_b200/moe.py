@@ -208,6 +208,9 @@ class MoE:
         asynchronous error or the stream has not finished after `timeout_ms`."""
         check(self._lib.nvmai_cuda_moe_ep_synchronize(self._h, _stream(stream), int(timeout_ms)), "ep_synchronize")
 
+    def debug_drop_prefill_copy(self) -> None:
+        check(self._lib.nvmai_cuda_moe_debug_drop_prefill_copy(self._h), "debug_drop_prefill_copy")
+
     def debug_host_delay(self, ms: int, stream=None) -> None:
         check(self._lib.nvmai_cuda_moe_debug_host_delay(self._h, _stream(stream), int(ms)), "debug_host_delay")
 

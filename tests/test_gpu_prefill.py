@@ -197,6 +197,30 @@ def test_prefill_deterministic():
     assert np.array_equal(y.cpu().numpy().reshape(33, cfg.d).view(np.uint32), got.view(np.uint32))
 
 
+def test_prefill_wait_that_runs_out_frees_tensor_memory_and_the_next_call_runs():
+    """a bounded wait of the tensor-core GEMM made to run out from the host side (one block leaves out one copy of its
+    own activation rows; nothing faults): the block sets the status word, frees its tensor memory and returns,
+    synchronize reports the timeout once, and the same call then gives the same bits as before"""
+    from nvmai_b200 import _lib
+    from nvmai_b200.moe import debug_set_wait_limit
+    host, cfg = _case(4, fmt.META_BF16, fmt.OUT_FP32, 96, seed=390)
+    moe, dl, x, good, *_ = _run_prefill(host, cfg, 96, seed=391)
+    xd = gu.to_dev(x)
+    y = gu.dev_empty(96 * cfg.d, "f32")
+    debug_set_wait_limit(20_000_000)            # 20 ms instead of a second
+    try:
+        moe.debug_drop_prefill_copy()
+        moe.layer_prefill(0, xd, 96, y_out=y)
+        with pytest.raises(_lib.NvmaiError) as err:
+            moe.synchronize()
+        assert err.value.code == _lib.ETIMEOUT
+    finally:
+        debug_set_wait_limit(0)
+    moe.layer_prefill(0, xd, 96, y_out=y)        # tensor memory was released: the blocks of this call can allocate it
+    moe.synchronize()
+    assert np.array_equal(y.cpu().numpy().reshape(96, cfg.d).view(np.uint32), good.view(np.uint32))
+
+
 @pytest.mark.parametrize("bits", [4, 8])
 def test_prefill_shape_of_the_reference_test_runs_on_the_grouped_kernels(bits):
     """PrefillGroupedRoutedMoETests+Execution.swift:8-109 runs d = f = 64, 3 tokens, top-2 of 16 experts, 4- and 8-bit:
