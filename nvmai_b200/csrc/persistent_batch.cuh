@@ -474,14 +474,18 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
             __syncwarp();
             // the warp that made the list requests this block's first gate/up tiles at once
             const uint32_t tiles = base * tiles_per_expert;
-            const int mine = tiles > c ? (int)((tiles - c + G - 1) / G) : 0;
-            if (lane < mine && lane < (int)p.slots) issue_tile(lane, ly, c + (uint32_t)lane * G);
+            const int mine = (int)(tiles / G + (c < tiles % G ? 1u : 0u));
+            const uint32_t first = c * (tiles / G) + min(c, tiles % G);
+            if (lane < mine && lane < (int)p.slots) issue_tile(lane, ly, first + (uint32_t)lane);
         }
         __syncthreads();
         if (!has_down && tid == 0) st_tagged(p.xbeat + c, tag, 0.0f);      // this block has read the layer's logits
         const int n_pairs = (int)n_pairs_s[0];
         const uint32_t tiles_total = (uint32_t)n_pairs * tiles_per_expert;
-        const int n_my = tiles_total > c ? (int)((tiles_total - c + G - 1) / G) : 0;
+        // a block's tiles are consecutive in (pair, feature) order: mostly one pair, whose row's fragments are
+        // prepared once
+        const int n_my = (int)(tiles_total / G + (c < tiles_total % G ? 1u : 0u));
+        const uint32_t tile0 = c * (tiles_total / G) + min(c, tiles_total % G);
         for (int j = 0; j < n_my && j < (int)p.slots; ++j) fly_p2 |= 1u << j;
         mark(3);
         // ---- the shared expert's down tile against all rows, while the first gate/up tiles travel: the rows' shared
@@ -525,6 +529,8 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
         }
         bool down_issued = false;
         ok = true;
+        PdXFrag<BITS> xf;
+        int xf_tok = -1;
         for (int b0 = 0; b0 < n_my && ok; b0 += kPbBatchTiles) {
             const int nb = min(kPbBatchTiles, n_my - b0);
             for (int j = b0; j < b0 + nb; ++j) {
@@ -538,22 +544,24 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
                     fly_p3 |= (1u << min(n_pairs, kMaxTopK)) - 1u;
                 }
                 down_issued = true;
-                const uint32_t id = c + (uint32_t)j * G;
+                const uint32_t id = tile0 + (uint32_t)j;
                 const int tok = (int)pair_row[id / tiles_per_expert];
-                PdXFrag<BITS> xf;
-                xf.prepare(xs + (size_t)tok * D, xsum_s + (size_t)tok * groups_d, D);
+                if (tok != xf_tok) {
+                    xf.prepare(xs + (size_t)tok * D, xsum_s + (size_t)tok * groups_d, D);
+                    xf_tok = tok;
+                }
                 pd_tile_partial<BITS, META>(smem + L.p2 + (size_t)slot * L.p2_step, PL, D, xs + (size_t)tok * D,
                                             xsum_s + (size_t)tok * groups_d, xf, red + (size_t)(j - b0) * kPdGroupWarps * 16);
                 if (j + (int)p.slots < n_my) {
                     if (!__syncthreads_and(ok)) { ok = false; break; }
-                    if (tid == 0) issue_tile(slot, ly, c + (uint32_t)(j + p.slots) * G);
+                    if (tid == 0) issue_tile(slot, ly, tile0 + (uint32_t)(j + p.slots));
                     fly_p2 |= 1u << slot;
                 }
             }
             if (!__syncthreads_and(ok)) { ok = false; break; }
             if (tid < kTileFeatures * nb) {
                 const int j = b0 + tid / kTileFeatures, f = tid % kTileFeatures;
-                const uint32_t id = c + (uint32_t)j * G;
+                const uint32_t id = tile0 + (uint32_t)j;
                 st_tagged(p.xacts + (size_t)(id / tiles_per_expert) * F + (id % tiles_per_expert) * kTileFeatures + f, tag,
                           pd_tile_result<OUT>(red + (size_t)(j - b0) * kPdGroupWarps * 16, f, p.act, false));
             }
