@@ -533,30 +533,51 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
         int xf_tok = -1;
         for (int b0 = 0; b0 < n_my && ok; b0 += kPbBatchTiles) {
             const int nb = min(kPbBatchTiles, n_my - b0);
-            for (int j = b0; j < b0 + nb; ++j) {
+            for (int j = b0; j < b0 + nb;) {
                 const int slot = j % (int)p.slots;
+                const uint32_t id = tile0 + (uint32_t)j;
+                const int tok = (int)pair_row[id / tiles_per_expert];
+                // two consecutive tiles of the same row go through the tensor-core steps together
+                const bool two = p.slots >= 2 && j + 1 < b0 + nb && (int)pair_row[(id + 1) / tiles_per_expert] == tok;
+                const int slot1 = (j + 1) % (int)p.slots;
                 ok = pd_mbar_wait(bar_p2(slot), (ph_p2 >> slot) & 1u, p.status) && ok;
                 ph_p2 ^= 1u << slot; fly_p2 &= ~(1u << slot);
+                if (two) {
+                    ok = pd_mbar_wait(bar_p2(slot1), (ph_p2 >> slot1) & 1u, p.status) && ok;
+                    ph_p2 ^= 1u << slot1; fly_p2 &= ~(1u << slot1);
+                }
                 if (j == 0) mark(4);
-                if (j == n_my - 1) mark(11);
+                if (j + (two ? 1 : 0) == n_my - 1) mark(11);
                 if (!down_issued && has_down) {
                     if (warp == 1 && lane < min(n_pairs, kMaxTopK)) issue_pair_down(lane, ly, lane);
                     fly_p3 |= (1u << min(n_pairs, kMaxTopK)) - 1u;
                 }
                 down_issued = true;
-                const uint32_t id = tile0 + (uint32_t)j;
-                const int tok = (int)pair_row[id / tiles_per_expert];
                 if (tok != xf_tok) {
                     xf.prepare(xs + (size_t)tok * D, xsum_s + (size_t)tok * groups_d, D);
                     xf_tok = tok;
                 }
-                pd_tile_partial<BITS, META>(smem + L.p2 + (size_t)slot * L.p2_step, PL, D, xs + (size_t)tok * D,
-                                            xsum_s + (size_t)tok * groups_d, xf, red + (size_t)(j - b0) * kPdGroupWarps * 16);
-                if (j + (int)p.slots < n_my) {
-                    if (!__syncthreads_and(ok)) { ok = false; break; }
-                    if (tid == 0) issue_tile(slot, ly, tile0 + (uint32_t)(j + p.slots));
-                    fly_p2 |= 1u << slot;
+                float *red0 = red + (size_t)(j - b0) * kPdGroupWarps * 16;
+                if (two && xf.fast) {
+                    pd_tile_partial2<BITS, META>(smem + L.p2 + (size_t)slot * L.p2_step, smem + L.p2 + (size_t)slot1 * L.p2_step,
+                                                 L.tile_meta_s, L.tile_meta_b, D, xf, red0, red0 + kPdGroupWarps * 16);
+                } else {
+                    pd_tile_partial<BITS, META>(smem + L.p2 + (size_t)slot * L.p2_step, PL, D, xs + (size_t)tok * D,
+                                                xsum_s + (size_t)tok * groups_d, xf, red0);
+                    if (two)
+                        pd_tile_partial<BITS, META>(smem + L.p2 + (size_t)slot1 * L.p2_step, PL, D, xs + (size_t)tok * D,
+                                                    xsum_s + (size_t)tok * groups_d, xf, red0 + kPdGroupWarps * 16);
                 }
+                if (j + (int)p.slots < n_my) {      // the slots just read take the tiles `slots` further on
+                    if (!__syncthreads_and(ok)) { ok = false; break; }
+                    if (tid == 0) {
+                        issue_tile(slot, ly, tile0 + (uint32_t)(j + p.slots));
+                        if (two && j + 1 + (int)p.slots < n_my) issue_tile(slot1, ly, tile0 + (uint32_t)(j + 1 + p.slots));
+                    }
+                    fly_p2 |= 1u << slot;
+                    if (two && j + 1 + (int)p.slots < n_my) fly_p2 |= 1u << slot1;
+                }
+                j += two ? 2 : 1;
             }
             if (!__syncthreads_and(ok)) { ok = false; break; }
             if (tid < kTileFeatures * nb) {

@@ -347,6 +347,39 @@ __device__ __forceinline__ void swz_accumulate_prepared(const unsigned char *box
     }
 }
 
+// Two tiles against the same prepared fragments (two consecutive gate/up tiles of one pair): the two tiles' chains are
+// independent, so their loads and tensor-core steps overlap; each tile's own arithmetic is that of the function above.
+template <int BITS, int META, int NG>
+__device__ __forceinline__ void swz_accumulate_prepared2(const unsigned char *const (&box_a)[2], const unsigned char *const (&box_b)[2],
+                                                         int rows_per_chunk, int ra, int rb, const uint16_t *const (&s)[2],
+                                                         const uint16_t *const (&b)[2], int ma, int mb, int groups_total, int g_begin,
+                                                         const uint32_t (&xb)[NG][8], const float (&xsum)[NG], float (&acc)[2][4]) {
+    using vec = typename GroupBytes<BITS>::vec;
+    using MW = typename MetaWord<NG>::type;
+    const int t = threadIdx.x & 3;
+    MW sa[2], sb[2], ba[2], bb[2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        sa[m] = *reinterpret_cast<const MW *>(s[m] + ma * groups_total + g_begin);
+        sb[m] = *reinterpret_cast<const MW *>(s[m] + mb * groups_total + g_begin);
+        ba[m] = *reinterpret_cast<const MW *>(b[m] + ma * groups_total + g_begin);
+        bb[m] = *reinterpret_cast<const MW *>(b[m] + mb * groups_total + g_begin);
+    }
+#pragma unroll
+    for (int j = 0; j < NG; ++j) {
+        vec wa[2], wb[2];
+        uint16_t s0[2], s1[2], b0[2], b1[2];
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            wa[m] = *reinterpret_cast<const vec *>(box_a[m] + swz_offset<BITS>(g_begin + j, ra, t, rows_per_chunk));
+            wb[m] = *reinterpret_cast<const vec *>(box_b[m] + swz_offset<BITS>(g_begin + j, rb, t, rows_per_chunk));
+            s0[m] = meta_pick(sa[m], j); s1[m] = meta_pick(sb[m], j);
+            b0[m] = meta_pick(ba[m], j); b1[m] = meta_pick(bb[m], j);
+        }
+        group_step<BITS, META, 2, true>(wa, wb, s0, s1, b0, b1, xb[j], xsum[j], 0.0f, acc);
+    }
+}
+
 // the same over any group range, activation fragments read from the row in shared memory
 template <int BITS, int META>
 __device__ __forceinline__ void swz_accumulate_range(const unsigned char *box_a, const unsigned char *box_b, int rows_per_chunk,
@@ -437,6 +470,27 @@ __device__ __forceinline__ void pd_tile_partial(const unsigned char *tile, const
     if (t == 0) {
         red_tile[warp * 16 + g] = acc[0][0];
         red_tile[warp * 16 + g + 8] = acc[0][2];
+    }
+}
+
+// two staged tiles of the same row at once (the fast path only; the caller falls back to two single calls otherwise)
+template <int BITS, int META>
+__device__ __forceinline__ void pd_tile_partial2(const unsigned char *tile0, const unsigned char *tile1, size_t tile_meta_s,
+                                                 size_t tile_meta_b, int D, const PdXFrag<BITS> &xf, float *red0, float *red1) {
+    const int warp = (threadIdx.x >> 5) & (kPdGroupWarps - 1), lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const size_t up = (size_t)kTileFeatures * D * BITS / 8;
+    const unsigned char *const gate_box[2] = {tile0, tile1};
+    const unsigned char *const up_box[2] = {tile0 + up, tile1 + up};
+    const uint16_t *const ms[2] = {reinterpret_cast<const uint16_t *>(tile0 + tile_meta_s), reinterpret_cast<const uint16_t *>(tile1 + tile_meta_s)};
+    const uint16_t *const mb[2] = {reinterpret_cast<const uint16_t *>(tile0 + tile_meta_b), reinterpret_cast<const uint16_t *>(tile1 + tile_meta_b)};
+    float acc[2][4] = {};
+    swz_accumulate_prepared2<BITS, META, 4>(gate_box, up_box, kTileFeatures, g, g, ms, mb, g, g + 8, D / kGroup, xf.g_begin, xf.xb, xf.xsum, acc);
+    if (t == 0) {
+        red0[warp * 16 + g] = acc[0][0];
+        red0[warp * 16 + g + 8] = acc[0][2];
+        red1[warp * 16 + g] = acc[1][0];
+        red1[warp * 16 + g + 8] = acc[1][2];
     }
 }
 
