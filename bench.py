@@ -166,7 +166,8 @@ def base_record(args, n_gpus: int) -> dict:
     return {
         "metric": METRIC, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
         "higher_is_better": True, "vs_baseline": None, "data": "synthetic",
-        "config": {"workload": f"configs[3]: 40-layer MoE FFN stack, 35B-A3B shape, {args.bits}-bit, batch-1 decode",
+        "config": {"workload": f"configs[3]: 40-layer MoE FFN stack, 35B-A3B shape, {args.bits}-bit, "
+                               + ("batch-1 decode" if args.tokens == 1 else f"decode of {args.tokens} independent rows per GPU and step"),
                    "d": D, "f": F, "experts": E, "top_k": K, "layers": args.layers, "bits": args.bits,
                    "meta": "bf16", "router": "dense fp16", "tokens_per_step": args.tokens},
     }
@@ -302,12 +303,14 @@ def run_ours(args) -> None:
     rec = None
     if rank == 0:
         peak, which = measured_peaks()
-        staged = tokens != 1 or os.environ.get("NVMAI_CUDA_DECODE_MODE", "0") == "1"
-        if staged:
-            roof = stage2_roofline(moe, cfg, devs, args, stream, peak, which)
-        else:
+        forced_staged = os.environ.get("NVMAI_CUDA_DECODE_MODE", "0") == "1"
+        if tokens == 1 and not forced_staged:
             roof = resident_roofline(moe, args, xs, x_in, y, stream, peak, which)
-        step_bytes = args.layers * layer_bytes(args.bits)
+        elif 2 <= tokens <= 8 and not forced_staged:
+            roof = batch_roofline(moe, args, tokens, ms_per_step, peak, which)
+        else:
+            roof = stage2_roofline(moe, cfg, devs, args, stream, peak, which)
+        step_bytes = roof["bytes_per_launch"] if 2 <= tokens <= 8 and not forced_staged else args.layers * layer_bytes(args.bits)
         roof["step_bytes"] = step_bytes
         roof["step_frac"] = step_bytes / (ms_per_step / 1e3) / 1e9 / peak
         rec = base_record(args, world)
@@ -899,9 +902,9 @@ def run_prefill(args) -> None:
 # dram__bytes_read.sum + dram__bytes_write.sum of one stage2_kernel launch, from an ncu capture of the 4-bit
 # kernel (the 8-bit kernel has not been captured)
 STAGE2_DRAM_BYTES_PER_LAUNCH = {4: 9508352, 8: None}
-# the same for the resident decode kernel, per LAYER: an ncu capture of a 4-layer, 4-bit step read 68,077,056 B
-# and wrote 1,295,616 B; the traffic of a step grows with its number of layers
-RESIDENT_DRAM_BYTES_PER_LAYER = {4: (68077056 + 1295616) // 4, 8: None}
+# the same for the resident decode kernel, per LAYER: an ncu capture of a 4-layer, 4-bit step read 68,057,600 B
+# and wrote 1,360,384 B; the traffic of a step grows with its number of layers
+RESIDENT_DRAM_BYTES_PER_LAYER = {4: (68057600 + 1360384) // 4, 8: None}
 
 
 def resident_roofline(moe, args, xs, x_in, y, stream, peak: float, which: str) -> dict:
@@ -928,6 +931,22 @@ def resident_roofline(moe, args, xs, x_in, y, stream, peak: float, which: str) -
             "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
             "traffic": None if per_layer is None else per_layer * args.layers, "bytes_per_launch": nbytes,
             "us_per_launch": us}
+
+
+def batch_roofline(moe, args, tokens: int, ms_per_step: float, peak: float, which: str) -> dict:
+    """2..8 rows per step run as one launch of the resident batch kernel.  Its algorithmic bytes follow the routing:
+    per layer every DISTINCT expert the rows selected (read back from the step's own routing record) once, plus the
+    shared expert, the router, the gate row and the rows themselves."""
+    log = moe.read_route_log_rows(tokens)                     # [layers][rows][K] of the last step
+    blob = expert_bytes(args.bits)
+    fixed = blob + E * D * 2 + D * 2 + tokens * (D * 2 + D * 4)
+    distinct = [int(np.unique(log[l]).size) for l in range(log.shape[0])]
+    nbytes = sum(d * blob + fixed for d in distinct)
+    achieved = nbytes / (ms_per_step * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "persistent_batch_kernel (one launch = all layers of the step, %d rows)" % tokens,
+            "achieved": achieved, "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "bytes_per_launch": nbytes, "us_per_launch": ms_per_step * 1e3,
+            "distinct_experts_per_layer_mean": float(np.mean(distinct))}
 
 
 def device_layer_to_host(dev, torch) -> dict:

@@ -503,25 +503,61 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
             }
             if (!__syncthreads_and(ok)) { alive = false; break; }
             pb_group_sums(sact, Fs, T, sxsum);
-            __syncthreads();
-            if (warp >= kPbWarps - kDownSplit) {
-                const int half = warp - (kPbWarps - kDownSplit);
+            ok = pd_mbar_wait(bar_p3(kMaxTopK), (ph_p3 >> kMaxTopK) & 1u, p.status);
+            if (!__syncthreads_and(ok)) { alive = false; break; }
+            {
                 const int groups = Fs / kGroup, gpw = (groups + kDownSplit - 1) / kDownSplit;
-                const int g_begin = min(half * gpw, groups), g_end = min(g_begin + gpw, groups);
-                ok_sd = pd_mbar_wait(bar_p3(kMaxTopK), (ph_p3 >> kMaxTopK) & 1u, p.status);
-                if (ok_sd) {
-                    const uint32_t w_bytes = (uint32_t)(kTileRows * Fs * BITS / 8);
-                    const uint16_t *ms = reinterpret_cast<const uint16_t *>(sdbuf + w_bytes);
-                    float acc[1][4] = {};
-                    swz_accumulate_cols<BITS, META>(sdbuf, sdbuf, kTileRows, g, g + 8, ms, ms + kTileRows * groups, g, g + 8, groups,
-                                                    g_begin, g_end, sact, Fs, T, sxsum, acc);
-                    float *sp = sh_part + (size_t)half * 16 * kPbMaxRows;
+                const uint32_t w_bytes = (uint32_t)(kTileRows * Fs * BITS / 8);
+                const uint16_t *ms = reinterpret_cast<const uint16_t *>(sdbuf + w_bytes), *mbias = ms + kTileRows * groups;
+                const bool spread = (size_t)groups * 32 * sizeof(float4) <= (size_t)kPdGroupWarps * 16 * kPbMaxRows * sizeof(float);
+                if (spread) {
+                    // the tensor-core products of the groups over all eight warps (red is idle here), then the two
+                    // halves' fp32 chains in group order by the two warps that own them: the bits of one warp per half
+                    using vec = typename GroupBytes<BITS>::vec;
+                    float4 *dbuf = reinterpret_cast<float4 *>(red);
+                    const __half *xrow = g < T ? sact + (size_t)g * Fs : nullptr;
+                    for (int G = warp; G < groups; G += kPbWarps) {
+                        const vec wa = *reinterpret_cast<const vec *>(sdbuf + swz_offset<BITS>(G, g, t4, kTileRows));
+                        const vec wb = *reinterpret_cast<const vec *>(sdbuf + swz_offset<BITS>(G, g + 8, t4, kTileRows));
+                        uint32_t xb[8];
+                        if (xrow != nullptr) {
+                            const uint4 *xp = reinterpret_cast<const uint4 *>(xrow + (size_t)G * kGroup + t4 * 16);
+                            permute_x<BITS>(xp[0], xp[1], xb);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) xb[i] = 0u;
+                        }
+                        float d[4];
+                        group_products<BITS>(wa, wb, xb, d);
+                        dbuf[G * 32 + lane] = make_float4(d[0], d[1], d[2], d[3]);
+                    }
+                    __syncthreads();
+                }
+                if (warp >= kPbWarps - kDownSplit) {
+                    const int half = warp - (kPbWarps - kDownSplit);
+                    const int g_begin = min(half * gpw, groups), g_end = min(g_begin + gpw, groups);
                     const int c0 = 2 * t4, c1 = 2 * t4 + 1;
+                    float acc[1][4] = {};
+                    if (spread) {
+                        const float4 *dbuf = reinterpret_cast<const float4 *>(red);
+                        for (int G = g_begin; G < g_end; ++G) {
+                            const float4 dv = dbuf[G * 32 + lane];
+                            const float d[4] = {dv.x, dv.y, dv.z, dv.w};
+                            group_chain<META>(d, ms[g * groups + G], ms[(g + 8) * groups + G], mbias[g * groups + G],
+                                              mbias[(g + 8) * groups + G], c0 < T ? sxsum[c0 * groups + G] : 0.0f,
+                                              c1 < T ? sxsum[c1 * groups + G] : 0.0f, acc[0]);
+                        }
+                    } else {
+                        swz_accumulate_cols<BITS, META>(sdbuf, sdbuf, kTileRows, g, g + 8, ms, mbias, g, g + 8, groups, g_begin, g_end,
+                                                        sact, Fs, T, sxsum, acc);
+                    }
+                    float *sp = sh_part + (size_t)half * 16 * kPbMaxRows;
                     sp[g * kPbMaxRows + c0] = acc[0][0] * (c0 < T ? scale_s[c0] : 0.0f);
                     sp[g * kPbMaxRows + c1] = acc[0][1] * (c1 < T ? scale_s[c1] : 0.0f);
                     sp[(g + 8) * kPbMaxRows + c0] = acc[0][2] * (c0 < T ? scale_s[c0] : 0.0f);
                     sp[(g + 8) * kPbMaxRows + c1] = acc[0][3] * (c1 < T ? scale_s[c1] : 0.0f);
                 }
+                if (spread) __syncthreads();        // red goes back to the gate/up batches
             }
             ph_p3 ^= 1u << kMaxTopK; fly_p3 &= ~(1u << kMaxTopK);
             // (a wait that gave up is seen by the whole block at the barrier after the gate/up tiles)

@@ -112,6 +112,30 @@ __device__ __forceinline__ void group_step(const typename GroupBytes<BITS>::vec 
     }
 }
 
+// The two halves of group_step for one tile, for callers that spread the tensor-core products of a row's groups
+// over several warps and then run the fp32 chain in group order in one place: the chain sees exactly the
+// products group_step would have handed it, so the bits are group_step's.
+template <int BITS>
+__device__ __forceinline__ void group_products(const typename GroupBytes<BITS>::vec &wa, const typename GroupBytes<BITS>::vec &wb,
+                                               const uint32_t (&xb)[8], float (&d)[4]) {
+    uint32_t pa[8], pb[8];
+    unpack_group<BITS>(wa, pa);
+    unpack_group<BITS>(wb, pb);
+    d[0] = d[1] = d[2] = d[3] = 0.f;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) mma16816(d, pa[2 * s], pb[2 * s], pa[2 * s + 1], pb[2 * s + 1], xb[2 * s], xb[2 * s + 1]);
+}
+template <int META>
+__device__ __forceinline__ void group_chain(const float (&d)[4], uint16_t sa, uint16_t sb, uint16_t ba, uint16_t bb, float xsum0,
+                                            float xsum1, float (&acc)[4]) {
+    const float fsa = meta_to_float<META>(sa) * kCodeUnscale, fsb = meta_to_float<META>(sb) * kCodeUnscale;
+    const float fba = meta_to_float<META>(ba), fbb = meta_to_float<META>(bb);
+    acc[0] = fmaf(fsa, d[0], acc[0]); acc[0] = fmaf(fba, xsum0, acc[0]);
+    acc[2] = fmaf(fsb, d[2], acc[2]); acc[2] = fmaf(fbb, xsum0, acc[2]);
+    acc[1] = fmaf(fsa, d[1], acc[1]); acc[1] = fmaf(fba, xsum1, acc[1]);
+    acc[3] = fmaf(fsb, d[3], acc[3]); acc[3] = fmaf(fbb, xsum1, acc[3]);
+}
+
 // A 16-row tile staged in shared memory by bulk copies: rows `row_stride` bytes
 // apart (row bytes + padding, see tile_row_stride), scales and biases as
 // [16][groups_total] 16-bit arrays.
