@@ -58,3 +58,22 @@ def test_synthesized_trace_has_the_requested_reuse():
     assert 0.36 < st["reuse"] < 0.48          # kept experts plus chance repeats of popular ones
     assert all(len(set(r)) == 8 for r in tr.experts.tolist())
     assert rt.synthesize(50, 1, reuse=0.0, zipf=0.0, seed=4).stats()["reuse"] < 0.1
+
+
+def test_route_log_of_a_step_round_trips_through_the_trace_format():
+    """the [layers][rows][top_k] record a resident-kernel step leaves behind, written as `position layer e0..e7`
+    lines and parsed back: row r of the step is position first + r"""
+    rng = np.random.default_rng(3)
+    layers, rows, k, e = 5, 3, 8, 64
+    log = np.stack([[rng.choice(e, size=k, replace=False) for _ in range(rows)] for _ in range(layers)]).astype(np.uint32)
+    tr = rt.from_route_log(log, 40, num_experts=e)
+    text = tr.format()
+    assert len(text.splitlines()) == layers * rows
+    assert text.splitlines()[0].split()[:2] == ["40", "0"]
+    back = rt.parse(text, num_experts=e, top_k=k)
+    for l in range(layers):
+        pos, ids = back.layer_rows(l)
+        assert pos.tolist() == [40, 41, 42]
+        np.testing.assert_array_equal(ids, log[l].astype(np.int32))
+    one = rt.from_route_log(log[:, 0, :], 7, num_experts=e)          # a one-row step: [layers][top_k]
+    assert len(one) == layers and int(one.positions[0]) == 7
