@@ -87,6 +87,32 @@ def ep_stack_step(backend, dist, group, x_own, *, world: int, layers: int):
     return y
 
 
+def ep_replicated_stack_step(backend, dist, group, x_own, *, world: int, layers: int):
+    """The step structure of the fused expert-parallel decode kernel (up to 8 rows in total), written with
+    collectives: ONE all-gather of the rows, then per layer every rank routes ALL rows, computes the shares of the
+    pairs whose expert it holds and the shared expert for all rows, the shares are exchanged (an all-gather here,
+    peer stores from inside the kernel there) and added in rank order to the shared expert's rows on every rank, so
+    that all ranks hold the same bits for every row and the next layer needs nothing else from the peers.  Returns
+    this rank's rows of the last layer's output."""
+    import torch
+    b_own = x_own.shape[0]
+    rows = world * b_own
+    x_all = torch.empty((rows, x_own.shape[1]), dtype=x_own.dtype, device=x_own.device)
+    dist.all_gather_into_tensor(x_all, x_own.contiguous(), group=group)
+    y = None
+    for layer in range(layers):
+        idx, w = backend.router(layer, x_all)
+        share = backend.routed_partial(layer, x_all, idx, w)             # [rows, D] fp32: this rank's experts only
+        shares = torch.empty((world * rows, share.shape[1]), dtype=share.dtype, device=share.device)
+        dist.all_gather_into_tensor(shares, share.contiguous(), group=group)     # rank r's rows at [r * rows, (r + 1) * rows)
+        h1 = backend.shared(layer, x_all)
+        y = backend.finalize(shares, h1, world, rows)                            # rank-ordered sum, all rows
+        if layer + 1 < layers:
+            x_all = backend.renorm(y)
+    rank = dist.get_rank(group)
+    return y[rank * b_own:(rank + 1) * b_own]
+
+
 class LibraryBackend:
     """The CUDA library as the arithmetic of the expert-parallel driver.  The handle
     must have been given this rank's expert map and its local blobs per layer."""

@@ -17,7 +17,8 @@ for p_ in (ROOT, ROOT / "tests"):
 
 from nvmai_b200 import MoEConfig, synthetic  # noqa: E402
 from nvmai_b200 import format as fmt  # noqa: E402
-from nvmai_b200.ep import NOT_LOCAL, ExpertPlacement, ep_layer_step  # noqa: E402
+from nvmai_b200.ep import (NOT_LOCAL, ExpertPlacement, ep_layer_step, ep_replicated_stack_step,  # noqa: E402
+                           ep_stack_step)
 
 D, F, E, K = 128, 64, 16, 8
 
@@ -97,6 +98,13 @@ class OracleBackend:
             y = y + recv.view(world, b_own, -1)[r]
         return y
 
+    def renorm(self, y):
+        import torch
+        v = y.numpy().astype(np.float64)
+        scale = 1.0 / np.sqrt(np.mean(v * v, axis=1, keepdims=True) + 1e-6)
+        bits = self.orc.f32_to_f16_bits((v * scale).astype(np.float32).reshape(-1)).reshape(v.shape)
+        return torch.from_numpy(bits.view(np.int16).copy()).view(torch.float16)
+
 
 def _rank_main(rank, world, port, mode, fail_rank, out_dir):
     try:
@@ -107,14 +115,20 @@ def _rank_main(rank, world, port, mode, fail_rank, out_dir):
         from datetime import timedelta
         dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=20))
         cfg, host = _cfg(), _host_layer()
-        pl = ExpertPlacement(E, world, mode)
+        pl = ExpertPlacement(E, world, mode.replace("stack-", ""))
         backend = OracleBackend(host, cfg, pl, rank)
         b_own = 2
         x_all = synthetic.hidden_rows(5, world * b_own, D)
         x_own = torch.from_numpy(x_all[rank * b_own:(rank + 1) * b_own].view(np.int16).copy()).view(torch.float16)
         if rank == fail_rank:
             raise RuntimeError("injected failure before the first collective")
-        y = ep_layer_step(backend, dist, None, 0, x_own, world=world)
+        if mode.startswith("stack-"):
+            # two chained layers both ways: rows owned and shares sent to the owners, and every rank keeping all rows
+            y = ep_stack_step(backend, dist, None, x_own, world=world, layers=2)
+            z = ep_replicated_stack_step(backend, dist, None, x_own, world=world, layers=2)
+            np.save(os.path.join(out_dir, f"z{rank}.npy"), z.numpy())
+        else:
+            y = ep_layer_step(backend, dist, None, 0, x_own, world=world)
         np.save(os.path.join(out_dir, f"y{rank}.npy"), y.numpy())
         dist.destroy_process_group()
     except Exception:
@@ -157,6 +171,29 @@ def test_two_rank_expert_parallel_layer_equals_single_rank_oracle(mode, tmp_path
         for j in range(2):
             _, _, want, _, _ = gu.oracle_decode(L, cfg, np.ascontiguousarray(x_all[rank * 2 + j]))
             assert orc.rel_error(y[j], want) < 1e-5, (rank, j)
+
+
+def test_two_rank_stack_keeping_all_rows_equals_the_owner_exchange_and_the_oracle_chain(tmp_path):
+    """the step structure of the fused expert-parallel kernel (every rank keeps all rows, shares added in rank order on
+    every rank) against the owner-mode exchange and against one rank running the chain alone"""
+    import gpu_util as gu
+    from oracle import oracle as orc
+    codes = _spawn(2, "stack-strided", tmp_path, port=29547)
+    errs = [p.read_text() for p in tmp_path.glob("err*.txt")]
+    assert codes == [0, 0], errs
+    cfg, host = _cfg(), _host_layer()
+    L, keep = gu.oracle_layer(host, cfg)
+    x_all = synthetic.hidden_rows(5, 4, D)
+    for rank in range(2):
+        y, z = np.load(tmp_path / f"y{rank}.npy"), np.load(tmp_path / f"z{rank}.npy")
+        for j in range(2):
+            assert orc.rel_error(z[j], y[j]) < 1e-6, (rank, j)
+            x = np.ascontiguousarray(x_all[rank * 2 + j])
+            _, _, h2, _, _ = gu.oracle_decode(L, cfg, x)
+            scale = 1.0 / np.sqrt(np.mean(h2.astype(np.float64) ** 2) + 1e-6)
+            x = orc.f32_to_f16_bits((h2.astype(np.float64) * scale).astype(np.float32))
+            _, _, want, _, _ = gu.oracle_decode(L, cfg, x)
+            assert orc.rel_error(z[j], want) < 2e-4, (rank, j)
 
 
 def test_a_rank_that_raises_does_not_hang_the_others(tmp_path):
