@@ -5,6 +5,7 @@
 #include "../../include/nvmai_cuda_moe.h"
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <fcntl.h>
 #include <unistd.h>
 #include <cerrno>
@@ -141,6 +142,23 @@ struct nvmai_cuda_moe {
 };
 
 namespace {
+
+// NVTX ranges around the entry points, named after the roles the reference's runner gives its command buffers
+// (recordKernelGPU(role:), RealForwardRunner.swift:3839-3844, :3224-3225, :3393-3418, :3574), so that a timeline of the
+// host reads like the reference's NVMAI_KERNEL_STATS.  On when NVMAI_CUDA_NVTX=1 is in the environment at the first
+// call; without a profiler attached a range costs a function-pointer check.
+inline bool nvtx_on() {
+    static const bool on = [] { const char *v = std::getenv("NVMAI_CUDA_NVTX"); return v && std::atoi(v) != 0; }();
+    return on;
+}
+struct NvtxRange {
+    bool on;
+    explicit NvtxRange(const char *role) : on(nvtx_on()) { if (on) nvtxRangePushA(role); }
+    ~NvtxRange() { if (on) nvtxRangePop(); }
+    NvtxRange(const NvtxRange &) = delete;
+    NvtxRange &operator=(const NvtxRange &) = delete;
+};
+
 
 inline size_t out_size(uint32_t out_dtype) { return out_dtype == NVMAI_OUT_FP16 ? 2 : 4; }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -1268,6 +1286,7 @@ int nvmai_cuda_moe_register_layer(nvmai_cuda_moe *h, uint32_t layer, const nvmai
 
 int nvmai_cuda_moe_router(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride, uint32_t tokens,
                           uint32_t *out_idx, void *out_w_f16, void *stream) {
+    NvtxRange nvtx_range("attn_tail_router");
     int rc = check_layer(h, layer);
     if (rc) return rc;
     if (!x_f16 || !out_idx || !out_w_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
@@ -1280,6 +1299,7 @@ int nvmai_cuda_moe_router(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, 
 
 int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t x_stride,
                                  uint32_t tokens, void *h1, void *stream) {
+    NvtxRange nvtx_range("shared_expert");
     int rc = check_layer(h, layer);
     if (rc) return rc;
     const auto &c = h->cfg;
@@ -1293,6 +1313,7 @@ int nvmai_cuda_moe_shared_expert(nvmai_cuda_moe *h, uint32_t layer, const void *
 int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_host,
                                  const nvmai_expert_offsets *offsets, const void *x_f16, void *acts_f16,
                                  const uint32_t *active_slots_host, uint32_t active_count, void *stream) {
+    NvtxRange nvtx_range("moe_phase1_hit");
     if (!h || !blobs_host || !offsets || !x_f16 || !acts_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
     const auto &c = h->cfg;
     if (c.top_k != (uint32_t)kMaxTopK) return NVMAI_CUDA_EINVAL;     // MoE.swift:442-445
@@ -1319,6 +1340,7 @@ int nvmai_cuda_moe_routed_phase1(nvmai_cuda_moe *h, const void *const *blobs_hos
 int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_host,
                                  const nvmai_expert_offsets *offsets, const void *acts_f16,
                                  const void *routing_w_f16, const void *residual, void *y, void *stream) {
+    NvtxRange nvtx_range("moe_phase2_reduce");
     if (!h || !blobs_host || !offsets || !acts_f16 || !routing_w_f16 || !residual || !y) return NVMAI_CUDA_EINVAL;
     if (!aligned16(acts_f16)) return NVMAI_CUDA_EINVAL;
     const auto &c = h->cfg;
@@ -1340,6 +1362,7 @@ int nvmai_cuda_moe_routed_phase2(nvmai_cuda_moe *h, const void *const *blobs_hos
 
 int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
                                 void *hidden_inout, void *h2_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    NvtxRange nvtx_range("moe_phase1_2_routed");
     int rc = check_layer(h, layer);
     if (rc) return rc;
     if (!x_f16 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
@@ -1361,6 +1384,7 @@ int nvmai_cuda_moe_layer_decode(nvmai_cuda_moe *h, uint32_t layer, const void *x
 // to the second row's blocks by the L2.
 int nvmai_cuda_moe_layer_verify_pair(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, void *hidden_inout,
                                      void *h2_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    NvtxRange nvtx_range("verify_routed_pair");
     int rc = check_layer(h, layer);
     if (rc) return rc;
     if (h->cfg.max_tokens < 2) return NVMAI_CUDA_ERANGE;
@@ -1374,6 +1398,7 @@ int nvmai_cuda_moe_layer_verify_pair(nvmai_cuda_moe *h, uint32_t layer, const vo
 int nvmai_cuda_moe_layer_decode_prenorm(nvmai_cuda_moe *h, uint32_t layer, void *hidden_inout, const void *attn_delta_f16,
                                         const void *norm_weight_bf16, float eps, uint32_t tokens, void *h2_out,
                                         void *x_out_f16, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    NvtxRange nvtx_range("moe_phase1_2_routed");
     int rc = check_layer(h, layer);
     if (rc) return rc;
     if (!hidden_inout || !norm_weight_bf16 || !(eps >= 0.0f)) return NVMAI_CUDA_EINVAL;
@@ -1398,6 +1423,7 @@ int nvmai_cuda_moe_layer_decode_fused_norms(nvmai_cuda_moe *h, uint32_t layer, v
                                             const void *norm_weight_bf16, float eps, uint32_t tokens,
                                             const void *next_norm_weight_bf16, float next_eps, void *x_next_out_f16,
                                             void *h2_out, void *x_out_f16, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    NvtxRange nvtx_range("moe_phase1_2_routed");
     if (!h) return NVMAI_CUDA_EINVAL;
     if (!next_norm_weight_bf16 || !x_next_out_f16 || !(next_eps >= 0.0f)) return NVMAI_CUDA_EINVAL;
     h->next_norm = NextNorm{static_cast<const uint16_t *>(next_norm_weight_bf16), next_eps, static_cast<__half *>(x_next_out_f16),
@@ -1410,6 +1436,7 @@ int nvmai_cuda_moe_layer_decode_fused_norms(nvmai_cuda_moe *h, uint32_t layer, v
 
 int nvmai_cuda_moe_layer_prefill(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
                                  void *hidden_inout, void *y_out, uint32_t *out_idx, void *out_w_f16, void *stream) {
+    NvtxRange nvtx_range("prefill_routed_tile");
     int rc = check_layer(h, layer);
     if (rc) return rc;
     const auto &c = h->cfg;
@@ -1476,6 +1503,7 @@ int nvmai_cuda_moe_set_expert_map(nvmai_cuda_moe *h, const uint32_t *map_host, u
 
 int nvmai_cuda_moe_routed_partial(nvmai_cuda_moe *h, uint32_t layer, const void *x_f16, uint32_t tokens,
                                   const uint32_t *idx, const void *w_f16, float *share_f32, void *stream) {
+    NvtxRange nvtx_range("prefill_routed_tile");
     int rc = check_layer(h, layer);
     if (rc) return rc;
     if (!x_f16 || !idx || !w_f16 || !share_f32 || !aligned16(x_f16)) return NVMAI_CUDA_EINVAL;
@@ -1494,6 +1522,7 @@ int nvmai_cuda_moe_routed_partial(nvmai_cuda_moe *h, uint32_t layer, const void 
 
 int nvmai_cuda_moe_ep_finalize(nvmai_cuda_moe *h, const float *shares_f32, uint32_t ranks, const void *h1,
                                uint32_t tokens, void *y, void *hidden_inout, void *stream) {
+    NvtxRange nvtx_range("prefill_moe_reduce");
     if (!h || !shares_f32 || ranks == 0 || tokens == 0) return NVMAI_CUDA_EINVAL;
     EpFinalizeParams p{shares_f32, ranks, h1, y, hidden_inout, tokens, h->cfg.d};
     const size_t n = (size_t)tokens * h->cfg.d;
@@ -1534,6 +1563,7 @@ static int stack_enqueue(nvmai_cuda_moe *h, const __half *x0, uint32_t tokens, v
 }
 
 int nvmai_cuda_moe_stack_decode(nvmai_cuda_moe *h, const void *x0_f16, uint32_t tokens, void *y_last, void *stream) {
+    NvtxRange nvtx_range("moe_stack_decode");
     if (!h || !x0_f16 || !y_last || !aligned16(x0_f16)) return NVMAI_CUDA_EINVAL;
     const auto &c = h->cfg;
     if (tokens == 0 || tokens > c.max_tokens) return NVMAI_CUDA_ERANGE;
@@ -1847,6 +1877,7 @@ static bool ep_replicated_mode(const nvmai_cuda_moe *h, uint32_t rows_own) {
 }
 
 int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uint32_t rows_own, void *y_own, void *stream) {
+    NvtxRange nvtx_range("moe_ep_stack_decode");
     if (!h || !x_own_f16 || !y_own || !aligned16(x_own_f16)) return NVMAI_CUDA_EINVAL;
     if (!h->ep_comm || !h->expert_map) return NVMAI_CUDA_EINVAL;    // ep_init and set_expert_map come first
     if (rows_own == 0 || rows_own > h->ep_rows_own) return NVMAI_CUDA_ERANGE;

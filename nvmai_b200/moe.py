@@ -290,8 +290,15 @@ class MoE:
     def set_trace(self, enable: bool) -> None:
         check(self._lib.nvmai_cuda_moe_set_trace(self._h, int(enable)), "set_trace")
 
+    # what the three staged launches of a layer do, in the reference's role names (recordKernelGPU(role:),
+    # RealForwardRunner.swift:3839-3844)
+    TRACE_STAGE_ROLES = ("attn_tail_router + shared_expert (router logits, shared gate/up, gate row)",
+                         "moe_phase1_hit (routed gate/up + activation)",
+                         "moe_phase1_2_routed tail (routed down, weighted sum, shared down, gate)")
+
     def read_trace(self, layers: int | None = None):
-        """-> uint64 array [layers, 3, 8]: {start, end, six phase marks of block 0} GPU-timer ns per stage launch."""
+        """-> uint64 array [layers, 3, 8]: {start, end, six phase marks of block 0} GPU-timer ns per stage launch
+        (the stages are TRACE_STAGE_ROLES)."""
         import numpy as np
         n = self.config.num_layers if layers is None else layers
         out = np.zeros((n, 3, 8), dtype=np.uint64)

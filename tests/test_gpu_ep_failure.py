@@ -25,6 +25,7 @@ def _fake_nccl() -> Path:
 def _run(scenario: str, extra_env: dict) -> dict:
     env = dict(os.environ)
     env["NVMAI_CUDA_NCCL_LIB"] = str(_fake_nccl())
+    env["NVMAI_CUDA_NVTX"] = "1"           # the host-side ranges run too (without a profiler they record nothing)
     env.update(extra_env)
     r = subprocess.run([sys.executable, str(ROOT / "tests" / "ep_failure_child.py"), scenario], env=env, capture_output=True,
                        text=True, timeout=300)
