@@ -169,7 +169,8 @@ def base_record(args, n_gpus: int) -> dict:
         "config": {"workload": f"configs[3]: 40-layer MoE FFN stack, 35B-A3B shape, {args.bits}-bit, "
                                + ("batch-1 decode" if args.tokens == 1 else f"decode of {args.tokens} independent rows per GPU and step"),
                    "d": D, "f": F, "experts": E, "top_k": K, "layers": args.layers, "bits": args.bits,
-                   "meta": "bf16", "router": "dense fp16", "tokens_per_step": args.tokens},
+                   "meta": "bf16", "router": "dense fp16", "tokens_per_step": args.tokens,
+                   "l2": "working set 679 MB (4-bit) / 1246 MB (8-bit) per step exceeds the 126 MB L2; inputs rotate"},
     }
 
 
@@ -319,7 +320,6 @@ def run_ours(args) -> None:
                     "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": tokens * D * 2,
                             "d2h_bytes_per_step": tokens * D * 4},
                     "roofline": roof})
-        rec["config"]["l2"] = "working set 679 MB (4-bit) / 1246 MB (8-bit) per step exceeds the 126 MB L2; inputs rotate"
         if world == 1 and not args.no_cpu_baseline:
             layers = min(args.layers, args.ref_layers)
             cpu = CpuReferenceStack(args.bits, layers)
