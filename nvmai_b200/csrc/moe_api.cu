@@ -129,6 +129,7 @@ struct nvmai_cuda_moe {
     unsigned int *pd_epoch = nullptr;
     uint32_t *pd_route_log = nullptr;     // [num_layers][rows of the step <= 8][top_k]
     uint32_t pd_route_rows = 1;           // rows of the last resident-kernel step
+    size_t ep_xin_off = 0;                // byte offset of the fused dispatch's row area inside ep_xchg
     bool pf_debug_drop = false;           // test hook: the next gate/up GEMM launch leaves out one copy (its waits run out)
     int sm_count = 0;
     // 0: a single-token stack step takes the one-launch kernel when the shape allows it; 1: always the staged
@@ -1054,7 +1055,8 @@ bool pb_plan(const nvmai_cuda_moe *h, uint32_t T, PbPlan &plan) {
 // world == 1: every expert is local (or the handle's map says which are, for tests); world > 1: recv[r] = rank r's
 // receive area as mapped in this process.
 int pb_launch(nvmai_cuda_moe *h, const PbPlan &plan, const __half *x_all, uint32_t T, void *y_all, uint32_t rank, uint32_t world,
-              unsigned long long *const *recv, cudaStream_t st) {
+              unsigned long long *const *recv, cudaStream_t st, unsigned long long *const *xin = nullptr,
+              const __half *x_own = nullptr, void *y_own = nullptr, uint32_t rows_own = 1) {
     const auto &c = h->cfg;
     const PbXchg X(c, kPbMaxRows, (uint32_t)h->sm_count);
     const bool gated = c.shared_f != 0 && c.shared_gate_kind != NVMAI_GATE_NONE;
@@ -1065,7 +1067,11 @@ int pb_launch(nvmai_cuda_moe *h, const PbPlan &plan, const __half *x_all, uint32
     p.xacts = h->pb_xchg + X.acts; p.xy = h->pb_xchg + X.y; p.xbeat = h->pb_xchg + X.beat;
     p.expert_map = h->expert_map;
     p.rank = rank; p.world = world;
-    for (uint32_t r = 0; r < world && r < (uint32_t)kEpMaxRanks; ++r) p.recv[r] = recv ? recv[r] : nullptr;
+    for (uint32_t r = 0; r < world && r < (uint32_t)kEpMaxRanks; ++r) {
+        p.recv[r] = recv ? recv[r] : nullptr;
+        p.xin[r] = xin ? xin[r] : nullptr;
+    }
+    p.x_own = x_own; p.y_own = y_own; p.rows_own = rows_own ? rows_own : 1;
     p.epoch = h->pd_epoch; p.status = h->status; p.route_log = h->pd_route_log;
     h->pd_route_rows = T;
     p.trace = h->trace_on ? h->pd_trace : nullptr;
@@ -1671,7 +1677,9 @@ int nvmai_cuda_moe_ep_init(nvmai_cuda_moe *h, const void *id_host, uint32_t rank
     {
         // counters (4 KB), then the receive area: [2][world][rows][D] 64-bit words (the resident kernel's tagged shares;
         // the staged peer exchange uses the first half of it as fp32 rows)
-        const size_t xbytes = 4096 + 2 * rows * c.d * sizeof(unsigned long long) * world;
+        // ... and the row area of the fused dispatch: [rows][D / 2] words (two halves per word)
+        h->ep_xin_off = 4096 + 2 * rows * c.d * sizeof(unsigned long long) * world;
+        const size_t xbytes = h->ep_xin_off + rows * (c.d / 2) * sizeof(unsigned long long);
         if (world > (uint32_t)kEpMaxRanks || c.num_layers > (uint32_t)kEpMaxLayers ||
             cudaMalloc(reinterpret_cast<void **>(&h->ep_xchg), xbytes) != cudaSuccess ||
             cudaMemset(h->ep_xchg, 0, xbytes) != cudaSuccess ||
@@ -1894,15 +1902,13 @@ int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uin
         const uint32_t T = h->ep_world * rows_own;
         PbPlan plan;
         if (T <= (uint32_t)kPbMaxRows && pb_plan(h, T, plan) && pd_prepare(h, st) == NVMAI_CUDA_OK) {
-            const NcclApi &nccl = nccl_api();
-            const size_t own_elems = (size_t)rows_own * c.d;
-            if (nccl.AllGather(x, h->ep_x_all, own_elems, kNcclFloat16, h->ep_comm, st) != kNcclSuccess) return NVMAI_CUDA_ENCCL;
-            unsigned long long *recv[kEpMaxRanks] = {};
-            for (uint32_t r = 0; r < h->ep_world; ++r) recv[r] = reinterpret_cast<unsigned long long *>(h->ep_peer_base[r] + 4096);
-            int rc = pb_launch(h, plan, h->ep_x_all, T, h->y, h->ep_rank, h->ep_world, recv, st);
-            if (rc) return rc;
-            return record(h, cudaMemcpyAsync(y_own, static_cast<const char *>(h->y) + (size_t)h->ep_rank * own_elems * out_size(c.out_dtype),
-                                             own_elems * out_size(c.out_dtype), cudaMemcpyDeviceToDevice, st));
+            // the dispatch and the combine both live in the kernel: no collective call, no copy around the launch
+            unsigned long long *recv[kEpMaxRanks] = {}, *xin[kEpMaxRanks] = {};
+            for (uint32_t r = 0; r < h->ep_world; ++r) {
+                recv[r] = reinterpret_cast<unsigned long long *>(h->ep_peer_base[r] + 4096);
+                xin[r] = reinterpret_cast<unsigned long long *>(h->ep_peer_base[r] + h->ep_xin_off);
+            }
+            return pb_launch(h, plan, nullptr, T, h->y, h->ep_rank, h->ep_world, recv, st, xin, x, y_own, rows_own);
         }
     }
     if (st == nullptr || cs != cudaStreamCaptureStatusNone) return (ep_replicated_mode(h, rows_own) ? ep_stack_enqueue_replicated(h, x, rows_own, y_own, st) : ep_stack_enqueue(h, x, rows_own, y_own, st));

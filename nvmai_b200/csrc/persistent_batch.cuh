@@ -44,6 +44,9 @@ __device__ __forceinline__ void st_tagged_sys(unsigned long long *p, uint32_t ta
     const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
+__device__ __forceinline__ void ld_tagged2_sys(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
 __device__ __forceinline__ unsigned long long ld_tagged_sys(const unsigned long long *p) {
     unsigned long long w;
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
@@ -119,6 +122,14 @@ struct PbParams {
     const uint32_t *expert_map;       // global expert -> index of the blob this rank holds, or kPbNotLocal; nullptr: all local
     uint32_t rank, world;
     unsigned long long *recv[kEpMaxRanks];    // every rank's receive area as mapped here: [2][world][T][D] words
+    // The dispatch fused in: with xin set, x_own holds only THIS rank's rows_own rows (fp16 [rows_own][D]); the kernel
+    // stores them as tagged words (two halves per word) into every rank's row area xin[q] ([T][D / 2] words) and reads all
+    // T rows back from its own area, instead of an all-gather before the launch.  Rows of rank r are rows
+    // r * rows_own ... of the step.  y_own (optional): only this rank's rows of the last block output go there.
+    unsigned long long *xin[kEpMaxRanks];
+    const __half *x_own;
+    void *y_own;
+    uint32_t rows_own;
     unsigned int *epoch;
     unsigned int *status;
     uint32_t *route_log;              // optional [num_layers][T][K]
@@ -301,7 +312,41 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
         // pairs 2 (i + 256 j) of a row (one 16-byte load for two tagged words); a row's sum of squares is reduced
         // thread, warp, block in that fixed order, so a row's bits do not depend on how many rows travel with it ----
         bool ok = true;
-        if (l == 0) {
+        if (l == 0 && p.world > 1 && p.xin[0] != nullptr) {
+            // the step's rows: this rank's go out to every rank (each block a slice of them), all ranks' come in
+            const int half_d = D / 2, own_words = (int)p.rows_own * half_d;
+            for (int i = (int)c * kPbThreads + tid; i < own_words; i += (int)G * kPbThreads) {
+                const float bits = __uint_as_float(reinterpret_cast<const uint32_t *>(p.x_own)[i]);
+                const size_t at = (size_t)p.rank * own_words + i;
+                for (uint32_t q = 0; q < p.world; ++q) st_tagged_sys(p.xin[q] + at, tag, bits);
+            }
+            const unsigned long long *mine = p.xin[p.rank];
+            const int pairs_total = T * half_d / 2;                 // 16-byte pairs of words = 4 halves each
+            for (int base = 0; base < pairs_total && ok; base += 16 * kPbThreads) {
+                uint32_t pending = 0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (base + j * kPbThreads + tid < pairs_total) pending |= 1u << j;
+                PollClock clk;
+                while (pending) {
+                    const uint32_t round = pending;
+                    unsigned long long wa[16], wb[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        wa[j] = wb[j] = 0ull;
+                        if ((round >> j) & 1u) ld_tagged2_sys(mine + 2 * (size_t)(base + j * kPbThreads + tid), wa[j], wb[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (((round >> j) & 1u) && (tag_is(wa[j], tag) & tag_is(wb[j], tag))) {
+                            *reinterpret_cast<uint2 *>(xs + 4 * (size_t)(base + j * kPbThreads + tid)) =
+                                make_uint2((uint32_t)wa[j], (uint32_t)wb[j]);
+                            pending &= ~(1u << j);
+                        }
+                    if (pending && clk.expired(p.status)) { atomicExch(p.status, 1u); ok = false; break; }
+                }
+            }
+        } else if (l == 0) {
             for (int i = tid * 8; i < T * D; i += kPbThreads * 8)
                 *reinterpret_cast<uint4 *>(xs + i) = *reinterpret_cast<const uint4 *>(p.x0 + i);
         } else {
@@ -725,7 +770,11 @@ __global__ void __launch_bounds__(kPbThreads, 1) persistent_batch_kernel(PbParam
                 }
                 const float yv = round_out<OUT>(acc);
                 st_tagged(p.xy + (size_t)frow * D + row0 + fr, tag, yv);
-                if (last) store_out<OUT>(p.y_last, (size_t)frow * D + row0 + fr, yv);
+                if (last) {
+                    if (p.y_own == nullptr) store_out<OUT>(p.y_last, (size_t)frow * D + row0 + fr, yv);
+                    else if ((uint32_t)frow / p.rows_own == p.rank)
+                        store_out<OUT>(p.y_own, (size_t)(frow - (int)(p.rank * p.rows_own)) * D + row0 + fr, yv);
+                }
             }
             if (!__syncthreads_and(ok)) { alive = false; break; }
             mark(9);
