@@ -521,9 +521,9 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
                                  "frac": args.layers * layer_bytes(args.bits) * tokens / (ms_per_step / 1e3) / 1e9 / peak,
                                  "traffic": None}})
         if resident:
-            exchange = ("one resident kernel per rank and step: every rank keeps all rows, the share rows of a rank's experts "
-                        "cross NVLink as tagged 64-bit peer stores from inside the down phase (no collective per layer); one "
-                        "NCCL all-gather of the step's rows before the kernel")
+            exchange = ("one resident kernel per rank and step and nothing else: every rank keeps all rows; the step's rows are "
+                        "gathered at layer 0 and the share rows of a rank's experts exchanged in every layer's down phase, both as "
+                        "tagged 64-bit peer stores over NVLink from inside the kernel (no collective call)")
             rec["roofline"]["kernel"] = "persistent_batch_kernel (one launch per rank = all layers of the step)"
         elif native and world * tokens < 24:
             exchange = ("all_gather(fp32 share rows) per layer, NCCL" if args.ep_exchange != "p2p" else

@@ -20,7 +20,9 @@
 // area for the other ranks' shares of the same 16 features, and adds them in rank order
 // to the shared expert's row: every rank ends the layer with the same bits for every row and
 // needs nothing else from its peers.  Receive areas are double-buffered by layer parity: a
-// rank can be at most one layer ahead of the slowest reader of its stores.
+// rank can be at most one layer ahead of the slowest reader of its stores.  The rows of a
+// step are gathered the same way at layer 0 (two halves per tagged word), so a step of an
+// expert-parallel rank is this one launch and nothing else.
 //
 // Rounding points are the decode block's (shader semantics).  Differences from the single-row
 // kernel, none of which changes a bit within a row's block for one rank: the input norm of a
