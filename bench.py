@@ -433,9 +433,11 @@ def run_ours_ep(args, torch, dist, rank: int, world: int, local: int) -> None:
 
         for i in range(max(args.warmup, 10)):
             step(i)
+        # the clock sampler starts (a process spawn on rank 0) BEFORE the barrier that opens the timed region:
+        # otherwise the other ranks' first collective would wait for rank 0 inside their timed region
+        sampler = ClockSampler(local) if rank == 0 else None
         dist.barrier()
         torch.cuda.synchronize()
-        sampler = ClockSampler(local) if rank == 0 else None
         l0 = launch_count()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record(stream)
@@ -730,9 +732,11 @@ def run_batch_layer_ep(args, torch, dist, rank: int, world: int, local: int) -> 
     with torch.cuda.stream(stream):
         for i in range(max(args.warmup, 5)):
             step(i)
+        # the clock sampler starts (a process spawn on rank 0) BEFORE the barrier that opens the timed region:
+        # otherwise the other ranks' first collective would wait for rank 0 inside their timed region
+        sampler = ClockSampler(local) if rank == 0 else None
         dist.barrier()
         torch.cuda.synchronize()
-        sampler = ClockSampler(local) if rank == 0 else None
         l0 = launch_count()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record(stream)
@@ -754,6 +758,8 @@ def run_batch_layer_ep(args, torch, dist, rank: int, world: int, local: int) -> 
         clocks = sampler.stop() if sampler else None
     assert torch.isfinite(y_own).all(), "non-finite output"
     times = torch.tensor([ms, compute_ms], dtype=torch.float64, device="cuda")
+    every = torch.empty(world, 2, dtype=torch.float64, device="cuda")
+    dist.all_gather_into_tensor(every, times.view(1, 2))
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms = float(times[0]) / args.steps
     if rank == 0:
@@ -769,7 +775,9 @@ def run_batch_layer_ep(args, torch, dist, rank: int, world: int, local: int) -> 
                           "max_over_mean_pairs_per_gpu": round(max(per) / (sum(per) / world), 3),
                           "all_gather_bytes_in_per_gpu": (world - 1) * own * D * 2,
                           "all_to_all_bytes_out_per_gpu": (world - 1) * own * D * 4,
-                          "routed_kernels_alone_ms_max_over_gpus": float(times[1])}}
+                          "routed_kernels_alone_ms_max_over_gpus": float(times[1]),
+                          "routed_kernels_alone_ms_per_gpu": [round(float(v), 4) for v in every[:, 1].cpu()],
+                          "step_ms_per_gpu": [round(float(v) / args.steps, 4) for v in every[:, 0].cpu()]}}
         print(json.dumps(rec), flush=True)
 
 
