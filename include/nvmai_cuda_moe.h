@@ -335,7 +335,13 @@ NVMAI_API int nvmai_cuda_moe_ep_peer_attach(nvmai_cuda_moe *h, const void *handl
  * rows, local experts' shares, all-to-all of the shares to the rows' owners, rank-
  * ordered sum + shared expert, RMS renormalisation.  Every rank must call it with the
  * same rows_own, the same number of times.  The first call per (x, y, rows, stream)
- * issues plain launches, the second captures a CUDA graph, later ones replay it. */
+ * issues plain launches, the second captures a CUDA graph, later ones replay it.
+ * With the peers attached (ep_peer_attach) and at most 8 rows in total, a step is ONE
+ * launch of the resident kernel per rank and nothing else: the rows are gathered and the
+ * shares exchanged by tagged peer stores over NVLink from inside that kernel (no
+ * collective call); every rank keeps all rows.  A peer that stops makes the kernel's
+ * bounded wait run out (NVMAI_CUDA_ETIMEOUT from the synchronize calls); the ranks then
+ * call ep_init again before the next step, since their step counters may differ. */
 NVMAI_API int nvmai_cuda_moe_ep_stack_decode(nvmai_cuda_moe *h, const void *x_own_f16, uint32_t rows_own, void *y_own,
                                              void *stream);
 
