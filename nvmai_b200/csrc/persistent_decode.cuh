@@ -511,11 +511,11 @@ __device__ __forceinline__ float pd_tile_result(const float *red_tile, int f, ui
 // Polls the `n` tagged values of an activation row and writes the part [begin, begin + count)
 // to shared memory as fp16 (scaled by a power of two into fp16 range when the values are
 // fp32: exact, they carry 11 significant bits).  One warp.
-template <int OUT>
-__device__ __noinline__ bool pd_stage_row(const unsigned long long *src, uint32_t tag, int n, int begin, int count,
+template <int OUT, int KEEP>
+__device__ __noinline__ bool pd_stage_row_n(const unsigned long long *src, uint32_t tag, int n, int begin, int count,
                                           __half *smem_row, float &scale_up, unsigned int *status) {
     const int lane = threadIdx.x & 31;
-    constexpr int kKeep = 8;
+    constexpr int kKeep = KEEP;     // four words per lane and step: rows of up to 128 * KEEP values
     float4 keep[kKeep];
     uint32_t pending = 0;
 #pragma unroll
@@ -572,6 +572,15 @@ __device__ __noinline__ bool pd_stage_row(const unsigned long long *src, uint32_
     }
     __syncwarp();
     return true;
+}
+
+// rows of up to 512 values (the benchmark's) take the half-size copy of the code: what a layer executes once should
+// stay small (instruction cache)
+template <int OUT>
+__device__ __forceinline__ bool pd_stage_row(const unsigned long long *src, uint32_t tag, int n, int begin, int count,
+                                             __half *smem_row, float &scale_up, unsigned int *status) {
+    if (n <= 512) return pd_stage_row_n<OUT, 4>(src, tag, n, begin, count, smem_row, scale_up, status);
+    return pd_stage_row_n<OUT, 8>(src, tag, n, begin, count, smem_row, scale_up, status);
 }
 
 // one half of the groups of a staged down tile against a staged activation row: rows g and g+8 of the tile
