@@ -841,6 +841,9 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_decode_kernel(PdPara
             __syncthreads();
         }
         mark(0);
+        // this warp's fragments of the row: the shared expert's tile and the routed tiles multiply the same x
+        PdXFrag<BITS> xf;
+        if (has_stile || n_my != 0) xf.prepare(xs, xsum_s, D);
 
         // ---- phase 1a: router logits (every block waits for all of them next), or the scalar gate ----
         if (has_rows) {
@@ -869,11 +872,7 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_decode_kernel(PdPara
             const bool ok = pd_mbar_wait(bar_p1s, ph_p1s & 1u, p.status);
             ph_p1s ^= 1u; fly_p1s = 0;
             if (!__syncthreads_and(ok)) { alive = false; break; }
-            if (grp == 0) {
-                PdXFrag<BITS> xf;
-                xf.prepare(xs, xsum_s, D);
-                pd_tile_partial<BITS, META>(p1sbuf, L, D, xs, xsum_s, xf, red);
-            }
+            if (grp == 0) pd_tile_partial<BITS, META>(p1sbuf, L, D, xs, xsum_s, xf, red);
             __syncthreads();
             if (tid < kTileFeatures && !mute)     // the shared expert rounds gate and up before the activation
                 st_tagged(p.xsact + c * kTileFeatures + tid, tag, pd_tile_result<OUT>(red, tid, p.act, true));
@@ -927,8 +926,6 @@ __global__ void __launch_bounds__(kPdThreads, 1) persistent_decode_kernel(PdPara
 
         // ---- phase 2: routed gate/up + activation; the two warp groups take two tiles at a time ----
         if (n_my != 0) {
-            PdXFrag<BITS> xf;
-            xf.prepare(xs, xsum_s, D);
             bool ok = true;
             for (int j0 = 0; j0 < n_my; j0 += kPdGroups) {
                 const int j = j0 + grp;
