@@ -337,10 +337,13 @@ __device__ __forceinline__ void swz_accumulate_prepared(const unsigned char *box
     const MW sb = *reinterpret_cast<const MW *>(s + mb * groups_total + g_begin);
     const MW ba = *reinterpret_cast<const MW *>(b + ma * groups_total + g_begin);
     const MW bb = *reinterpret_cast<const MW *>(b + mb * groups_total + g_begin);
+    // g_begin is a multiple of NG (= 4) at every call: written as 4 * (g_begin / 4) + j, the group index shows the
+    // compiler which of its bits are the constant j, and the swizzle of the four groups folds to a few operations
+    const int g4 = (g_begin >> 2) << 2;
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
-        const vec wa[1] = {*reinterpret_cast<const vec *>(box_a + swz_offset<BITS>(g_begin + j, ra, t, rows_per_chunk))};
-        const vec wb[1] = {*reinterpret_cast<const vec *>(box_b + swz_offset<BITS>(g_begin + j, rb, t, rows_per_chunk))};
+        const vec wa[1] = {*reinterpret_cast<const vec *>(box_a + swz_offset<BITS>(g4 + j, ra, t, rows_per_chunk))};
+        const vec wb[1] = {*reinterpret_cast<const vec *>(box_b + swz_offset<BITS>(g4 + j, rb, t, rows_per_chunk))};
         const uint16_t s0[1] = {meta_pick(sa, j)}, s1[1] = {meta_pick(sb, j)};
         const uint16_t b0[1] = {meta_pick(ba, j)}, b1[1] = {meta_pick(bb, j)};
         group_step<BITS, META, 1, true>(wa, wb, s0, s1, b0, b1, xb[j], xsum[j], 0.0f, acc);
@@ -365,14 +368,15 @@ __device__ __forceinline__ void swz_accumulate_prepared2(const unsigned char *co
         ba[m] = *reinterpret_cast<const MW *>(b[m] + ma * groups_total + g_begin);
         bb[m] = *reinterpret_cast<const MW *>(b[m] + mb * groups_total + g_begin);
     }
+    const int g4 = (g_begin >> 2) << 2;         // g_begin is a multiple of 4, see above
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
         vec wa[2], wb[2];
         uint16_t s0[2], s1[2], b0[2], b1[2];
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
-            wa[m] = *reinterpret_cast<const vec *>(box_a[m] + swz_offset<BITS>(g_begin + j, ra, t, rows_per_chunk));
-            wb[m] = *reinterpret_cast<const vec *>(box_b[m] + swz_offset<BITS>(g_begin + j, rb, t, rows_per_chunk));
+            wa[m] = *reinterpret_cast<const vec *>(box_a[m] + swz_offset<BITS>(g4 + j, ra, t, rows_per_chunk));
+            wb[m] = *reinterpret_cast<const vec *>(box_b[m] + swz_offset<BITS>(g4 + j, rb, t, rows_per_chunk));
             s0[m] = meta_pick(sa[m], j); s1[m] = meta_pick(sb[m], j);
             b0[m] = meta_pick(ba[m], j); b1[m] = meta_pick(bb[m], j);
         }
